@@ -1,0 +1,248 @@
+// RMSNorm (forward, with the residual / partial-sum reduction of a row-parallel linear folded
+// in), RMSNorm backward, embedding gather, and the small element-wise kernels of the model
+// (SwiGLU forward/backward, stand-alone RoPE forward/backward).
+//
+// Numerics follow the reference model (models/model.py:370-377, 400-412): statistics in fp32,
+// the normalised value rounded to bf16 before the multiplication with the bf16 weight.
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace e2h {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();
+  if (lane == 0) red[warp] = v;
+  __syncthreads();
+  const int nw = (blockDim.x + 31) >> 5;
+  float t = (lane < nw) ? red[lane] : 0.f;
+  t = warp_sum(t);
+  return t;
+}
+
+// One CTA per token row.
+//   h_in      : bf16 [T, dim]  residual stream (or nullptr when `tokens` is given)
+//   tokens    : int32 [T]      when set, the row is gathered from `emb` instead of h_in
+//   partials  : fp32 [n_part, T, dim] partial sums of a row-parallel linear (split-K slabs or
+//               one slab per tensor-parallel rank); added to the row when n_part > 0
+//   h_out     : bf16 [T, dim]  updated residual stream (written when non-null)
+//   x_out     : bf16 [T, dim]  rmsnorm(h) * weight     (written when non-null)
+//   flags     : optional int32 [n_part]; slab i is read only once flags[i] >= flag_want
+//               (set by the peer that pushed it); bounded wait.
+__global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
+                                   const int* __restrict__ tokens,
+                                   const __nv_bfloat16* __restrict__ emb,
+                                   const float* __restrict__ partials, int n_part,
+                                   long long part_stride, const __nv_bfloat16* __restrict__ weight,
+                                   __nv_bfloat16* __restrict__ h_out,
+                                   __nv_bfloat16* __restrict__ x_out, float* __restrict__ rstd_out,
+                                   int dim, float eps, const int* flags, int flag_want,
+                                   int* status) {
+  extern __shared__ float row[];  // dim floats + 32
+  float* red = row + dim;
+  const int t = blockIdx.x;
+  const __nv_bfloat16* src =
+      tokens ? emb + (long long)tokens[t] * dim : (h_in ? h_in + (long long)t * dim : nullptr);
+  if (flags != nullptr && threadIdx.x < n_part) wait_flag_ge(flags + threadIdx.x, flag_want, status);
+  if (flags != nullptr) __syncthreads();
+  float ss = 0.f;
+  for (int i = threadIdx.x * 2; i < dim; i += blockDim.x * 2) {
+    float a = 0.f, b = 0.f;
+    if (src) {
+      const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(src + i);
+      a = __bfloat162float(v.x);
+      b = __bfloat162float(v.y);
+    }
+    if (n_part > 0) {
+      float pa = 0.f, pb = 0.f;
+      for (int s = 0; s < n_part; ++s) {
+        const float2 pv =
+            *reinterpret_cast<const float2*>(partials + s * part_stride + (long long)t * dim + i);
+        pa += pv.x;
+        pb += pv.y;
+      }
+      // the linear's output is a bf16 tensor in the reference; round before the residual add
+      a = bf16_round(a + bf16_round(pa));
+      b = bf16_round(b + bf16_round(pb));
+    }
+    row[i] = a;
+    row[i + 1] = b;
+    ss += a * a + b * b;
+    if (h_out) {
+      __nv_bfloat162 o;
+      o.x = __float2bfloat16_rn(a);
+      o.y = __float2bfloat16_rn(b);
+      *reinterpret_cast<__nv_bfloat162*>(h_out + (long long)t * dim + i) = o;
+    }
+  }
+  if (x_out == nullptr) return;
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / dim + eps);
+  if (rstd_out && threadIdx.x == 0) rstd_out[t] = rstd;
+  for (int i = threadIdx.x * 2; i < dim; i += blockDim.x * 2) {
+    const __nv_bfloat162 w = *reinterpret_cast<const __nv_bfloat162*>(weight + i);
+    __nv_bfloat162 o;
+    o.x = __float2bfloat16_rn(bf16_round(row[i] * rstd) * __bfloat162float(w.x));
+    o.y = __float2bfloat16_rn(bf16_round(row[i + 1] * rstd) * __bfloat162float(w.y));
+    *reinterpret_cast<__nv_bfloat162*>(x_out + (long long)t * dim + i) = o;
+  }
+}
+
+// RMSNorm backward for one row per CTA:  y = bf16(x * rstd) * w
+//   dx = rstd * (dy*w) - x * rstd^3 / dim * sum(dy*w*x);   dres (optional) is added to dx.
+// The weight is frozen in this framework (as in the reference's FrozenRMSNorm), so no dw.
+__global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
+                                   const __nv_bfloat16* __restrict__ dy,
+                                   const __nv_bfloat16* __restrict__ weight,
+                                   const __nv_bfloat16* __restrict__ dres,
+                                   __nv_bfloat16* __restrict__ dx, int dim, float eps) {
+  extern __shared__ float row[];
+  float* red = row + 2 * dim;
+  const long long base = (long long)blockIdx.x * dim;
+  float ss = 0.f, dot = 0.f;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    const float xv = __bfloat162float(x[base + i]);
+    const float g = __bfloat162float(dy[base + i]) * __bfloat162float(weight[i]);
+    row[i] = xv;
+    row[dim + i] = g;
+    ss += xv * xv;
+    dot += xv * g;
+  }
+  ss = block_sum(ss, red);
+  dot = block_sum(dot, red);
+  const float rstd = rsqrtf(ss / dim + eps);
+  const float coef = dot * rstd * rstd * rstd / dim;
+  for (int i = threadIdx.x; i < dim; i += blockDim.x) {
+    float v = row[dim + i] * rstd - row[i] * coef;
+    if (dres) v += __bfloat162float(dres[base + i]);
+    dx[base + i] = __float2bfloat16_rn(v);
+  }
+}
+
+// out[t, :] = table[tokens[t], :]
+__global__ void embedding_kernel(const int* __restrict__ tokens,
+                                 const __nv_bfloat16* __restrict__ table,
+                                 __nv_bfloat16* __restrict__ out, int dim) {
+  const int t = blockIdx.x;
+  const uint4* src = reinterpret_cast<const uint4*>(table + (long long)tokens[t] * dim);
+  uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * dim);
+  for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+}
+
+// act = bf16(bf16(silu(g)) * u)
+__global__ void swiglu_fwd_kernel(const __nv_bfloat16* __restrict__ g,
+                                  const __nv_bfloat16* __restrict__ u,
+                                  __nv_bfloat16* __restrict__ out, long long n) {
+  const long long i = (blockIdx.x * (long long)blockDim.x + threadIdx.x) * 2;
+  if (i >= n) return;
+  const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(g + i);
+  const __nv_bfloat162 uv = *reinterpret_cast<const __nv_bfloat162*>(u + i);
+  __nv_bfloat162 o;
+  o.x = __float2bfloat16_rn(bf16_round(silu(__bfloat162float(gv.x))) * __bfloat162float(uv.x));
+  o.y = __float2bfloat16_rn(bf16_round(silu(__bfloat162float(gv.y))) * __bfloat162float(uv.y));
+  *reinterpret_cast<__nv_bfloat162*>(out + i) = o;
+}
+
+// dg = dact * u * silu'(g),  du = dact * silu(g)
+__global__ void swiglu_bwd_kernel(const __nv_bfloat16* __restrict__ g,
+                                  const __nv_bfloat16* __restrict__ u,
+                                  const __nv_bfloat16* __restrict__ dact,
+                                  __nv_bfloat16* __restrict__ dg, __nv_bfloat16* __restrict__ du,
+                                  long long n) {
+  const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const float gv = __bfloat162float(g[i]), uv = __bfloat162float(u[i]);
+  const float d = __bfloat162float(dact[i]);
+  const float sig = 1.f / (1.f + __expf(-gv));
+  const float sl = gv * sig;
+  dg[i] = __float2bfloat16_rn(d * uv * (sig * (1.f + gv * (1.f - sig))));
+  du[i] = __float2bfloat16_rn(d * sl);
+}
+
+// Stand-alone interleaved-pair RoPE on x[T, n_heads, head_dim]; position of token t is
+// pos[t]. `inverse` applies the transposed rotation (the backward pass).
+__global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out,
+                            const __nv_bfloat16* __restrict__ freqs, const int* __restrict__ pos,
+                            int n_heads, int head_dim, long long ld, int inverse) {
+  const int t = blockIdx.x;
+  const int half = head_dim / 2;
+  const int p = pos[t];
+  for (int i = threadIdx.x; i < n_heads * half; i += blockDim.x) {
+    const int h = i / half, j = i - h * half;
+    const long long o = (long long)t * ld + h * head_dim + 2 * j;
+    const float x0 = __bfloat162float(x[o]), x1 = __bfloat162float(x[o + 1]);
+    const float c = __bfloat162float(freqs[((long long)p * half + j) * 2]);
+    float s = __bfloat162float(freqs[((long long)p * half + j) * 2 + 1]);
+    if (inverse) s = -s;
+    out[o] = __float2bfloat16_rn(x0 * c - x1 * s);
+    out[o + 1] = __float2bfloat16_rn(x1 * c + x0 * s);
+  }
+}
+
+}  // namespace e2h
+
+using namespace e2h;
+
+extern "C" {
+
+int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb, const float* partials,
+                    int n_part, long long part_stride, const void* weight, void* h_out,
+                    void* x_out, float* rstd_out, int T, int dim, float eps, const int* flags,
+                    int flag_want, int* status, void* stream) {
+  if (dim % 2) return -1;
+  const int threads = dim >= 2048 ? 512 : 128;
+  const size_t smem = (dim + 32) * sizeof(float);
+  rmsnorm_fwd_kernel<<<T, threads, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, partials, n_part,
+      part_stride, (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out,
+      rstd_out, dim, eps, flags, flag_want, status);
+  return (int)cudaGetLastError();
+}
+
+int e2h_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const void* dres, void* dx,
+                    int T, int dim, float eps, void* stream) {
+  const int threads = dim >= 2048 ? 512 : 128;
+  const size_t smem = (2 * dim + 32) * sizeof(float);
+  rmsnorm_bwd_kernel<<<T, threads, smem, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)weight,
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dim, eps);
+  return (int)cudaGetLastError();
+}
+
+int e2h_embedding(const int* tokens, const void* table, void* out, int T, int dim, void* stream) {
+  if (dim % 8) return -1;
+  embedding_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(tokens, (const __nv_bfloat16*)table,
+                                                        (__nv_bfloat16*)out, dim);
+  return (int)cudaGetLastError();
+}
+
+int e2h_swiglu_fwd(const void* g, const void* u, void* out, long long n, void* stream) {
+  if (n % 2) return -1;
+  const long long blocks = (n / 2 + 255) / 256;
+  swiglu_fwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)out, n);
+  return (int)cudaGetLastError();
+}
+
+int e2h_swiglu_bwd(const void* g, const void* u, const void* dact, void* dg, void* du, long long n,
+                   void* stream) {
+  const long long blocks = (n + 255) / 256;
+  swiglu_bwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (const __nv_bfloat16*)dact,
+      (__nv_bfloat16*)dg, (__nv_bfloat16*)du, n);
+  return (int)cudaGetLastError();
+}
+
+int e2h_rope(const void* x, void* out, const void* freqs, const int* pos, int T, int n_heads,
+             int head_dim, long long ld, int inverse, void* stream) {
+  rope_kernel<<<T, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
+                                                   (const __nv_bfloat16*)freqs, pos, n_heads,
+                                                   head_dim, ld, inverse);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

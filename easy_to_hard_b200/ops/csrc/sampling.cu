@@ -1,0 +1,164 @@
+// Fused sampler: temperature, top-k pivot mask, exponential-race sampling, EOS tracking and
+// position advance, one CTA per sequence, no host synchronisation.
+//
+// Semantics of the reference sampler (models/rl_model.py:347-379, inference_generate.py:53-85):
+//   logits / max(T, 1e-5); pivot = k-th largest; values < pivot are dropped (ties with the
+//   pivot are kept); probabilities p = softmax; token = argmax(p / q), q ~ Exp(1) i.i.d.
+// argmax(p/q) does not depend on the softmax normaliser, so the kernel maximises
+//   x_i / T - log(q_i)          over the kept entries
+// and never materialises probabilities. Greedy decoding (temperature == 0) is the plain
+// argmax with ties going to the lowest index.
+//
+// The k-th largest value is found exactly with a 4-pass, 8-bit radix select over the
+// order-preserving integer image of the fp32 logits; the logits row (<= 128 KiB) stays in L2.
+#include <cuda_runtime.h>
+#include <float.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace e2h {
+
+__device__ __forceinline__ uint32_t float_key(float x) {
+  const uint32_t u = __float_as_uint(x);
+  return (u & 0x80000000u) ? ~u : (u | 0x80000000u);  // larger float -> larger key
+}
+
+// Philox4x32-10 counter-based generator.
+__device__ __forceinline__ uint4 philox(uint4 ctr, uint2 key) {
+#pragma unroll
+  for (int i = 0; i < 10; ++i) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, ctr.x), lo0 = 0xD2511F53u * ctr.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, ctr.z), lo1 = 0xCD9E8D57u * ctr.z;
+    ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+    key.x += 0x9E3779B9u;
+    key.y += 0xBB67AE85u;
+  }
+  return ctr;
+}
+
+constexpr int kSampThreads = 512;
+
+// logits   : fp32 [B, ld]
+// pos_ptr  : device scalar, position of the token that produced these logits; the sampled
+//            token is stored at seq[b, pos+1]; the last CTA to finish stores pos+1 back.
+// next_tok : int32 [B], input of the next decode step
+// eos_flag : int32 [B], sticky
+__global__ void __launch_bounds__(kSampThreads)
+sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float temperature,
+              int top_k, unsigned long long seed, int* pos_ptr, int advance_pos,
+              int* __restrict__ next_tok, int* __restrict__ seq, long long seq_ld, int seq_len,
+              int eos_id, int* __restrict__ eos_flag, int* __restrict__ n_unfinished,
+              unsigned int* ticket) {
+  __shared__ unsigned int hist[256];
+  __shared__ uint32_t sh_prefix, sh_remaining;
+  __shared__ float red_v[kSampThreads / 32];
+  __shared__ int red_i[kSampThreads / 32];
+  const int b = blockIdx.x;
+  const float* row = logits + (long long)b * ld;
+  const int pos = *pos_ptr;
+  const bool greedy = temperature <= 0.f;
+
+  uint32_t pivot_key = 0;  // keep everything
+  if (!greedy && top_k > 0 && top_k < vocab) {
+    // radix select of the k-th largest key, most significant byte first
+    uint32_t prefix = 0, mask = 0;
+    uint32_t remaining = top_k;
+    for (int shift = 24; shift >= 0; shift -= 8) {
+      for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
+      __syncthreads();
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+        const uint32_t key = float_key(row[i]);
+        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+      }
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        uint32_t rem = remaining;
+        int bin = 255;
+        for (; bin > 0; --bin) {
+          if (hist[bin] >= rem) break;
+          rem -= hist[bin];
+        }
+        sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
+        sh_remaining = rem;
+      }
+      __syncthreads();
+      prefix = sh_prefix;
+      remaining = sh_remaining;
+      mask |= 255u << shift;
+    }
+    pivot_key = prefix;
+  }
+
+  const float inv_t = greedy ? 1.f : 1.f / fmaxf(temperature, 1e-5f);
+  float best = -FLT_MAX;
+  int best_i = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float x = row[i];
+    if (float_key(x) < pivot_key) continue;
+    float score = x * inv_t;
+    if (!greedy) {
+      const uint4 r = philox(make_uint4((uint32_t)i, (uint32_t)b, (uint32_t)pos, 0u),
+                             make_uint2((uint32_t)seed, (uint32_t)(seed >> 32)));
+      const float u = (static_cast<float>(r.x >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0,1)
+      const float qexp = -__logf(u);                                                  // Exp(1)
+      score -= __logf(qexp);
+    }
+    if (score > best || (score == best && i < best_i)) {
+      best = score;
+      best_i = i;
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+    if (ov > best || (ov == best && oi < best_i)) {
+      best = ov;
+      best_i = oi;
+    }
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) {
+    red_v[warp] = best;
+    red_i[warp] = best_i;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kSampThreads / 32; ++w) {
+      if (red_v[w] > best || (red_v[w] == best && red_i[w] < best_i)) {
+        best = red_v[w];
+        best_i = red_i[w];
+      }
+    }
+    const int tok = best_i;
+    next_tok[b] = tok;
+    if (seq != nullptr && pos + 1 < seq_len) seq[(long long)b * seq_ld + pos + 1] = tok;
+    if (eos_flag != nullptr && eos_id >= 0 && tok == eos_id) {
+      if (atomicExch(&eos_flag[b], 1) == 0 && n_unfinished != nullptr)
+        atomicSub(n_unfinished, 1);
+    }
+    if (advance_pos) {
+      __threadfence();
+      const unsigned int done = atomicAdd(ticket, 1u);
+      if (done == gridDim.x - 1) {  // every CTA has read *pos_ptr by now
+        *ticket = 0;
+        *pos_ptr = pos + 1;
+      }
+    }
+  }
+}
+
+}  // namespace e2h
+
+extern "C" int e2h_sample(const float* logits, long long ld, int B, int vocab, float temperature,
+                          int top_k, unsigned long long seed, int* pos_ptr, int advance_pos,
+                          int* next_tok, int* seq, long long seq_ld, int seq_len, int eos_id,
+                          int* eos_flag, int* n_unfinished, unsigned int* ticket, void* stream) {
+  using namespace e2h;
+  if (advance_pos && ticket == nullptr) return -1;
+  sample_kernel<<<B, kSampThreads, 0, (cudaStream_t)stream>>>(
+      logits, ld, vocab, temperature, top_k, seed, pos_ptr, advance_pos, next_tok, seq, seq_ld,
+      seq_len, eos_id, eos_flag, n_unfinished, ticket);
+  return (int)cudaGetLastError();
+}

@@ -1,0 +1,146 @@
+"""Front-ends of the non-GEMM kernels. CUDA tensors run the native sm_100a kernels; CPU
+tensors run the PyTorch restatements in ``reference.py`` (the oracle of the tests)."""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from . import _lib, reference
+
+
+def _s():
+    return _lib.stream()
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if not x.is_cuda:
+        return reference.rmsnorm(x, weight, eps)
+    dim = x.shape[-1]
+    x2 = x.reshape(-1, dim)
+    assert x2.is_contiguous() and x.dtype == torch.bfloat16
+    if out is None:
+        out = torch.empty_like(x2)
+    rc = _lib.lib().e2h_rmsnorm_fwd(x2.data_ptr(), None, None, None, 0, 0, weight.data_ptr(),
+                                    None, out.data_ptr(), None, x2.shape[0], dim, eps, None, 0,
+                                    _lib.status_word(x.device).data_ptr(), _s())
+    _lib.check(rc, "rmsnorm_fwd")
+    return out.view(x.shape)
+
+
+def fused_residual_rmsnorm(h: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
+                           *, partials: Optional[torch.Tensor] = None,
+                           tokens: Optional[torch.Tensor] = None,
+                           emb: Optional[torch.Tensor] = None,
+                           h_out: Optional[torch.Tensor] = None,
+                           x_out: Optional[torch.Tensor] = None,
+                           flags: Optional[torch.Tensor] = None, flag_want: int = 0):
+    """h' = (h | emb[tokens]) + sum_i partials[i];  x = rmsnorm(h') * weight.
+
+    `partials` fp32 [n, T, dim] holds the partial sums of a row-parallel linear (one slab per
+    tensor-parallel rank); `flags` int32 [n] are waited on (bounded) before a slab is read."""
+    ref = tokens if tokens is not None else h
+    T = ref.shape[0]
+    dim = (emb if tokens is not None else h).shape[-1]
+    n_part = 0 if partials is None else partials.shape[0]
+    rc = _lib.lib().e2h_rmsnorm_fwd(
+        _lib.ptr(h) if tokens is None else None, _lib.ptr(tokens), _lib.ptr(emb),
+        _lib.ptr(partials), n_part, 0 if partials is None else partials.stride(0),
+        _lib.ptr(weight), _lib.ptr(h_out), _lib.ptr(x_out), None, T, dim, eps,
+        _lib.ptr(flags), flag_want, _lib.status_word(ref.device).data_ptr(), _s())
+    _lib.check(rc, "rmsnorm_fwd")
+    return h_out, x_out
+
+
+def rmsnorm_bwd(x, dy, weight, eps, dres=None):
+    dim = x.shape[-1]
+    x2, dy2 = x.reshape(-1, dim), dy.reshape(-1, dim)
+    dx = torch.empty_like(x2)
+    rc = _lib.lib().e2h_rmsnorm_bwd(x2.data_ptr(), dy2.data_ptr(), weight.data_ptr(),
+                                    _lib.ptr(dres), dx.data_ptr(), x2.shape[0], dim, eps, _s())
+    _lib.check(rc, "rmsnorm_bwd")
+    return dx.view(x.shape)
+
+
+def embedding(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
+    if not table.is_cuda:
+        return torch.nn.functional.embedding(tokens.long(), table)
+    tk = tokens.reshape(-1).to(torch.int32)
+    out = torch.empty(tk.numel(), table.shape[1], dtype=table.dtype, device=table.device)
+    _lib.check(_lib.lib().e2h_embedding(tk.data_ptr(), table.data_ptr(), out.data_ptr(),
+                                        tk.numel(), table.shape[1], _s()), "embedding")
+    return out.view(*tokens.shape, table.shape[1])
+
+
+def swiglu(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    if not g.is_cuda:
+        return reference.swiglu(g, u)
+    out = torch.empty_like(g)
+    _lib.check(_lib.lib().e2h_swiglu_fwd(g.data_ptr(), u.data_ptr(), out.data_ptr(), g.numel(),
+                                         _s()), "swiglu_fwd")
+    return out
+
+
+def swiglu_bwd(g, u, dact):
+    dg, du = torch.empty_like(g), torch.empty_like(u)
+    _lib.check(_lib.lib().e2h_swiglu_bwd(g.data_ptr(), u.data_ptr(), dact.data_ptr(),
+                                         dg.data_ptr(), du.data_ptr(), g.numel(), _s()),
+               "swiglu_bwd")
+    return dg, du
+
+
+def rope(x: torch.Tensor, freqs: torch.Tensor, pos: torch.Tensor, n_heads: int, head_dim: int,
+         inverse: bool = False, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [T, >= n_heads*head_dim] (row stride = x.stride(0)); rotates the first n_heads heads."""
+    if out is None:
+        out = torch.empty_like(x)
+    assert out.stride(0) == x.stride(0)
+    _lib.check(_lib.lib().e2h_rope(x.data_ptr(), out.data_ptr(), freqs.data_ptr(),
+                                   pos.data_ptr(), x.shape[0], n_heads, head_dim, x.stride(0),
+                                   int(inverse), _s()), "rope")
+    return out
+
+
+def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor,
+                left_pad: Optional[torch.Tensor], n_head: int, out: Optional[torch.Tensor] = None,
+                n_split: int = 0, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One query token per sequence against the static cache, live range [left_pad[b], pos].
+
+    q [B, n_head*D] bf16; caches [max_batch, n_kv, smax, D]; pos int32 device scalar."""
+    B = q.shape[0]
+    n_kv, smax, D = kcache.shape[1], kcache.shape[2], kcache.shape[3]
+    if out is None:
+        out = torch.empty_like(q)
+    if n_split <= 0:
+        n_split = 1
+        while B * n_kv * n_split < 296 and n_split < 16:
+            n_split *= 2
+    if n_split > 1 and scratch is None:
+        scratch = torch.empty(B * n_head * n_split * (D + 2), dtype=torch.float32,
+                              device=q.device)
+    rc = _lib.lib().e2h_attn_decode(q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(),
+                                    out.data_ptr(), _lib.ptr(scratch), pos.data_ptr(),
+                                    _lib.ptr(left_pad), B, n_head, n_kv, D, smax,
+                                    1.0 / math.sqrt(D), n_split, _s())
+    _lib.check(rc, "attn_decode")
+    return out
+
+
+def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int], seed: int,
+           pos: torch.Tensor, next_tok: torch.Tensor, advance_pos: bool = True,
+           seq: Optional[torch.Tensor] = None, eos_id: int = -1,
+           eos_flag: Optional[torch.Tensor] = None, n_unfinished: Optional[torch.Tensor] = None,
+           ticket: Optional[torch.Tensor] = None, vocab: Optional[int] = None) -> torch.Tensor:
+    """Fused top-k / temperature / exponential-race sampler (fp32 logits [B, ld])."""
+    B = logits.shape[0]
+    vocab = vocab or logits.shape[1]
+    rc = _lib.lib().e2h_sample(
+        logits.data_ptr(), logits.stride(0), B, vocab, float(temperature),
+        int(top_k) if top_k else 0, int(seed) & (2 ** 64 - 1), pos.data_ptr(), int(advance_pos),
+        next_tok.data_ptr(), _lib.ptr(seq), 0 if seq is None else seq.stride(0),
+        0 if seq is None else seq.shape[1], int(eos_id), _lib.ptr(eos_flag),
+        _lib.ptr(n_unfinished), _lib.ptr(ticket), _s())
+    _lib.check(rc, "sample")
+    return next_tok

@@ -1,0 +1,173 @@
+"""Python front-end of the tcgen05 GEMM (csrc/gemm_umma.cu) and its fused epilogues.
+
+Every function takes 2-D bf16 CUDA tensors whose last dimension is contiguous. The
+"feature" operand (a weight ``[F, K]``) rides on the TMEM lanes and the "token" operand
+(activations ``[T, K]``) on the TMEM columns, so ``linear(x, w)`` = ``x @ w.T`` is the
+natural call for any token count.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Optional
+
+import torch
+
+from . import _lib
+from ._lib import (EPI_DUAL_STORE, EPI_RESIDUAL, EPI_ROPE_KV, EPI_ROWMAJOR_BF16,
+                   EPI_ROWMAJOR_F32_ACC, EPI_STORE_BF16, EPI_STORE_F32, EPI_SWIGLU, GemmParams)
+
+N_SM = 148
+
+
+def _ld(t: torch.Tensor) -> int:
+    assert t.dim() == 2 and t.stride(1) == 1, "operands must be 2-D with a contiguous last dim"
+    return t.stride(0)
+
+
+def pick_tiles(F: int, T: int, K: int, dual: bool, splitk: Optional[int], bn: Optional[int],
+               stages: int = 0):
+    """Token-tile width, cluster split-K factor and pipeline depth.
+
+    Few tiles (decode: T <= 64..128) => split K across a cluster until about two CTAs per SM
+    stream the weight (the stage count is then cut so that two CTAs fit in one SM's shared
+    memory); many tiles => the widest tile and the deepest pipeline that fit."""
+    if bn is None:
+        if T <= 64:
+            bn = 64
+        elif T <= 128 or dual:
+            bn = 128
+        else:
+            bn = 256
+    tiles = -(-F // 128) * -(-T // bn)
+    kb = -(-K // 64)
+    if splitk is None:
+        splitk = 1
+        if bn <= 128:
+            while (splitk < 8 and tiles * splitk * 2 <= 2 * N_SM and kb // (splitk * 2) >= 4
+                   and bn % (splitk * 2 * 8) == 0):
+                splitk *= 2
+    if stages <= 0 and N_SM < tiles * splitk <= 2 * N_SM:
+        stage_bytes = 16384 * (2 if dual else 1) + bn * 128
+        xchg = (splitk - 1) * (bn // splitk) * 512 * (2 if dual else 1) if splitk > 1 else 0
+        stages = max(2, (113 * 1024 - 2048 - xchg) // stage_bytes)
+    return bn, splitk, stages
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tensor] = None,
+         a2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None,
+         aux: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
+         a_mn_major: bool = False, b_mn_major: bool = False, accumulate: bool = False,
+         splitk: Optional[int] = None, bn: Optional[int] = None, stages: int = 0,
+         rope: Optional[dict] = None, pdl: bool = False) -> None:
+    """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T])."""
+    assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    if a_mn_major:
+        K, F = a.shape
+    else:
+        F, K = a.shape
+    if b_mn_major:
+        Kb, T = b.shape
+    else:
+        T, Kb = b.shape
+    assert K == Kb, f"contraction mismatch {K} vs {Kb}"
+    dual = a2 is not None
+    bn, splitk, stages = pick_tiles(F, T, K, dual, splitk, bn, stages)
+    p = GemmParams()
+    p.F, p.T, p.K = F, T, K
+    p.splitk, p.epi, p.stages = splitk, epi, stages
+    p.a_mn_major, p.b_mn_major = int(a_mn_major), int(b_mn_major)
+    p.bn, p.dual, p.accumulate, p.pdl = bn, int(dual), int(accumulate), int(pdl)
+    p.lda, p.ldb = _ld(a), _ld(b)
+    p.a, p.b = a.data_ptr(), b.data_ptr()
+    if dual:
+        assert a2.shape == a.shape
+        p.a2, p.lda2 = a2.data_ptr(), _ld(a2)
+    if out is not None:
+        p.out, p.ldo = out.data_ptr(), out.stride(0)
+    if out2 is not None:
+        p.out2, p.ldo2 = out2.data_ptr(), out2.stride(0)
+    if aux is not None:
+        p.aux = aux.data_ptr()
+    if scale is not None:
+        assert scale.dtype == torch.float32
+        p.scale = scale.data_ptr()
+    if rope is not None:
+        p.freqs = rope["freqs"].data_ptr()
+        p.pos_base = rope["pos_base"].data_ptr()
+        p.sq = rope["sq"]
+        p.n_head, p.n_kv, p.head_dim = rope["n_head"], rope["n_kv"], rope["head_dim"]
+        p.smax = rope["smax"]
+        p.kcache, p.vcache = rope["kcache"].data_ptr(), rope["vcache"].data_ptr()
+    p.status = _lib.status_word(a.device).data_ptr()
+    _lib.check(_lib.lib().e2h_gemm_umma(C.byref(p), _lib.stream()), "e2h_gemm_umma")
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype=torch.bfloat16, scale=None, **kw) -> torch.Tensor:
+    """x [T, K] @ w[F, K]^T -> [T, F]."""
+    T, F = x.shape[0], w.shape[0]
+    if out is None:
+        out = torch.empty(T, F, dtype=out_dtype, device=x.device)
+    epi = EPI_STORE_BF16 if out.dtype == torch.bfloat16 else EPI_STORE_F32
+    gemm(w, x, epi=epi, out=out, scale=scale, **kw)
+    return out
+
+
+def linear_residual(x, w, residual, out=None, scale=None, **kw):
+    """residual + x @ w^T (bf16)."""
+    if out is None:
+        out = torch.empty_like(residual)
+    assert out.stride(0) == residual.stride(0)
+    gemm(w, x, epi=EPI_RESIDUAL, out=out, aux=residual, scale=scale, **kw)
+    return out
+
+
+def linear_swiglu(x, w1, w3, out=None, **kw):
+    """silu(x @ w1^T) * (x @ w3^T) with both products accumulated in one pass over x."""
+    if out is None:
+        out = torch.empty(x.shape[0], w1.shape[0], dtype=torch.bfloat16, device=x.device)
+    gemm(w1, x, a2=w3, epi=EPI_SWIGLU, out=out, **kw)
+    return out
+
+
+def linear_dual(x, w1, w3, out1=None, out2=None, **kw):
+    """(x @ w1^T, x @ w3^T) in one pass (training forward keeps both for the backward)."""
+    T, F = x.shape[0], w1.shape[0]
+    if out1 is None:
+        out1 = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
+    if out2 is None:
+        out2 = torch.empty(T, F, dtype=torch.bfloat16, device=x.device)
+    gemm(w1, x, a2=w3, epi=EPI_DUAL_STORE, out=out1, out2=out2, **kw)
+    return out1, out2
+
+
+def linear_qkv_rope(x, wqkv, q_out, *, freqs, pos_base, sq, n_head, n_kv, head_dim, kcache,
+                    vcache, **kw):
+    """Fused QKV projection + RoPE(q, k) + scatter of k, v into the static KV cache.
+
+    q_out [T, n_head*head_dim]; caches [max_batch, n_kv, smax, head_dim]; token t belongs to
+    sequence t // sq and sits at cache position pos_base + t % sq."""
+    rope = dict(freqs=freqs, pos_base=pos_base, sq=sq, n_head=n_head, n_kv=n_kv,
+                head_dim=head_dim, smax=kcache.shape[2], kcache=kcache, vcache=vcache)
+    gemm(wqkv, x, epi=EPI_ROPE_KV, out=q_out, rope=rope, **kw)
+    return q_out
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor, out=None, **kw) -> torch.Tensor:
+    """dx [T, K] = dy [T, F] @ w [F, K] (w read as an MN-major operand, no transpose copy)."""
+    T, K = dy.shape[0], w.shape[1]
+    if out is None:
+        out = torch.empty(T, K, dtype=torch.bfloat16, device=dy.device)
+    gemm(w, dy, epi=EPI_STORE_BF16, out=out, a_mn_major=True, **kw)
+    return out
+
+
+def linear_wgrad(dy: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None,
+                 accumulate: bool = False, **kw) -> torch.Tensor:
+    """dw [F, K] (+)= dy[T, F]^T @ x[T, K]; fp32 (gradient accumulation buffer) or bf16 out."""
+    F, K = dy.shape[1], x.shape[1]
+    if out is None:
+        out = torch.zeros(F, K, dtype=torch.float32, device=dy.device)
+    epi = EPI_ROWMAJOR_F32_ACC if out.dtype == torch.float32 else EPI_ROWMAJOR_BF16
+    gemm(dy, x, epi=epi, out=out, a_mn_major=True, b_mn_major=True, accumulate=accumulate, **kw)
+    return out
