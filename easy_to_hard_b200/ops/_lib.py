@@ -36,6 +36,10 @@ class GemmParams(C.Structure):
         ("smax", C.c_int),
         ("kcache", C.c_void_p), ("vcache", C.c_void_p),
         ("status", C.c_void_p),
+        ("tf", C.c_int),
+        ("kps", C.c_int),
+        ("debug_mode", C.c_int),
+        ("a_tiled", C.c_int),
     ]
 
 
@@ -60,6 +64,9 @@ _SIGNATURES = {
     "e2h_swiglu_bwd": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "e2h_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp],
     "e2h_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp],
+    "e2h_adamw": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _vp],
+    "e2h_sqnorm": [_vp, _ll, _i, _vp, _vp],
+    "e2h_clip_coef": [_vp, _f, _vp, _vp, _vp],
     "e2h_sample": [_vp, _ll, _i, _i, _f, _i, _ull, _vp, _i, _vp, _vp, _ll, _i, _i, _vp, _vp,
                    _vp, _vp],
 }

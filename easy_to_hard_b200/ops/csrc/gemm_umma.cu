@@ -27,7 +27,7 @@
 
 namespace e2h {
 
-constexpr int kTileF = 128;       // features per tile = TMEM lanes = UMMA M
+constexpr int kTileF = 128;       // default features per tile = TMEM lanes = UMMA M (64 also supported)
 constexpr int kTileK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
 constexpr int kThreads = 192;
@@ -43,19 +43,28 @@ struct Ctrl {
 };
 static_assert(sizeof(Ctrl) <= kCtrlBytes, "control block too large");
 
+// Accumulation chains: rotating the k-steps over several accumulators was measured and does
+// not change the k-loop time (dependent tcgen05.mma on one accumulator pipeline back to back),
+// so a single chain is used; the indexing below stays general.
 template <int BN, bool DUAL>
+struct Chains {
+  static constexpr int value = 1;
+};
+
+template <int BN, bool DUAL, int TF>
 struct SmemPlan {
-  static constexpr int a_bytes = kTileF * kTileK * 2;  // 16 KiB
+  static constexpr int a_bytes = TF * kTileK * 2;  // 16 KiB (8 KiB for 64-feature tiles)
   static constexpr int b_bytes = BN * kTileK * 2;
   static constexpr int stage_bytes = a_bytes * (DUAL ? 2 : 1) + b_bytes;
-  static constexpr int acc_cols = BN * (DUAL ? 2 : 1);
+  static constexpr int nacc = Chains<BN, DUAL>::value;
+  static constexpr int acc_cols = BN * (DUAL ? 2 : 1) * nacc;
   static constexpr int tmem_cols = acc_cols <= 32 ? 32 : acc_cols <= 64 ? 64 : acc_cols <= 128 ? 128 : acc_cols <= 256 ? 256 : 512;
 };
 
 // Exchange buffer for the cluster reduce: (S-1) sender slots x (BN/S) columns x 128 lanes fp32.
-__host__ __device__ inline int xchg_bytes(int bn, int splitk, int dual) {
+__host__ __device__ inline int xchg_bytes(int bn, int splitk, int dual, int tf) {
   if (splitk <= 1) return 0;
-  return (splitk - 1) * (bn / splitk) * kTileF * 4 * (dual ? 2 : 1);
+  return (splitk - 1) * (bn / splitk) * tf * 4 * (dual ? 2 : 1);
 }
 
 struct EpiCtx {
@@ -195,11 +204,11 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
   }
 }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, int TF>
 __global__ void __launch_bounds__(kThreads, 1)
 umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                  const __grid_constant__ CUtensorMap tmB, const E2hGemmParams p) {
-  using Plan = SmemPlan<BN, DUAL>;
+  using Plan = SmemPlan<BN, DUAL, TF>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the swizzle atom
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
@@ -207,19 +216,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem);
   uint8_t* tiles = smem + kCtrlBytes;
   const int stages = p.stages;
-  float* xchg = reinterpret_cast<float*>(tiles + (size_t)stages * Plan::stage_bytes);
+  float* xchg = reinterpret_cast<float*>(tiles + (size_t)stages * p.kps * Plan::stage_bytes);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int S = p.splitk;
   const int rank = (S > 1) ? (int)cluster_ctarank() : 0;
-  const int f0 = blockIdx.x * kTileF;
+  const int f0 = blockIdx.x * TF;
   const int t0 = blockIdx.y * BN;
 
   const int kb_total = (p.K + kTileK - 1) / kTileK;
   const int kb_begin = (int)((long long)rank * kb_total / S);
   const int kb_end = (int)((long long)(rank + 1) * kb_total / S);
   const int n_kb = kb_end - kb_begin;
+  const int kps = p.kps;                          // k blocks per pipeline stage
+  const int n_it = (n_kb + kps - 1) / kps;
 
   volatile int* abort_flag = &ctrl->abort_flag;
 
@@ -251,30 +262,59 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ---------------- TMA producer ----------------
     const uint64_t pol_a = policy_evict_first();
     int armed = 0;
-    for (int it = 0; it < n_kb; ++it) {
+    for (int it = 0; it < n_it; ++it) {
       const int s = it % stages;
       const uint32_t ph = (it / stages) & 1;
       if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, p.status,
                      kStatusTimeoutEmpty))
         break;
       const uint32_t bar = smem_u32(&ctrl->full[s]);
-      mbar_expect_tx(bar, Plan::stage_bytes);
-      uint8_t* st = tiles + (size_t)s * Plan::stage_bytes;
-      const int k0 = (kb_begin + it) * kTileK;
-      const uint32_t a_dst = smem_u32(st);
-      if (!p.a_mn_major) {
-        tma_load_2d_hint(a_dst, &tmA, k0, f0, bar, pol_a);
-        if (DUAL) tma_load_2d_hint(a_dst + Plan::a_bytes, &tmA2, k0, f0, bar, pol_a);
-      } else {
-        tma_load_2d(a_dst, &tmA, f0, k0, bar);
-        tma_load_2d(a_dst + 8192, &tmA, f0 + 64, k0, bar);
+      if (p.debug_mode == 2 || p.debug_mode == 4) {  // timing experiment: no loads
+        mbar_arrive(bar);
+        armed = it + 1;
+        continue;
       }
-      const uint32_t b_dst = a_dst + Plan::a_bytes * (DUAL ? 2 : 1);
-      if (!p.b_mn_major) {
-        tma_load_2d(b_dst, &tmB, k0, t0, bar);
-      } else {
+      const int kcount = min(kps, n_kb - it * kps);
+      if (kps > 1) {
+        // one 3-D box per operand brings kps k-blocks (rows x 64 x kps): two TMA instructions
+        // per stage instead of 2*kps. The box is always full size (out-of-range k-blocks are
+        // zero filled), k-blocks past this CTA's range are loaded but never multiplied.
+        uint8_t* st = tiles + (size_t)s * kps * Plan::stage_bytes;
+        const int kb = kb_begin + it * kps;
+        const uint32_t a_dst = smem_u32(st);
+        mbar_expect_tx(bar, kps * Plan::stage_bytes);
+        tma_load_3d_hint(a_dst, &tmA, 0, f0, kb, bar, pol_a);
+        if (DUAL) tma_load_3d_hint(a_dst + kps * Plan::a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
+        tma_load_3d(a_dst + kps * Plan::a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0, kb, bar);
+        armed = it + 1;
+        continue;
+      }
+      mbar_expect_tx(bar, kcount * Plan::stage_bytes);
+      for (int kk = 0; kk < kcount; ++kk) {
+        uint8_t* st = tiles + ((size_t)s * kps + kk) * Plan::stage_bytes;
+        const int kb = kb_begin + it * kps + kk;
+        const int k0 = kb * kTileK;
+        const uint32_t a_dst = smem_u32(st);
+        if (p.a_tiled) {
+          // tile-major weight: tile (feature tile, k block) is one contiguous TF x 64 block
+          const int row = (blockIdx.x * kb_total + kb) * TF;
+          tma_load_2d_hint(a_dst, &tmA, 0, row, bar, pol_a);
+          if (DUAL) tma_load_2d_hint(a_dst + Plan::a_bytes, &tmA2, 0, row, bar, pol_a);
+        } else if (!p.a_mn_major) {
+          tma_load_2d_hint(a_dst, &tmA, k0, f0, bar, pol_a);
+          if (DUAL) tma_load_2d_hint(a_dst + Plan::a_bytes, &tmA2, k0, f0, bar, pol_a);
+        } else {
+          tma_load_2d(a_dst, &tmA, f0, k0, bar);
+          if (TF == 128) tma_load_2d(a_dst + 8192, &tmA, f0 + 64, k0, bar);
+        }
+        const uint32_t b_dst = a_dst + Plan::a_bytes * (DUAL ? 2 : 1);
+        if (!p.b_mn_major) {
+          tma_load_2d(b_dst, &tmB, k0, t0, bar);
+        } else {
 #pragma unroll
-        for (int c = 0; c < BN / 64; ++c) tma_load_2d(b_dst + c * 8192, &tmB, t0 + c * 64, k0, bar);
+          for (int c = 0; c < BN / 64; ++c)
+            tma_load_2d(b_dst + c * 8192, &tmB, t0 + c * 64, k0, bar);
+        }
       }
       armed = it + 1;
     }
@@ -289,30 +329,42 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     }
   } else if (warp == 1 && lane == 0) {
     // ---------------- UMMA issuer ----------------
-    const uint32_t idesc = make_idesc_bf16(kTileF, BN, p.a_mn_major, p.b_mn_major);
+    const uint32_t idesc = make_idesc_bf16(TF, BN, p.a_mn_major, p.b_mn_major);
     const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u;
     const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
     const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u;
     const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
+    constexpr int NACC = Plan::nacc;
     bool ok = true;
-    for (int it = 0; it < n_kb && ok; ++it) {
+    for (int it = 0; it < n_it && ok; ++it) {
       const int s = it % stages;
       const uint32_t ph = (it / stages) & 1;
       ok = mbar_wait(smem_u32(&ctrl->full[s]), ph, abort_flag, p.status, kStatusTimeoutFull);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t a_base = smem_u32(tiles + (size_t)s * Plan::stage_bytes);
-      const uint32_t b_base = a_base + Plan::a_bytes * (DUAL ? 2 : 1);
+      if (p.debug_mode == 1 || p.debug_mode == 4) {  // timing experiment: no tensor-core work
+        mbar_arrive(smem_u32(&ctrl->empty[s]));
+        continue;
+      }
+      const int kcount = min(kps, n_kb - it * kps);
+      for (int kk = 0; kk < kcount; ++kk) {
+        // kps == 1: stage = [A][A2][B]; kps > 1: stage = [A x kps][A2 x kps][B x kps]
+        const uint32_t st_base = smem_u32(tiles + (size_t)s * kps * Plan::stage_bytes);
+        const uint32_t a_base = st_base + kk * Plan::a_bytes;
+        const uint32_t a2_base = a_base + kps * Plan::a_bytes;
+        const uint32_t b_base =
+            st_base + kps * Plan::a_bytes * (DUAL ? 2 : 1) + kk * Plan::b_bytes;
 #pragma unroll
-      for (int k = 0; k < kTileK / kUmmaK; ++k) {
-        const uint64_t bdesc = make_sw128_desc(b_base + k * b_kstep, b_lbo, 1024);
-        const uint64_t adesc = make_sw128_desc(a_base + k * a_kstep, a_lbo, 1024);
-        const uint32_t acc = (it > 0 || k > 0) ? 1u : 0u;
-        umma_f16(tmem_base, adesc, bdesc, idesc, acc);
-        if (DUAL) {
-          const uint64_t a2desc =
-              make_sw128_desc(a_base + Plan::a_bytes + k * a_kstep, a_lbo, 1024);
-          umma_f16(tmem_base + BN, a2desc, bdesc, idesc, acc);
+        for (int k = 0; k < kTileK / kUmmaK; ++k) {
+          const uint64_t bdesc = make_sw128_desc(b_base + k * b_kstep, b_lbo, 1024);
+          const uint64_t adesc = make_sw128_desc(a_base + k * a_kstep, a_lbo, 1024);
+          const int chain = k % NACC;
+          const uint32_t acc = (it > 0 || kk > 0 || k >= NACC) ? 1u : 0u;
+          umma_f16(tmem_base + chain * BN, adesc, bdesc, idesc, acc);
+          if (DUAL) {
+            const uint64_t a2desc = make_sw128_desc(a2_base + k * a_kstep, a_lbo, 1024);
+            umma_f16(tmem_base + (NACC + chain) * BN, a2desc, bdesc, idesc, acc);
+          }
         }
       }
       umma_commit(smem_u32(&ctrl->empty[s]));  // stage reusable once these UMMAs have read it
@@ -323,13 +375,27 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // ---------------- epilogue warps: accumulator -> registers ----------------
   const bool is_epi = warp >= 2;
   const int q = warp & 3;                 // TMEM lane quarter this warp may touch
-  const int lane_row = q * 32 + lane;
+  // M = 128: accumulator row r sits on TMEM lane r. M = 64: row r sits on lane
+  // (r / 16) * 32 + r % 16, i.e. only the lower 16 lanes of each warp's quarter hold rows.
+  const int lane_row = (TF == 128) ? q * 32 + lane : q * 16 + (lane & 15);
+  const bool lane_valid = (TF == 128) || lane < 16;
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   const int slice = BN / S;               // token columns this CTA finishes
+  // issue the TMEM load of 8 token columns of accumulator `a` (0, or 1 = second operand of a
+  // dual GEMM); the caller waits once for a whole group of loads
+  auto issue_acc = [&](int a, int col, float* v) {
+    static_assert(Plan::nacc == 1, "epilogue assumes one accumulation chain");
+    tmem_ld_x8(taddr + a * BN + col, v);
+  };
   bool acc_ok = true;
   if (is_epi) {
-    acc_ok = mbar_wait(smem_u32(&ctrl->tmem_full), 0, abort_flag, p.status,
-                       kStatusTimeoutTmemFull);
+    // one lane per warp polls (with back-off); the rest of the warp parks at the syncwarp
+    int ok_i = 1;
+    if (lane == 0)
+      ok_i = mbar_wait_relaxed(smem_u32(&ctrl->tmem_full), 0, abort_flag, p.status,
+                               kStatusTimeoutTmemFull) ? 1 : 0;
+    ok_i = __shfl_sync(0xffffffffu, ok_i, 0);
+    acc_ok = ok_i != 0;
     tc_fence_after();
     if (S > 1 && acc_ok && n_kb > 0) {
       // reduce-scatter: send the columns owned by each peer into that peer's exchange buffer
@@ -338,19 +404,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const int slot = rank < peer ? rank : rank - 1;
         for (int c = 0; c < slice; c += 8) {
           float v[8];
-          tmem_ld_x8(taddr + peer * slice + c, v);
+          issue_acc(0, peer * slice + c, v);
           tmem_ld_wait();
-          const uint32_t base = smem_u32(xchg) + ((slot * slice + c) * kTileF + lane_row) * 4;
-#pragma unroll
-          for (int j = 0; j < 8; ++j)
-            st_cluster_f32(mapa_shared(base + j * kTileF * 4, peer), v[j]);
-          if (DUAL) {
-            tmem_ld_x8(taddr + BN + peer * slice + c, v);
-            tmem_ld_wait();
-            const uint32_t base2 = base + (S - 1) * slice * kTileF * 4;
+          const uint32_t base = smem_u32(xchg) + ((slot * slice + c) * TF + lane_row) * 4;
+          if (lane_valid) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
-              st_cluster_f32(mapa_shared(base2 + j * kTileF * 4, peer), v[j]);
+              st_cluster_f32(mapa_shared(base + j * TF * 4, peer), v[j]);
+          }
+          if (DUAL) {
+            issue_acc(1, peer * slice + c, v);
+            tmem_ld_wait();
+            const uint32_t base2 = base + (S - 1) * slice * TF * 4;
+            if (lane_valid) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j)
+                st_cluster_f32(mapa_shared(base2 + j * TF * 4, peer), v[j]);
+            }
           }
         }
       }
@@ -361,32 +431,46 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
 
   if (p.pdl) pdl_launch_dependents();
 
-  if (is_epi && acc_ok) {
+  if (is_epi && acc_ok && p.debug_mode != 3) {
     const int c_begin = rank * slice;
-    const int f = f0 + lane_row;
-    for (int c = 0; c < slice; c += 8) {
-      float v[8], v2[8];
+    const int f = lane_valid ? f0 + lane_row : p.F;  // rows past F are masked in the epilogue
+    for (int c = 0; c < slice; c += 32) {
+      // up to 32 columns per round trip to tensor memory
+      const int nb = (slice - c) >= 32 ? 4 : (slice - c) / 8;
+      float v[32], v2[DUAL ? 32 : 1];
       if (n_kb > 0) {
-        tmem_ld_x8(taddr + c_begin + c, v);
-        if (DUAL) tmem_ld_x8(taddr + BN + c_begin + c, v2);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          if (b < nb) {
+            issue_acc(0, c_begin + c + 8 * b, v + 8 * b);
+            if constexpr (DUAL) issue_acc(1, c_begin + c + 8 * b, v2 + 8 * b);
+          }
+        }
         tmem_ld_wait();
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) v[j] = v2[j] = 0.f;
-      }
-      if (S > 1) {
-        for (int slot = 0; slot < S - 1; ++slot) {
-          const float* src = xchg + (size_t)(slot * slice + c) * kTileF + lane_row;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] += src[j * kTileF];
-          if (DUAL) {
-            const float* src2 = src + (size_t)(S - 1) * slice * kTileF;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v2[j] += src2[j * kTileF];
-          }
+        for (int j = 0; j < 32; ++j) {
+          v[j] = 0.f;
+          if constexpr (DUAL) v2[j] = 0.f;
         }
       }
-      epilogue8<DUAL>(p, f, t0 + c_begin + c, v, v2);
+#pragma unroll
+      for (int b = 0; b < 4; ++b) {
+        if (b >= nb) continue;
+        if (S > 1) {
+          for (int slot = 0; slot < S - 1; ++slot) {
+            const float* src = xchg + (size_t)(slot * slice + c + 8 * b) * TF + lane_row;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[8 * b + j] += src[j * TF];
+            if constexpr (DUAL) {
+              const float* src2 = src + (size_t)(S - 1) * slice * TF;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v2[8 * b + j] += src2[j * TF];
+            }
+          }
+        }
+        epilogue8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2);
+      }
     }
   }
 
@@ -433,14 +517,31 @@ static int make_map(CUtensorMap* m, const void* base, long long inner, long long
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-template <int BN, bool DUAL>
+// 3-D view of a K-major bf16 operand [rows, K] (K % 64 == 0): {64, rows, K/64}, so that one box
+// {64, box_rows, kps} brings kps consecutive 64-wide k-blocks as kps swizzled tiles.
+static int make_map3d(CUtensorMap* m, const void* base, long long K, long long rows, long long ld,
+                      int box_rows, int kps) {
+  EncodeTiledFn fn = get_encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)kps};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <int BN, bool DUAL, int TF>
 static int launch(const E2hGemmParams& p, const CUtensorMap& ta, const CUtensorMap& ta2,
                   const CUtensorMap& tb, cudaStream_t stream) {
-  using Plan = SmemPlan<BN, DUAL>;
-  const size_t smem = 1024 /*alignment slack*/ + kCtrlBytes + (size_t)p.stages * Plan::stage_bytes +
-                      xchg_bytes(BN, p.splitk, DUAL);
+  using Plan = SmemPlan<BN, DUAL, TF>;
+  const size_t smem = 1024 /*alignment slack*/ + kCtrlBytes +
+                      (size_t)p.stages * p.kps * Plan::stage_bytes +
+                      xchg_bytes(BN, p.splitk, DUAL, TF);
   if (smem > 227 * 1024) return -12;
-  auto kern = umma_gemm_kernel<BN, DUAL>;
+  auto kern = umma_gemm_kernel<BN, DUAL, TF>;
   static size_t configured = 0;  // per instantiation
   if (smem > configured) {
     cudaError_t e =
@@ -450,7 +551,7 @@ static int launch(const E2hGemmParams& p, const CUtensorMap& ta, const CUtensorM
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((p.F + kTileF - 1) / kTileF, (p.T + BN - 1) / BN, p.splitk);
+  cfg.gridDim = dim3((p.F + TF - 1) / TF, (p.T + BN - 1) / BN, p.splitk);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -485,25 +586,51 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
   const int kb_total = (p.K + kTileK - 1) / kTileK;
   if (kb_total < p.splitk) return -4;
   if (p.dual && (p.a_mn_major || p.a2 == nullptr)) return -5;
+  if (p.a_tiled && p.a_mn_major) return -5;
   if ((p.lda % 8) || (p.ldb % 8) || (p.dual && (p.lda2 % 8))) return -6;  // 16-byte strides for TMA
   if (((uintptr_t)p.a & 15) || ((uintptr_t)p.b & 15)) return -7;
-  const int stage_bytes = 16384 * (p.dual ? 2 : 1) + p.bn * 128;
-  const int budget = 227 * 1024 - 2048 - xchg_bytes(p.bn, p.splitk, p.dual);
+  if (p.tf != 64 && p.tf != 128) p.tf = 128;
+  if (p.tf == 64 && p.bn == 256) return -9;
+  if (p.kps < 1) p.kps = 1;
+  if (p.kps > 8) p.kps = 8;
+  // several k-blocks per stage ride on 3-D boxes: K-major operands with K % 64 == 0 only
+  if (p.a_mn_major || p.b_mn_major || p.a_tiled || (p.K % 64) != 0) p.kps = 1;
+  const int stage_bytes = p.kps * (p.tf * 128 * (p.dual ? 2 : 1) + p.bn * 128);
+  const int budget = 227 * 1024 - 2048 - xchg_bytes(p.bn, p.splitk, p.dual, p.tf);
   int max_stages = budget / stage_bytes;
   if (max_stages > kMaxStages) max_stages = kMaxStages;
   if (p.stages <= 0 || p.stages > max_stages) p.stages = max_stages;
   if (p.stages < 1) return -8;
-  if (p.stages > kb_total) p.stages = kb_total < 1 ? 1 : kb_total;
+  {
+    const int n_it = (kb_total / p.splitk + p.kps - 1) / p.kps;
+    if (p.stages > n_it) p.stages = n_it < 1 ? 1 : n_it;
+  }
 
   CUtensorMap ta, ta2, tb;
   int r;
-  if (!p.a_mn_major)
-    r = make_map(&ta, p.a, p.K, p.F, p.lda, kTileF);
+  const long long tiled_rows = (long long)((p.F + p.tf - 1) / p.tf) * kb_total * p.tf;
+  if (p.kps > 1) {
+    r = make_map3d(&ta, p.a, p.K, p.F, p.lda, p.tf, p.kps);
+    if (r) return r;
+    if (p.dual) {
+      r = make_map3d(&ta2, p.a2, p.K, p.F, p.lda2, p.tf, p.kps);
+      if (r) return r;
+    } else {
+      ta2 = ta;
+    }
+    r = make_map3d(&tb, p.b, p.K, p.T, p.ldb, p.bn, p.kps);
+    if (r) return r;
+  } else {
+  if (p.a_tiled)
+    r = make_map(&ta, p.a, 64, tiled_rows, 64, p.tf);
+  else if (!p.a_mn_major)
+    r = make_map(&ta, p.a, p.K, p.F, p.lda, p.tf);
   else
     r = make_map(&ta, p.a, p.F, p.K, p.lda, 64);
   if (r) return r;
   if (p.dual) {
-    r = make_map(&ta2, p.a2, p.K, p.F, p.lda2, kTileF);
+    r = p.a_tiled ? make_map(&ta2, p.a2, 64, tiled_rows, 64, p.tf)
+                  : make_map(&ta2, p.a2, p.K, p.F, p.lda2, p.tf);
     if (r) return r;
   } else {
     ta2 = ta;
@@ -513,16 +640,26 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
   else
     r = make_map(&tb, p.b, p.T, p.K, p.ldb, 64);
   if (r) return r;
+  }
 
-#define E2H_DISPATCH(BN_, DUAL_) return launch<BN_, DUAL_>(p, ta, ta2, tb, stream)
+#define E2H_DISPATCH(BN_, DUAL_, TF_) return launch<BN_, DUAL_, TF_>(p, ta, ta2, tb, stream)
+  if (p.tf == 64) {
+    if (p.dual) {
+      if (p.bn == 64) E2H_DISPATCH(64, true, 64);
+      E2H_DISPATCH(128, true, 64);
+    } else {
+      if (p.bn == 64) E2H_DISPATCH(64, false, 64);
+      E2H_DISPATCH(128, false, 64);
+    }
+  }
   if (p.dual) {
-    if (p.bn == 64) E2H_DISPATCH(64, true);
-    if (p.bn == 128) E2H_DISPATCH(128, true);
-    E2H_DISPATCH(256, true);
+    if (p.bn == 64) E2H_DISPATCH(64, true, 128);
+    if (p.bn == 128) E2H_DISPATCH(128, true, 128);
+    E2H_DISPATCH(256, true, 128);
   } else {
-    if (p.bn == 64) E2H_DISPATCH(64, false);
-    if (p.bn == 128) E2H_DISPATCH(128, false);
-    E2H_DISPATCH(256, false);
+    if (p.bn == 64) E2H_DISPATCH(64, false, 128);
+    if (p.bn == 128) E2H_DISPATCH(128, false, 128);
+    E2H_DISPATCH(256, false, 128);
   }
 #undef E2H_DISPATCH
 }

@@ -48,6 +48,11 @@ struct E2hGemmParams {
   void* kcache;          // bf16 [max_batch, n_kv, smax, head_dim]
   void* vcache;
   int* status;           // int32 status word (0 = ok)
+  int tf;                // features per tile: 128 (default) or 64 (more CTAs for skinny GEMMs)
+  int kps;               // 64-wide k blocks per pipeline stage (1..8): amortises the barrier
+                         // hand-shake when the per-block tensor work is tiny (decode)
+  int debug_mode;        // 0; timing experiments only: 1 = skip the MMAs, 2 = skip the loads
+  int a_tiled;           // A (and A2) stored tile-major: [F/tf][ceil(K/64)][tf][64], zero padded
 };
 
 #ifdef __cplusplus

@@ -89,6 +89,28 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
   }
 }
 
+// Same, for waits that last a whole main loop (the epilogue waiting for the accumulator): backs
+// off with nanosleep so that the polling does not compete with the producer's and the MMA
+// thread's own barrier traffic.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint32_t bar, uint32_t parity,
+                                                  volatile int* abort_flag, int* status,
+                                                  int code) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long t0 = clock64();
+  unsigned ns = 64;
+  while (true) {
+    __nanosleep(ns);
+    if (ns < 512) ns *= 2;
+    if (mbar_try_wait(bar, parity)) return true;
+    if (*abort_flag) return false;
+    if (clock64() - t0 > kWaitLimitCycles) {
+      *abort_flag = 1;
+      if (status) atomicCAS(status, 0, code);
+      return false;
+    }
+  }
+}
+
 // ---- TMA ---------------------------------------------------------------------------------------
 __device__ __forceinline__ void tma_prefetch_desc(const void* tmap) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(tmap)) : "memory");
@@ -116,6 +138,15 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const void* tmap, int 
       "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
       "{%2, %3, %4}], [%5];"
       ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(bar)
+      : "memory");
+}
+__device__ __forceinline__ void tma_load_3d_hint(uint32_t dst, const void* tmap, int x, int y,
+                                                 int z, uint32_t bar, uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint "
+      "[%0], [%1, {%2, %3, %4}], [%5], %6;"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(x), "r"(y), "r"(z), "r"(bar),
+      "l"(policy)
       : "memory");
 }
 __device__ __forceinline__ uint64_t policy_evict_first() {

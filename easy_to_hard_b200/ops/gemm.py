@@ -24,13 +24,23 @@ def _ld(t: torch.Tensor) -> int:
     return t.stride(0)
 
 
-def pick_tiles(F: int, T: int, K: int, dual: bool, splitk: Optional[int], bn: Optional[int],
-               stages: int = 0):
-    """Token-tile width, cluster split-K factor and pipeline depth.
+def _smem_bytes(bn: int, tf: int, dual: bool, splitk: int, stages: int, kps: int = 1) -> int:
+    stage = kps * (tf * 128 * (2 if dual else 1) + bn * 128)
+    xchg = (splitk - 1) * (bn // splitk) * tf * 4 * (2 if dual else 1) if splitk > 1 else 0
+    return 2048 + stages * stage + xchg
 
-    Few tiles (decode: T <= 64..128) => split K across a cluster until about two CTAs per SM
-    stream the weight (the stage count is then cut so that two CTAs fit in one SM's shared
-    memory); many tiles => the widest tile and the deepest pipeline that fit."""
+
+def pick_tiles(F: int, T: int, K: int, dual: bool, splitk: Optional[int], bn: Optional[int],
+               stages: int = 0, tf: Optional[int] = None, kps: int = 0):
+    """Tile shape (features x tokens), cluster split-K factor, pipeline depth and k-blocks per
+    pipeline stage.
+
+    Skinny GEMMs (decode: at most one token tile) stream the weight once, so the aim is one CTA
+    per SM on as many of the 148 SMs as possible: K is split across a cluster while the CTA count
+    stays <= 148, and several 64-wide k-blocks share one pipeline stage because the per-stage
+    barrier hand-shake (not the tensor work) bounds the k-loop at this size. Measured on B200:
+    4 k-blocks per stage for a single accumulator, 2 for the dual (SwiGLU) one or when the tiles
+    need more than one wave. Large GEMMs take the widest tile, one k-block per stage."""
     if bn is None:
         if T <= 64:
             bn = 64
@@ -38,19 +48,28 @@ def pick_tiles(F: int, T: int, K: int, dual: bool, splitk: Optional[int], bn: Op
             bn = 128
         else:
             bn = 256
-    tiles = -(-F // 128) * -(-T // bn)
     kb = -(-K // 64)
+    t_tiles = -(-T // bn)
+    skinny = bn <= 128 and t_tiles == 1
+    if tf is None:
+        tf = 128
+    if tf == 64 and bn == 256:
+        tf = 128
+    tiles = -(-F // tf) * t_tiles
     if splitk is None:
         splitk = 1
-        if bn <= 128:
-            while (splitk < 8 and tiles * splitk * 2 <= 2 * N_SM and kb // (splitk * 2) >= 4
+        if skinny:
+            while (splitk < 8 and tiles * splitk * 2 <= N_SM and kb // (splitk * 2) >= 4
                    and bn % (splitk * 2 * 8) == 0):
                 splitk *= 2
-    if stages <= 0 and N_SM < tiles * splitk <= 2 * N_SM:
-        stage_bytes = 16384 * (2 if dual else 1) + bn * 128
-        xchg = (splitk - 1) * (bn // splitk) * 512 * (2 if dual else 1) if splitk > 1 else 0
-        stages = max(2, (113 * 1024 - 2048 - xchg) // stage_bytes)
-    return bn, splitk, stages
+    if kps <= 0:
+        if not skinny or K % 64:
+            kps = 1
+        elif dual or tiles * splitk > N_SM:
+            kps = 2
+        else:
+            kps = 4
+    return bn, splitk, stages, tf, kps
 
 
 def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tensor] = None,
@@ -58,10 +77,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          aux: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
          a_mn_major: bool = False, b_mn_major: bool = False, accumulate: bool = False,
          splitk: Optional[int] = None, bn: Optional[int] = None, stages: int = 0,
-         rope: Optional[dict] = None, pdl: bool = False) -> None:
+         rope: Optional[dict] = None, pdl: bool = False, tf: Optional[int] = None,
+         tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T])."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
-    if a_mn_major:
+    if tiled_shape is not None:      # a is a TiledWeight payload: logical shape given
+        F, K = tiled_shape
+        assert tf is not None, "a tile-major weight fixes the feature-tile height"
+    elif a_mn_major:
         K, F = a.shape
     else:
         F, K = a.shape
@@ -71,17 +94,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         T, Kb = b.shape
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
     dual = a2 is not None
-    bn, splitk, stages = pick_tiles(F, T, K, dual, splitk, bn, stages)
+    bn, splitk, stages, tf, kps = pick_tiles(F, T, K, dual, splitk, bn, stages, tf, kps)
     p = GemmParams()
     p.F, p.T, p.K = F, T, K
     p.splitk, p.epi, p.stages = splitk, epi, stages
     p.a_mn_major, p.b_mn_major = int(a_mn_major), int(b_mn_major)
     p.bn, p.dual, p.accumulate, p.pdl = bn, int(dual), int(accumulate), int(pdl)
-    p.lda, p.ldb = _ld(a), _ld(b)
+    p.tf = tf
+    p.debug_mode = debug_mode
+    p.kps = kps
+    p.a_tiled = int(tiled_shape is not None)
+    p.lda, p.ldb = (64 if tiled_shape is not None else _ld(a)), _ld(b)
     p.a, p.b = a.data_ptr(), b.data_ptr()
     if dual:
         assert a2.shape == a.shape
-        p.a2, p.lda2 = a2.data_ptr(), _ld(a2)
+        p.a2, p.lda2 = a2.data_ptr(), (64 if tiled_shape is not None else _ld(a2))
     if out is not None:
         p.out, p.ldo = out.data_ptr(), out.stride(0)
     if out2 is not None:
@@ -100,6 +127,18 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         p.kcache, p.vcache = rope["kcache"].data_ptr(), rope["vcache"].data_ptr()
     p.status = _lib.status_word(a.device).data_ptr()
     _lib.check(_lib.lib().e2h_gemm_umma(C.byref(p), _lib.stream()), "e2h_gemm_umma")
+
+
+def tile_weight(w: torch.Tensor, tf: int = 128) -> torch.Tensor:
+    """[F, K] -> tile-major [ceil(F/tf) * ceil(K/64) * tf, 64] (zero padded): every (tf x 64)
+    tile that one CTA streams per k-step is one contiguous block, so the weight stream is a
+    sequence of full-page DRAM bursts instead of 128-byte pieces one row pitch apart."""
+    F, K = w.shape
+    Fp, Kp = -(-F // tf) * tf, -(-K // 64) * 64
+    if (Fp, Kp) != (F, K):
+        w = torch.nn.functional.pad(w, (0, Kp - K, 0, Fp - F))
+    return (w.view(Fp // tf, tf, Kp // 64, 64).permute(0, 2, 1, 3).contiguous()
+            .view(Fp // tf * (Kp // 64) * tf, 64))
 
 
 def linear(x: torch.Tensor, w: torch.Tensor, out: Optional[torch.Tensor] = None,

@@ -35,7 +35,8 @@ SHAPES = [  # (T, F, K)
 
 @pytest.mark.parametrize("T,F,K", SHAPES)
 @pytest.mark.parametrize("splitk", [None, 1, 2, 4, 8])
-def test_linear_bf16(T, F, K, splitk):
+@pytest.mark.parametrize("tf", [128, 64])
+def test_linear_bf16(T, F, K, splitk, tf):
     from easy_to_hard_b200.ops import gemm
     x, w = _mk(T, K, seed=1), _mk(F, K, scale=1 / math.sqrt(K), seed=2)
     kb = -(-K // 64)
@@ -44,7 +45,9 @@ def test_linear_bf16(T, F, K, splitk):
         if kb < splitk:
             pytest.skip("fewer K blocks than splits")
         bn = 64 if T <= 64 else 128
-    y = gemm.linear(x, w, splitk=splitk, bn=bn)
+    if tf == 64 and (bn or (64 if T <= 64 else 128 if T <= 128 else 256)) == 256:
+        bn = 128
+    y = gemm.linear(x, w, splitk=splitk, bn=bn, tf=tf if splitk is not None else None)
     _check_status()
     _close(y, x.float() @ w.float().T)
 
@@ -60,17 +63,18 @@ def test_linear_tile_widths_and_f32(bn):
 
 
 @pytest.mark.parametrize("T,splitk", [(64, 1), (64, 2), (64, 4), (200, 1), (1000, 1)])
-def test_swiglu_and_dual(T, splitk):
+@pytest.mark.parametrize("tf", [128, 64])
+def test_swiglu_and_dual(T, splitk, tf):
     from easy_to_hard_b200.ops import gemm
     K, F = 512, 688
     x = _mk(T, K, seed=5)
     w1, w3 = _mk(F, K, scale=1 / math.sqrt(K), seed=6), _mk(F, K, scale=1 / math.sqrt(K), seed=7)
-    y = gemm.linear_swiglu(x, w1, w3, splitk=splitk)
+    y = gemm.linear_swiglu(x, w1, w3, splitk=splitk, tf=tf)
     g = (x.float() @ w1.float().T).bfloat16()
     u = (x.float() @ w3.float().T).bfloat16()
     _check_status()
     _close(y, torch.nn.functional.silu(g) * u)
-    o1, o2 = gemm.linear_dual(x, w1, w3, splitk=splitk)
+    o1, o2 = gemm.linear_dual(x, w1, w3, splitk=splitk, tf=tf)
     _check_status()
     _close(o1, g)
     _close(o2, u)
@@ -104,7 +108,8 @@ def test_dgrad_wgrad(T, F, K):
 
 @pytest.mark.parametrize("sq,B,n_head,n_kv,D", [(1, 64, 8, 8, 128), (16, 3, 8, 2, 64),
                                                  (1, 5, 4, 4, 64)])
-def test_qkv_rope_kv(sq, B, n_head, n_kv, D):
+@pytest.mark.parametrize("tf", [128, 64])
+def test_qkv_rope_kv(sq, B, n_head, n_kv, D, tf):
     from easy_to_hard_b200.ops import gemm, reference
     dim, smax, pos0 = 512, 64, 7
     T = B * sq
@@ -116,7 +121,7 @@ def test_qkv_rope_kv(sq, B, n_head, n_kv, D):
     q = torch.empty(T, n_head * D, dtype=torch.bfloat16, device="cuda")
     pos = torch.tensor([pos0], dtype=torch.int32, device="cuda")
     gemm.linear_qkv_rope(x, wqkv, q, freqs=freqs, pos_base=pos, sq=sq, n_head=n_head, n_kv=n_kv,
-                         head_dim=D, kcache=kc, vcache=vc)
+                         head_dim=D, kcache=kc, vcache=vc, tf=tf)
     _check_status()
     qkv = (x.float() @ wqkv.float().T).bfloat16().view(B, sq, -1)
     qr, kr, vr = qkv.split([n_head * D, n_kv * D, n_kv * D], dim=-1)
