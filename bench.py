@@ -1,0 +1,254 @@
+"""Headline benchmark: batched decode tokens/s of the Llemma-7B architecture.
+
+    python bench.py [--gpus N --steps K --warmup W] [--impl ours|reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \
+        --master-port P bench.py --gpus N --steps K --warmup W
+
+Workload (fixed): LLaMA-2-7B architecture with the Llemma vocabulary (32 layers, dim 4096, 32
+heads, ffn 11008, vocab 32016, RoPE theta 1e6), random normal(0, 0.02) bf16 weights, batch 64,
+256-token random prompts, 512 new tokens, temperature 0.7, top-k 50, static KV cache, tensor
+parallel over the N GPUs. One "step" is one whole batched generation (prefill + 511 decode
+steps); ``value`` = 64 * 512 * K / time, the reference's own metric
+(inference_generate.py:484-492: decoded tokens x batch / time, prefill included), device-timed
+with CUDA events between barriers, max over ranks.
+
+``e2e`` is the same metric through the public API (``inference_generate.generate``) with the
+prompt copied from pinned host memory and the generated tokens copied back to pinned host memory
+inside the timed region of every step.
+
+``--impl reference`` runs the unmodified reference from ``baseline/_ref`` (its ``Transformer``,
+``apply_tp`` and ``generate`` with its ``torch.compile``'d decode step) on the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+BATCH, PROMPT, NEW = 64, 256, 512
+TEMPERATURE, TOP_K = 0.7, 50
+MODEL = "llemma-7b-32016"
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine")
+    return ap.parse_args()
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index: int):
+        self.gpu, self.proc, self.lines = gpu_index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
+                 "-lms", "200", "-i", str(self.gpu)],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._pump, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _pump(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            pass
+        sm, smax, reasons = [], None, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for ln in self.lines:
+            parts = [p.strip() for p in ln.split(",")]
+            if len(parts) < 7:
+                continue
+            try:
+                sm.append(float(parts[0]))
+                smax = float(parts[1])
+            except ValueError:
+                continue
+            for n, v in zip(names, parts[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": smax,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+def dist_setup(n):
+    import torch
+    import torch.distributed as dist
+    rank = int(os.environ.get("RANK", 0))
+    local = int(os.environ.get("LOCAL_RANK", 0))
+    world = int(os.environ.get("WORLD_SIZE", 1))
+    torch.cuda.set_device(local)
+    if world > 1 and not dist.is_initialized():
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    return rank, local, world
+
+
+def max_over_ranks(x: float) -> float:
+    import torch
+    import torch.distributed as dist
+    if not dist.is_initialized():
+        return x
+    t = torch.tensor([x], dtype=torch.float64, device="cuda")
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def barrier_sync():
+    import torch
+    import torch.distributed as dist
+    if dist.is_initialized():
+        dist.barrier()
+    torch.cuda.synchronize()
+
+
+def timed(fn, steps):
+    """K calls of fn between barriers, CUDA events on the launching stream; ms, max over ranks."""
+    import torch
+    barrier_sync()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        fn(i)
+    e1.record()
+    barrier_sync()
+    return max_over_ranks(e0.elapsed_time(e1))
+
+
+def run_ours(a):
+    import torch
+    rank, local, world = dist_setup(a.gpus)
+    from easy_to_hard_b200.models.model import ModelArgs, Transformer
+    from easy_to_hard_b200.models import tp
+    from easy_to_hard_b200.models.engine import get_engine
+    from easy_to_hard_b200.ops import _lib
+    import inference_generate as api
+
+    tp.initialize_model_parallel(world)
+    cfg = ModelArgs.from_name(MODEL)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = Transformer(cfg, freeze_tok_embeddings=True, freeze_output=True,
+                            freeze_norm=True).to(torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    for name, t in list(model.named_parameters()) + list(model.named_buffers()):
+        if t.dim() == 2:
+            t.data.normal_(0.0, 0.02, generator=g)
+    if world > 1:
+        tp.apply_tp(model)
+        torch.cuda.empty_cache()
+    model.eval()
+    eng = get_engine(model, BATCH, PROMPT + NEW, reduce=a.reduce)
+
+    gen = torch.Generator().manual_seed(7)
+    host_prompts = [torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), generator=gen,
+                                  dtype=torch.int32).pin_memory()
+                    for _ in range(a.steps + a.warmup)]
+    dev_prompts = [p.cuda() for p in host_prompts]
+    host_out = torch.empty(BATCH, PROMPT + NEW, dtype=torch.int32).pin_memory()
+
+    def step_device(i):
+        api.generate(model, dev_prompts[i % len(dev_prompts)], None, NEW,
+                     temperature=TEMPERATURE, top_k=TOP_K, seed=i)
+
+    def step_e2e(i):
+        p = host_prompts[i % len(host_prompts)].to("cuda", non_blocking=True)
+        seq, _ = api.generate(model, p, None, NEW, temperature=TEMPERATURE, top_k=TOP_K, seed=i)
+        host_out.copy_(seq, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(a.warmup):
+        step_device(i)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda i: step_device(a.warmup + i), a.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(lambda i: step_e2e(a.warmup + i), a.steps)
+    status = _lib.read_status()
+    toks = BATCH * NEW * a.steps
+    key = next(iter(eng._graphs)) if eng._graphs else None
+    launches = (eng.prefill_launches + (NEW - 1) * eng.decode_launches(key)) * a.steps
+    if rank == 0:
+        out = {
+            "metric": "batched_decode_tokens_per_s", "value": toks / (ms / 1e3),
+            "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
+            "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random token ids, random-init weights)",
+            "impl": "ours",
+            "config": {"model": "Llemma-7B architecture (llemma-7b-32016)",
+                       "global_batch": BATCH, "seq_len": PROMPT + NEW, "prompt_len": PROMPT,
+                       "new_tokens": NEW, "temperature": TEMPERATURE, "top_k": TOP_K,
+                       "parallelism": f"tp{world}", "tp_reduce": eng.reduce,
+                       "step": "one batched generation: prefill + 511 decode steps",
+                       "l2": "inputs larger than L2 (weights 13.5 GB + KV cache stream per step)"},
+            "clocks": clocks,
+            "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": BATCH * PROMPT * 4,
+                    "d2h_bytes_per_step": BATCH * (PROMPT + NEW) * 4},
+            "gpu_launches": launches, "kernel_status": status,
+        }
+        print(json.dumps(out), flush=True)
+
+
+def run_reference(a):
+    """The unmodified reference on the same workload, through its own generate()."""
+    ref_dir = os.path.join(ROOT, "baseline", "_ref")
+
+    def unavailable(why):
+        if int(os.environ.get("RANK", 0)) == 0:
+            print(json.dumps({"impl": "reference", "unavailable": why}), flush=True)
+
+    if not os.path.isdir(os.path.join(ref_dir, "models")):
+        return unavailable("reference is not installed under baseline/_ref "
+                           "(no setup.py/pyproject in the reference; see DESIGN.md)")
+    try:
+        from baseline import reference_runner
+    except Exception as e:  # noqa: BLE001
+        return unavailable(f"reference runner import failed: {type(e).__name__}: {e}")
+    try:
+        reference_runner.run(a, dict(batch=BATCH, prompt=PROMPT, new=NEW, temperature=TEMPERATURE,
+                                     top_k=TOP_K), ClockSampler)
+    except Exception as e:  # noqa: BLE001
+        unavailable(f"reference failed: {type(e).__name__}: {str(e)[:300]}")
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+    try:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+    except Exception:
+        pass

@@ -75,6 +75,10 @@ class DecodeEngine:
         self.logits = torch.empty(B, self.vocab, dtype=torch.float32, device=dev)
         self.partial = (torch.empty(1, B, self.dim, dtype=torch.float32, device=dev)
                         if self.reduce == "nccl" else None)
+        self.rp = None
+        if self.reduce == "p2p":
+            from ..parallel.symm import RowParallelReduce
+            self.rp = RowParallelReduce(B, self.dim, groups.get_model_parallel_group())
         self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
         self.next_tok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.left_pad = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -99,6 +103,24 @@ class DecodeEngine:
             dist.all_reduce(part, group=groups.get_model_parallel_group())
             Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                       x_out=x_out)
+            self._count(2)
+        elif self.reduce == "p2p":
+            T = x.shape[0]
+            if T > self.rp.T:  # prefill-sized inputs take the NCCL route
+                part = torch.empty(1, T, self.dim, dtype=torch.float32, device=self.dev)
+                gemm.linear(x, w, out=part[0])
+                dist.all_reduce(part, group=groups.get_model_parallel_group())
+                Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
+                                          x_out=x_out)
+            else:
+                rp = self.rp
+                s = rp.slot()
+                gemm.linear(x, w, out=rp.partial_out(s, T), signal=rp.signal_ptrs(s),
+                            ticket=rp.gemm_ticket[s:s + 1])
+                Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=rp.partial_ptrs(s),
+                                          h_out=h_out, x_out=x_out, flags=rp.flags(s),
+                                          use_count=rp.use_count[s:s + 1],
+                                          ticket=rp.norm_ticket[s:s + 1], T=T, dim=self.dim)
             self._count(2)
         else:
             raise ValueError(self.reduce)
@@ -252,3 +274,15 @@ class DecodeEngine:
 def _freqs(S, D, base, dev):
     from ..ops import reference
     return reference.precompute_freqs_cis(S, D, base, dtype=torch.bfloat16, device=dev)
+
+
+def get_engine(model, batch_size: int, seq_length: int, **kw) -> DecodeEngine:
+    """Engine cached on the model; rebuilt when a larger batch / sequence is requested."""
+    eng = getattr(model, "_decode_engine", None)
+    if eng is None or eng.B < batch_size or eng.S < seq_length:
+        if eng is not None:
+            del model._decode_engine
+            torch.cuda.empty_cache()
+        eng = DecodeEngine(model, batch_size, seq_length, **kw)
+        model._decode_engine = eng
+    return eng

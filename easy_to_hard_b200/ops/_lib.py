@@ -39,6 +39,9 @@ class GemmParams(C.Structure):
         ("tf", C.c_int),
         ("kps", C.c_int),
         ("debug_mode", C.c_int),
+        ("n_signal", C.c_int),
+        ("signal", C.c_void_p * 8),
+        ("ticket", C.c_void_p),
         ("a_tiled", C.c_int),
     ]
 
@@ -56,8 +59,8 @@ _vp, _i, _ll, _f, _ull = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulong
 
 _SIGNATURES = {
     "e2h_gemm_umma": [C.POINTER(GemmParams), _vp],
-    "e2h_rmsnorm_fwd": [_vp, _vp, _vp, _vp, _i, _ll, _vp, _vp, _vp, _vp, _i, _i, _f, _vp, _i,
-                        _vp, _vp],
+    "e2h_rmsnorm_fwd": [_vp, _vp, _vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
+                        _vp, _vp, _vp, _vp, _vp],
     "e2h_rmsnorm_bwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "e2h_embedding": [_vp, _vp, _vp, _i, _i, _vp],
     "e2h_swiglu_fwd": [_vp, _vp, _vp, _ll, _vp],

@@ -52,6 +52,9 @@ struct E2hGemmParams {
   int kps;               // 64-wide k blocks per pipeline stage (1..8): amortises the barrier
                          // hand-shake when the per-block tensor work is tiny (decode)
   int debug_mode;        // 0; timing experiments only: 1 = skip the MMAs, 2 = skip the loads
+  int n_signal;          // > 0: bump signal[0..n_signal) by one when the whole grid is done
+  int* signal[8];        // flag words (local or peer-GPU memory), one per tensor-parallel rank
+  unsigned int* ticket;  // grid completion counter (local, zero between launches)
   int a_tiled;           // A (and A2) stored tile-major: [F/tf][ceil(K/64)][tf][64], zero padded
 };
 

@@ -24,31 +24,41 @@ __device__ __forceinline__ float block_sum(float v, float* red) {
   return t;
 }
 
+struct PartPtrs {
+  const float* p[8];   // one fp32 [T, dim] partial per split / tensor-parallel rank
+};
+
 // One CTA per token row.
 //   h_in      : bf16 [T, dim]  residual stream (or nullptr when `tokens` is given)
 //   tokens    : int32 [T]      when set, the row is gathered from `emb` instead of h_in
-//   partials  : fp32 [n_part, T, dim] partial sums of a row-parallel linear (split-K slabs or
-//               one slab per tensor-parallel rank); added to the row when n_part > 0
+//   parts     : n_part fp32 [T, dim] partial sums of a row-parallel linear (one per
+//               tensor-parallel rank; the pointers may be peer-GPU addresses, read with
+//               system-scope loads over NVLink); added to the row when n_part > 0
 //   h_out     : bf16 [T, dim]  updated residual stream (written when non-null)
 //   x_out     : bf16 [T, dim]  rmsnorm(h) * weight     (written when non-null)
-//   flags     : optional int32 [n_part]; slab i is read only once flags[i] >= flag_want
-//               (set by the peer that pushed it); bounded wait.
+//   flags     : optional int32 [n_part] in local memory; rank i bumps flags[i] by one when its
+//               partial for this use is complete. The kernel waits (bounded) for
+//               flags[i] >= *use_count + 1; the last CTA to finish bumps *use_count, so the
+//               protocol needs no host-side epoch and replays inside a CUDA graph.
 __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
                                    const int* __restrict__ tokens,
                                    const __nv_bfloat16* __restrict__ emb,
-                                   const float* __restrict__ partials, int n_part,
-                                   long long part_stride, const __nv_bfloat16* __restrict__ weight,
+                                   const PartPtrs parts, int n_part,
+                                   const __nv_bfloat16* __restrict__ weight,
                                    __nv_bfloat16* __restrict__ h_out,
                                    __nv_bfloat16* __restrict__ x_out, float* __restrict__ rstd_out,
-                                   int dim, float eps, const int* flags, int flag_want,
-                                   int* status) {
+                                   int dim, float eps, const int* flags, int* use_count,
+                                   unsigned int* ticket, int* status) {
   extern __shared__ float row[];  // dim floats + 32
   float* red = row + dim;
   const int t = blockIdx.x;
   const __nv_bfloat16* src =
       tokens ? emb + (long long)tokens[t] * dim : (h_in ? h_in + (long long)t * dim : nullptr);
-  if (flags != nullptr && threadIdx.x < n_part) wait_flag_ge(flags + threadIdx.x, flag_want, status);
-  if (flags != nullptr) __syncthreads();
+  if (flags != nullptr) {
+    const int want = *use_count + 1;
+    if (threadIdx.x < n_part) wait_flag_ge(flags + threadIdx.x, want, status);
+    __syncthreads();
+  }
   float ss = 0.f;
   for (int i = threadIdx.x * 2; i < dim; i += blockDim.x * 2) {
     float a = 0.f, b = 0.f;
@@ -60,8 +70,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
     if (n_part > 0) {
       float pa = 0.f, pb = 0.f;
       for (int s = 0; s < n_part; ++s) {
-        const float2 pv =
-            *reinterpret_cast<const float2*>(partials + s * part_stride + (long long)t * dim + i);
+        const float* src = parts.p[s] + (long long)t * dim + i;
+        const float2 pv = flags ? ld_sys_f32x2(src) : *reinterpret_cast<const float2*>(src);
         pa += pv.x;
         pb += pv.y;
       }
@@ -77,6 +87,17 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
       o.x = __float2bfloat16_rn(a);
       o.y = __float2bfloat16_rn(b);
       *reinterpret_cast<__nv_bfloat162*>(h_out + (long long)t * dim + i) = o;
+    }
+  }
+  if (flags != nullptr) {
+    // all reads of this use are done: the last CTA advances the use counter
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+        *ticket = 0;
+        *use_count = *use_count + 1;
+      }
     }
   }
   if (x_out == nullptr) return;
@@ -189,17 +210,21 @@ using namespace e2h;
 
 extern "C" {
 
-int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb, const float* partials,
-                    int n_part, long long part_stride, const void* weight, void* h_out,
+int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
+                    const void* const* part_ptrs, int n_part, const void* weight, void* h_out,
                     void* x_out, float* rstd_out, int T, int dim, float eps, const int* flags,
-                    int flag_want, int* status, void* stream) {
-  if (dim % 2) return -1;
+                    int* use_count, unsigned int* ticket, int* status, void* stream) {
+  if (dim % 2 || n_part > 8) return -1;
+  if (flags != nullptr && (use_count == nullptr || ticket == nullptr)) return -2;
+  PartPtrs parts;
+  for (int i = 0; i < 8; ++i)
+    parts.p[i] = i < n_part ? static_cast<const float*>(part_ptrs[i]) : nullptr;
   const int threads = dim >= 2048 ? 512 : 128;
   const size_t smem = (dim + 32) * sizeof(float);
   rmsnorm_fwd_kernel<<<T, threads, smem, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, partials, n_part,
-      part_stride, (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out,
-      rstd_out, dim, eps, flags, flag_want, status);
+      (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, parts, n_part,
+      (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, rstd_out, dim,
+      eps, flags, use_count, ticket, status);
   return (int)cudaGetLastError();
 }
 

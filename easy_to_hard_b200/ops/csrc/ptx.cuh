@@ -302,6 +302,16 @@ __device__ __forceinline__ int ld_acquire_gpu(const int* p) {
   asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
   return v;
 }
+// System-scope (L1-bypassing) loads: data that a peer GPU wrote, or that lives in a peer's memory.
+__device__ __forceinline__ float2 ld_sys_f32x2(const float* p) {
+  float2 v;
+  asm volatile("ld.relaxed.sys.global.v2.f32 {%0, %1}, [%2];" : "=f"(v.x), "=f"(v.y) : "l"(p)
+               : "memory");
+  return v;
+}
+__device__ __forceinline__ void red_release_sys_add(int* p, int v) {
+  asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
 // Bounded wait for *p >= want. Returns false (and records kStatusTimeoutFlag) on time-out.
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status) {
   const long long t0 = clock64();

@@ -14,6 +14,15 @@ def _s():
     return _lib.stream()
 
 
+def _part_array(parts):
+    """ctypes array of up to 8 device pointers from tensors / raw addresses."""
+    import ctypes as C
+    arr = (C.c_void_p * 8)()
+    for i, t in enumerate(parts):
+        arr[i] = t if isinstance(t, int) else t.data_ptr()
+    return arr
+
+
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
             out: Optional[torch.Tensor] = None) -> torch.Tensor:
     if not x.is_cuda:
@@ -23,33 +32,45 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
     assert x2.is_contiguous() and x.dtype == torch.bfloat16
     if out is None:
         out = torch.empty_like(x2)
-    rc = _lib.lib().e2h_rmsnorm_fwd(x2.data_ptr(), None, None, None, 0, 0, weight.data_ptr(),
-                                    None, out.data_ptr(), None, x2.shape[0], dim, eps, None, 0,
+    rc = _lib.lib().e2h_rmsnorm_fwd(x2.data_ptr(), None, None, _part_array([]), 0,
+                                    weight.data_ptr(), None, out.data_ptr(), None, x2.shape[0],
+                                    dim, eps, None, None, None,
                                     _lib.status_word(x.device).data_ptr(), _s())
     _lib.check(rc, "rmsnorm_fwd")
     return out.view(x.shape)
 
 
 def fused_residual_rmsnorm(h: Optional[torch.Tensor], weight: Optional[torch.Tensor], eps: float,
-                           *, partials: Optional[torch.Tensor] = None,
-                           tokens: Optional[torch.Tensor] = None,
+                           *, partials=None, tokens: Optional[torch.Tensor] = None,
                            emb: Optional[torch.Tensor] = None,
                            h_out: Optional[torch.Tensor] = None,
                            x_out: Optional[torch.Tensor] = None,
-                           flags: Optional[torch.Tensor] = None, flag_want: int = 0):
+                           flags: Optional[torch.Tensor] = None,
+                           use_count: Optional[torch.Tensor] = None,
+                           ticket: Optional[torch.Tensor] = None, T: Optional[int] = None,
+                           dim: Optional[int] = None):
     """h' = (h | emb[tokens]) + sum_i partials[i];  x = rmsnorm(h') * weight.
 
-    `partials` fp32 [n, T, dim] holds the partial sums of a row-parallel linear (one slab per
-    tensor-parallel rank); `flags` int32 [n] are waited on (bounded) before a slab is read."""
-    ref = tokens if tokens is not None else h
-    T = ref.shape[0]
-    dim = (emb if tokens is not None else h).shape[-1]
-    n_part = 0 if partials is None else partials.shape[0]
+    ``partials`` is an fp32 tensor [n, T, dim] or a list of n fp32 [T, dim] tensors / raw device
+    addresses (a tensor-parallel peer's buffer, read over NVLink). With ``flags`` (int32 [n],
+    local) the kernel first waits, bounded, until every rank has bumped its flag for this use
+    (``use_count`` and ``ticket`` are the device-side counters of the protocol)."""
+    ref = tokens if tokens is not None else (h if h is not None else x_out)
+    T = T if T is not None else ref.shape[0]
+    if dim is None:
+        dim = (emb if tokens is not None else (h if h is not None else x_out)).shape[-1]
+    if partials is None:
+        parts = []
+    elif torch.is_tensor(partials):
+        parts = [partials[i] for i in range(partials.shape[0])]
+    else:
+        parts = list(partials)
+    dev = ref.device
     rc = _lib.lib().e2h_rmsnorm_fwd(
         _lib.ptr(h) if tokens is None else None, _lib.ptr(tokens), _lib.ptr(emb),
-        _lib.ptr(partials), n_part, 0 if partials is None else partials.stride(0),
-        _lib.ptr(weight), _lib.ptr(h_out), _lib.ptr(x_out), None, T, dim, eps,
-        _lib.ptr(flags), flag_want, _lib.status_word(ref.device).data_ptr(), _s())
+        _part_array(parts), len(parts), _lib.ptr(weight), _lib.ptr(h_out), _lib.ptr(x_out), None,
+        T, dim, eps, _lib.ptr(flags), _lib.ptr(use_count), _lib.ptr(ticket),
+        _lib.status_word(dev).data_ptr(), _s())
     _lib.check(rc, "rmsnorm_fwd")
     return h_out, x_out
 

@@ -78,7 +78,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          a_mn_major: bool = False, b_mn_major: bool = False, accumulate: bool = False,
          splitk: Optional[int] = None, bn: Optional[int] = None, stages: int = 0,
          rope: Optional[dict] = None, pdl: bool = False, tf: Optional[int] = None,
-         tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0) -> None:
+         tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
+         signal=None, ticket: Optional[torch.Tensor] = None) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T])."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     if tiled_shape is not None:      # a is a TiledWeight payload: logical shape given
@@ -102,6 +103,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     p.bn, p.dual, p.accumulate, p.pdl = bn, int(dual), int(accumulate), int(pdl)
     p.tf = tf
     p.debug_mode = debug_mode
+    if signal:
+        assert ticket is not None and len(signal) <= 8
+        p.n_signal = len(signal)
+        for i, f in enumerate(signal):
+            p.signal[i] = f if isinstance(f, int) else f.data_ptr()
+        p.ticket = ticket.data_ptr()
     p.kps = kps
     p.a_tiled = int(tiled_shape is not None)
     p.lda, p.ldb = (64 if tiled_shape is not None else _ld(a)), _ld(b)
