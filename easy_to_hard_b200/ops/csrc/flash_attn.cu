@@ -1,0 +1,418 @@
+// Causal flash attention (forward) on tcgen05 tensor cores, head_dim 128 or 64.
+//
+// One CTA = one (batch, head, 128-query block). Roles (192 threads):
+//   warp 0    TMA producer: Q once, then K / V tiles (128 keys) through two-deep rings
+//   warp 1    UMMA issuer:  S = Q K^T  (TMEM cols [0,128)),  O_blk = P V  (TMEM cols [128,256))
+//   warps 2-5 softmax: thread r owns query row r. It reads its row of S from TMEM (no
+//             cross-thread reduction for max / sum), writes P = exp(S - m) as bf16 into shared
+//             memory in the 128-byte-swizzled K-major layout the UMMA expects, and keeps the
+//             running output row O (fp32, head_dim registers), rescaled by exp(m_old - m_new).
+// S(j+1) is issued as soon as S(j) has been read out, so the tensor core works on the next
+// score tile while the softmax of the current one runs.
+//
+// Masking follows the reference model (models/model.py:221-228, 338-344): key j is visible to
+// query i when j <= i + (Sk - Sq) and j >= left_pad[b], or when j is the diagonal; with
+// left_pad == nullptr this is plain causal attention (training, scoring, reward models).
+// Layouts are given by strides, so Q/K/V may be views into the fused qkv activation or the
+// static KV cache ([B, Hkv, Smax, D]).
+//
+// All mbarrier waits are bounded; a time-out sets the status word and the CTA still reaches
+// every barrier and frees its tensor memory.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <float.h>
+#include <string.h>
+#include <mutex>
+
+#include "ptx.cuh"
+
+namespace e2h {
+
+constexpr int kBQ = 128;   // queries per CTA
+constexpr int kBK = 128;   // keys per tile
+
+struct FlashParams {
+  int B, H, Hkv, Sq, Sk, D;
+  float scale;              // 1/sqrt(D)
+  const int* left_pad;      // [B] or nullptr
+  __nv_bfloat16* out;       // [B, Sq, H, D] with strides o_sb, o_ss, o_sh (elements)
+  long long o_sb, o_ss, o_sh;
+  float* lse;               // [B, H, Sq] or nullptr
+  int* status;
+};
+
+struct FlashCtrl {
+  uint64_t q_full;
+  uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
+  uint64_t s_full, s_empty, p_full, o_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const void* tmap, int c0, int c1, int c2,
+                                            int c3, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, "
+      "{%2, %3, %4, %5}], [%6];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(c0), "r"(c1), "r"(c2), "r"(c3),
+      "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, float* v) {
+  uint32_t r[32];
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,"
+      "%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+        "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]),
+        "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]),
+        "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]),
+        "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+#pragma unroll
+  for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// D = head_dim (64 or 128). Tiles are stored as D/64 column halves of [rows x 64] bf16, each
+// half 128-byte swizzled (what a TMA box {64, rows} produces).
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                 const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
+  constexpr int NH = D / 64;                 // 64-wide halves of the head dimension
+  constexpr int kHalfBytes = 128 * 128;      // [128 rows x 64] bf16
+  constexpr int kTileBytes = NH * kHalfBytes;
+  constexpr int kPBytes = 2 * kHalfBytes;    // P: [128 q x 128 keys]
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  FlashCtrl* ctrl = reinterpret_cast<FlashCtrl*>(smem);
+  uint8_t* q_s = smem + 1024;
+  uint8_t* k_s = q_s + kTileBytes;           // 2 stages
+  uint8_t* v_s = k_s + 2 * kTileBytes;       // 2 stages
+  uint8_t* p_s = v_s + 2 * kTileBytes;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = qb * kBQ;
+  const int off = p.Sk - p.Sq;                        // query i sits at key position i + off
+  const int lp = p.left_pad ? p.left_pad[b] : 0;
+  // key tiles this query block needs: from the left-pad boundary (or the block's own diagonal
+  // when the whole block is padding) to the diagonal of its last row
+  const int last_key = min(p.Sk - 1, q0 + kBQ - 1 + off);
+  const int first_key = max(0, min(lp, q0 + off));
+  const int j_begin = first_key / kBK;
+  const int j_end = last_key / kBK + 1;
+  const int n_j = j_end - j_begin;
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctrl->q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&ctrl->k_full[s]), 1);
+      mbar_init(smem_u32(&ctrl->k_empty[s]), 1);
+      mbar_init(smem_u32(&ctrl->v_full[s]), 1);
+      mbar_init(smem_u32(&ctrl->v_empty[s]), 1);
+    }
+    mbar_init(smem_u32(&ctrl->s_full), 1);
+    mbar_init(smem_u32(&ctrl->s_empty), 4);   // one arrival per softmax warp
+    mbar_init(smem_u32(&ctrl->p_full), 4);
+    mbar_init(smem_u32(&ctrl->o_full), 1);
+    ctrl->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), 256);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_s = ctrl->tmem_base;
+  const uint32_t tmem_o = tmem_s + 128;
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    mbar_expect_tx(smem_u32(&ctrl->q_full), kTileBytes);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf)
+      tma_load_4d(smem_u32(q_s + hf * kHalfBytes), &tmQ, hf * 64, q0, h, b,
+                  smem_u32(&ctrl->q_full));
+    for (int it = 0; it < n_j; ++it) {
+      const int s = it & 1;
+      const uint32_t ph = (it >> 1) & 1;
+      const int key0 = (j_begin + it) * kBK;
+      if (!mbar_wait(smem_u32(&ctrl->k_empty[s]), ph ^ 1, abort_flag, p.status,
+                     kStatusTimeoutEmpty))
+        break;
+      mbar_expect_tx(smem_u32(&ctrl->k_full[s]), kTileBytes);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+        tma_load_4d(smem_u32(k_s + s * kTileBytes + hf * kHalfBytes), &tmK, hf * 64, key0, hk, b,
+                    smem_u32(&ctrl->k_full[s]));
+      if (!mbar_wait(smem_u32(&ctrl->v_empty[s]), ph ^ 1, abort_flag, p.status,
+                     kStatusTimeoutEmpty))
+        break;
+      mbar_expect_tx(smem_u32(&ctrl->v_full[s]), kTileBytes);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf)
+        tma_load_4d(smem_u32(v_s + s * kTileBytes + hf * kHalfBytes), &tmV, hf * 64, key0, hk, b,
+                    smem_u32(&ctrl->v_full[s]));
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- UMMA issuer ----------------
+    const uint32_t idesc_s = make_idesc_bf16(128, kBK, 0, 0);   // S = Q K^T, both K-major
+    const uint32_t idesc_o = make_idesc_bf16(128, D, 0, 1);     // O = P V, V is MN-major
+    bool ok = mbar_wait(smem_u32(&ctrl->q_full), 0, abort_flag, p.status, kStatusTimeoutFull);
+    auto issue_s = [&](int it) {
+      const int s = it & 1;
+      ok = ok && mbar_wait(smem_u32(&ctrl->k_full[s]), (it >> 1) & 1, abort_flag, p.status,
+                           kStatusTimeoutFull);
+      if (!ok) return;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s + s * kTileBytes);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t o = (kk / 4) * kHalfBytes + (kk % 4) * 32;
+        umma_f16(tmem_s, make_sw128_desc(qa + o, 16, 1024), make_sw128_desc(ka + o, 16, 1024),
+                 idesc_s, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(smem_u32(&ctrl->k_empty[s]));
+      umma_commit(smem_u32(&ctrl->s_full));
+    };
+    if (n_j > 0) issue_s(0);
+    for (int it = 0; it < n_j && ok; ++it) {
+      const int s = it & 1;
+      if (it + 1 < n_j) {
+        // S(it) has been read out of tensor memory: the next score tile may overwrite it
+        ok = mbar_wait(smem_u32(&ctrl->s_empty), it & 1, abort_flag, p.status,
+                       kStatusTimeoutTmemEmpty);
+        if (!ok) break;
+        issue_s(it + 1);
+        if (!ok) break;
+      }
+      ok = mbar_wait(smem_u32(&ctrl->p_full), it & 1, abort_flag, p.status, kStatusTimeoutFull) &&
+           mbar_wait(smem_u32(&ctrl->v_full[s]), (it >> 1) & 1, abort_flag, p.status,
+                     kStatusTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * kTileBytes);
+#pragma unroll
+      for (int kk = 0; kk < kBK / 16; ++kk) {
+        const uint64_t adesc =
+            make_sw128_desc(pa + (kk / 4) * kHalfBytes + (kk % 4) * 32, 16, 1024);
+        const uint64_t bdesc = make_sw128_desc(va + kk * 2048, kHalfBytes, 1024);
+        umma_f16(tmem_o, adesc, bdesc, idesc_o, kk > 0 ? 1u : 0u);
+      }
+      umma_commit(smem_u32(&ctrl->v_empty[s]));
+      umma_commit(smem_u32(&ctrl->o_full));
+    }
+  }
+
+  if (warp >= 2) {
+    // ---------------- softmax / output warps ----------------
+    const int qrt = warp & 3;
+    const int row = qrt * 32 + lane;                 // query row within the block = TMEM lane
+    const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
+    const int qi = q0 + row;                          // query index
+    const int qpos = qi + off;                        // its key position (diagonal)
+    const float sl2 = p.scale * 1.4426950408889634f;  // scale * log2(e)
+    float m = -FLT_MAX, l = 0.f;
+    float o_acc[D];
+#pragma unroll
+    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_j; ++it) {
+      const int key0 = (j_begin + it) * kBK;
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->s_full), it & 1, abort_flag, p.status,
+                             kStatusTimeoutTmemFull);
+      tc_fence_after();
+      ok = __all_sync(0xffffffffu, ok);
+      // pass 1: row maximum of the visible scores (32 columns per trip to tensor memory)
+      float mx = m;
+#pragma unroll
+      for (int c = 0; c < kBK; c += 32) {
+        float sv[32];
+        if (ok) tmem_ld_x32(tmem_s + lane_off + c, sv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const int j = key0 + c + i;
+          const bool vis = (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+          if (vis) mx = fmaxf(mx, sv[i] * sl2);
+        }
+      }
+      const float alpha = (m == -FLT_MAX) ? 0.f : exp2f(m - mx);
+      const float msafe = (mx == -FLT_MAX) ? 0.f : mx;
+      float rs = 0.f;
+      // pass 2: P = exp2(s - m) as bf16 into shared memory: [128 x 64] halves, the 16-byte
+      // chunk c of a row lands at chunk position (c ^ (row & 7))
+      uint8_t* prow = p_s + row * 128;
+#pragma unroll
+      for (int c = 0; c < kBK; c += 32) {
+        float sv[32];
+        if (ok) tmem_ld_x32(tmem_s + lane_off + c, sv);
+        tmem_ld_wait();
+#pragma unroll
+        for (int c8 = 0; c8 < 4; ++c8) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float pv[2];
+#pragma unroll
+            for (int u = 0; u < 2; ++u) {
+              const int i = c8 * 8 + 2 * e + u;
+              const int j = key0 + c + i;
+              const bool vis = (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+              pv[u] = vis ? exp2f(sv[i] * sl2 - msafe) : 0.f;
+            }
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(pv[0], pv[1]);
+            // the row sum uses the rounded values that the PV product will see
+            rs += __bfloat162float(pk.x) + __bfloat162float(pk.y);
+            packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+          }
+          const int col8 = (c >> 3) + c8;            // 16-byte chunk index within the row
+          const int half = col8 >> 3, chunk = col8 & 7;
+          *reinterpret_cast<uint4*>(prow + half * kHalfBytes + ((chunk ^ (row & 7)) << 4)) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty));
+      l = l * alpha + rs;
+      m = mx;
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->p_full));
+      // O = O * alpha + P V
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->o_full), it & 1, abort_flag, p.status,
+                             kStatusTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        float ov[32];
+        if (ok) tmem_ld_x32(tmem_o + lane_off + c, ov);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i) o_acc[c + i] = o_acc[c + i] * alpha + ov[i];
+      }
+      tc_fence_before();
+    }
+    if (ok && qi < p.Sq) {
+      const float inv = l > 0.f ? 1.f / l : 0.f;
+      __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)qi * p.o_ss +
+                            (long long)h * p.o_sh;
+#pragma unroll
+      for (int c = 0; c < D; c += 8) {
+        uint32_t packed[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const __nv_bfloat162 pk =
+              __floats2bfloat162_rn(o_acc[c + 2 * e] * inv, o_acc[c + 2 * e + 1] * inv);
+          packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+        }
+        *reinterpret_cast<uint4*>(orow + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+      }
+      if (p.lse)
+        p.lse[((long long)b * p.H + h) * p.Sq + qi] =
+            (l > 0.f) ? (m * 0.6931471805599453f + logf(l)) : -FLT_MAX;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(ctrl->tmem_base, 256);
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                                  const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn flash_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+  });
+  return fn;
+}
+
+// [B, S, H, D] view with element strides (sb, ss, sh), D contiguous: dims {D, S, H, B}.
+static int make_map4d(CUtensorMap* m, const void* base, int D, int S, int H, int B, long long sb,
+                      long long ss, long long sh, int box_rows) {
+  EncodeTiledFn fn = flash_encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[4] = {(cuuint64_t)D, (cuuint64_t)S, (cuuint64_t)H, (cuuint64_t)B};
+  cuuint64_t strides[3] = {(cuuint64_t)ss * 2, (cuuint64_t)sh * 2, (cuuint64_t)sb * 2};
+  cuuint32_t box[4] = {64u, (cuuint32_t)box_rows, 1u, 1u};
+  cuuint32_t estr[4] = {1u, 1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+}  // namespace e2h
+
+// q: [B, Sq, H, D] view (strides q_sb, q_ss, q_sh); k, v: [B, Sk, Hkv, D] views; out like q.
+extern "C" int e2h_flash_fwd(const void* q, long long q_sb, long long q_ss, long long q_sh,
+                             const void* k, const void* v, long long k_sb, long long k_ss,
+                             long long k_sh, void* out, long long o_sb, long long o_ss,
+                             long long o_sh, float* lse, const int* left_pad, int B, int H,
+                             int Hkv, int Sq, int Sk, int D, float scale, int* status,
+                             void* stream) {
+  using namespace e2h;
+  if (D != 128 && D != 64) return -1;
+  if (H % Hkv) return -2;
+  if ((q_ss % 8) || (q_sh % 8) || (q_sb % 8) || (k_ss % 8) || (k_sh % 8) || (k_sb % 8)) return -3;
+  CUtensorMap tq, tk, tv;
+  int r = make_map4d(&tq, q, D, Sq, H, B, q_sb, q_ss, q_sh, kBQ);
+  if (r) return r;
+  r = make_map4d(&tk, k, D, Sk, Hkv, B, k_sb, k_ss, k_sh, kBK);
+  if (r) return r;
+  r = make_map4d(&tv, v, D, Sk, Hkv, B, k_sb, k_ss, k_sh, kBK);
+  if (r) return r;
+  FlashParams p;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk; p.D = D;
+  p.scale = scale; p.left_pad = left_pad;
+  p.out = static_cast<__nv_bfloat16*>(out);
+  p.o_sb = o_sb; p.o_ss = o_ss; p.o_sh = o_sh;
+  p.lse = lse; p.status = status;
+  dim3 grid((Sq + kBQ - 1) / kBQ, H, B);
+  const int tile = (D / 64) * 128 * 128;
+  const size_t smem = 1024 + 1024 + 5 * (size_t)tile + 2 * 128 * 128;
+  cudaError_t e;
+  if (D == 128) {
+    static bool done = false;
+    if (!done) {
+      e = cudaFuncSetAttribute(flash_fwd_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      done = true;
+    }
+    flash_fwd_kernel<128><<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  } else {
+    static bool done = false;
+    if (!done) {
+      e = cudaFuncSetAttribute(flash_fwd_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      done = true;
+    }
+    flash_fwd_kernel<64><<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+  }
+  return (int)cudaGetLastError();
+}
