@@ -44,6 +44,8 @@ def parse():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine")
+    ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch in the "
+                    "decode graph (1) or plain stream order (0)")
     return ap.parse_args()
 
 
@@ -164,7 +166,7 @@ def run_ours(a):
         tp.apply_tp(model)
         torch.cuda.empty_cache()
     model.eval()
-    eng = get_engine(model, BATCH, PROMPT + NEW, reduce=a.reduce)
+    eng = get_engine(model, BATCH, PROMPT + NEW, reduce=a.reduce, use_pdl=bool(a.pdl))
 
     gen = torch.Generator().manual_seed(7)
     host_prompts = [torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), generator=gen,
@@ -246,9 +248,18 @@ if __name__ == "__main__":
         run_reference(args)
     else:
         run_ours(args)
+    # Leave without tearing NCCL down: destroying a communicator whose kernels sit in captured
+    # CUDA graphs can block at interpreter exit. Every rank has synchronised and the result
+    # line is flushed, so a hard exit is safe.
     try:
+        import torch
         import torch.distributed as dist
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
         if dist.is_initialized():
-            dist.destroy_process_group()
+            dist.barrier()
     except Exception:
         pass
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)

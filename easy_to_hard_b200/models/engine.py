@@ -40,7 +40,7 @@ from ..parallel import groups
 
 class DecodeEngine:
     def __init__(self, model, max_batch_size: int, max_seq_length: int,
-                 reduce: str = "auto", use_graph: bool = True):
+                 reduce: str = "auto", use_graph: bool = True, use_pdl: bool = True):
         cfg = model.config
         self.model = model
         self.cfg = cfg
@@ -48,6 +48,7 @@ class DecodeEngine:
         self.dev = model.output.weight.device
         assert self.dev.type == "cuda", "DecodeEngine needs a CUDA device"
         self.use_graph = use_graph
+        self.use_pdl = use_pdl
         self.B = max_batch_size
         self.S = (max_seq_length + 7) // 8 * 8
         blk0 = model.layers[0].attention
@@ -184,8 +185,13 @@ class DecodeEngine:
         torch.cuda.current_stream().wait_stream(s)
         g = torch.cuda.CUDAGraph()
         self.launches_per_step = 0
-        with torch.cuda.graph(g):
-            self._decode_step(*key)
+        # programmatic dependent launch: each kernel's prologue overlaps its predecessor's tail
+        old_pdl = _lib.lib().e2h_set_pdl(1 if self.use_pdl else 0)
+        try:
+            with torch.cuda.graph(g):
+                self._decode_step(*key)
+        finally:
+            _lib.lib().e2h_set_pdl(old_pdl)
         for t, v in zip((self.pos, self.next_tok, self.seq, self.eos_flag, self.n_unfinished),
                         saved):
             t.copy_(v)

@@ -59,6 +59,7 @@ _vp, _i, _ll, _f, _ull = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulong
 
 _SIGNATURES = {
     "e2h_gemm_umma": [C.POINTER(GemmParams), _vp],
+    "e2h_gemm_persistent": [C.POINTER(GemmParams), _vp],
     "e2h_rmsnorm_fwd": [_vp, _vp, _vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
                         _vp, _vp, _vp, _vp, _vp],
     "e2h_rmsnorm_bwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
@@ -72,6 +73,7 @@ _SIGNATURES = {
     "e2h_clip_coef": [_vp, _f, _vp, _vp, _vp],
     "e2h_flash_fwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _vp,
                       _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "e2h_set_pdl": [_i],
     "e2h_sample": [_vp, _ll, _i, _i, _f, _i, _ull, _vp, _i, _vp, _vp, _ll, _i, _i, _vp, _vp,
                    _vp, _vp],
 }

@@ -16,6 +16,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace e2h {
@@ -53,6 +54,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const bool lane_active = hl < LPK;
   const int slot = warp * 2 + half;
 
+  pdl_wait_prior();
+  pdl_launch_dependents();
   const int pos = *pos_ptr;              // index of the newest token (already in the cache)
   int start = left_pad ? left_pad[b] : 0;
   if (start > pos) start = pos;
@@ -191,6 +194,8 @@ template <int D>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial,
                                          __nv_bfloat16* __restrict__ out, int n_split) {
   const long long bh = blockIdx.x;
+  pdl_wait_prior();
+  pdl_launch_dependents();
   const float* pp = partial + bh * n_split * (D + 2);
   float mm = -FLT_MAX;
   for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, pp[s * (D + 2) + D]);
@@ -211,13 +216,14 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
                          const int* pos, const int* left_pad, int B, int n_head, int n_kv, int smax,
                          float scale, int n_split, cudaStream_t stream) {
   dim3 grid(n_kv * B, n_split);
-  attn_decode_kernel<D, G><<<grid, kWarps * 32, 0, stream>>>(
-      (const __nv_bfloat16*)q, (const __nv_bfloat16*)k, (const __nv_bfloat16*)v,
-      (__nv_bfloat16*)out, partial, pos, left_pad, n_head, n_kv, smax, scale, n_split);
-  if (n_split > 1)
-    attn_decode_merge_kernel<D><<<B * n_head, 128, 0, stream>>>(partial, (__nv_bfloat16*)out,
-                                                                n_split);
-  return (int)cudaGetLastError();
+  cudaError_t e = launch(attn_decode_kernel<D, G>, grid, dim3(kWarps * 32), 0, stream,
+                         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
+                         (const __nv_bfloat16*)v, (__nv_bfloat16*)out, partial, pos, left_pad,
+                         n_head, n_kv, smax, scale, n_split);
+  if (e == cudaSuccess && n_split > 1)
+    e = launch(attn_decode_merge_kernel<D>, dim3(B * n_head), dim3(128), 0, stream,
+               (const float*)partial, (__nv_bfloat16*)out, n_split);
+  return (int)e;
 }
 
 }  // namespace e2h

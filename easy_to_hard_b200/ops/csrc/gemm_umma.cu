@@ -22,7 +22,9 @@
 #include <string.h>
 #include <mutex>
 
+#include "gemm_epilogue.cuh"
 #include "gemm_umma.cuh"
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace e2h {
@@ -65,143 +67,6 @@ struct SmemPlan {
 __host__ __device__ inline int xchg_bytes(int bn, int splitk, int dual, int tf) {
   if (splitk <= 1) return 0;
   return (splitk - 1) * (bn / splitk) * tf * 4 * (dual ? 2 : 1);
-}
-
-struct EpiCtx {
-  int f;        // global feature index of this thread (may be >= F: masked)
-  int t0;       // first token column of the 8-column group
-};
-
-// Applies the epilogue to 8 consecutive token columns of one feature.
-template <bool DUAL>
-__device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0, float* v,
-                                          float* v2) {
-  const bool f_ok = f < p.F;
-  if (p.scale != nullptr) {
-    const float s = f_ok ? p.scale[f] : 0.f;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) v[j] *= s;
-  }
-  switch (p.epi) {
-    case E2H_EPI_STORE_BF16: {
-      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int t = t0 + j;
-        if (f_ok && t < p.T) out[(long long)t * p.ldo + f] = __float2bfloat16_rn(v[j]);
-      }
-    } break;
-    case E2H_EPI_STORE_F32: {
-      float* out = static_cast<float*>(p.out);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int t = t0 + j;
-        if (f_ok && t < p.T) out[(long long)t * p.ldo + f] = v[j];
-      }
-    } break;
-    case E2H_EPI_RESIDUAL: {
-      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-      const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(p.aux);
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int t = t0 + j;
-        if (f_ok && t < p.T) {
-          const long long o = (long long)t * p.ldo + f;
-          out[o] = __float2bfloat16_rn(bf16_round(v[j]) + __bfloat162float(res[o]));
-        }
-      }
-    } break;
-    case E2H_EPI_SWIGLU: {
-      if constexpr (DUAL) {
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = t0 + j;
-          if (f_ok && t < p.T) {
-            const float g = bf16_round(v[j]);
-            const float u = bf16_round(v2[j]);
-            out[(long long)t * p.ldo + f] = __float2bfloat16_rn(bf16_round(silu(g)) * u);
-          }
-        }
-      }
-    } break;
-    case E2H_EPI_DUAL_STORE: {
-      if constexpr (DUAL) {
-        __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-        __nv_bfloat16* out2 = static_cast<__nv_bfloat16*>(p.out2);
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = t0 + j;
-          if (f_ok && t < p.T) {
-            out[(long long)t * p.ldo + f] = __float2bfloat16_rn(v[j]);
-            out2[(long long)t * p.ldo2 + f] = __float2bfloat16_rn(v2[j]);
-          }
-        }
-      }
-    } break;
-    case E2H_EPI_ROWMAJOR_F32_ACC: {
-      float* out = static_cast<float*>(p.out);
-      if (f_ok) {
-        float* row = out + (long long)f * p.ldo;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = t0 + j;
-          if (t < p.T) row[t] = p.accumulate ? row[t] + v[j] : v[j];
-        }
-      }
-    } break;
-    case E2H_EPI_ROWMAJOR_BF16: {
-      __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-      if (f_ok) {
-        __nv_bfloat16* row = out + (long long)f * p.ldo;
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = t0 + j;
-          if (t < p.T) row[t] = __float2bfloat16_rn(v[j]);
-        }
-      }
-    } break;
-    case E2H_EPI_ROPE_KV: {
-      // Feature f belongs to head f / head_dim of the fused [q; k; v] projection. RoPE rotates
-      // the interleaved pair (2i, 2i+1): the partner value sits in the neighbouring lane.
-      const int D = p.head_dim;
-      const int head = f / D;
-      const int d = f - head * D;
-      const bool is_q = head < p.n_head;
-      const bool is_k = !is_q && head < p.n_head + p.n_kv;
-      const bool is_v = !is_q && !is_k;
-      const __nv_bfloat16* freqs = static_cast<const __nv_bfloat16*>(p.freqs);
-      const int pos0 = *p.pos_base;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int t = t0 + j;
-        const float x = bf16_round(v[j]);
-        const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
-        if (!(f_ok && t < p.T)) continue;
-        const int b = t / p.sq;
-        const int s = t - b * p.sq;
-        const int pos = pos0 + s;
-        float y = x;
-        if (!is_v) {
-          const long long fo = ((long long)pos * (D / 2) + (d >> 1)) * 2;
-          const float c = __bfloat162float(freqs[fo]);
-          const float sn = __bfloat162float(freqs[fo + 1]);
-          y = (d & 1) ? (x * c + partner * sn) : (x * c - partner * sn);
-        }
-        const __nv_bfloat16 yb = __float2bfloat16_rn(y);
-        if (is_q) {
-          static_cast<__nv_bfloat16*>(p.out)[(long long)t * p.ldo + f] = yb;
-        } else {
-          const int hk = is_k ? head - p.n_head : head - p.n_head - p.n_kv;
-          __nv_bfloat16* cache = static_cast<__nv_bfloat16*>(is_k ? p.kcache : p.vcache);
-          if (pos < p.smax)
-            cache[(((long long)b * p.n_kv + hk) * p.smax + pos) * D + d] = yb;
-        }
-      }
-    } break;
-    default:
-      break;
-  }
 }
 
 template <int BN, bool DUAL, int TF>
@@ -256,7 +121,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = ctrl->tmem_base;
   if (S > 1) cluster_sync_all();  // every CTA of the cluster is resident before DSMEM traffic
 
-  if (p.pdl) pdl_wait_prior();    // inputs written by the previous kernel are visible from here
+  pdl_wait_prior();         // inputs written by the previous kernel are visible from here
+  pdl_launch_dependents();  // the next kernel may begin its own prologue
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
@@ -429,7 +295,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   __syncwarp();
   if (S > 1) cluster_sync_all();
 
-  if (p.pdl) pdl_launch_dependents();
 
   if (is_epi && acc_ok && p.debug_mode != 3) {
     const int c_begin = rank * slice;
@@ -576,7 +441,7 @@ static int launch(const E2hGemmParams& p, const CUtensorMap& ta, const CUtensorM
     attrs[na].val.clusterDim.z = p.splitk;
     ++na;
   }
-  if (p.pdl) {
+  if (p.pdl || g_pdl) {
     attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attrs[na].val.programmaticStreamSerializationAllowed = 1;
     ++na;

@@ -8,6 +8,7 @@
 #include <cuda_bf16.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace e2h {
@@ -52,6 +53,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
   extern __shared__ float row[];  // dim floats + 32
   float* red = row + dim;
   const int t = blockIdx.x;
+  pdl_wait_prior();
+  pdl_launch_dependents();
   const __nv_bfloat16* src =
       tokens ? emb + (long long)tokens[t] * dim : (h_in ? h_in + (long long)t * dim : nullptr);
   if (flags != nullptr) {
@@ -221,11 +224,10 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
     parts.p[i] = i < n_part ? static_cast<const float*>(part_ptrs[i]) : nullptr;
   const int threads = dim >= 2048 ? 512 : 128;
   const size_t smem = (dim + 32) * sizeof(float);
-  rmsnorm_fwd_kernel<<<T, threads, smem, (cudaStream_t)stream>>>(
-      (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, parts, n_part,
-      (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, rstd_out, dim,
-      eps, flags, use_count, ticket, status);
-  return (int)cudaGetLastError();
+  return (int)launch(rmsnorm_fwd_kernel, dim3(T), dim3(threads), smem, (cudaStream_t)stream,
+                     (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, parts, n_part,
+                     (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out,
+                     rstd_out, dim, eps, flags, use_count, ticket, status);
 }
 
 int e2h_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const void* dres, void* dx,
@@ -268,6 +270,13 @@ int e2h_rope(const void* x, void* out, const void* freqs, const int* pos, int T,
                                                    (const __nv_bfloat16*)freqs, pos, n_heads,
                                                    head_dim, ld, inverse);
   return (int)cudaGetLastError();
+}
+
+// Process-wide switch for programmatic dependent launch (see launch.cuh).
+int e2h_set_pdl(int on) {
+  const int old = e2h::g_pdl;
+  e2h::g_pdl = on ? 1 : 0;
+  return old;
 }
 
 }  // extern "C"

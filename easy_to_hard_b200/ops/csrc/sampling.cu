@@ -15,6 +15,7 @@
 #include <float.h>
 #include <stdint.h>
 
+#include "launch.cuh"
 #include "ptx.cuh"
 
 namespace e2h {
@@ -56,6 +57,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
   __shared__ int red_i[kSampThreads / 32];
   const int b = blockIdx.x;
   const float* row = logits + (long long)b * ld;
+  pdl_wait_prior();
+  pdl_launch_dependents();
   const int pos = *pos_ptr;
   const bool greedy = temperature <= 0.f;
 
@@ -157,8 +160,7 @@ extern "C" int e2h_sample(const float* logits, long long ld, int B, int vocab, f
                           int* eos_flag, int* n_unfinished, unsigned int* ticket, void* stream) {
   using namespace e2h;
   if (advance_pos && ticket == nullptr) return -1;
-  sample_kernel<<<B, kSampThreads, 0, (cudaStream_t)stream>>>(
-      logits, ld, vocab, temperature, top_k, seed, pos_ptr, advance_pos, next_tok, seq, seq_ld,
-      seq_len, eos_id, eos_flag, n_unfinished, ticket);
-  return (int)cudaGetLastError();
+  return (int)launch(sample_kernel, dim3(B), dim3(kSampThreads), 0, (cudaStream_t)stream, logits,
+                     ld, vocab, temperature, top_k, seed, pos_ptr, advance_pos, next_tok, seq,
+                     seq_ld, seq_len, eos_id, eos_flag, n_unfinished, ticket);
 }

@@ -79,7 +79,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          splitk: Optional[int] = None, bn: Optional[int] = None, stages: int = 0,
          rope: Optional[dict] = None, pdl: bool = False, tf: Optional[int] = None,
          tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
-         signal=None, ticket: Optional[torch.Tensor] = None) -> None:
+         signal=None, ticket: Optional[torch.Tensor] = None,
+         persistent: Optional[bool] = None) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T])."""
     assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
     if tiled_shape is not None:      # a is a TiledWeight payload: logical shape given
@@ -133,7 +134,16 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         p.smax = rope["smax"]
         p.kcache, p.vcache = rope["kcache"].data_ptr(), rope["vcache"].data_ptr()
     p.status = _lib.status_word(a.device).data_ptr()
-    _lib.check(_lib.lib().e2h_gemm_umma(C.byref(p), _lib.stream()), "e2h_gemm_umma")
+    # more than one token tile: the persistent kernel (double-buffered accumulator, TMA-store
+    # epilogue); skinny / split-K shapes: the latency-oriented one-tile-per-CTA kernel
+    big = (persistent if persistent is not None else
+           (T > bn and splitk == 1 and tf == 128 and tiled_shape is None and debug_mode == 0
+            and bn >= 128))
+    if big:
+        _lib.check(_lib.lib().e2h_gemm_persistent(C.byref(p), _lib.stream()),
+                   "e2h_gemm_persistent")
+    else:
+        _lib.check(_lib.lib().e2h_gemm_umma(C.byref(p), _lib.stream()), "e2h_gemm_umma")
 
 
 def tile_weight(w: torch.Tensor, tf: int = 128) -> torch.Tensor:
