@@ -1,0 +1,138 @@
+"""One transformer block as an explicit forward / backward over the sm_100a kernels.
+
+The reference trains through ``torch.utils.checkpoint`` around ``TransformerBlock``
+(models/model.py:233-243): only the block input is kept and the block is re-run in the
+backward pass. ``block_forward`` / ``block_backward`` are that recomputation written out as a
+fixed sequence of fused kernels (tcgen05 GEMMs with residual / SwiGLU epilogues, flash
+attention forward and backward, RMSNorm, RoPE), with the tensor-parallel collectives at the
+same places as ``parallel.collectives``:
+
+    x ── rmsnorm ─[gather]─ wqkv ─ rope ─ flash ─ wo ─[reduce]─ (+x) = h
+    h ── rmsnorm ─[gather]─ w1,w3 ─ swiglu ─ w2 ─[reduce]─ (+h) = out
+
+Activations are token-major ``[B*S, features]`` bf16. Weight gradients are written straight
+into caller-provided buffers (bf16 ``[out, in]`` views of a flat gradient buffer), which is what
+lets the sharded-data-parallel wrapper reduce-scatter a whole block's gradients in one go.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+import torch.distributed as dist
+
+from ..ops import flash, functional as Fn, gemm
+from ..parallel import groups
+
+
+@dataclass
+class BlockShape:
+    B: int
+    S: int
+    n_head: int      # local (per tensor-parallel rank) query heads
+    n_kv: int        # local kv heads
+    head_dim: int
+    eps: float
+    tp: int = 1
+    sequence_parallel: bool = False
+
+
+def _tp_all_reduce(t: torch.Tensor, shape: BlockShape) -> torch.Tensor:
+    if shape.tp > 1:
+        dist.all_reduce(t, group=groups.get_model_parallel_group())
+    return t
+
+
+def _sp_gather(t: torch.Tensor, shape: BlockShape) -> torch.Tensor:
+    """[T/tp, F] -> [T, F] along tokens (sequence parallel)."""
+    out = torch.empty(t.shape[0] * shape.tp, t.shape[1], dtype=t.dtype, device=t.device)
+    dist.all_gather_into_tensor(out, t.contiguous(), group=groups.get_model_parallel_group())
+    return out
+
+
+def _sp_reduce_scatter(t: torch.Tensor, shape: BlockShape) -> torch.Tensor:
+    out = torch.empty(t.shape[0] // shape.tp, t.shape[1], dtype=t.dtype, device=t.device)
+    dist.reduce_scatter_tensor(out, t.contiguous(), group=groups.get_model_parallel_group())
+    return out
+
+
+def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tensor,
+                  pos: torch.Tensor, shape: BlockShape, keep: bool = False):
+    """x [T, dim] (T = B*S, or B*S/tp rows under sequence parallelism). ``w`` holds bf16
+    ``wqkv, wo, w1, w3, w2`` and the two norm weights. Returns ``out`` and, with ``keep``, the
+    intermediates the backward needs."""
+    H, Hkv, D = shape.n_head, shape.n_kv, shape.head_dim
+    sp = shape.sequence_parallel and shape.tp > 1
+    xn1 = Fn.rmsnorm(x, w["attention_norm"], shape.eps)
+    xn1f = _sp_gather(xn1, shape) if sp else xn1
+    T = xn1f.shape[0]
+    qkv = gemm.linear(xn1f, w["wqkv"])
+    Fn.rope(qkv, freqs, pos, H + Hkv, D, out=qkv)          # q and k heads, in place
+    q = qkv[:, : H * D].view(shape.B, shape.S, H, D)
+    k = qkv[:, H * D: (H + Hkv) * D].view(shape.B, shape.S, Hkv, D)
+    v = qkv[:, (H + Hkv) * D:].view(shape.B, shape.S, Hkv, D)
+    o, lse = flash.flash_fwd(q, k, v, None, return_lse=True)
+    o2 = o.view(T, H * D)
+    if shape.tp == 1:
+        h = gemm.linear_residual(o2, w["wo"], x)
+    else:
+        part = gemm.linear(o2, w["wo"])
+        part = _sp_reduce_scatter(part, shape) if sp else _tp_all_reduce(part, shape)
+        h = part.add_(x)
+    xn2 = Fn.rmsnorm(h, w["ffn_norm"], shape.eps)
+    xn2f = _sp_gather(xn2, shape) if sp else xn2
+    g, u = gemm.linear_dual(xn2f, w["w1"], w["w3"])
+    act = Fn.swiglu(g, u)
+    if shape.tp == 1:
+        out = gemm.linear_residual(act, w["w2"], h)
+    else:
+        part = gemm.linear(act, w["w2"])
+        part = _sp_reduce_scatter(part, shape) if sp else _tp_all_reduce(part, shape)
+        out = part.add_(h)
+    if not keep:
+        return out, None
+    return out, dict(xn1f=xn1f, qkv=qkv, q=q, k=k, v=v, o=o, lse=lse, h=h, xn2f=xn2f, g=g, u=u,
+                     act=act)
+
+
+def block_backward(dy: torch.Tensor, x: torch.Tensor, w: Dict[str, torch.Tensor],
+                   grads: Dict[str, torch.Tensor], freqs: torch.Tensor, pos: torch.Tensor,
+                   shape: BlockShape, accumulate: bool = False) -> torch.Tensor:
+    """Recompute the block from its input ``x``, then back-propagate ``dy``. Weight gradients go
+    to ``grads[name]`` (``[out, in]`` bf16 or fp32; added to when ``accumulate``). Returns dx."""
+    H, Hkv, D = shape.n_head, shape.n_kv, shape.head_dim
+    sp = shape.sequence_parallel and shape.tp > 1
+    _, a = block_forward(x, w, freqs, pos, shape, keep=True)
+    T = a["xn1f"].shape[0]
+
+    def wgrad(name, d_out, inp):
+        gemm.linear_wgrad(d_out, inp, out=grads[name], accumulate=accumulate)
+
+    # ---- feed-forward: out = h + w2(act) ----
+    dyf = _sp_gather(dy, shape) if sp else dy
+    d_act = gemm.linear_dgrad(dyf, w["w2"])
+    wgrad("w2", dyf, a["act"])
+    dg, du = Fn.swiglu_bwd(a["g"], a["u"], d_act)
+    d_xn2 = gemm.linear_dgrad(dg, w["w1"])
+    gemm.gemm(w["w3"], du, epi=gemm.EPI_RESIDUAL, out=d_xn2, aux=d_xn2, a_mn_major=True)
+    wgrad("w1", dg, a["xn2f"])
+    wgrad("w3", du, a["xn2f"])
+    if shape.tp > 1:
+        d_xn2 = _sp_reduce_scatter(d_xn2, shape) if sp else _tp_all_reduce(d_xn2, shape)
+    dh = Fn.rmsnorm_bwd(a["h"], d_xn2, w["ffn_norm"], shape.eps, dres=dy)
+    # ---- attention: h = x + wo(o) ----
+    dhf = _sp_gather(dh, shape) if sp else dh
+    d_o = gemm.linear_dgrad(dhf, w["wo"])
+    wgrad("wo", dhf, a["o"].view(T, H * D))
+    dqkv = torch.empty_like(a["qkv"])   # dq | dk | dv written in place by the attention backward
+    flash.flash_bwd(a["q"], a["k"], a["v"], a["o"], d_o.view(shape.B, shape.S, H, D), a["lse"],
+                    dq=dqkv[:, : H * D].view(shape.B, shape.S, H, D),
+                    dk=dqkv[:, H * D: (H + Hkv) * D].view(shape.B, shape.S, Hkv, D),
+                    dv=dqkv[:, (H + Hkv) * D:].view(shape.B, shape.S, Hkv, D))
+    Fn.rope(dqkv, freqs, pos, H + Hkv, D, inverse=True, out=dqkv)
+    d_xn1 = gemm.linear_dgrad(dqkv, w["wqkv"])
+    wgrad("wqkv", dqkv, a["xn1f"])
+    if shape.tp > 1:
+        d_xn1 = _sp_reduce_scatter(d_xn1, shape) if sp else _tp_all_reduce(d_xn1, shape)
+    return Fn.rmsnorm_bwd(x, d_xn1, w["attention_norm"], shape.eps, dres=dh)

@@ -74,6 +74,11 @@ _SIGNATURES = {
     "e2h_flash_fwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _vp,
                       _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
     "e2h_set_pdl": [_i],
+    "e2h_flash_bwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll,
+                      _ll, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp,
+                      _vp],
+    "e2h_ce_stats": [_vp, _ll, _i, _i, _vp, _i, _f, _vp, _vp],
+    "e2h_ce_grad": [_vp, _ll, _i, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "e2h_sample": [_vp, _ll, _i, _i, _f, _i, _ull, _vp, _i, _vp, _vp, _ll, _i, _i, _vp, _vp,
                    _vp, _vp],
 }

@@ -333,6 +333,446 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp == 1) tmem_dealloc(ctrl->tmem_base, 256);
 }
 
+// =============================================================================================
+// Backward pass. Two kernels recompute the probabilities from (Q, K, lse):
+//   flash_bwd_dkdv_kernel : one CTA per (batch, kv head, 128-key block); loops over the query
+//                           blocks (and the query heads of the group) that see those keys;
+//                           dV += P^T dO and dK += dS^T Q accumulate in tensor memory.
+//   flash_bwd_dq_kernel   : one CTA per (batch, head, 128-query block); loops over key blocks;
+//                           dQ += dS K accumulates in tensor memory.
+// with P = exp(S*scale - lse), dP = dO V^T, dS = P o (dP - delta) * scale and
+// delta = rowsum(dO o O) from flash_delta_kernel. Splitting the work this way recomputes S and
+// dP twice but needs no atomics and is deterministic.
+// Shared-memory tiles are [128 rows x 64] bf16 halves with the 128-byte swizzle, so the same
+// tile serves as a K-major operand (contraction along the row) or an MN-major operand
+// (contraction across rows): P / dS are written once and used both ways.
+// =============================================================================================
+
+struct FlashBwdParams {
+  int B, H, Hkv, Sq, Sk, D;
+  float scale;
+  const int* left_pad;
+  const float* lse;      // [B, H, Sq]
+  const float* delta;    // [B, H, Sq]
+  __nv_bfloat16* dq;     // like q   (strides q_sb, q_ss, q_sh)
+  __nv_bfloat16* dk;     // like k/v (strides k_sb, k_ss, k_sh)
+  __nv_bfloat16* dv;
+  long long q_sb, q_ss, q_sh, k_sb, k_ss, k_sh;
+  int* status;
+};
+
+struct BwdCtrl {
+  uint64_t once_full, it_full, it_empty, sdp_full, pds_full, done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+// delta[b, h, i] = sum_d O[b,i,h,d] * dO[b,i,h,d]
+__global__ void flash_delta_kernel(const __nv_bfloat16* __restrict__ o,
+                                   const __nv_bfloat16* __restrict__ d_o, float* __restrict__ delta,
+                                   long long sb, long long ss, long long sh, long long dsb,
+                                   long long dss, long long dsh, int H, int Sq, int D) {
+  const int warp_global = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const int total = gridDim.y * H * Sq;  // gridDim.y = B
+  (void)total;
+  const int b = blockIdx.y;
+  if (warp_global >= H * Sq) return;
+  const int h = warp_global / Sq, i = warp_global - h * Sq;
+  const __nv_bfloat16* po = o + b * sb + (long long)i * ss + (long long)h * sh;
+  const __nv_bfloat16* pd = d_o + b * dsb + (long long)i * dss + (long long)h * dsh;
+  float acc = 0.f;
+  for (int d = lane; d < D; d += 32) acc += __bfloat162float(po[d]) * __bfloat162float(pd[d]);
+  acc = warp_sum(acc);
+  if (lane == 0) delta[((long long)b * H + h) * Sq + i] = acc;
+}
+
+// bf16 row of 32 values -> swizzled [128 x 64] halves (row-major, 16-byte chunk c at c ^ (row&7))
+__device__ __forceinline__ void store_row32(uint8_t* tile, int row, int col0, const float* v) {
+#pragma unroll
+  for (int c8 = 0; c8 < 4; ++c8) {
+    uint32_t packed[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat162 pk = __floats2bfloat162_rn(v[c8 * 8 + 2 * e], v[c8 * 8 + 2 * e + 1]);
+      packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+    }
+    const int col8 = (col0 >> 3) + c8;
+    const int half = col8 >> 3, chunk = col8 & 7;
+    *reinterpret_cast<uint4*>(tile + half * (128 * 128) + row * 128 +
+                              ((chunk ^ (row & 7)) << 4)) =
+        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+  }
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                      const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                      const FlashBwdParams p) {
+  constexpr int NH = D / 64;
+  constexpr int kHalf = 128 * 128;
+  constexpr int kTile = NH * kHalf;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  BwdCtrl* ctrl = reinterpret_cast<BwdCtrl*>(smem);
+  uint8_t* k_s = smem + 1024;
+  uint8_t* v_s = k_s + kTile;
+  uint8_t* q_s = v_s + kTile;
+  uint8_t* do_s = q_s + kTile;
+  uint8_t* p_s = do_s + kTile;          // [128 q x 128 keys]
+  uint8_t* ds_s = p_s + 2 * kHalf;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int jb = blockIdx.x, hk = blockIdx.y, b = blockIdx.z;
+  const int G = p.H / p.Hkv;
+  const int key0 = jb * kBK;
+  const int off = p.Sk - p.Sq;
+  const int lp = p.left_pad ? p.left_pad[b] : 0;
+  const int i_begin = max(0, key0 - off) / kBQ;
+  const int n_q = (p.Sq + kBQ - 1) / kBQ;
+  const int n_i = max(0, n_q - i_begin);
+  const int n_it = n_i * G;
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctrl->once_full), 1);
+    mbar_init(smem_u32(&ctrl->it_full), 1);
+    mbar_init(smem_u32(&ctrl->it_empty), 1);
+    mbar_init(smem_u32(&ctrl->sdp_full), 1);
+    mbar_init(smem_u32(&ctrl->pds_full), 4);
+    mbar_init(smem_u32(&ctrl->done), 1);
+    ctrl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm_s = ctrl->tmem_base, tm_dp = tm_s + 128, tm_dv = tm_s + 256, tm_dk = tm_s + 384;
+
+  if (warp == 0 && lane == 0) {
+    mbar_expect_tx(smem_u32(&ctrl->once_full), 2 * kTile);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+      tma_load_4d(smem_u32(k_s + hf * kHalf), &tmK, hf * 64, key0, hk, b, smem_u32(&ctrl->once_full));
+      tma_load_4d(smem_u32(v_s + hf * kHalf), &tmV, hf * 64, key0, hk, b, smem_u32(&ctrl->once_full));
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int g = it / n_i, i = i_begin + it % n_i;
+      const int h = hk * G + g;
+      if (!mbar_wait(smem_u32(&ctrl->it_empty), (it & 1) ^ 1, abort_flag, p.status,
+                     kStatusTimeoutEmpty))
+        break;
+      mbar_expect_tx(smem_u32(&ctrl->it_full), 2 * kTile);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        tma_load_4d(smem_u32(q_s + hf * kHalf), &tmQ, hf * 64, i * kBQ, h, b, smem_u32(&ctrl->it_full));
+        tma_load_4d(smem_u32(do_s + hf * kHalf), &tmDO, hf * 64, i * kBQ, h, b, smem_u32(&ctrl->it_full));
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    const uint32_t id_kk = make_idesc_bf16(128, 128, 0, 0);   // S, dP: both operands K-major
+    const uint32_t id_mm = make_idesc_bf16(128, D, 1, 1);     // dV, dK: both MN-major
+    bool ok = mbar_wait(smem_u32(&ctrl->once_full), 0, abort_flag, p.status, kStatusTimeoutFull);
+    for (int it = 0; it < n_it && ok; ++it) {
+      ok = mbar_wait(smem_u32(&ctrl->it_full), it & 1, abort_flag, p.status, kStatusTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s), va = smem_u32(v_s), da = smem_u32(do_s);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
+        umma_f16(tm_s, make_sw128_desc(qa + o, 16, 1024), make_sw128_desc(ka + o, 16, 1024), id_kk,
+                 kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
+        umma_f16(tm_dp, make_sw128_desc(da + o, 16, 1024), make_sw128_desc(va + o, 16, 1024), id_kk,
+                 kk > 0 ? 1u : 0u);
+      }
+      umma_commit(smem_u32(&ctrl->sdp_full));
+      ok = mbar_wait(smem_u32(&ctrl->pds_full), it & 1, abort_flag, p.status, kStatusTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t pa = smem_u32(p_s), sa = smem_u32(ds_s);
+#pragma unroll
+      for (int kk = 0; kk < kBQ / 16; ++kk) {   // contraction over the 128 queries
+        const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
+        umma_f16(tm_dv, make_sw128_desc(pa + kk * 2048, kHalf, 1024),
+                 make_sw128_desc(da + kk * 2048, kHalf, 1024), id_mm, acc);
+        umma_f16(tm_dk, make_sw128_desc(sa + kk * 2048, kHalf, 1024),
+                 make_sw128_desc(qa + kk * 2048, kHalf, 1024), id_mm, acc);
+      }
+      umma_commit(smem_u32(&ctrl->it_empty));
+    }
+    umma_commit(smem_u32(&ctrl->done));
+  }
+
+  if (warp >= 2) {
+    const int qrt = warp & 3;
+    const int row = qrt * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int g = it / n_i, i = i_begin + it % n_i;
+      const int h = hk * G + g;
+      const int qi = i * kBQ + row;
+      const int qpos = qi + off;
+      const bool q_ok = qi < p.Sq;
+      const float lse2 = q_ok ? p.lse[((long long)b * p.H + h) * p.Sq + qi] * 1.4426950408889634f : 0.f;
+      const float dl = q_ok ? p.delta[((long long)b * p.H + h) * p.Sq + qi] : 0.f;
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->sdp_full), it & 1, abort_flag, p.status,
+                             kStatusTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < kBK; c += 32) {
+        float sv[32], dp[32];
+        if (ok) {
+          tmem_ld_x32(tm_s + lane_off + c, sv);
+          tmem_ld_x32(tm_dp + lane_off + c, dp);
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int j = key0 + c + e;
+          const bool vis = q_ok && (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+          const float pr = vis ? exp2f(sv[e] * sl2 - lse2) : 0.f;
+          sv[e] = pr;
+          dp[e] = pr * (dp[e] - dl) * p.scale;
+        }
+        store_row32(p_s, row, c, sv);
+        store_row32(ds_s, row, c, dp);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->pds_full));
+    }
+    if (ok) ok = mbar_wait(smem_u32(&ctrl->done), 0, abort_flag, p.status, kStatusTimeoutTmemFull);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    const int kj = key0 + row;
+    if (ok) {
+      __nv_bfloat16* dkrow = p.dk + (long long)b * p.k_sb + (long long)kj * p.k_ss + (long long)hk * p.k_sh;
+      __nv_bfloat16* dvrow = p.dv + (long long)b * p.k_sb + (long long)kj * p.k_ss + (long long)hk * p.k_sh;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        float a[32], bq[32];
+        if (n_it > 0) {
+          tmem_ld_x32(tm_dv + lane_off + c, a);
+          tmem_ld_x32(tm_dk + lane_off + c, bq);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) a[e] = bq[e] = 0.f;
+        }
+        if (kj < p.Sk) {
+#pragma unroll
+          for (int e = 0; e < 32; e += 8) {
+            uint32_t pv[4], pk[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+              const __nv_bfloat162 x = __floats2bfloat162_rn(a[e + 2 * u], a[e + 2 * u + 1]);
+              const __nv_bfloat162 y = __floats2bfloat162_rn(bq[e + 2 * u], bq[e + 2 * u + 1]);
+              pv[u] = *reinterpret_cast<const uint32_t*>(&x);
+              pk[u] = *reinterpret_cast<const uint32_t*>(&y);
+            }
+            *reinterpret_cast<uint4*>(dvrow + c + e) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
+            *reinterpret_cast<uint4*>(dkrow + c + e) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(ctrl->tmem_base, 512);
+}
+
+template <int D>
+__global__ void __launch_bounds__(192, 1)
+flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                    const FlashBwdParams p) {
+  constexpr int NH = D / 64;
+  constexpr int kHalf = 128 * 128;
+  constexpr int kTile = NH * kHalf;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  BwdCtrl* ctrl = reinterpret_cast<BwdCtrl*>(smem);
+  uint8_t* q_s = smem + 1024;
+  uint8_t* do_s = q_s + kTile;
+  uint8_t* k_s = do_s + kTile;
+  uint8_t* v_s = k_s + kTile;
+  uint8_t* ds_s = v_s + kTile;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int hk = h / (p.H / p.Hkv);
+  const int q0 = qb * kBQ;
+  const int off = p.Sk - p.Sq;
+  const int lp = p.left_pad ? p.left_pad[b] : 0;
+  const int last_key = min(p.Sk - 1, q0 + kBQ - 1 + off);
+  const int first_key = max(0, min(lp, q0 + off));
+  const int j_begin = first_key / kBK;
+  const int n_it = last_key / kBK + 1 - j_begin;
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&ctrl->once_full), 1);
+    mbar_init(smem_u32(&ctrl->it_full), 1);
+    mbar_init(smem_u32(&ctrl->it_empty), 1);
+    mbar_init(smem_u32(&ctrl->sdp_full), 1);
+    mbar_init(smem_u32(&ctrl->pds_full), 4);
+    mbar_init(smem_u32(&ctrl->done), 1);
+    ctrl->abort_flag = 0;
+    fence_mbar_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tm_s = ctrl->tmem_base, tm_dp = tm_s + 128, tm_dq = tm_s + 256;
+
+  if (warp == 0 && lane == 0) {
+    mbar_expect_tx(smem_u32(&ctrl->once_full), 2 * kTile);
+#pragma unroll
+    for (int hf = 0; hf < NH; ++hf) {
+      tma_load_4d(smem_u32(q_s + hf * kHalf), &tmQ, hf * 64, q0, h, b, smem_u32(&ctrl->once_full));
+      tma_load_4d(smem_u32(do_s + hf * kHalf), &tmDO, hf * 64, q0, h, b, smem_u32(&ctrl->once_full));
+    }
+    for (int it = 0; it < n_it; ++it) {
+      const int k0 = (j_begin + it) * kBK;
+      if (!mbar_wait(smem_u32(&ctrl->it_empty), (it & 1) ^ 1, abort_flag, p.status,
+                     kStatusTimeoutEmpty))
+        break;
+      mbar_expect_tx(smem_u32(&ctrl->it_full), 2 * kTile);
+#pragma unroll
+      for (int hf = 0; hf < NH; ++hf) {
+        tma_load_4d(smem_u32(k_s + hf * kHalf), &tmK, hf * 64, k0, hk, b, smem_u32(&ctrl->it_full));
+        tma_load_4d(smem_u32(v_s + hf * kHalf), &tmV, hf * 64, k0, hk, b, smem_u32(&ctrl->it_full));
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    const uint32_t id_kk = make_idesc_bf16(128, 128, 0, 0);
+    const uint32_t id_dq = make_idesc_bf16(128, D, 0, 1);     // dQ = dS K: K tile is MN-major
+    bool ok = mbar_wait(smem_u32(&ctrl->once_full), 0, abort_flag, p.status, kStatusTimeoutFull);
+    for (int it = 0; it < n_it && ok; ++it) {
+      ok = mbar_wait(smem_u32(&ctrl->it_full), it & 1, abort_flag, p.status, kStatusTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t qa = smem_u32(q_s), ka = smem_u32(k_s), va = smem_u32(v_s), da = smem_u32(do_s);
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
+        umma_f16(tm_s, make_sw128_desc(qa + o, 16, 1024), make_sw128_desc(ka + o, 16, 1024), id_kk,
+                 kk > 0 ? 1u : 0u);
+      }
+#pragma unroll
+      for (int kk = 0; kk < D / 16; ++kk) {
+        const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
+        umma_f16(tm_dp, make_sw128_desc(da + o, 16, 1024), make_sw128_desc(va + o, 16, 1024), id_kk,
+                 kk > 0 ? 1u : 0u);
+      }
+      umma_commit(smem_u32(&ctrl->sdp_full));
+      ok = mbar_wait(smem_u32(&ctrl->pds_full), it & 1, abort_flag, p.status, kStatusTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t sa = smem_u32(ds_s);
+#pragma unroll
+      for (int kk = 0; kk < kBK / 16; ++kk) {   // contraction over the 128 keys
+        umma_f16(tm_dq, make_sw128_desc(sa + (kk / 4) * kHalf + (kk % 4) * 32, 16, 1024),
+                 make_sw128_desc(ka + kk * 2048, kHalf, 1024), id_dq, (it > 0 || kk > 0) ? 1u : 0u);
+      }
+      umma_commit(smem_u32(&ctrl->it_empty));
+    }
+    umma_commit(smem_u32(&ctrl->done));
+  }
+
+  if (warp >= 2) {
+    const int qrt = warp & 3;
+    const int row = qrt * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
+    const float sl2 = p.scale * 1.4426950408889634f;
+    const int qi = q0 + row, qpos = qi + off;
+    const bool q_ok = qi < p.Sq;
+    const float lse2 = q_ok ? p.lse[((long long)b * p.H + h) * p.Sq + qi] * 1.4426950408889634f : 0.f;
+    const float dl = q_ok ? p.delta[((long long)b * p.H + h) * p.Sq + qi] : 0.f;
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int key0 = (j_begin + it) * kBK;
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->sdp_full), it & 1, abort_flag, p.status,
+                             kStatusTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+#pragma unroll
+      for (int c = 0; c < kBK; c += 32) {
+        float sv[32], dp[32];
+        if (ok) {
+          tmem_ld_x32(tm_s + lane_off + c, sv);
+          tmem_ld_x32(tm_dp + lane_off + c, dp);
+        }
+        tmem_ld_wait();
+#pragma unroll
+        for (int e = 0; e < 32; ++e) {
+          const int j = key0 + c + e;
+          const bool vis = q_ok && (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+          const float pr = vis ? exp2f(sv[e] * sl2 - lse2) : 0.f;
+          dp[e] = pr * (dp[e] - dl) * p.scale;
+        }
+        store_row32(ds_s, row, c, dp);
+      }
+      tc_fence_before();
+      fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->pds_full));
+    }
+    if (ok) ok = mbar_wait(smem_u32(&ctrl->done), 0, abort_flag, p.status, kStatusTimeoutTmemFull);
+    ok = __all_sync(0xffffffffu, ok);
+    tc_fence_after();
+    if (ok) {   // warp-uniform: the TMEM loads are warp-collective, only the stores are per row
+      __nv_bfloat16* dqrow = p.dq + (long long)b * p.q_sb + (long long)qi * p.q_ss + (long long)h * p.q_sh;
+#pragma unroll
+      for (int c = 0; c < D; c += 32) {
+        float a[32];
+        if (n_it > 0) {
+          tmem_ld_x32(tm_dq + lane_off + c, a);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) a[e] = 0.f;
+        }
+        if (!q_ok) continue;
+#pragma unroll
+        for (int e = 0; e < 32; e += 8) {
+          uint32_t pk[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const __nv_bfloat162 x = __floats2bfloat162_rn(a[e + 2 * u], a[e + 2 * u + 1]);
+            pk[u] = *reinterpret_cast<const uint32_t*>(&x);
+          }
+          *reinterpret_cast<uint4*>(dqrow + c + e) = make_uint4(pk[0], pk[1], pk[2], pk[3]);
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(ctrl->tmem_base, 512);
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
                                   const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
                                   const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
@@ -414,5 +854,64 @@ extern "C" int e2h_flash_fwd(const void* q, long long q_sb, long long q_ss, long
     }
     flash_fwd_kernel<64><<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
   }
+  return (int)cudaGetLastError();
+}
+
+// dO, O: [B, Sq, H, D] views; dq like q; dk, dv like k. delta: fp32 scratch [B, H, Sq].
+extern "C" int e2h_flash_bwd(const void* q, long long q_sb, long long q_ss, long long q_sh,
+                             const void* k, const void* v, long long k_sb, long long k_ss,
+                             long long k_sh, const void* o, long long o_sb, long long o_ss,
+                             long long o_sh, const void* d_o, long long do_sb, long long do_ss,
+                             long long do_sh, const float* lse, float* delta, void* dq, void* dk,
+                             void* dv, const int* left_pad, int B, int H, int Hkv, int Sq, int Sk,
+                             int D, float scale, int* status, void* stream_v) {
+  using namespace e2h;
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  if (D != 128 && D != 64) return -1;
+  if (H % Hkv) return -2;
+  CUtensorMap tq, tk, tv, tdo;
+  int r = make_map4d(&tq, q, D, Sq, H, B, q_sb, q_ss, q_sh, kBQ);
+  if (r) return r;
+  r = make_map4d(&tk, k, D, Sk, Hkv, B, k_sb, k_ss, k_sh, kBK);
+  if (r) return r;
+  r = make_map4d(&tv, v, D, Sk, Hkv, B, k_sb, k_ss, k_sh, kBK);
+  if (r) return r;
+  r = make_map4d(&tdo, d_o, D, Sq, H, B, do_sb, do_ss, do_sh, kBQ);
+  if (r) return r;
+  {
+    const int warps = H * Sq;
+    dim3 grid((warps * 32 + 255) / 256, B);
+    flash_delta_kernel<<<grid, 256, 0, stream>>>(
+        (const __nv_bfloat16*)o, (const __nv_bfloat16*)d_o, delta, o_sb, o_ss, o_sh, do_sb, do_ss,
+        do_sh, H, Sq, D);
+  }
+  FlashBwdParams p;
+  p.B = B; p.H = H; p.Hkv = Hkv; p.Sq = Sq; p.Sk = Sk; p.D = D;
+  p.scale = scale; p.left_pad = left_pad; p.lse = lse; p.delta = delta;
+  p.dq = (__nv_bfloat16*)dq; p.dk = (__nv_bfloat16*)dk; p.dv = (__nv_bfloat16*)dv;
+  p.q_sb = q_sb; p.q_ss = q_ss; p.q_sh = q_sh; p.k_sb = k_sb; p.k_ss = k_ss; p.k_sh = k_sh;
+  p.status = status;
+  const int tile = (D / 64) * 128 * 128;
+  const size_t smem_kv = 2048 + 4 * (size_t)tile + 4 * 128 * 128;
+  const size_t smem_q = 2048 + 4 * (size_t)tile + 2 * 128 * 128;
+  dim3 gkv((Sk + kBK - 1) / kBK, Hkv, B), gq((Sq + kBQ - 1) / kBQ, H, B);
+  cudaError_t e;
+#define E2H_BWD(D_)                                                                              \
+  {                                                                                              \
+    static bool done = false;                                                                    \
+    if (!done) {                                                                                 \
+      e = cudaFuncSetAttribute(flash_bwd_dkdv_kernel<D_>,                                        \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_kv);       \
+      if (e != cudaSuccess) return (int)e;                                                       \
+      e = cudaFuncSetAttribute(flash_bwd_dq_kernel<D_>,                                          \
+                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_q);        \
+      if (e != cudaSuccess) return (int)e;                                                       \
+      done = true;                                                                               \
+    }                                                                                            \
+    flash_bwd_dkdv_kernel<D_><<<gkv, 192, smem_kv, stream>>>(tq, tk, tv, tdo, p);                \
+    flash_bwd_dq_kernel<D_><<<gq, 192, smem_q, stream>>>(tq, tk, tv, tdo, p);                    \
+  }
+  if (D == 128) E2H_BWD(128) else E2H_BWD(64)
+#undef E2H_BWD
   return (int)cudaGetLastError();
 }

@@ -111,32 +111,36 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
       const bool is_q = head < p.n_head;
       const bool is_k = !is_q && head < p.n_head + p.n_kv;
       const bool is_v = !is_q && !is_k;
-      const __nv_bfloat16* freqs = static_cast<const __nv_bfloat16*>(p.freqs);
+      const __nv_bfloat162* freqs2 = static_cast<const __nv_bfloat162*>(p.freqs);  // (cos, sin)
       const int pos0 = *p.pos_base;
+      const int hk = is_k ? head - p.n_head : head - p.n_head - p.n_kv;
+      __nv_bfloat16* cache = static_cast<__nv_bfloat16*>(is_k ? p.kcache : p.vcache);
+      // one division per 8 tokens: (sequence, offset) advance incrementally
+      int b = t0 / p.sq;
+      int s = t0 - b * p.sq;
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int t = t0 + j;
         const float x = bf16_round(v[j]);
         const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
-        if (!(f_ok && t < p.T)) continue;
-        const int b = t / p.sq;
-        const int s = t - b * p.sq;
         const int pos = pos0 + s;
+        const int bb = b;
+        if (++s == p.sq) {
+          s = 0;
+          ++b;
+        }
+        if (!(f_ok && t < p.T)) continue;
         float y = x;
         if (!is_v) {
-          const long long fo = ((long long)pos * (D / 2) + (d >> 1)) * 2;
-          const float c = __bfloat162float(freqs[fo]);
-          const float sn = __bfloat162float(freqs[fo + 1]);
+          const __nv_bfloat162 cs = freqs2[(long long)pos * (D / 2) + (d >> 1)];
+          const float c = __bfloat162float(cs.x), sn = __bfloat162float(cs.y);
           y = (d & 1) ? (x * c + partner * sn) : (x * c - partner * sn);
         }
         const __nv_bfloat16 yb = __float2bfloat16_rn(y);
         if (is_q) {
           static_cast<__nv_bfloat16*>(p.out)[(long long)t * p.ldo + f] = yb;
-        } else {
-          const int hk = is_k ? head - p.n_head : head - p.n_head - p.n_kv;
-          __nv_bfloat16* cache = static_cast<__nv_bfloat16*>(is_k ? p.kcache : p.vcache);
-          if (pos < p.smax)
-            cache[(((long long)b * p.n_kv + hk) * p.smax + pos) * D + d] = yb;
+        } else if (pos < p.smax) {
+          cache[(((long long)bb * p.n_kv + hk) * p.smax + pos) * D + d] = yb;
         }
       }
     } break;

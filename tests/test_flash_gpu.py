@@ -54,3 +54,62 @@ def test_prefill_attention_cache_layout():
     want = reference.attention(q.transpose(1, 2), kc[:B, :, :S], vc[:B, :, :S], mask)
     err = (out.view(B, S, H, D).transpose(1, 2).float() - want.float()).abs().max().item()
     assert err < 3e-2, f"max err {err}"
+
+
+@pytest.mark.parametrize("B,H,Hkv,S,D", [(2, 4, 4, 256, 128), (1, 8, 2, 300, 128),
+                                         (2, 4, 4, 128, 64), (1, 2, 2, 768, 128)])
+def test_flash_bwd(B, H, Hkv, S, D):
+    from easy_to_hard_b200.ops import _lib, flash
+    q, k, v = _mk(B, S, H, D, seed=7), _mk(B, S, Hkv, D, seed=8), _mk(B, S, Hkv, D, seed=9)
+    d_o = _mk(B, S, H, D, seed=10)
+    qf, kf, vf = (t.float().requires_grad_(True) for t in (q, k, v))
+    kk = kf.repeat_interleave(H // Hkv, 2)
+    vv = vf.repeat_interleave(H // Hkv, 2)
+    s = torch.einsum("bihd,bjhd->bhij", qf, kk) / D ** 0.5
+    mask = torch.ones(S, S, dtype=torch.bool, device="cuda").tril()
+    p = torch.softmax(s.masked_fill(~mask, float("-inf")), -1)
+    ref = torch.einsum("bhij,bjhd->bihd", p, vv)
+    ref.backward(d_o.float())
+    qg, kg, vg = (t.clone().requires_grad_(True) for t in (q, k, v))
+    out = flash.causal_attention(qg, kg, vg)
+    out.backward(d_o)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    for got, want, name in ((qg.grad, qf.grad, "dq"), (kg.grad, kf.grad, "dk"),
+                            (vg.grad, vf.grad, "dv")):
+        scale = want.abs().max().item()
+        err = (got.float() - want).abs().max().item()
+        assert err < 3e-2 * scale + 2e-2, f"{name}: err {err} (scale {scale})"
+
+
+@pytest.mark.parametrize("N,V,world", [(300, 32016, 1), (64, 1024, 1), (128, 1024, 4)])
+def test_fused_ce_stats_and_grad(N, V, world):
+    """Fused CE kernels vs fp32 PyTorch, incl. the shard-combine arithmetic of vocab parallel."""
+    from easy_to_hard_b200.ops import loss
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = torch.randn(N, V, generator=g, device="cuda") * 3
+    tg = torch.randint(0, V, (N,), device="cuda", generator=g)
+    temp = 0.7
+    per = V // world
+    m = torch.stack([loss.ce_stats(logits[:, r * per:(r + 1) * per].contiguous(), tg, temp,
+                                   r * per) for r in range(world)])
+    gm = m[..., 0].max(0).values
+    w = torch.exp(m[..., 0] - gm)
+    s, tgt, u = (m[..., 1] * w).sum(0), m[..., 2].sum(0), (m[..., 3] * w).sum(0)
+    lse = gm + torch.log(s)
+    ent = lse - u / s
+    z = (logits / temp).requires_grad_(True)
+    lp_ref = torch.log_softmax(z, -1)
+    want_lp = lp_ref.gather(-1, tg[:, None]).squeeze(-1)
+    want_ent = -(lp_ref.exp() * lp_ref).sum(-1)
+    assert torch.allclose(tgt - lse, want_lp, rtol=1e-4, atol=1e-4)
+    assert torch.allclose(ent, want_ent, rtol=1e-3, atol=1e-3)
+    g_lp = torch.randn(N, generator=g, device="cuda")
+    g_en = torch.randn(N, generator=g, device="cuda")
+    (want_lp * g_lp + want_ent * g_en).sum().backward()
+    want = z.grad / temp
+    for r in range(world):
+        dl = loss.ce_grad(logits[:, r * per:(r + 1) * per].contiguous(), tg, lse, ent, g_lp,
+                          g_en, temp, r * per)
+        ref = want[:, r * per:(r + 1) * per]
+        assert (dl.float() - ref).abs().max().item() < 2e-2 * ref.abs().max().item() + 1e-3
