@@ -1,0 +1,484 @@
+"""Sharded data parallelism (ZeRO-3 style) for the LLaMA block stack, replacing the reference's
+PyTorch-FSDP1 wrapping (training_utils/trainer_utils.py:70-99, ppo_trainer.py:1357-1392).
+
+Layout. Every transformer block (plus one "root" unit for any other trainable tensor, e.g. a
+reward head) owns one flat parameter: the trainable tensors of the block concatenated, padded
+to a multiple of the data-parallel world size and split evenly. Each rank keeps
+
+* ``shard``      fp32 (``param_dtype``) master copy of its slice -- what the optimizer updates,
+* ``shard_lp``   the same slice in ``compute_dtype`` (bf16) -- what is all-gathered; refreshed by
+                 the fused Adam kernel in the same pass that updates the master copy,
+* ``shard.grad`` fp32 accumulator of the reduce-scattered gradient.
+
+Step. ``forward`` walks the blocks; for block i the flat bf16 parameter is all-gathered into one
+of two rotating buffers (the gather of block i+1 is issued on a side stream while block i
+computes), the block runs with activation checkpointing semantics (only its input is saved),
+and in the backward pass the parameter is gathered again, the block is recomputed and
+back-propagated, its weight gradients land in one flat bf16 buffer that is reduce-scattered
+(averaged over the group) into ``shard.grad``.
+
+On CUDA the block itself is ``models.fused_block`` (explicit kernel sequence); on CPU (gloo
+plumbing tests) it is the ``TransformerBlock`` module under ``torch.autograd``.
+
+The wrapper also produces the data-parallel-unsharded views that checkpoints need
+(``full_state_dict`` / ``full_optim_state_dict`` keyed by parameter name, and their loaders),
+so checkpoint files stay in the reference's format.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Iterator, List, Optional, Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from ..ops import functional as Fn
+from . import collectives as coll
+from . import groups
+
+BLOCK_PARAM_ORDER = ("attention.wqkv", "attention.wo", "feed_forward.w1", "feed_forward.w3",
+                     "feed_forward.w2")
+
+
+def _group_size(group) -> Tuple[int, int]:
+    if group is None or not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
+class ShardUnit:
+    """One flat parameter: a list of (fqn, nn.Parameter) sharded over the data-parallel group."""
+
+    def __init__(self, named_params: List[Tuple[str, nn.Parameter]], group, param_dtype,
+                 compute_dtype, reduce_dtype):
+        self.group = group
+        self.world, self.rank = _group_size(group)
+        self.names = [n for n, _ in named_params]
+        self.params = [p for _, p in named_params]
+        self.shapes = [tuple(p.shape) for p in self.params]
+        self.numels = [p.numel() for p in self.params]
+        self.offsets = [0]
+        for n in self.numels:
+            self.offsets.append(self.offsets[-1] + n)
+        self.total = self.offsets[-1]
+        self.shard_size = -(-self.total // self.world)
+        # keep shards 16-byte aligned in bf16 for the gather / TMA consumers
+        self.shard_size = -(-self.shard_size // 8) * 8
+        self.padded = self.shard_size * self.world
+        self.compute_dtype, self.reduce_dtype = compute_dtype, reduce_dtype
+        dev = self.params[0].device
+        flat = torch.zeros(self.padded, dtype=param_dtype, device=dev)
+        for p, o, n in zip(self.params, self.offsets, self.numels):
+            flat[o:o + n] = p.data.reshape(-1).to(param_dtype)
+        lo = self.rank * self.shard_size
+        self.shard = nn.Parameter(flat[lo:lo + self.shard_size].clone())
+        self.shard_lp = self.shard.data.to(compute_dtype)
+        if compute_dtype != param_dtype:
+            # the fused AdamW kernel refreshes the low-precision copy while it updates the master
+            self.shard._lp_copy = self.shard_lp
+        del flat
+        for p in self.params:             # the full tensors only exist while gathered
+            p.data = torch.empty(0, dtype=compute_dtype, device=dev)
+        self.gathered_in: Optional[torch.Tensor] = None
+
+    # -------------------------------------------------------------- parameters
+    def gather_into(self, buf: torch.Tensor) -> None:
+        """All-gather the bf16 shards into ``buf`` and point the parameters at views of it."""
+        full = buf[: self.padded]
+        if self.world > 1:
+            dist.all_gather_into_tensor(full, self.shard_lp, group=self.group)
+        else:
+            full.copy_(self.shard_lp)
+        for p, o, n, shp in zip(self.params, self.offsets, self.numels, self.shapes):
+            p.data = full[o:o + n].view(shp)
+        self.gathered_in = buf
+
+    def release(self) -> None:
+        for p in self.params:
+            p.data = torch.empty(0, dtype=self.compute_dtype, device=p.device)
+        self.gathered_in = None
+
+    def grad_views(self, gradbuf: torch.Tensor) -> Dict[str, torch.Tensor]:
+        full = gradbuf[: self.padded]
+        return {n: full[o:o + k].view(shp)
+                for n, o, k, shp in zip(self.names, self.offsets, self.numels, self.shapes)}
+
+    def reduce_grads(self, gradbuf: torch.Tensor) -> None:
+        """Average the flat gradient over the group and add this rank's slice to shard.grad."""
+        full = gradbuf[: self.padded]
+        if self.padded > self.total:
+            full[self.total:].zero_()
+        if self.world > 1:
+            red = full.to(self.reduce_dtype) if full.dtype != self.reduce_dtype else full
+            out = torch.empty(self.shard_size, dtype=red.dtype, device=red.device)
+            if red.device.type == "cpu":
+                dist.all_reduce(red, group=self.group)
+                out.copy_(red[self.rank * self.shard_size:(self.rank + 1) * self.shard_size])
+            else:
+                dist.reduce_scatter_tensor(out, red, group=self.group)
+            out = out.to(self.shard.dtype).div_(self.world)
+        else:
+            out = full[: self.shard_size].to(self.shard.dtype)
+        if self.shard.grad is None:
+            self.shard.grad = out.clone() if out.data_ptr() == full.data_ptr() else out
+        else:
+            self.shard.grad.add_(out)
+
+    def refresh_low_precision(self) -> None:
+        """After an update of the master shard that did not write the low-precision copy."""
+        self.shard_lp.copy_(self.shard.data)
+
+    # -------------------------------------------------------------- full (unsharded) views
+    def full_flat(self, src_shard: torch.Tensor) -> torch.Tensor:
+        """Gather any per-rank shard-shaped tensor (master weights, Adam moments) to full size."""
+        if self.world == 1:
+            return src_shard.detach().clone()
+        out = torch.empty(self.padded, dtype=src_shard.dtype, device=src_shard.device)
+        dist.all_gather_into_tensor(out, src_shard.detach().contiguous(), group=self.group)
+        return out
+
+    def split_full(self, flat: torch.Tensor) -> Dict[str, torch.Tensor]:
+        return {n: flat[o:o + k].view(shp).clone()
+                for n, o, k, shp in zip(self.names, self.offsets, self.numels, self.shapes)}
+
+    def load_named(self, state: Dict[str, torch.Tensor], into: torch.Tensor) -> List[str]:
+        """Write this rank's slice of the named full tensors into a shard-shaped tensor."""
+        lo, hi = self.rank * self.shard_size, (self.rank + 1) * self.shard_size
+        missing = []
+        for n, o, k in zip(self.names, self.offsets, self.numels):
+            if n not in state:
+                missing.append(n)
+                continue
+            a, b = max(o, lo), min(o + k, hi)
+            if a < b:
+                src = state[n].reshape(-1)[a - o:b - o]
+                into.data[a - lo:b - lo] = src.to(device=into.device, dtype=into.dtype)
+        return missing
+
+
+class _BlockFn(torch.autograd.Function):
+    """Checkpointed, parameter-gathering execution of one block."""
+
+    @staticmethod
+    def forward(ctx, x, sdp, idx, B, S):
+        ctx.sdp, ctx.idx, ctx.BS = sdp, idx, (B, S)
+        ctx.save_for_backward(x)
+        with torch.no_grad():
+            return sdp._run_block(idx, x, B, S)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x,) = ctx.saved_tensors
+        dx = ctx.sdp._backward_block(ctx.idx, x, dy.contiguous(), *ctx.BS)
+        return dx, None, None, None, None
+
+
+class ShardedDataParallel(nn.Module):
+    def __init__(self, model: nn.Module, process_group=None, param_dtype=torch.float32,
+                 compute_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16,
+                 fused: Optional[bool] = None):
+        super().__init__()
+        self.module = model
+        backbone = getattr(model, "backbone_model", model)
+        self.backbone = backbone
+        self.group = process_group
+        self.world, self.rank = _group_size(process_group)
+        dev = backbone.output.weight.device
+        self.fused = (dev.type == "cuda") if fused is None else fused
+        self.compute_dtype = compute_dtype if self.fused else param_dtype
+        self.param_dtype = param_dtype
+        if self.fused:
+            # frozen tensors (embedding, norms, LM head, RoPE table) are only ever read by the
+            # bf16 kernels
+            for t in list(model.buffers()) + [p for p in model.parameters()
+                                              if not p.requires_grad]:
+                if t.is_floating_point() and t.dtype != compute_dtype:
+                    t.data = t.data.to(compute_dtype)
+        prefix = "backbone_model." if backbone is not model else ""
+        self.units: List[ShardUnit] = []
+        seen = set()
+        for i, blk in enumerate(backbone.layers):
+            named = []
+            for rel in BLOCK_PARAM_ORDER:
+                mod_name, _ = rel.split(".")
+                p = getattr(getattr(blk, mod_name), rel.split(".")[1]).weight
+                if isinstance(p, nn.Parameter) and p.requires_grad:
+                    named.append((f"{prefix}layers.{i}.{rel}.weight", p))
+                    seen.add(id(p))
+            assert named, "every block must have trainable tensors"
+            self.units.append(ShardUnit(named, process_group, param_dtype, self.compute_dtype,
+                                        reduce_dtype if self.fused else param_dtype))
+        rest = [(n, p) for n, p in model.named_parameters()
+                if p.requires_grad and id(p) not in seen]
+        self.root: Optional[ShardUnit] = None
+        if rest:
+            self.root = ShardUnit(rest, process_group, param_dtype, self.compute_dtype,
+                                  reduce_dtype if self.fused else param_dtype)
+        self._shards = nn.ParameterList([u.shard for u in self._all_units()])
+        biggest = max(u.padded for u in self._all_units())
+        self._param_bufs = [torch.empty(biggest, dtype=self.compute_dtype, device=dev)
+                            for _ in range(2)]
+        self._grad_buf = torch.empty(biggest, dtype=self.compute_dtype, device=dev)
+        self._root_buf = (torch.empty(self.root.padded, dtype=self.compute_dtype, device=dev)
+                          if self.root else None)
+        self._comm_stream = torch.cuda.Stream() if dev.type == "cuda" else None
+        self._pending: Dict[int, "torch.cuda.Event"] = {}
+        self.micro_step = 0
+        if self.root is not None:
+            self.root.gather_into(self._root_buf)   # small: stays gathered
+
+    # ------------------------------------------------------------------ plumbing
+    def _all_units(self) -> List[ShardUnit]:
+        return self.units + ([self.root] if self.root is not None else [])
+
+    def optimizer_parameters(self) -> Iterator[nn.Parameter]:
+        return iter(u.shard for u in self._all_units())
+
+    def grad_shards(self) -> Iterator[torch.Tensor]:
+        return (u.shard.grad for u in self._all_units() if u.shard.grad is not None)
+
+    def trainable_param_names(self) -> List[str]:
+        return [n for u in self._all_units() for n in u.names]
+
+    def _prefetch(self, idx: int) -> None:
+        if not (0 <= idx < len(self.units)) or idx in self._pending:
+            return
+        unit, buf = self.units[idx], self._param_bufs[idx % 2]
+        if self._comm_stream is None:
+            unit.gather_into(buf)
+            self._pending[idx] = None
+            return
+        self._comm_stream.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(self._comm_stream):
+            unit.gather_into(buf)
+            ev = torch.cuda.Event()
+            ev.record(self._comm_stream)
+        self._pending[idx] = ev
+
+    def _acquire(self, idx: int, nxt: int) -> ShardUnit:
+        self._prefetch(idx)
+        ev = self._pending.pop(idx)
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+        self._prefetch(nxt)        # overlaps with the compute of block idx
+        return self.units[idx]
+
+    def _block_weights(self, blk, unit: ShardUnit) -> Dict[str, torch.Tensor]:
+        a, f = blk.attention, blk.feed_forward
+        cd = self.compute_dtype
+        return dict(wqkv=a.wqkv.weight.data, wo=a.wo.weight.data, w1=f.w1.weight.data,
+                    w3=f.w3.weight.data, w2=f.w2.weight.data,
+                    attention_norm=blk.attention_norm.weight.to(cd),
+                    ffn_norm=blk.ffn_norm.weight.to(cd))
+
+    def _shape(self, blk, B, S):
+        from ..models.fused_block import BlockShape
+        a = blk.attention
+        return BlockShape(B, S, a.n_head, a.n_local_heads, a.head_dim, self.backbone.config.norm_eps,
+                          tp=getattr(a, "tp_size", 1),
+                          sequence_parallel=getattr(a, "sequence_parallel", False))
+
+    def _run_block(self, idx: int, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+        unit = self._acquire(idx, idx + 1)
+        blk = self.backbone.layers[idx]
+        if self.fused:
+            from ..models import fused_block as fb
+            out, _ = fb.block_forward(x, self._block_weights(blk, unit), self._freqs, self._pos,
+                                      self._shape(blk, B, S))
+        else:
+            out = blk(x, self._input_pos, self._freqs_pos, None, True)
+        unit.release()
+        return out
+
+    def _backward_block(self, idx: int, x: torch.Tensor, dy: torch.Tensor, B: int, S: int):
+        unit = self._acquire(idx, idx - 1)
+        blk = self.backbone.layers[idx]
+        if self.fused:
+            from ..models import fused_block as fb
+            views = unit.grad_views(self._grad_buf)
+            grads = {n.split(".")[-2]: v for n, v in views.items()}
+            dx = fb.block_backward(dy, x, self._block_weights(blk, unit), grads, self._freqs,
+                                   self._pos, self._shape(blk, B, S))
+        else:
+            for p in unit.params:
+                p.grad = None
+                p.requires_grad_(True)
+            with torch.enable_grad():
+                xin = x.detach().requires_grad_(True)
+                out = blk(xin, self._input_pos, self._freqs_pos, None, True)
+                torch.autograd.backward(out, dy)
+            dx = xin.grad
+            for (n, v), p in zip(unit.grad_views(self._grad_buf).items(), unit.params):
+                v.copy_(p.grad if p.grad is not None else torch.zeros_like(v))
+                p.grad = None
+        unit.release()
+        unit.reduce_grads(self._grad_buf)
+        return dx
+
+    # ------------------------------------------------------------------ forward
+    def hidden_states(self, idx: torch.Tensor) -> torch.Tensor:
+        """Token ids [B, S] -> final-norm hidden states [B, S, dim] (differentiable w.r.t. the
+        sharded block parameters)."""
+        bb = self.backbone
+        B, S = idx.shape
+        dev = idx.device
+        if bb.freqs_cis is None or bb.max_seq_length < S or bb.max_batch_size < B:
+            bb.setup_caches(B, S, kv_cache=False)
+        self._input_pos = torch.arange(S, device=dev)
+        self._freqs_pos = bb.freqs_cis[:S]
+        self._freqs = bb.freqs_cis
+        self._pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
+        self._pending.clear()
+        x = bb.embed(idx)
+        sp = bb.sequence_parallel and bb.tp_size > 1 and self.training
+        if sp:                       # rows of the batch are split over the tensor-parallel ranks
+            x = coll.scatter_to_sequence_parallel(x)
+        if self.fused:
+            x = x.to(self.compute_dtype).reshape(-1, x.shape[-1])
+        # the block function needs an input that is part of the graph to get a backward call
+        x = x.detach().requires_grad_(True) if torch.is_grad_enabled() else x
+        for i in range(len(bb.layers)):
+            x = _BlockFn.apply(x, self, i, B, S)
+        x = _rmsnorm_autograd(x, bb.norm.weight, bb.config.norm_eps)
+        if sp:
+            x = coll.gather_from_sequence_parallel(x, tensor_parallel_output_grad=False)
+        return x.view(B, S, -1)
+
+    def forward(self, idx: torch.Tensor, *args, **kwargs):
+        """Same call convention as the wrapped model (logits for a ``Transformer``, rewards for
+        a ``RewardModel``)."""
+        hidden = self.hidden_states(idx)
+        if self.backbone is not self.module:      # reward / value model
+            rewards = self.module.token_rewards(hidden.to(self.backbone.output.weight.dtype))
+            eos_pos = kwargs.get("eos_pos", args[0] if args else None)
+            if eos_pos is not None:
+                rewards = torch.gather(rewards, 1, eos_pos.unsqueeze(-1).long()).squeeze(-1)
+            return rewards
+        return torch.nn.functional.linear(hidden, self.backbone.output.weight.to(hidden.dtype))
+
+    def token_logprobs(self, idx: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
+                       temperature: float = 1.0):
+        """(log p(labels[t]) per token [B, S], entropy [B, S]) without materialising logits."""
+        from ..ops import loss
+        hidden = self.hidden_states(idx)
+        B, S, dim = hidden.shape
+        w = self.backbone.output.weight
+        lp, ent = loss.linear_logprobs(hidden.reshape(B * S, dim).to(w.dtype), w,
+                                       labels.reshape(-1), ignore_index, temperature)
+        return lp.view(B, S), ent.view(B, S)
+
+    def zero_grad(self, set_to_none: bool = True) -> None:
+        for u in self._all_units():
+            u.shard.grad = None
+
+    def finish_backward(self) -> None:
+        """Reduce the root unit's gradients (tensors outside the block stack)."""
+        if self.root is None:
+            return
+        views = self.root.grad_views(self._grad_buf)
+        for (n, v), p in zip(views.items(), self.root.params):
+            v.copy_(p.grad if p.grad is not None else torch.zeros_like(v))
+            p.grad = None
+        self.root.reduce_grads(self._grad_buf)
+
+    def after_optimizer_step(self, lp_written: bool = False) -> None:
+        """``lp_written``: the optimizer kernel already refreshed the low-precision shards."""
+        if not lp_written:
+            for u in self._all_units():
+                u.refresh_low_precision()
+        if self.root is not None:
+            self.root.gather_into(self._root_buf)
+
+    # ------------------------------------------------------------------ checkpoints
+    def full_state_dict(self, rank0_only: bool = True) -> Optional[Dict[str, torch.Tensor]]:
+        out = {}
+        for u in self._all_units():
+            flat = u.full_flat(u.shard.data)
+            if not rank0_only or self.rank == 0:
+                out.update({k: v.cpu() for k, v in u.split_full(flat).items()})
+        if rank0_only and self.rank != 0:
+            return None
+        for n, b in self.module.named_buffers():
+            out.setdefault(n, b.detach().cpu())
+        return out
+
+    def load_full_state_dict(self, state: Dict[str, torch.Tensor], strict: bool = False):
+        missing = []
+        for u in self._all_units():
+            missing += u.load_named(state, u.shard)
+            u.refresh_low_precision()
+        bufs = dict(self.module.named_buffers())
+        for k, v in state.items():
+            if k in bufs and bufs[k].shape == v.shape:
+                bufs[k].data.copy_(v)
+        if self.root is not None:
+            self.root.gather_into(self._root_buf)
+        if strict and missing:
+            raise KeyError(f"missing parameters: {missing}")
+        return missing
+
+    def full_optim_state_dict(self, optimizer, rank0_only: bool = True):
+        """Optimizer state keyed by parameter name, data-parallel-unsharded:
+        {"state": {fqn: {"step", "exp_avg", "exp_avg_sq"}}, "param_groups": [...]}"""
+        state = {}
+        for u in self._all_units():
+            st = optimizer.state.get(u.shard, {})
+            if not st:
+                continue
+            dev = u.shard.device
+            m = u.split_full(u.full_flat(st["exp_avg"].to(dev)))
+            v = u.split_full(u.full_flat(st["exp_avg_sq"].to(dev)))
+            if not rank0_only or self.rank == 0:
+                for n in u.names:
+                    state[n] = {"step": int(st["step"]), "exp_avg": m[n].cpu(),
+                                "exp_avg_sq": v[n].cpu()}
+        if rank0_only and self.rank != 0:
+            return None
+        groups_ = [{k: v for k, v in g.items() if k != "params"} for g in optimizer.param_groups]
+        for g in groups_:
+            g["params"] = list(state.keys())
+        return {"state": state, "param_groups": groups_}
+
+    def load_full_optim_state_dict(self, osd, optimizer) -> None:
+        """Every rank reads the full state (from its own copy of the checkpoint file) and keeps
+        its slice."""
+        if osd is None:
+            return
+        for u in self._all_units():
+            if not all(n in osd["state"] for n in u.names):
+                continue
+            st = optimizer.state[u.shard]
+            ref = optimizer._new_state(u.shard) if hasattr(optimizer, "_new_state") else {
+                "step": 0, "exp_avg": torch.zeros_like(u.shard),
+                "exp_avg_sq": torch.zeros_like(u.shard)}
+            for key in ("exp_avg", "exp_avg_sq"):
+                tmp = torch.zeros_like(u.shard.data)
+                u.load_named({n: osd["state"][n][key] for n in u.names}, tmp)
+                ref[key].copy_(tmp.to(ref[key].dtype))
+            ref["step"] = int(osd["state"][u.names[0]]["step"])
+            st.update(ref)
+        for g, saved in zip(optimizer.param_groups, osd.get("param_groups", [])):
+            for k, v in saved.items():
+                if k != "params":
+                    g[k] = v
+
+
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        ctx.save_for_backward(x, weight)
+        ctx.eps = eps
+        return Fn.rmsnorm(x, weight, eps)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, weight = ctx.saved_tensors
+        return Fn.rmsnorm_bwd(x, dy.contiguous(), weight, ctx.eps), None, None
+
+
+def _rmsnorm_autograd(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _RMSNormFn.apply(x.contiguous(), weight.to(x.dtype), eps)
+    from ..ops import reference
+    return reference.rmsnorm(x, weight, eps)

@@ -89,7 +89,8 @@ class MemoryEfficientAdamW(Optimizer):
                     m_dev, v_dev = m, v
                 fused_adamw_(p.data, g.data, m_dev, v_dev, lr=group["lr"], beta1=beta1,
                              beta2=beta2, eps=group["eps"], weight_decay=wd, step=st["step"],
-                             clip_coef=self.clip_coef)
+                             clip_coef=self.clip_coef,
+                             bf16_copy=getattr(p, "_lp_copy", None))
                 if m_dev is not m:
                     m.copy_(m_dev, non_blocking=True)
                     v.copy_(v_dev, non_blocking=True)

@@ -1,0 +1,245 @@
+"""Worker bodies for the multi-process CPU (gloo) tests. Every worker writes its result with
+``torch.save`` to ``<out>/rank<k>.pt``; the test process compares the files."""
+from __future__ import annotations
+
+import datetime
+import os
+import socket
+import sys
+import traceback
+
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+
+def free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _entry(rank, world, port, fn, out, kwargs):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
+                      LOCAL_RANK=str(rank), WORLD_SIZE=str(world))
+    torch.set_num_threads(1)
+    try:
+        if world > 1:
+            dist.init_process_group("gloo", rank=rank, world_size=world,
+                                    timeout=datetime.timedelta(seconds=kwargs.pop("pg_timeout", 120)))
+        res = fn(rank, world, **kwargs)
+        torch.save(res, os.path.join(out, f"rank{rank}.pt"))
+    except Exception:  # noqa: BLE001 -- the parent only sees files
+        with open(os.path.join(out, f"rank{rank}.err"), "w") as f:
+            f.write(traceback.format_exc())
+        raise
+    finally:
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+def run(fn, world: int, out: str, **kwargs):
+    """Run ``fn(rank, world, **kwargs)`` on ``world`` gloo ranks; returns the per-rank results."""
+    os.makedirs(out, exist_ok=True)
+    port = free_port()
+    if world == 1:
+        saved = {k: os.environ.get(k) for k in ("MASTER_ADDR", "MASTER_PORT", "RANK", "LOCAL_RANK",
+                                                "WORLD_SIZE")}
+        try:
+            _entry(0, 1, port, fn, out, dict(kwargs))
+        finally:
+            for k, v in saved.items():
+                if v is None:
+                    os.environ.pop(k, None)
+                else:
+                    os.environ[k] = v
+    else:
+        mp.spawn(_entry, args=(world, port, fn, out, dict(kwargs)), nprocs=world, join=True)
+    return [torch.load(os.path.join(out, f"rank{r}.pt"), weights_only=False)
+            for r in range(world)]
+
+
+# ------------------------------------------------------------------------------- model helpers
+
+def tiny_model(seed=0, dtype=torch.float32, vocab_parallel=False, name="tiny-llama"):
+    from easy_to_hard_b200.models.model import Transformer
+    torch.manual_seed(seed)
+    m = Transformer.from_name(name, freeze_tok_embeddings=True, freeze_output=True,
+                              freeze_norm=True, vocab_parallel=vocab_parallel)
+    g = torch.Generator().manual_seed(seed + 1)
+    for _, t in list(m.named_parameters()) + list(m.named_buffers()):
+        if t.dim() == 2:
+            t.data.copy_(torch.randn(t.shape, generator=g) * 0.05)
+    return m.to(dtype)
+
+
+def sft_batch(vocab=1024, batch=4, seq=128, seed=3):
+    g = torch.Generator().manual_seed(seed)
+    ids = torch.randint(0, vocab, (batch, seq), generator=g)
+    labels = ids.clone()
+    labels[:, :64] = -100            # loss over positions 64..127 only
+    return ids, labels
+
+
+def _merged_state(sdp):
+    """Full (data-parallel-unsharded) state dict; tensor-parallel shards stay as they are."""
+    return sdp.full_state_dict(rank0_only=False)
+
+
+def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_parallel=False,
+                          steps=1, micro=None, gen=True):
+    """One (or more) SFT steps on the tiny model with TP=tp, DP=world/tp, then greedy decode."""
+    from easy_to_hard_b200.models import tp as tpm
+    from easy_to_hard_b200.parallel import groups
+    from easy_to_hard_b200.parallel.fsdp import ShardedDataParallel
+    from easy_to_hard_b200.training import SFTStepper
+    from easy_to_hard_b200.utils.memory_efficient_adam import MemoryEfficientAdamW
+    from easy_to_hard_b200.models.rl_model import generate_tokens
+    from easy_to_hard_b200.utils.checkpoint_utils import merge_tp_checkpoint
+
+    tpm.initialize_model_parallel(tp)
+    model = tiny_model(vocab_parallel=vocab_parallel)
+    heads = (model.config.n_head, model.config.n_local_heads)
+    if tp > 1:
+        tpm.apply_tp(model, requires_grad=True, sequence_parallel=sequence_parallel)
+    for n, p in model.named_parameters():
+        p.requires_grad_(True)
+    sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group())
+    sdp.train()
+    opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=1e-4, weight_decay=0.0,
+                               optim_dtype=torch.float32, optim_device=torch.device("cpu"))
+    stepper = SFTStepper(sdp, opt)
+    ids, labels = sft_batch()
+    dp, dp_rank = groups.get_data_parallel_world_size(), groups.get_data_parallel_rank()
+    per = ids.shape[0] // dp                       # every data-parallel rank takes its rows
+    my_ids, my_lab = ids[dp_rank * per:(dp_rank + 1) * per], labels[dp_rank * per:(dp_rank + 1) * per]
+    losses, norms = [], []
+    for _ in range(steps):
+        loss, gn = stepper.step(my_ids, my_lab, micro)
+        l = loss.detach().clone()
+        if dp > 1:
+            dist.all_reduce(l, group=groups.get_data_parallel_group())
+            l /= dp
+        losses.append(float(l))
+        norms.append(float(gn))
+    state = _merged_state(sdp)
+    state = {k: v for k, v in state.items() if "layers" in k and k.endswith("weight")
+             and "norm" not in k}
+    if tp > 1:   # gather the tensor-parallel shards and merge them to the TP=1 layout
+        shards = [None] * tp
+        dist.all_gather_object(shards, state, group=groups.get_model_parallel_group())
+        state = merge_tp_checkpoint(shards, heads=heads)
+    out = {"loss": losses, "grad_norm": norms, "state": state}
+    if gen:
+        # decode with the updated weights through the plain module path
+        for u in sdp.units:
+            u.gather_into(torch.empty(u.padded, dtype=u.shard.dtype))
+        model.eval()
+        g = torch.Generator().manual_seed(11)
+        prompts = torch.randint(0, 1024, (4, 32), generator=g)
+        with torch.no_grad():
+            seq = generate_tokens(model, prompts, None, 16, temperature=0.0, top_k=None,
+                                  eos_id=None)
+        out["tokens"] = seq
+    return out
+
+
+def checkpoint_roundtrip(rank, world, tp=1, save_dir=None):
+    """Train 2 steps, save through checkpoint_utils, train 1 more; a fresh model resumes from the
+    file and must reproduce the third step."""
+    from types import SimpleNamespace
+    from easy_to_hard_b200.models import tp as tpm
+    from easy_to_hard_b200.parallel import groups
+    from easy_to_hard_b200.parallel.fsdp import ShardedDataParallel
+    from easy_to_hard_b200.training import SFTStepper
+    from easy_to_hard_b200.utils import checkpoint_utils as cu
+    from easy_to_hard_b200.utils.memory_efficient_adam import MemoryEfficientAdamW
+    from easy_to_hard_b200.utils.trainer_utils import get_cosine_schedule_with_warmup
+
+    tpm.initialize_model_parallel(tp)
+
+    def build():
+        model = tiny_model()
+        if tp > 1:
+            tpm.apply_tp(model, requires_grad=True)
+        model.requires_grad_(True)
+        names = [n for n, p in model.named_parameters() if p.requires_grad]
+        sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group())
+        sdp.train()
+        opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=1e-3,
+                                   optim_dtype=torch.float32, optim_device=torch.device("cpu"))
+        sch = get_cosine_schedule_with_warmup(opt, 1, 10)
+        return sdp, opt, sch, names
+
+    ids, labels = sft_batch(batch=2 * max(1, world // tp))
+    dp, dp_rank = groups.get_data_parallel_world_size(), groups.get_data_parallel_rank()
+    per = ids.shape[0] // dp
+    my = slice(dp_rank * per, (dp_rank + 1) * per)
+    sdp, opt, sch, names = build()
+    st = SFTStepper(sdp, opt, sch)
+    for _ in range(2):
+        st.step(ids[my], labels[my])
+    path = cu.get_checkpoint_path(save_dir, 0, 2, groups.get_model_parallel_rank(), "")
+    cu.save_checkpoint(path, sdp, opt, sch, 0, 2, groups.get_model_parallel_rank(), False, None,
+                       True, names, "", None, torch.float32)
+    if dist.is_initialized():
+        dist.barrier()
+    l3, _ = st.step(ids[my], labels[my])
+
+    sdp2, opt2, sch2, _ = build()
+    found, epoch, step = cu.get_latest_checkpoint_path(save_dir)
+    cu.load_checkpoint(found, sdp2, opt2, sch2, use_fsdp=True)
+    st2 = SFTStepper(sdp2, opt2, sch2)
+    l3b, _ = st2.step(ids[my], labels[my])
+    a, b = sdp.full_state_dict(rank0_only=False), sdp2.full_state_dict(rank0_only=False)
+    diff = max(float((a[k].float() - b[k].float()).abs().max()) for k in a if "layers" in k)
+    return {"l3": float(l3), "l3_resumed": float(l3b), "step": step, "param_diff": diff,
+            "lr": (sch.get_last_lr()[0], sch2.get_last_lr()[0])}
+
+
+# ------------------------------------------------------------------------------- failure paths
+
+def rank_raises(rank, world, bad_rank=1):
+    """A rank fails on the host between steps; the others learn of it from the store before the
+    next collective (no collective is left hanging)."""
+    from easy_to_hard_b200.parallel.health import HealthMonitor
+    mon = HealthMonitor(rank, world, heartbeat_s=0.05, dead_after_s=1.0)
+    mon.start()
+    status = "ok"
+    try:
+        for step in range(50):
+            mon.check()                      # raises PeerFailure if someone reported an error
+            if rank == bad_rank and step == 3:
+                raise RuntimeError("injected host-side failure")
+            t = torch.ones(4)
+            dist.all_reduce(t)
+            import time
+            time.sleep(0.02)
+    except RuntimeError as e:
+        if "injected" in str(e):
+            mon.report_failure(str(e))
+            status = "failed"
+        else:
+            status = f"peer-failure:{e}"
+    except Exception as e:  # noqa: BLE001
+        status = f"peer-failure:{type(e).__name__}"
+    finally:
+        mon.stop()
+    return status
+
+
+def rank_never_joins(rank, world):
+    """Rank 1 leaves before the collective; a short process-group timeout ends the others' wait
+    with an error instead of a hang."""
+    if rank == 1:
+        return "left"
+    try:
+        t = torch.ones(2)
+        dist.all_reduce(t)
+        return "completed"
+    except Exception as e:  # noqa: BLE001
+        return f"error:{type(e).__name__}"
