@@ -43,6 +43,10 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="decode", choices=["decode", "sft"],
+                    help="decode: batched generation (headline); sft: full-parameter SFT step")
+    ap.add_argument("--micro", type=int, default=8, help="sft: sequences per micro batch")
+    ap.add_argument("--tp", type=int, default=1, help="sft: tensor-parallel size (rest is FSDP)")
     ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch in the "
                     "decode graph (1) or plain stream order (0)")
@@ -215,6 +219,115 @@ def run_ours(a):
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": BATCH * PROMPT * 4,
                     "d2h_bytes_per_step": BATCH * (PROMPT + NEW) * 4},
+            "gpu_launches": launches, "kernel_status": status,
+        }
+        print(json.dumps(out), flush=True)
+
+
+SFT_SEQ, SFT_GLOBAL_BATCH = 768, 64
+
+
+def sft_batches(n, vocab, per_rank, rank):
+    """Random token ids; per sequence a prompt of 64..384 tokens whose labels are ignored
+    (cross-entropy on the response tokens only). Pinned host tensors."""
+    import torch
+    gen = torch.Generator().manual_seed(100 + rank)
+    out = []
+    for _ in range(n):
+        ids = torch.randint(0, vocab, (per_rank, SFT_SEQ), generator=gen, dtype=torch.int64)
+        plen = torch.randint(64, 385, (per_rank, 1), generator=gen)
+        labels = ids.clone()
+        labels[torch.arange(SFT_SEQ)[None, :] < plen] = -100
+        out.append((ids.pin_memory(), labels.pin_memory()))
+    return out
+
+
+def run_ours_sft(a):
+    """Full-parameter SFT step of the 7B architecture: fp32 master weights, bf16 compute, AdamW
+    with bf16 moments (lr 2e-5, betas 0.9/0.95), global batch 64 x 768 tokens, TP=a.tp x
+    sharded data parallel over the rest. value = trained tokens/s of the whole job."""
+    import torch
+    rank, local, world = dist_setup(a.gpus)
+    from easy_to_hard_b200.models.model import ModelArgs, Transformer
+    from easy_to_hard_b200.models import tp
+    from easy_to_hard_b200.parallel import groups
+    from easy_to_hard_b200.parallel.fsdp import ShardedDataParallel
+    from easy_to_hard_b200.training import SFTStepper, prepare_batch
+    from easy_to_hard_b200.utils.memory_efficient_adam import MemoryEfficientAdamW
+    from easy_to_hard_b200.ops import _lib
+
+    tp.initialize_model_parallel(a.tp)
+    dp = world // a.tp
+    cfg = ModelArgs.from_name(MODEL)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = Transformer(cfg, freeze_tok_embeddings=True, freeze_output=True,
+                            freeze_norm=True).to(torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    for name, t in list(model.named_parameters()) + list(model.named_buffers()):
+        if t.dim() == 2:
+            t.data.normal_(0.0, 0.02, generator=g)
+    if a.tp > 1:
+        tp.apply_tp(model, requires_grad=True)
+    model.requires_grad_(True)
+    sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group(),
+                              param_dtype=torch.float32, compute_dtype=torch.bfloat16,
+                              reduce_dtype=torch.bfloat16)
+    sdp.train()
+    torch.cuda.empty_cache()
+    opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=2e-5, betas=(0.9, 0.95),
+                               weight_decay=0.0, optim_dtype=torch.bfloat16,
+                               optim_device=torch.device("cuda"))
+    stepper = SFTStepper(sdp, opt)
+    per_rank = SFT_GLOBAL_BATCH // world            # rows each rank loads; a TP group pools them
+    host = sft_batches(a.steps + a.warmup, cfg.vocab_size, per_rank, rank)
+    dev = [(i.cuda(), l.cuda()) for i, l in host]
+    host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+    micro = a.micro
+
+    def step_device(i):
+        ids, labels = prepare_batch(*dev[i % len(dev)], -1, 0, a.tp > 1)
+        stepper.step(ids, labels, micro)
+
+    def step_e2e(i):
+        ids, labels = host[i % len(host)]
+        ids = ids.to("cuda", non_blocking=True)
+        labels = labels.to("cuda", non_blocking=True)
+        ids, labels = prepare_batch(ids, labels, -1, 0, a.tp > 1)
+        loss, _ = stepper.step(ids, labels, micro)
+        host_loss.copy_(loss.float().reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(a.warmup):
+        step_device(i)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda i: step_device(a.warmup + i), a.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(lambda i: step_e2e(a.warmup + i), a.steps)
+    status = _lib.read_status()
+    toks = SFT_GLOBAL_BATCH * SFT_SEQ * a.steps
+    n_micro = -(-(per_rank * a.tp) // micro)
+    # per block and micro batch: forward 9 kernels, backward recompute 9 + 17; plus CE chunks
+    launches = (cfg.n_layer * (9 + 26) * n_micro + cfg.n_layer * 2 + 40) * a.steps
+    if rank == 0:
+        flops = 6 * 6.74e9 * SFT_GLOBAL_BATCH * SFT_SEQ * (4.0 / 3.0)   # with recomputation
+        out = {
+            "metric": "sft_train_tokens_per_s", "value": toks / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random token ids, random-init weights)", "impl": "ours",
+            "config": {"model": "Llemma-7B architecture (llemma-7b-32016)",
+                       "global_batch": SFT_GLOBAL_BATCH, "seq_len": SFT_SEQ,
+                       "micro_batch": micro, "parallelism": f"tp{a.tp}xfsdp{dp}",
+                       "optimizer": "AdamW lr 2e-5 betas 0.9/0.95, fp32 master, bf16 moments",
+                       "loss": "cross-entropy on response tokens (prompt 64..384 masked)",
+                       "l2": "inputs larger than L2 (13 GB of bf16 weights per pass)",
+                       "model_tflops_per_gpu": flops / (ms / a.steps / 1e3) / 1e12 / world},
+            "clocks": clocks,
+            "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": 2 * per_rank * SFT_SEQ * 8, "d2h_bytes_per_step": 4},
             "gpu_launches": launches, "kernel_status": status,
         }
         print(json.dumps(out), flush=True)
