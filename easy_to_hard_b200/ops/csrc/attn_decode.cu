@@ -252,3 +252,79 @@ extern "C" int e2h_attn_decode(const void* q, const void* kcache, const void* vc
 #undef E2H_GO
   return -3;  // unsupported (head_dim, group) pair: callers fall back to per-head launches
 }
+
+// ---------------------------------------------------------------------------------------------
+// Non-allocating variant (declared in attn_decode_static.h). The split-KV partial results go to
+// a fixed array in device memory instead of a caller-provided buffer, so the call allocates
+// nothing and needs nothing allocated for it.
+#include <cstdio>
+#include <mutex>
+
+#include "attn_decode_static.h"
+
+namespace e2h {
+// room for 64 sequences x 32 heads x 8 splits x (128 + 2) floats = 8.125 MiB
+constexpr long long kStaticPartialFloats = 64LL * 32 * 8 * (128 + 2);
+static __device__ __align__(256) float g_static_partial[kStaticPartialFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_partial_ptr[kMaxDevices];   // per device, filled on that device's first call
+static std::mutex g_static_partial_mu;
+
+static int static_partial_for_current_device(float** ptr) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= kMaxDevices) return -5;
+  std::lock_guard<std::mutex> lock(g_static_partial_mu);
+  if (g_static_partial_ptr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_static_partial);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "e2h_attn_decode_static: cudaGetSymbolAddress failed: %s\n",
+              cudaGetErrorString(e));
+      return (int)e;
+    }
+    g_static_partial_ptr[dev] = p;
+  }
+  *ptr = g_static_partial_ptr[dev];
+  return 0;
+}
+}  // namespace e2h
+
+extern "C" int e2h_attn_decode_static(const void* q, const void* kcache, const void* vcache,
+                                      void* out, const int* pos, const int* left_pad, int B,
+                                      int n_head, int n_kv, int head_dim, int smax, float scale,
+                                      int n_split, void* stream_v) {
+  using namespace e2h;
+  if (B < 1 || n_head < 1 || n_kv < 1 || n_split < 1 || n_head % n_kv) return -1;
+  const long long need = (long long)B * n_head * n_split * (head_dim + 2);
+  if (n_split > 1 && need > kStaticPartialFloats) {
+    fprintf(stderr,
+            "e2h_attn_decode_static: B*n_head*n_split*(head_dim+2) = %lld floats exceeds the "
+            "fixed scratch of %lld floats (64 x 32 heads x 8 splits x head_dim 128); use fewer "
+            "splits or e2h_attn_decode with a caller-provided buffer\n",
+            need, kStaticPartialFloats);
+    return -4;
+  }
+  float* partial = nullptr;
+  if (n_split > 1) {
+    const int rc = static_partial_for_current_device(&partial);
+    if (rc != 0) return rc;
+  }
+  cudaStream_t stream = (cudaStream_t)stream_v;
+  const int G = n_head / n_kv;
+#define E2H_GO(D_, G_)                                                                          \
+  return launch_decode<D_, G_>(q, kcache, vcache, out, partial, pos, left_pad, B, n_head, n_kv, \
+                               smax, scale, n_split, stream)
+  if (head_dim == 128) {
+    if (G == 1) E2H_GO(128, 1);
+    if (G == 4) E2H_GO(128, 4);
+    if (G == 8) E2H_GO(128, 8);
+  } else if (head_dim == 64) {
+    if (G == 1) E2H_GO(64, 1);
+    if (G == 4) E2H_GO(64, 4);
+  }
+#undef E2H_GO
+  return -3;
+}
