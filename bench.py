@@ -359,6 +359,8 @@ if __name__ == "__main__":
     args = parse()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "sft":
+        run_ours_sft(args)
     else:
         run_ours(args)
     # Leave without tearing NCCL down: destroying a communicator whose kernels sit in captured

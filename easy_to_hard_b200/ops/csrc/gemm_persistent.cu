@@ -93,7 +93,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                             const __grid_constant__ CUtensorMap tmB,
                             const __grid_constant__ CUtensorMap tmOut,
                             const __grid_constant__ CUtensorMap tmRes, const E2hGemmParams p,
-                            const int staged) {
+                            const int staged, const int mn3d) {
   constexpr int A_BYTES = 128 * 128;                  // 128 features x 64 k, bf16
   constexpr int B_BYTES = BN * 128;
   constexpr int STAGE = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
@@ -165,6 +165,9 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         if (!p.a_mn_major) {
           tma_load_2d(a_dst, &tmA, k0, f0, bar);
           if (DUAL) tma_load_2d(a_dst + A_BYTES, &tmA2, k0, f0, bar);
+        } else if (mn3d & 1) {
+          // one instruction for both 64-feature chunks: box (64, 64 k-rows, 2 chunks)
+          tma_load_3d(a_dst, &tmA, 0, k0, f0 >> 6, bar);
         } else {
           tma_load_2d(a_dst, &tmA, f0, k0, bar);
           tma_load_2d(a_dst + 8192, &tmA, f0 + 64, k0, bar);
@@ -172,6 +175,8 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         const uint32_t b_dst = a_dst + A_BYTES * (DUAL ? 2 : 1);
         if (!p.b_mn_major) {
           tma_load_2d(b_dst, &tmB, k0, t0, bar);
+        } else if (mn3d & 2) {
+          tma_load_3d(b_dst, &tmB, 0, k0, t0 >> 6, bar);
         } else {
 #pragma unroll
           for (int c = 0; c < BN / 64; ++c)
@@ -375,13 +380,36 @@ static int p_map(CUtensorMap* m, const void* base, long long inner, long long ou
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
+// MN-major operand [K rows, mn] (mn a multiple of 64) seen as (64, K, mn / 64): one box of
+// (64, 64, chunks) lands in shared memory as `chunks` consecutive 64 x 64 swizzled blocks, the
+// layout the MN-major UMMA descriptors expect, with a single TMA instruction.
+static int p_map_mn3d(CUtensorMap* m, const void* base, long long mn, long long k, long long ld,
+                      int chunks) {
+  PEncodeFn fn = p_encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[3] = {64, (cuuint64_t)k, (cuuint64_t)(mn / 64)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 2, 128};
+  cuuint32_t box[3] = {64, 64, (cuuint32_t)chunks};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides,
+                  box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
 template <int BN, bool DUAL>
 static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
   constexpr int STAGE = 128 * 128 * (DUAL ? 2 : 1) + BN * 128;
   CUtensorMap ta, ta2, tb, to, tr;
   int r;
-  r = p.a_mn_major ? p_map(&ta, p.a, p.F, p.K, p.lda, 64, 64, true)
-                   : p_map(&ta, p.a, p.K, p.F, p.lda, 64, 128, true);
+  int mn3d = 0;
+  if (p.a_mn_major && p.F % 64 == 0) {
+    mn3d |= 1;
+    r = p_map_mn3d(&ta, p.a, p.F, p.K, p.lda, 2);
+  } else {
+    r = p.a_mn_major ? p_map(&ta, p.a, p.F, p.K, p.lda, 64, 64, true)
+                     : p_map(&ta, p.a, p.K, p.F, p.lda, 64, 128, true);
+  }
   if (r) return r;
   if (DUAL) {
     r = p_map(&ta2, p.a2, p.K, p.F, p.lda2, 64, 128, true);
@@ -389,8 +417,13 @@ static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
   } else {
     ta2 = ta;
   }
-  r = p.b_mn_major ? p_map(&tb, p.b, p.T, p.K, p.ldb, 64, 64, true)
-                   : p_map(&tb, p.b, p.K, p.T, p.ldb, 64, BN, true);
+  if (p.b_mn_major && p.T % 64 == 0) {
+    mn3d |= 2;
+    r = p_map_mn3d(&tb, p.b, p.T, p.K, p.ldb, BN / 64);
+  } else {
+    r = p.b_mn_major ? p_map(&tb, p.b, p.T, p.K, p.ldb, 64, 64, true)
+                     : p_map(&tb, p.b, p.K, p.T, p.ldb, 64, BN, true);
+  }
   if (r) return r;
   int staged = (p.epi == E2H_EPI_STORE_BF16 || p.epi == E2H_EPI_RESIDUAL ||
                 (p.epi == E2H_EPI_SWIGLU && DUAL)) ? 1 : 0;
@@ -437,7 +470,7 @@ static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
   const int n_tiles = ((p.F + 127) / 128) * ((p.T + BN - 1) / BN);
   const int grid = n_tiles < n_sm ? n_tiles : n_sm;
   return (int)launch(kern, dim3(grid), dim3(kPThreads), smem, stream, ta, ta2, tb, to, tr, p,
-                     staged);
+                     staged, mn3d);
 }
 
 }  // namespace e2h

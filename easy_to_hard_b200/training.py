@@ -59,23 +59,30 @@ def model_forward_with_loss(model, input_ids: torch.Tensor, labels: torch.Tensor
                            ignore_index=IGNORE_INDEX, reduction="mean")
 
 
+def gather_tp_batch(tensors, use_tp: bool, sync_group=None):
+    """Make a batch identical on every rank of a tensor-parallel group by concatenating the
+    ranks' batches along dim 0 (train_sft.py:436-447 of the reference)."""
+    if not (use_tp and groups.get_model_parallel_world_size() > 1):
+        return tuple(tensors)
+    n = groups.get_model_parallel_world_size()
+    group = sync_group if sync_group is not None else groups.get_model_parallel_group()
+    out = []
+    for t in tensors:
+        t = t.contiguous()
+        full = torch.empty((t.shape[0] * n, *t.shape[1:]), dtype=t.dtype, device=t.device)
+        dist.all_gather_into_tensor(full, t, group=group)
+        out.append(full)
+    return tuple(out)
+
+
 def prepare_batch(input_ids: torch.Tensor, labels: torch.Tensor, pad_id: int, unk_id: int,
                   use_tp: bool, sync_group=None) -> Tuple[torch.Tensor, torch.Tensor]:
-    """Mask padded labels and make the batch identical on every rank of a tensor-parallel
-    group by concatenating the ranks' batches (train_sft.py:425-449 of the reference)."""
+    """Mask padded labels, replace a negative pad id in the inputs, pool the batch over the
+    tensor-parallel group (train_sft.py:425-449 of the reference)."""
     labels = labels.masked_fill(labels == pad_id, IGNORE_INDEX)
     if pad_id < 0:
         input_ids = input_ids.masked_fill(input_ids == pad_id, unk_id)
-    if use_tp and groups.get_model_parallel_world_size() > 1:
-        n = groups.get_model_parallel_world_size()
-        group = sync_group if sync_group is not None else groups.get_model_parallel_group()
-        ids = torch.empty((input_ids.shape[0] * n, input_ids.shape[1]), dtype=input_ids.dtype,
-                          device=input_ids.device)
-        lab = torch.empty_like(ids, dtype=labels.dtype)
-        dist.all_gather_into_tensor(ids, input_ids.contiguous(), group=group)
-        dist.all_gather_into_tensor(lab, labels.contiguous(), group=group)
-        return ids, lab
-    return input_ids, labels
+    return gather_tp_batch((input_ids, labels), use_tp, sync_group)
 
 
 class GradClipper:
@@ -103,29 +110,36 @@ class GradClipper:
         return self.norm
 
 
-class SFTStepper:
-    """zero_grad -> micro-batch forward/backward -> clip -> optimizer -> scheduler."""
+class TrainStepper:
+    """zero_grad -> micro-batch forward/backward -> clip -> optimizer -> scheduler, for any
+    ``loss_fn(model, *tensors)`` returning a loss or ``(loss, metrics)``."""
 
-    def __init__(self, model, optimizer, scheduler=None, max_grad_norm: float = 1.0):
+    def __init__(self, model, optimizer, scheduler=None, loss_fn=None, max_grad_norm: float = 1.0):
         self.model, self.optimizer, self.scheduler = model, optimizer, scheduler
+        self.loss_fn = loss_fn or model_forward_with_loss
         self.max_grad_norm = max_grad_norm
         self.sharded = isinstance(model, ShardedDataParallel)
         dev = next(iter(model.parameters())).device
         self.clipper = GradClipper(dev) if (dev.type == "cuda" and self.sharded
                                             and hasattr(optimizer, "clip_coef")) else None
+        self.metrics = None
 
-    def step(self, input_ids: torch.Tensor, labels: torch.Tensor,
-             micro_batch_size: Optional[int] = None):
-        """Returns (loss of the last micro batch, gradient norm before clipping); both stay on
-        the device."""
+    def step(self, *tensors: torch.Tensor, micro_batch_size: Optional[int] = None):
+        """``tensors`` share dim 0 (the batch). Returns (loss of the last micro batch, gradient
+        norm before clipping); both stay on the device. Metrics of the last micro batch, if the
+        loss function returns any, are left in ``self.metrics``."""
         model = self.model
         model.zero_grad()
-        n = input_ids.shape[0]
+        n = tensors[0].shape[0]
         mb = micro_batch_size or n
         scale = 1.0 / (-(-n // mb))
         loss = None
         for a in range(0, n, mb):
-            loss = model_forward_with_loss(model, input_ids[a:a + mb], labels[a:a + mb])
+            out = self.loss_fn(model, *[t[a:a + mb] for t in tensors])
+            if isinstance(out, tuple):
+                loss, self.metrics = out
+            else:
+                loss = out
             (loss * scale).backward()
         if self.sharded:
             model.finish_backward()
@@ -140,6 +154,14 @@ class SFTStepper:
         if self.scheduler is not None:
             self.scheduler.step()
         return loss.detach(), grad_norm
+
+
+class SFTStepper(TrainStepper):
+    def __init__(self, model, optimizer, scheduler=None, max_grad_norm: float = 1.0):
+        super().__init__(model, optimizer, scheduler, model_forward_with_loss, max_grad_norm)
+
+    def step(self, input_ids, labels, micro_batch_size: Optional[int] = None):
+        return super().step(input_ids, labels, micro_batch_size=micro_batch_size)
 
 
 def smoke_train_step(device="cuda:0"):
@@ -166,3 +188,42 @@ def smoke_train_step(device="cuda:0"):
     loss, gn = stepper.step(ids, ids.clone())
     torch.cuda.synchronize()
     return float(loss), float(gn)
+
+
+# ----------------------------------------------------------------------------- reward models
+
+def pointwise_reward_loss(model, input_ids: torch.Tensor, labels: torch.Tensor,
+                          weights: torch.Tensor) -> torch.Tensor:
+    """Weighted binary cross-entropy of the per-token reward against per-token labels
+    (train_rm_pointwise.py:78-112 of the reference): sum(w * bce) / (sum(w) + 1e-6)."""
+    rewards = model(input_ids)
+    loss = F.binary_cross_entropy_with_logits(rewards.float().view(-1), labels.float().view(-1),
+                                              reduction="none")
+    w = weights.float().view(-1)
+    return (loss * w).sum() / (w.sum() + 1e-6)
+
+
+def reward_modeling_metrics(logits: torch.Tensor, labels: torch.Tensor) -> dict:
+    """accuracy / positive rates of ``logits >= 0`` against 0/1 labels
+    (train_rm_pairwise.py:131-147 of the reference)."""
+    pred = (logits >= 0.0).long()
+    labels = labels.long()
+    return dict(accuracy=pred.eq(labels).float().mean(),
+                label_positive_rate=(labels == 1).float().mean(),
+                positive_rate=(pred == 1).float().mean(),
+                true_positive_rate=(pred * labels).float().sum() / labels.sum(),
+                false_positive_rate=(pred * (1 - labels)).float().sum() / (1 - labels).sum())
+
+
+def pairwise_reward_loss(model, input_ids: torch.Tensor, choice: torch.Tensor):
+    """``input_ids`` [B, 2, T] (0-padded on the right), ``choice`` [B, 1]: BCE of
+    ``reward(candidate 0) - reward(candidate 1)`` at the last non-pad token against ``choice``
+    (train_rm_pairwise.py:80-128 of the reference). Returns (loss, metrics)."""
+    B, C, T = input_ids.shape
+    assert C == 2 and choice.shape == (B, 1)
+    flat = input_ids.reshape(B * C, T)
+    eos_pos = flat.ne(0).long().sum(dim=-1) - 1
+    rewards = model(flat, eos_pos=eos_pos).view(B, C)
+    logits = (rewards[:, 0] - rewards[:, 1]).float()
+    loss = F.binary_cross_entropy_with_logits(logits.view(-1), choice.float().view(-1))
+    return loss, reward_modeling_metrics(logits.detach().view(-1), choice.view(-1))

@@ -1,0 +1,105 @@
+"""End-to-end runs of the training entry points on CPU: a tiny random ``model.pth`` in the
+gpt-fast layout, a sentencepiece ``tokenizer.model`` trained on the spot, a few JSON records,
+one epoch, checkpoint written, resume picks it up."""
+import json
+import os
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+WORDS = ("solve add subtract number answer question solution step therefore equals two three "
+         "four five six seven eight nine ten the of is we get so then x y z sum product").split()
+
+
+def _sentence(g, n):
+    return " ".join(WORDS[int(i)] for i in torch.randint(0, len(WORDS), (n,), generator=g))
+
+
+@pytest.fixture(scope="module")
+def workspace(tmp_path_factory):
+    import sentencepiece as spm
+    from easy_to_hard_b200.models.model import Transformer
+    root = tmp_path_factory.mktemp("ws")
+    model_dir = root / "tiny-llama"
+    model_dir.mkdir()
+    g = torch.Generator().manual_seed(0)
+    corpus = root / "corpus.txt"
+    corpus.write_text("\n".join(_sentence(g, 12) for _ in range(400)) +
+                      "\n# Question\n\n# Solution\n\n0 1 2 3 4 5 6 7 8 9 + - = .\n")
+    spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(model_dir / "tokenizer"),
+                                   vocab_size=200, model_type="bpe", bos_id=1, eos_id=2,
+                                   unk_id=0, pad_id=-1, byte_fallback=False,
+                                   character_coverage=1.0, minloglevel=2)
+    torch.manual_seed(0)
+    m = Transformer.from_name("tiny-llama")
+    for p in m.parameters():
+        if p.dim() == 2:
+            torch.nn.init.normal_(p, std=0.05)
+    torch.save(m.state_dict(), model_dir / "model.pth")
+
+    sft = [{"query": _sentence(g, 8), "output": _sentence(g, 10)} for _ in range(8)]
+    (root / "sft.json").write_text(json.dumps(sft))
+    prm = [{"input": _sentence(g, 8), "output_prefix": "", "output": _sentence(g, 6) + "\n\n",
+            "label": int(i % 2)} for i in range(8)]
+    (root / "prm.json").write_text(json.dumps(prm))
+    pairs = [{"input": _sentence(g, 6), "output_1": _sentence(g, 5), "output_2": _sentence(g, 5),
+              "preference": 1 + int(i % 2)} for i in range(8)]
+    (root / "pairs.json").write_text(json.dumps(pairs))
+    return root
+
+
+def _args(workspace, save_dir, **kw):
+    from easy_to_hard_b200.utils.arguments import Arguments
+    from easy_to_hard_b200.utils.hf_argparser import HfArgumentParser
+    argv = ["--do_train", "--checkpoint_path", str(workspace / "tiny-llama" / "model.pth"),
+            "--source_max_len", "32", "--target_max_len", "32", "--total_max_len", "64",
+            "--per_device_train_batch_size", "4", "--micro_train_batch_size", "2",
+            "--learning_rate", "1e-3", "--num_train_epochs", "1", "--save_strategy", "epoch",
+            "--save_dir", str(save_dir), "--param_dtype", "fp32", "--optim_dtype", "fp32",
+            "--compute_dtype", "fp32", "--report_to", "none", "--seed", "1"]
+    for k, v in kw.items():
+        argv += [f"--{k}"] + ([] if v is True else [str(v)])
+    return HfArgumentParser((Arguments,)).parse_args_into_dataclasses(argv)[0]
+
+
+def test_train_sft_end_to_end_and_resume(workspace, tmp_path):
+    import train_sft
+    save = tmp_path / "sft"
+    rec = train_sft.main(_args(workspace, save, dataset=str(workspace / "sft.json"),
+                               dataset_format="metamath"))
+    assert 3.0 < rec["loss"] < 8.0 and rec["grad_norm"] > 0
+    files = sorted(os.listdir(save))
+    assert "epoch_1_step_2_rank_0.pt" in files and "last_checkpoint" in files
+    ck = torch.load(save / "epoch_1_step_2_rank_0.pt", weights_only=False)
+    assert set(ck) >= {"model", "optimizer", "scheduler", "epoch", "global_step"}
+    assert all("layers." in k for k in ck["model"])            # only trainable tensors
+    assert "layers.0.attention.wqkv.weight" in ck["optimizer"]["state"]
+    # a second run resumes: nothing is left to train, the final checkpoint is rewritten
+    rec2 = train_sft.main(_args(workspace, save, dataset=str(workspace / "sft.json"),
+                                dataset_format="metamath", resume_from_checkpoint=True))
+    assert rec2 == {}
+
+
+def test_train_rm_pointwise_end_to_end(workspace, tmp_path):
+    import train_rm_pointwise
+    save = tmp_path / "prm"
+    rec = train_rm_pointwise.main(_args(workspace, save, dataset=str(workspace / "prm.json"),
+                                        dataset_format="prm-v2"))
+    assert 0.3 < rec["loss"] < 1.5
+    ck = torch.load(save / "epoch_1_step_2_rank_0.pt", weights_only=False)
+    assert "backbone_model.output.weight" in ck["model"]
+    assert ck["model"]["backbone_model.output.weight"].shape == (2, 256)
+
+
+def test_train_rm_pairwise_end_to_end(workspace, tmp_path):
+    import train_rm_pairwise
+    save = tmp_path / "orm"
+    rec = train_rm_pairwise.main(_args(workspace, save, dataset=str(workspace / "pairs.json")))
+    assert 0.3 < rec["loss"] < 1.5 and 0.0 <= rec["accuracy"] <= 1.0
+    assert (save / "epoch_1_step_2_rank_0.pt").exists()
