@@ -136,3 +136,41 @@ def block_backward(dy: torch.Tensor, x: torch.Tensor, w: Dict[str, torch.Tensor]
     if shape.tp > 1:
         d_xn1 = _sp_reduce_scatter(d_xn1, shape) if sp else _tp_all_reduce(d_xn1, shape)
     return Fn.rmsnorm_bwd(x, d_xn1, w["attention_norm"], shape.eps, dres=dh)
+
+
+def block_weights(blk) -> Dict[str, torch.Tensor]:
+    a, f = blk.attention, blk.feed_forward
+    return dict(wqkv=a.wqkv.weight, wo=a.wo.weight, w1=f.w1.weight, w3=f.w3.weight,
+                w2=f.w2.weight, attention_norm=blk.attention_norm.weight,
+                ffn_norm=blk.ffn_norm.weight)
+
+
+def can_fuse(model, idx: torch.Tensor) -> bool:
+    """The cache-less fused forward applies to a bf16 CUDA model with plain (unquantised)
+    linears."""
+    if not idx.is_cuda or not model.layers:
+        return False
+    blk = model.layers[0]
+    ws = block_weights(blk)
+    return all(isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and w.dim() >= 1
+               for w in ws.values()) and type(blk.attention.wqkv).__name__ in ("Linear",
+                                                                                "FrozenLinear")
+
+
+@torch.no_grad()
+def transformer_hidden(model, idx: torch.Tensor) -> torch.Tensor:
+    """Fully-causal forward of the whole stack without a KV cache (scoring, log-probs of given
+    sequences): token ids [B, S] -> final-norm hidden states [B, S, dim] bf16. Right padding is
+    harmless under the causal mask; the caller ignores padded positions."""
+    B, S = idx.shape
+    if model.freqs_cis is None or model.max_seq_length < S or model.max_batch_size < B:
+        model.setup_caches(B, S, kv_cache=False)
+    att = model.layers[0].attention
+    shape = BlockShape(B, S, att.n_head, att.n_local_heads, att.head_dim, model.config.norm_eps,
+                       tp=getattr(att, "tp_size", 1), sequence_parallel=False)
+    pos = torch.arange(S, device=idx.device, dtype=torch.int32).repeat(B)
+    x = model.embed(idx).to(torch.bfloat16).reshape(B * S, -1)
+    for blk in model.layers:
+        x, _ = block_forward(x, block_weights(blk), model.freqs_cis, pos, shape)
+    x = Fn.rmsnorm(x, model.norm.weight.to(torch.bfloat16), model.config.norm_eps)
+    return x.view(B, S, -1)

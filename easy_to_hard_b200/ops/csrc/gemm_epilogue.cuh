@@ -84,10 +84,23 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
       float* out = static_cast<float*>(p.out);
       if (f_ok) {
         float* row = out + (long long)f * p.ldo;
+        if (t0 + 8 <= p.T && (reinterpret_cast<uintptr_t>(row + t0) & 15) == 0) {
+          float4* dst = reinterpret_cast<float4*>(row + t0);
+          float4 lo = make_float4(v[0], v[1], v[2], v[3]);
+          float4 hi = make_float4(v[4], v[5], v[6], v[7]);
+          if (p.accumulate) {
+            const float4 a = dst[0], b = dst[1];
+            lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+            hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+          }
+          dst[0] = lo;
+          dst[1] = hi;
+        } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = t0 + j;
-          if (t < p.T) row[t] = p.accumulate ? row[t] + v[j] : v[j];
+          for (int j = 0; j < 8; ++j) {
+            const int t = t0 + j;
+            if (t < p.T) row[t] = p.accumulate ? row[t] + v[j] : v[j];
+          }
         }
       }
     } break;
@@ -95,10 +108,21 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
       if (f_ok) {
         __nv_bfloat16* row = out + (long long)f * p.ldo;
+        if (t0 + 8 <= p.T && (reinterpret_cast<uintptr_t>(row + t0) & 15) == 0) {
+          uint4 pk;
+          uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int t = t0 + j;
-          if (t < p.T) row[t] = __float2bfloat16_rn(v[j]);
+          for (int h = 0; h < 4; ++h) {
+            __nv_bfloat162 two = __floats2bfloat162_rn(v[2 * h], v[2 * h + 1]);
+            w[h] = *reinterpret_cast<uint32_t*>(&two);
+          }
+          *reinterpret_cast<uint4*>(row + t0) = pk;
+        } else {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const int t = t0 + j;
+            if (t < p.T) row[t] = __float2bfloat16_rn(v[j]);
+          }
         }
       }
     } break;

@@ -289,6 +289,31 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                            kStatusTimeoutFull);
           const float sc = (p.scale != nullptr && f < p.F) ? p.scale[f] : 1.f;
           __nv_bfloat16* so = reinterpret_cast<__nv_bfloat16*>(stage_out + b * kChunkBytes);
+          if (staged == 2) {
+            // feature-major output (weight gradients): this lane's 32 values are one 64-byte
+            // row of the staging tile; the 16-byte pieces are XOR-swizzled (64B TMA swizzle:
+            // address bits 4-5 ^= bits 7-8) so that the vector stores do not bank-conflict
+            uint8_t* row = reinterpret_cast<uint8_t*>(so) + lane_row * 64;
+#pragma unroll
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint4 pk;
+              uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+              for (int h = 0; h < 4; ++h) {
+                __nv_bfloat162 two = __floats2bfloat162_rn(v[c4 * 8 + 2 * h] * sc,
+                                                           v[c4 * 8 + 2 * h + 1] * sc);
+                w[h] = *reinterpret_cast<uint32_t*>(&two);
+              }
+              *reinterpret_cast<uint4*>(row + ((c4 ^ ((lane_row >> 1) & 3)) << 4)) = pk;
+            }
+            fence_proxy_async_smem();
+            epi_bar_sync();
+            if (et == 0 && ok && t0 + c * kChunkTok < p.T) {
+              tma_store_2d(&tmOut, smem_u32(so), t0 + c * kChunkTok, f0);
+              bulk_commit_group();
+            }
+            continue;
+          }
           const __nv_bfloat16* sr =
               reinterpret_cast<const __nv_bfloat16*>(stage_res + b * kChunkBytes);
 #pragma unroll
@@ -366,7 +391,7 @@ static PEncodeFn p_encode_fn() {
   return fn;
 }
 static int p_map(CUtensorMap* m, const void* base, long long inner, long long outer, long long ld,
-                 int box_inner, int box_rows, bool swizzle) {
+                 int box_inner, int box_rows, int swizzle) {
   PEncodeFn fn = p_encode_fn();
   if (!fn) return -10;
   cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
@@ -375,7 +400,9 @@ static int p_map(CUtensorMap* m, const void* base, long long inner, long long ou
   cuuint32_t estr[2] = {1u, 1u};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides,
                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  swizzle ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_NONE,
+                  swizzle == 1 ? CU_TENSOR_MAP_SWIZZLE_128B
+                               : (swizzle == 2 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                               : CU_TENSOR_MAP_SWIZZLE_NONE),
                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? 0 : -11;
 }
@@ -429,7 +456,13 @@ static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
                 (p.epi == E2H_EPI_SWIGLU && DUAL)) ? 1 : 0;
   if (staged && ((p.ldo % 8) || ((uintptr_t)p.out & 15))) staged = 0;
   if (staged && p.epi == E2H_EPI_RESIDUAL && ((uintptr_t)p.aux & 15)) staged = 0;
-  if (staged) {
+  if (!staged && p.epi == E2H_EPI_ROWMAJOR_BF16 && !p.accumulate && !DUAL && (p.ldo % 8) == 0 &&
+      ((uintptr_t)p.out & 15) == 0) {
+    staged = 2;
+    r = p_map(&to, p.out, p.T, p.F, p.ldo, kChunkTok, 128, 2);
+    if (r) return r;
+    tr = to;
+  } else if (staged) {
     r = p_map(&to, p.out, p.F, p.T, p.ldo, 128, kChunkTok, false);
     if (r) return r;
     if (p.epi == E2H_EPI_RESIDUAL) {
