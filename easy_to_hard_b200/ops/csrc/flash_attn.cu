@@ -46,6 +46,7 @@ struct FlashCtrl {
   uint64_t q_full;
   uint64_t k_full[2], k_empty[2], v_full[2], v_empty[2];
   uint64_t s_full, s_empty, p_full, o_full;
+  uint64_t p_empty[2];
   uint32_t tmem_base;
   int abort_flag;
 };
@@ -77,24 +78,75 @@ __device__ __forceinline__ void tmem_ld_x32(uint32_t taddr, float* v) {
   for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ void tmem_st_x32(uint32_t taddr, const float* v) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,"
+      "%25,%26,%27,%28,%29,%30,%31,%32};"
+      ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])),
+        "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])),
+        "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+        "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+        "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])),
+        "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])), "r"(__float_as_uint(v[16])),
+        "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+        "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])),
+        "r"(__float_as_uint(v[23])), "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])),
+        "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])), "r"(__float_as_uint(v[28])),
+        "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+// barrier among the two warps that share a block of 32 query rows
+__device__ __forceinline__ void pair_bar_sync(int id) {
+  asm volatile("bar.sync %0, 64;" ::"r"(id) : "memory");
+}
+
+constexpr int kFwdThreads = 320;
+constexpr float kRescaleThreshold = 8.f;   // log2 units: P stays below 2^8 between rescales
+
 // D = head_dim (64 or 128). Tiles are stored as D/64 column halves of [rows x 64] bf16, each
 // half 128-byte swizzled (what a TMA box {64, rows} produces).
+//
+// Roles (320 threads):
+//   warp 0     TMA producer: Q once, then K / V tiles (128 keys) through two-deep rings
+//   warp 1     UMMA issuer:  S = Q K^T (TMEM cols [0,128)),  O += P V (TMEM cols [128,128+D))
+//   warps 2-9  softmax: two threads per query row, one per 64-key half of the score tile
+//              (warps w and w+4 share rows and TMEM lanes). A thread loads its 64 scores in one
+//              trip, the pair exchanges row maxima through shared memory, and P = exp2(S - m)
+//              goes to a double-buffered shared-memory tile as the K-major A operand of PV.
+// O stays in tensor memory for the whole key loop. The running maximum is only raised -- and O
+// multiplied by exp2(m_old - m_new) in place (tcgen05.ld / .st) -- when some row of the warp
+// would otherwise exceed 2^8; otherwise the stale maximum keeps being used, which is exact
+// after the final division by the row sum. S(j+1) is issued as soon as S(j) is in registers and
+// PV(j) only waits for P(j), so the tensor core and the softmax warps overlap.
+// Score tiles that lie entirely below the diagonal and right of the left-pad boundary skip the
+// visibility tests.
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                  const __grid_constant__ CUtensorMap tmV, const FlashParams p) {
   constexpr int NH = D / 64;                 // 64-wide halves of the head dimension
   constexpr int kHalfBytes = 128 * 128;      // [128 rows x 64] bf16
   constexpr int kTileBytes = NH * kHalfBytes;
   constexpr int kPBytes = 2 * kHalfBytes;    // P: [128 q x 128 keys]
+  constexpr int DH = D / 2;                  // output columns per thread of a row pair
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
   FlashCtrl* ctrl = reinterpret_cast<FlashCtrl*>(smem);
-  uint8_t* q_s = smem + 1024;
+  float* xch = reinterpret_cast<float*>(smem + 1024);   // [2 halves][128 rows]
+  uint8_t* q_s = smem + 2048;
   uint8_t* k_s = q_s + kTileBytes;           // 2 stages
   uint8_t* v_s = k_s + 2 * kTileBytes;       // 2 stages
-  uint8_t* p_s = v_s + 2 * kTileBytes;
+  uint8_t* p_s = v_s + 2 * kTileBytes;       // 2 buffers
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
@@ -118,10 +170,11 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       mbar_init(smem_u32(&ctrl->k_empty[s]), 1);
       mbar_init(smem_u32(&ctrl->v_full[s]), 1);
       mbar_init(smem_u32(&ctrl->v_empty[s]), 1);
+      mbar_init(smem_u32(&ctrl->p_empty[s]), 1);
     }
     mbar_init(smem_u32(&ctrl->s_full), 1);
-    mbar_init(smem_u32(&ctrl->s_empty), 4);   // one arrival per softmax warp
-    mbar_init(smem_u32(&ctrl->p_full), 4);
+    mbar_init(smem_u32(&ctrl->s_empty), 8);   // one arrival per softmax warp
+    mbar_init(smem_u32(&ctrl->p_full), 8);
     mbar_init(smem_u32(&ctrl->o_full), 1);
     ctrl->abort_flag = 0;
     fence_mbar_init();
@@ -192,7 +245,7 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
     for (int it = 0; it < n_j && ok; ++it) {
       const int s = it & 1;
       if (it + 1 < n_j) {
-        // S(it) has been read out of tensor memory: the next score tile may overwrite it
+        // S(it) is in the softmax warps' registers: the next score tile may overwrite it
         ok = mbar_wait(smem_u32(&ctrl->s_empty), it & 1, abort_flag, p.status,
                        kStatusTimeoutTmemEmpty);
         if (!ok) break;
@@ -204,15 +257,17 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
                      kStatusTimeoutFull);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t pa = smem_u32(p_s), va = smem_u32(v_s + s * kTileBytes);
+      const uint32_t pa = smem_u32(p_s + (it & 1) * kPBytes);
+      const uint32_t va = smem_u32(v_s + s * kTileBytes);
 #pragma unroll
       for (int kk = 0; kk < kBK / 16; ++kk) {
         const uint64_t adesc =
             make_sw128_desc(pa + (kk / 4) * kHalfBytes + (kk % 4) * 32, 16, 1024);
         const uint64_t bdesc = make_sw128_desc(va + kk * 2048, kHalfBytes, 1024);
-        umma_f16(tmem_o, adesc, bdesc, idesc_o, kk > 0 ? 1u : 0u);
+        umma_f16(tmem_o, adesc, bdesc, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
       }
       umma_commit(smem_u32(&ctrl->v_empty[s]));
+      umma_commit(smem_u32(&ctrl->p_empty[it & 1]));
       umma_commit(smem_u32(&ctrl->o_full));
     }
   }
@@ -220,113 +275,142 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   if (warp >= 2) {
     // ---------------- softmax / output warps ----------------
     const int qrt = warp & 3;
-    const int row = qrt * 32 + lane;                 // query row within the block = TMEM lane
+    const int ch = (warp - 2) >> 2;                   // which 64-key half of the score tile
+    const int row = qrt * 32 + lane;                  // query row within the block = TMEM lane
     const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
     const int qi = q0 + row;                          // query index
     const int qpos = qi + off;                        // its key position (diagonal)
     const float sl2 = p.scale * 1.4426950408889634f;  // scale * log2(e)
     float m = -FLT_MAX, l = 0.f;
-    float o_acc[D];
-#pragma unroll
-    for (int i = 0; i < D; ++i) o_acc[i] = 0.f;
     bool ok = true;
     for (int it = 0; it < n_j; ++it) {
       const int key0 = (j_begin + it) * kBK;
       if (ok) ok = mbar_wait(smem_u32(&ctrl->s_full), it & 1, abort_flag, p.status,
                              kStatusTimeoutTmemFull);
-      tc_fence_after();
       ok = __all_sync(0xffffffffu, ok);
-      // pass 1: row maximum of the visible scores (32 columns per trip to tensor memory)
-      float mx = m;
-#pragma unroll
-      for (int c = 0; c < kBK; c += 32) {
-        float sv[32];
-        if (ok) tmem_ld_x32(tmem_s + lane_off + c, sv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const int j = key0 + c + i;
-          const bool vis = (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
-          if (vis) mx = fmaxf(mx, sv[i] * sl2);
-        }
+      tc_fence_after();
+      float sv[64];
+      if (ok) {
+        tmem_ld_x32(tmem_s + lane_off + ch * 64, sv);
+        tmem_ld_x32(tmem_s + lane_off + ch * 64 + 32, sv + 32);
       }
-      const float alpha = (m == -FLT_MAX) ? 0.f : exp2f(m - mx);
-      const float msafe = (mx == -FLT_MAX) ? 0.f : mx;
-      float rs = 0.f;
-      // pass 2: P = exp2(s - m) as bf16 into shared memory: [128 x 64] halves, the 16-byte
-      // chunk c of a row lands at chunk position (c ^ (row & 7))
-      uint8_t* prow = p_s + row * 128;
-#pragma unroll
-      for (int c = 0; c < kBK; c += 32) {
-        float sv[32];
-        if (ok) tmem_ld_x32(tmem_s + lane_off + c, sv);
-        tmem_ld_wait();
-#pragma unroll
-        for (int c8 = 0; c8 < 4; ++c8) {
-          uint32_t packed[4];
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float pv[2];
-#pragma unroll
-            for (int u = 0; u < 2; ++u) {
-              const int i = c8 * 8 + 2 * e + u;
-              const int j = key0 + c + i;
-              const bool vis = (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
-              pv[u] = vis ? exp2f(sv[i] * sl2 - msafe) : 0.f;
-            }
-            const __nv_bfloat162 pk = __floats2bfloat162_rn(pv[0], pv[1]);
-            // the row sum uses the rounded values that the PV product will see
-            rs += __bfloat162float(pk.x) + __bfloat162float(pk.y);
-            packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
-          }
-          const int col8 = (c >> 3) + c8;            // 16-byte chunk index within the row
-          const int half = col8 >> 3, chunk = col8 & 7;
-          *reinterpret_cast<uint4*>(prow + half * kHalfBytes + ((chunk ^ (row & 7)) << 4)) =
-              make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        }
-      }
+      tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->s_empty));
-      l = l * alpha + rs;
-      m = mx;
-      fence_proxy_async_smem();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&ctrl->p_full));
-      // O = O * alpha + P V
-      if (ok) ok = mbar_wait(smem_u32(&ctrl->o_full), it & 1, abort_flag, p.status,
-                             kStatusTimeoutTmemFull);
-      ok = __all_sync(0xffffffffu, ok);
-      tc_fence_after();
+      // scores in log2 units; invisible keys become -inf
+      const bool full_tile = (key0 + kBK - 1 <= q0 + off) && (key0 >= lp) && (key0 + kBK <= p.Sk);
+      float mx = -FLT_MAX;
+      if (full_tile) {
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
-        float ov[32];
-        if (ok) tmem_ld_x32(tmem_o + lane_off + c, ov);
-        tmem_ld_wait();
+        for (int i = 0; i < 64; ++i) {
+          sv[i] *= sl2;
+          mx = fmaxf(mx, sv[i]);
+        }
+      } else {
+        const int cbase = key0 + ch * 64;
 #pragma unroll
-        for (int i = 0; i < 32; ++i) o_acc[c + i] = o_acc[c + i] * alpha + ov[i];
+        for (int i = 0; i < 64; ++i) {
+          const int j = cbase + i;
+          const bool vis = (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+          sv[i] = vis ? sv[i] * sl2 : -INFINITY;
+          mx = fmaxf(mx, sv[i]);
+        }
       }
-      tc_fence_before();
-    }
-    if (ok && qi < p.Sq) {
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)qi * p.o_ss +
-                            (long long)h * p.o_sh;
+      xch[ch * 128 + row] = mx;
+      pair_bar_sync(1 + qrt);
+      const float m_new = fmaxf(m, fmaxf(mx, xch[(ch ^ 1) * 128 + row]));
+      pair_bar_sync(1 + qrt);
+      const bool need = (it > 0) && (m != -FLT_MAX) && (m_new - m > kRescaleThreshold);
+      if (__any_sync(0xffffffffu, need)) {
+        // raise the maximum of all 32 rows of this warp: O *= exp2(m_old - m_new) in place
+        const float alpha = (m == -FLT_MAX) ? 1.f : ex2_approx(m - m_new);
+        if (ok) ok = mbar_wait(smem_u32(&ctrl->o_full), (it - 1) & 1, abort_flag, p.status,
+                               kStatusTimeoutTmemFull);
+        ok = __all_sync(0xffffffffu, ok);
+        tc_fence_after();
 #pragma unroll
-      for (int c = 0; c < D; c += 8) {
+        for (int c = 0; c < DH; c += 32) {
+          float ov[32];
+          if (ok) tmem_ld_x32(tmem_o + lane_off + ch * DH + c, ov);
+          tmem_ld_wait();
+#pragma unroll
+          for (int i = 0; i < 32; ++i) ov[i] *= alpha;
+          if (ok) tmem_st_x32(tmem_o + lane_off + ch * DH + c, ov);
+        }
+        tmem_st_wait();
+        l *= alpha;
+        m = m_new;
+      } else if (m == -FLT_MAX) {
+        m = m_new;                                    // no history yet: nothing to rescale
+      }
+      const float msafe = (m == -FLT_MAX) ? 0.f : m;
+      // P(it) goes to buffer it & 1, free once PV(it - 2) has read it
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->p_empty[it & 1]), ((it >> 1) & 1) ^ 1, abort_flag,
+                             p.status, kStatusTimeoutEmpty);
+      ok = __all_sync(0xffffffffu, ok);
+      // [128 x 64] half `ch`, 128-byte rows, 16-byte chunk c at position (c ^ (row & 7))
+      uint8_t* prow = p_s + (it & 1) * kPBytes + ch * kHalfBytes + row * 128;
+      float rs = 0.f;
+#pragma unroll
+      for (int c8 = 0; c8 < 8; ++c8) {
         uint32_t packed[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const __nv_bfloat162 pk =
-              __floats2bfloat162_rn(o_acc[c + 2 * e] * inv, o_acc[c + 2 * e + 1] * inv);
+          const float p0 = ex2_approx(sv[c8 * 8 + 2 * e] - msafe);
+          const float p1 = ex2_approx(sv[c8 * 8 + 2 * e + 1] - msafe);
+          rs += p0 + p1;
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
           packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
         }
-        *reinterpret_cast<uint4*>(orow + c) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(prow + ((c8 ^ (row & 7)) << 4)) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
       }
-      if (p.lse)
-        p.lse[((long long)b * p.H + h) * p.Sq + qi] =
-            (l > 0.f) ? (m * 0.6931471805599453f + logf(l)) : -FLT_MAX;
+      l += rs;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->p_full));
     }
+    // ---- epilogue: O / l ----
+    if (n_j > 0) {
+      if (ok) ok = mbar_wait(smem_u32(&ctrl->o_full), (n_j - 1) & 1, abort_flag, p.status,
+                             kStatusTimeoutTmemFull);
+      ok = __all_sync(0xffffffffu, ok);
+      tc_fence_after();
+    }
+    xch[ch * 128 + row] = l;
+    pair_bar_sync(1 + qrt);
+    const float l_tot = l + xch[(ch ^ 1) * 128 + row];
+    const float inv = l_tot > 0.f ? 1.f / l_tot : 0.f;
+    const bool store = ok && qi < p.Sq;
+    __nv_bfloat16* orow = p.out + (long long)b * p.o_sb + (long long)qi * p.o_ss +
+                          (long long)h * p.o_sh + ch * DH;
+#pragma unroll
+    for (int c = 0; c < DH; c += 32) {
+      float ov[32];
+      if (ok && n_j > 0) tmem_ld_x32(tmem_o + lane_off + ch * DH + c, ov);   // warp-uniform
+      tmem_ld_wait();
+      if (store) {
+#pragma unroll
+        for (int c8 = 0; c8 < 32; c8 += 8) {
+          uint32_t packed[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float a0 = n_j > 0 ? ov[c8 + 2 * e] * inv : 0.f;
+            const float a1 = n_j > 0 ? ov[c8 + 2 * e + 1] * inv : 0.f;
+            const __nv_bfloat162 pk = __floats2bfloat162_rn(a0, a1);
+            packed[e] = *reinterpret_cast<const uint32_t*>(&pk);
+          }
+          *reinterpret_cast<uint4*>(orow + c + c8) =
+              make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        }
+      }
+    }
+    if (store && ch == 0 && p.lse)
+      p.lse[((long long)b * p.H + h) * p.Sq + qi] =
+          (l_tot > 0.f) ? (m * 0.6931471805599453f + logf(l_tot)) : -FLT_MAX;
+    tc_fence_before();
   }
   tc_fence_before();
   __syncthreads();
@@ -833,7 +917,7 @@ extern "C" int e2h_flash_fwd(const void* q, long long q_sb, long long q_ss, long
   p.lse = lse; p.status = status;
   dim3 grid((Sq + kBQ - 1) / kBQ, H, B);
   const int tile = (D / 64) * 128 * 128;
-  const size_t smem = 1024 + 1024 + 5 * (size_t)tile + 2 * 128 * 128;
+  const size_t smem = 1024 + 2048 + 5 * (size_t)tile + 2 * (2 * 128 * 128);
   cudaError_t e;
   if (D == 128) {
     static bool done = false;
@@ -843,7 +927,7 @@ extern "C" int e2h_flash_fwd(const void* q, long long q_sb, long long q_ss, long
       if (e != cudaSuccess) return (int)e;
       done = true;
     }
-    flash_fwd_kernel<128><<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    flash_fwd_kernel<128><<<grid, kFwdThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
   } else {
     static bool done = false;
     if (!done) {
@@ -852,7 +936,7 @@ extern "C" int e2h_flash_fwd(const void* q, long long q_sb, long long q_ss, long
       if (e != cudaSuccess) return (int)e;
       done = true;
     }
-    flash_fwd_kernel<64><<<grid, 192, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
+    flash_fwd_kernel<64><<<grid, kFwdThreads, smem, (cudaStream_t)stream>>>(tq, tk, tv, p);
   }
   return (int)cudaGetLastError();
 }
