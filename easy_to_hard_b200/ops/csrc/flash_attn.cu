@@ -490,7 +490,7 @@ __device__ __forceinline__ void store_row32(uint8_t* tile, int row, int col0, co
 }
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                       const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                       const FlashBwdParams p) {
@@ -525,7 +525,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
     mbar_init(smem_u32(&ctrl->it_full), 1);
     mbar_init(smem_u32(&ctrl->it_empty), 1);
     mbar_init(smem_u32(&ctrl->sdp_full), 1);
-    mbar_init(smem_u32(&ctrl->pds_full), 4);
+    mbar_init(smem_u32(&ctrl->pds_full), 8);   // one arrival per compute warp
     mbar_init(smem_u32(&ctrl->done), 1);
     ctrl->abort_flag = 0;
     fence_mbar_init();
@@ -600,6 +600,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 
   if (warp >= 2) {
     const int qrt = warp & 3;
+    const int ch = (warp - 2) >> 2;   // 64-column half handled by this thread of the row pair
     const int row = qrt * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
@@ -616,21 +617,34 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
                              kStatusTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
+      // interior tiles (all 128 x 128 pairs visible) skip the per-element visibility test
+      const bool full_tile = (key0 + kBK - 1 <= i * kBQ + off) && (key0 >= lp) &&
+                             (key0 + kBK <= p.Sk) && (i * kBQ + kBQ <= p.Sq);
 #pragma unroll
-      for (int c = 0; c < kBK; c += 32) {
+      for (int cc = 0; cc < 64; cc += 32) {
+        const int c = ch * 64 + cc;
         float sv[32], dp[32];
         if (ok) {
           tmem_ld_x32(tm_s + lane_off + c, sv);
           tmem_ld_x32(tm_dp + lane_off + c, dp);
         }
         tmem_ld_wait();
+        if (full_tile) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int j = key0 + c + e;
-          const bool vis = q_ok && (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
-          const float pr = vis ? exp2f(sv[e] * sl2 - lse2) : 0.f;
-          sv[e] = pr;
-          dp[e] = pr * (dp[e] - dl) * p.scale;
+          for (int e = 0; e < 32; ++e) {
+            const float pr = ex2_approx(sv[e] * sl2 - lse2);
+            sv[e] = pr;
+            dp[e] = pr * (dp[e] - dl) * p.scale;
+          }
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int j = key0 + c + e;
+            const bool vis = q_ok && (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+            const float pr = vis ? ex2_approx(sv[e] * sl2 - lse2) : 0.f;
+            sv[e] = pr;
+            dp[e] = pr * (dp[e] - dl) * p.scale;
+          }
         }
         store_row32(p_s, row, c, sv);
         store_row32(ds_s, row, c, dp);
@@ -648,7 +662,8 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
       __nv_bfloat16* dkrow = p.dk + (long long)b * p.k_sb + (long long)kj * p.k_ss + (long long)hk * p.k_sh;
       __nv_bfloat16* dvrow = p.dv + (long long)b * p.k_sb + (long long)kj * p.k_ss + (long long)hk * p.k_sh;
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
+      for (int cc = 0; cc < D / 2; cc += 32) {
+        const int c = ch * (D / 2) + cc;
         float a[32], bq[32];
         if (n_it > 0) {
           tmem_ld_x32(tm_dv + lane_off + c, a);
@@ -682,7 +697,7 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 }
 
 template <int D>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kFwdThreads, 1)
 flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                     const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                     const FlashBwdParams p) {
@@ -716,7 +731,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     mbar_init(smem_u32(&ctrl->it_full), 1);
     mbar_init(smem_u32(&ctrl->it_empty), 1);
     mbar_init(smem_u32(&ctrl->sdp_full), 1);
-    mbar_init(smem_u32(&ctrl->pds_full), 4);
+    mbar_init(smem_u32(&ctrl->pds_full), 8);   // one arrival per compute warp
     mbar_init(smem_u32(&ctrl->done), 1);
     ctrl->abort_flag = 0;
     fence_mbar_init();
@@ -787,6 +802,7 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 
   if (warp >= 2) {
     const int qrt = warp & 3;
+    const int ch = (warp - 2) >> 2;   // 64-column half handled by this thread of the row pair
     const int row = qrt * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(qrt * 32) << 16;
     const float sl2 = p.scale * 1.4426950408889634f;
@@ -801,20 +817,29 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
                              kStatusTimeoutTmemFull);
       ok = __all_sync(0xffffffffu, ok);
       tc_fence_after();
+      const bool full_tile = (key0 + kBK - 1 <= q0 + off) && (key0 >= lp) &&
+                             (key0 + kBK <= p.Sk) && (q0 + kBQ <= p.Sq);
 #pragma unroll
-      for (int c = 0; c < kBK; c += 32) {
+      for (int cc = 0; cc < 64; cc += 32) {
+        const int c = ch * 64 + cc;
         float sv[32], dp[32];
         if (ok) {
           tmem_ld_x32(tm_s + lane_off + c, sv);
           tmem_ld_x32(tm_dp + lane_off + c, dp);
         }
         tmem_ld_wait();
+        if (full_tile) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int j = key0 + c + e;
-          const bool vis = q_ok && (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
-          const float pr = vis ? exp2f(sv[e] * sl2 - lse2) : 0.f;
-          dp[e] = pr * (dp[e] - dl) * p.scale;
+          for (int e = 0; e < 32; ++e)
+            dp[e] = ex2_approx(sv[e] * sl2 - lse2) * (dp[e] - dl) * p.scale;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int j = key0 + c + e;
+            const bool vis = q_ok && (((j <= qpos) && (j >= lp)) || (j == qpos)) && j < p.Sk;
+            const float pr = vis ? ex2_approx(sv[e] * sl2 - lse2) : 0.f;
+            dp[e] = pr * (dp[e] - dl) * p.scale;
+          }
         }
         store_row32(ds_s, row, c, dp);
       }
@@ -829,7 +854,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
     if (ok) {   // warp-uniform: the TMEM loads are warp-collective, only the stores are per row
       __nv_bfloat16* dqrow = p.dq + (long long)b * p.q_sb + (long long)qi * p.q_ss + (long long)h * p.q_sh;
 #pragma unroll
-      for (int c = 0; c < D; c += 32) {
+      for (int cc = 0; cc < D / 2; cc += 32) {
+        const int c = ch * (D / 2) + cc;
         float a[32];
         if (n_it > 0) {
           tmem_ld_x32(tm_dq + lane_off + c, a);
@@ -992,8 +1018,8 @@ extern "C" int e2h_flash_bwd(const void* q, long long q_sb, long long q_ss, long
       if (e != cudaSuccess) return (int)e;                                                       \
       done = true;                                                                               \
     }                                                                                            \
-    flash_bwd_dkdv_kernel<D_><<<gkv, 192, smem_kv, stream>>>(tq, tk, tv, tdo, p);                \
-    flash_bwd_dq_kernel<D_><<<gq, 192, smem_q, stream>>>(tq, tk, tv, tdo, p);                    \
+    flash_bwd_dkdv_kernel<D_><<<gkv, kFwdThreads, smem_kv, stream>>>(tq, tk, tv, tdo, p);                \
+    flash_bwd_dq_kernel<D_><<<gq, kFwdThreads, smem_q, stream>>>(tq, tk, tv, tdo, p);                    \
   }
   if (D == 128) E2H_BWD(128) else E2H_BWD(64)
 #undef E2H_BWD
