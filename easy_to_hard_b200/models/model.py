@@ -293,6 +293,12 @@ class Transformer(nn.Module):
                 left_pad_mask_pos: Optional[Tensor] = None, fully_causal: bool = False,
                 return_hidden: bool = False) -> Tensor:
         assert self.freqs_cis is not None, "call setup_caches first"
+        if fully_causal and idx.is_cuda and not torch.is_grad_enabled():
+            # scoring / log-prob passes: the whole stack on the fused sm_100a kernels
+            from . import fused_block
+            if fused_block.can_fuse(self, idx):
+                x = fused_block.transformer_hidden(self, idx)
+                return x if return_hidden else self.output(x.to(self.output.weight.dtype))
         if input_pos is None:
             input_pos = torch.arange(idx.shape[1], device=idx.device)
         mask = None if fully_causal else self.build_mask(input_pos, left_pad_mask_pos)

@@ -62,6 +62,7 @@ class RewardModel(nn.Module):
             bb.setup_caches(idx.size(0), idx.size(-1), kv_cache=False)
         pos = torch.arange(idx.size(-1), device=idx.device)
         hidden = bb(idx, input_pos=pos, fully_causal=True, return_hidden=True)
+        hidden = hidden.to(bb.output.weight.dtype)
         rewards = self.token_rewards(hidden)
         if eos_pos is not None:
             rewards = batch_select(rewards, eos_pos.unsqueeze(-1)).squeeze(-1)

@@ -33,8 +33,10 @@ def workspace(tmp_path_factory):
     corpus.write_text("\n".join(_sentence(g, 12) for _ in range(400)) +
                       "\n# Question\n\n# Solution\n\n0 1 2 3 4 5 6 7 8 9 + - = .\n")
     spm.SentencePieceTrainer.train(input=str(corpus), model_prefix=str(model_dir / "tokenizer"),
-                                   vocab_size=200, model_type="bpe", bos_id=1, eos_id=2,
-                                   unk_id=0, pad_id=-1, byte_fallback=False,
+                                   vocab_size=400, model_type="bpe", bos_id=1, eos_id=2,
+                                   unk_id=0, pad_id=-1, byte_fallback=True,
+                                   normalization_rule_name="identity",
+                                   remove_extra_whitespaces=False,
                                    character_coverage=1.0, minloglevel=2)
     torch.manual_seed(0)
     m = Transformer.from_name("tiny-llama")
