@@ -138,23 +138,39 @@ def block_backward(dy: torch.Tensor, x: torch.Tensor, w: Dict[str, torch.Tensor]
     return Fn.rmsnorm_bwd(x, d_xn1, w["attention_norm"], shape.eps, dres=dh)
 
 
+def dense_weight(linear) -> torch.Tensor:
+    """The [out, in] weight of a linear module as the GEMM kernels read it. An int8 weight-only
+    module (``weight`` int8 + per-row ``scales``) is dequantised to bf16 on the fly: one extra
+    pass over the weight, which scoring passes over thousands of tokens do not notice."""
+    w = linear.weight
+    if w.dtype == torch.int8 and hasattr(linear, "scales"):
+        return (w.to(torch.bfloat16) * linear.scales.to(torch.bfloat16)[:, None]).contiguous()
+    return w
+
+
 def block_weights(blk) -> Dict[str, torch.Tensor]:
     a, f = blk.attention, blk.feed_forward
-    return dict(wqkv=a.wqkv.weight, wo=a.wo.weight, w1=f.w1.weight, w3=f.w3.weight,
-                w2=f.w2.weight, attention_norm=blk.attention_norm.weight,
-                ffn_norm=blk.ffn_norm.weight)
+    return dict(wqkv=dense_weight(a.wqkv), wo=dense_weight(a.wo), w1=dense_weight(f.w1),
+                w3=dense_weight(f.w3), w2=dense_weight(f.w2),
+                attention_norm=blk.attention_norm.weight, ffn_norm=blk.ffn_norm.weight)
 
 
 def can_fuse(model, idx: torch.Tensor) -> bool:
-    """The cache-less fused forward applies to a bf16 CUDA model with plain (unquantised)
-    linears."""
-    if not idx.is_cuda or not model.layers:
+    """The cache-less fused forward applies to a CUDA model whose norms are bf16 and whose
+    linears are plain bf16 or int8 weight-only modules."""
+    if not idx.is_cuda or not len(model.layers):
         return False
     blk = model.layers[0]
-    ws = block_weights(blk)
-    return all(isinstance(w, torch.Tensor) and w.dtype == torch.bfloat16 and w.dim() >= 1
-               for w in ws.values()) and type(blk.attention.wqkv).__name__ in ("Linear",
-                                                                                "FrozenLinear")
+    if blk.attention_norm.weight.dtype != torch.bfloat16:
+        return False
+    for lin in (blk.attention.wqkv, blk.attention.wo, blk.feed_forward.w1, blk.feed_forward.w3,
+                blk.feed_forward.w2):
+        w = getattr(lin, "weight", None)
+        if not isinstance(w, torch.Tensor) or w.dim() != 2:
+            return False
+        if not (w.dtype == torch.bfloat16 or (w.dtype == torch.int8 and hasattr(lin, "scales"))):
+            return False
+    return True
 
 
 @torch.no_grad()

@@ -284,6 +284,20 @@ class Transformer(nn.Module):
             mask = (mask & pad_ok) | diag
         return mask
 
+    def logprobs_and_entropy(self, inputs: Tensor, shifts, labels: Tensor, tlen: int,
+                             temperature: float, pad: int):
+        """Scoring hook of ``rl_model.AutoregressivePolicy.forward`` for an unsharded model:
+        hidden states of the right-pad-rotated ``inputs`` (fused kernels on CUDA under
+        ``no_grad``), then the LM head + log-softmax of the last ``tlen`` positions without
+        materialising the logits."""
+        from ..parallel.fsdp import lm_logprobs_and_entropy
+        B, L = inputs.shape
+        if self.freqs_cis is None or self.max_seq_length < L or self.max_batch_size < B:
+            self.setup_caches(B, L, kv_cache=self.kv_cache_enabled)
+        hidden = self(inputs, torch.arange(L, device=inputs.device), fully_causal=True,
+                      return_hidden=True)
+        return lm_logprobs_and_entropy(self, hidden, shifts, labels, tlen, temperature, pad)
+
     def embed(self, idx: Tensor) -> Tensor:
         if self.vocab_parallel and self.tp_size > 1:
             return coll.vocab_parallel_embedding(idx, self.tok_embeddings.weight)
@@ -298,7 +312,7 @@ class Transformer(nn.Module):
             from . import fused_block
             if fused_block.can_fuse(self, idx):
                 x = fused_block.transformer_hidden(self, idx)
-                return x if return_hidden else self.output(x.to(self.output.weight.dtype))
+                return x if return_hidden else self.head(x)
         if input_pos is None:
             input_pos = torch.arange(idx.shape[1], device=idx.device)
         mask = None if fully_causal else self.build_mask(input_pos, left_pad_mask_pos)
@@ -318,4 +332,16 @@ class Transformer(nn.Module):
             x = coll.gather_from_sequence_parallel(x, tensor_parallel_output_grad=False)
         if return_hidden:
             return x
-        return self.output(x)
+        return self.head(x)
+
+    def head(self, x: Tensor) -> Tensor:
+        """The output projection: LM head, or a reward / value head that may be sharded over its
+        input dimension (``models.tp.apply_reward_head_tp``)."""
+        out = self.output
+        if getattr(out, "tp_row_parallel", False):
+            from .tp import reward_head_forward
+            return reward_head_forward(out, x.to(out.weight.dtype))
+        w = getattr(out, "weight", None)
+        if isinstance(w, Tensor) and w.is_floating_point() and x.dtype != w.dtype:
+            x = x.to(w.dtype)
+        return out(x)

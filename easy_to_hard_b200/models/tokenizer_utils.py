@@ -191,7 +191,12 @@ class AcceleraTokenizer:
         if self.unk_id != self.pad_id:
             names[self.unk_id] = self.unk_token
         pieces, run = [], []
+        n_pieces = self.sp_model.get_piece_size()
         for tok in tokens:
+            if tok >= n_pieces or tok < 0:
+                # the model's vocabulary may be padded beyond the tokenizer's (Llemma: 32016
+                # rows for 32000 pieces); such ids decode to nothing instead of raising
+                continue
             if tok in names:
                 if not skip_special_tokens:
                     pieces.append(self.sp_model.decode(run) + names[tok])

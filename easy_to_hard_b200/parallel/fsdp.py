@@ -163,6 +163,8 @@ class _BlockFn(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, sdp, idx, B, S):
         ctx.sdp, ctx.idx, ctx.BS = sdp, idx, (B, S)
+        # position tables of this forward call (several calls may precede one backward)
+        ctx.tables = (sdp._input_pos, sdp._freqs_pos, sdp._freqs, sdp._pos)
         ctx.save_for_backward(x)
         with torch.no_grad():
             return sdp._run_block(idx, x, B, S)
@@ -170,6 +172,8 @@ class _BlockFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         (x,) = ctx.saved_tensors
+        sdp = ctx.sdp
+        sdp._input_pos, sdp._freqs_pos, sdp._freqs, sdp._pos = ctx.tables
         dx = ctx.sdp._backward_block(ctx.idx, x, dy.contiguous(), *ctx.BS)
         return dx, None, None, None, None
 
@@ -355,7 +359,11 @@ class ShardedDataParallel(nn.Module):
             if eos_pos is not None:
                 rewards = torch.gather(rewards, 1, eos_pos.unsqueeze(-1).long()).squeeze(-1)
             return rewards
-        return torch.nn.functional.linear(hidden, self.backbone.output.weight.to(hidden.dtype))
+        head = self.backbone.output
+        if getattr(head, "tp_row_parallel", False):      # value head sharded over its input dim
+            from ..models.tp import reward_head_forward
+            return reward_head_forward(head, hidden.to(head.weight.dtype))
+        return torch.nn.functional.linear(hidden, head.weight.to(hidden.dtype))
 
     def token_logprobs(self, idx: torch.Tensor, labels: torch.Tensor, ignore_index: int = -100,
                        temperature: float = 1.0):
@@ -367,6 +375,15 @@ class ShardedDataParallel(nn.Module):
         lp, ent = loss.linear_logprobs(hidden.reshape(B * S, dim).to(w.dtype), w,
                                        labels.reshape(-1), ignore_index, temperature)
         return lp.view(B, S), ent.view(B, S)
+
+    def logprobs_and_entropy(self, inputs: torch.Tensor, shifts, labels: torch.Tensor, tlen: int,
+                             temperature: float, pad: int):
+        """Log-probs and entropies of the last ``tlen`` positions of right-pad-rotated sequences
+        (the hook ``models.rl_model.AutoregressivePolicy.forward`` looks for): hidden states are
+        rotated back, positions ``[-tlen-1, -1)`` scored against ``labels`` through the fused
+        LM-head loss. Differentiable w.r.t. the sharded parameters."""
+        return lm_logprobs_and_entropy(self.backbone, self.hidden_states(inputs), shifts, labels,
+                                       tlen, temperature, pad)
 
     def zero_grad(self, set_to_none: bool = True) -> None:
         for u in self._all_units():
@@ -462,6 +479,27 @@ class ShardedDataParallel(nn.Module):
             for k, v in saved.items():
                 if k != "params":
                     g[k] = v
+
+
+def lm_logprobs_and_entropy(backbone, hidden: torch.Tensor, shifts, labels: torch.Tensor,
+                            tlen: int, temperature: float, pad: int):
+    """hidden [B, L, dim] of right-pad-rotated sequences -> (logprobs, entropies) [B, tlen] of
+    ``labels`` (0 where ``labels == pad``) at original positions ``[-tlen-1, -1)``."""
+    from ..models.rl_model import restore_from_right_pad_sequences
+    from ..ops import loss
+    hidden = restore_from_right_pad_sequences(hidden, shifts)[:, -tlen - 1: -1]
+    B = hidden.shape[0]
+    from ..models.fused_block import dense_weight
+    w = dense_weight(backbone.output)
+    if w.dtype == torch.int8:            # CPU int8 module: dequantise in the activation dtype
+        w = w.to(hidden.dtype) * backbone.output.scales.to(hidden.dtype)[:, None]
+    kw = {}
+    if backbone.vocab_parallel and backbone.tp_size > 1:
+        kw = dict(vocab_start=groups.get_model_parallel_rank() * w.shape[0],
+                  group=groups.get_model_parallel_group(), world=backbone.tp_size)
+    lp, ent = loss.linear_logprobs(hidden.reshape(B * tlen, -1).to(w.dtype).contiguous(), w,
+                                   labels.reshape(-1), pad, temperature, **kw)
+    return lp.view(B, tlen), ent.view(B, tlen)
 
 
 class _RMSNormFn(torch.autograd.Function):

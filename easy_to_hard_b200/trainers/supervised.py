@@ -49,6 +49,9 @@ class Task:
     metric_keys: Sequence[str] = field(default_factory=tuple)
     init_from_resume: bool = False  # skip the warm-start checkpoint when resuming (RM trainers)
     print_keys: Sequence[str] = ("input_ids",)
+    # (args, checkpoint_path, init_path, device, use_tp) -> loss_fn, for losses that need more
+    # state than the trained model (DPO's frozen reference policy)
+    make_loss: Optional[Callable] = None
 
 
 def _log(rank0: bool, *a):
@@ -147,7 +150,9 @@ def run(args, task: Task) -> Dict:
     # after pooling, a tensor-parallel group holds the concatenation of its ranks' batches
     micro_global = micro * groups.get_model_parallel_world_size()
 
-    stepper = TrainStepper(model, optimizer, scheduler, task.loss_fn, task.max_grad_norm)
+    loss_fn = (task.make_loss(args, checkpoint_path, init_path, device, use_tp)
+               if task.make_loss is not None else task.loss_fn)
+    stepper = TrainStepper(model, optimizer, scheduler, loss_fn, task.max_grad_norm)
     monitor = HealthMonitor(dist.get_rank(), world).start() if use_tp else None
     epoch_length = len(loader)
     record: Dict = {}

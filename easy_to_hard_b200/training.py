@@ -227,3 +227,63 @@ def pairwise_reward_loss(model, input_ids: torch.Tensor, choice: torch.Tensor):
     logits = (rewards[:, 0] - rewards[:, 1]).float()
     loss = F.binary_cross_entropy_with_logits(logits.view(-1), choice.float().view(-1))
     return loss, reward_modeling_metrics(logits.detach().view(-1), choice.view(-1))
+
+
+# ----------------------------------------------------------------------------- DPO
+
+def sequence_logprobs(model, input_ids: torch.Tensor, labels: torch.Tensor):
+    """Sum over the non-ignored positions of log p(labels[:, t+1] | input_ids[:, :t+1]) and the
+    number of such positions, per sequence. Works for a sharded (trainable) policy and for a
+    plain frozen ``Transformer``; on CUDA neither materialises the logits."""
+    B, S = input_ids.shape
+    tgt = torch.full_like(labels, IGNORE_INDEX)
+    tgt[:, :-1] = labels[:, 1:]
+    backbone = getattr(model, "backbone", model)
+    if isinstance(model, ShardedDataParallel):
+        hidden = model.hidden_states(input_ids)
+    else:
+        model.setup_caches(max_batch_size=B, max_seq_length=S, kv_cache=False)
+        hidden = model(input_ids, torch.arange(S, device=input_ids.device), fully_causal=True,
+                       return_hidden=True)
+    w = backbone.output.weight
+    vp = backbone.vocab_parallel and backbone.tp_size > 1
+    kw = {}
+    if vp:
+        kw = dict(vocab_start=groups.get_model_parallel_rank() * w.shape[0],
+                  group=groups.get_model_parallel_group(), world=backbone.tp_size)
+    lp, _ = loss_ops.linear_logprobs(hidden.reshape(B * S, -1).to(w.dtype), w, tgt.reshape(-1),
+                                     IGNORE_INDEX, **kw)
+    count = (tgt != IGNORE_INDEX).float().sum(dim=-1)
+    return lp.view(B, S).sum(dim=-1), count
+
+
+def dpo_loss(model, ref_model, input_ids_w, labels_w, input_ids_l, labels_l, win_rate_w,
+             win_rate_l, beta: float = 0.1, label_smoothing: float = 0.0, variant: str = "dpo"):
+    """DPO and its variants (train_rl_dpo.py:77-196 of the reference): ``dpo`` (with optional
+    conservative label smoothing), ``ipo``, ``rpo``; ``average`` in the variant name divides the
+    sequence log-probs by their token counts. Returns (loss, metrics)."""
+    with torch.no_grad():
+        ref_w, n_w = sequence_logprobs(ref_model, input_ids_w, labels_w)
+        ref_l, n_l = sequence_logprobs(ref_model, input_ids_l, labels_l)
+    lp_w, _ = sequence_logprobs(model, input_ids_w, labels_w)
+    lp_l, _ = sequence_logprobs(model, input_ids_l, labels_l)
+    if "average" in variant:
+        ref_w, ref_l = ref_w / (n_w + 1e-8), ref_l / (n_l + 1e-8)
+        lp_w, lp_l = lp_w / (n_w + 1e-8), lp_l / (n_l + 1e-8)
+    logits_1, logits_2 = lp_w - ref_w, lp_l - ref_l
+    logits = logits_1 - logits_2
+    win_rate_w, win_rate_l = win_rate_w.view(lp_w.shape).float(), win_rate_l.view(lp_l.shape).float()
+    if "ipo" in variant:
+        loss = (logits - 1.0 / (2 * beta)).pow(2).mean()
+    elif "rpo" in variant:
+        loss = ((logits_1 - (1.0 / beta) * (win_rate_w - 0.5)).pow(2).mean()
+                + (logits_2 - (1.0 / beta) * (win_rate_l - 0.5)).pow(2).mean()) / 2.0
+    elif label_smoothing == 0.0:
+        loss = -F.logsigmoid(beta * logits).mean()
+    else:
+        loss = (-F.logsigmoid(beta * logits).mean() * (1 - label_smoothing)
+                - F.logsigmoid(-beta * logits).mean() * label_smoothing)
+    metrics = {"accuracy": (logits > 0.0).float().mean().detach(),
+               "accuracy_policy": (lp_w > lp_l).float().mean().detach(),
+               "accuracy_reference": (ref_w > ref_l).float().mean().detach()}
+    return loss, metrics

@@ -105,3 +105,15 @@ def test_train_rm_pairwise_end_to_end(workspace, tmp_path):
     rec = train_rm_pairwise.main(_args(workspace, save, dataset=str(workspace / "pairs.json")))
     assert 0.3 < rec["loss"] < 1.5 and 0.0 <= rec["accuracy"] <= 1.0
     assert (save / "epoch_1_step_2_rank_0.pt").exists()
+
+
+@pytest.mark.parametrize("variant", ["dpo", "ipo", "rpo_average"])
+def test_train_rl_dpo_end_to_end(workspace, tmp_path, variant):
+    import train_rl_dpo
+    save = tmp_path / "dpo"
+    rec = train_rl_dpo.main(_args(workspace, save, dataset=str(workspace / "pairs.json"),
+                                  dpo_variant=variant, dpo_beta=0.1))
+    assert rec["loss"] >= 0 and 0.0 <= rec["accuracy"] <= 1.0
+    if variant == "dpo":       # policy == reference at the start: loss starts at ln 2
+        assert abs(rec["loss"] - 0.693) < 0.1
+    assert (save / "epoch_1_step_2_rank_0.pt").exists()
