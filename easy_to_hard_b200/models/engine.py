@@ -89,18 +89,50 @@ class DecodeEngine:
         self.ticket = torch.zeros(1, dtype=torch.int32, device=dev)
         self._graphs = {}
         self.launches_per_step = 0
+        self.W = [self._layer_weights(blk) for blk in model.layers]
+
+    # ------------------------------------------------------------------ weights
+    @staticmethod
+    def _dense(linear):
+        """(bf16 [out, in] weight, per-output-feature fp32 scale or None) as the GEMM kernels
+        read them. bf16 modules hand out their own tensor (in-place updates of the model, e.g.
+        the PPO rollout sync, are seen by captured graphs). Weight-only int8 becomes the exact
+        bf16 image of the integers plus its scales, applied in the GEMM epilogue exactly where
+        the reference multiplies (models/quantize.py:397-398); int4-g128 (tinygemm packing) is
+        unpacked and dequantised once."""
+        w = linear.weight
+        if w.dtype == torch.int8 and hasattr(linear, "scales"):
+            return w.to(torch.bfloat16).contiguous(), linear.scales.float().contiguous()
+        if w.dtype == torch.int32 and hasattr(linear, "scales_and_zeros"):
+            from . import quantize as qz
+            q = qz.unpack_int4_tinygemm(w, linear.inner_k_tiles)
+            full = qz.group_dequantize_tensor(q, linear.scales_and_zeros, 4, linear.groupsize)
+            k = getattr(linear, "origin_in_features", full.shape[1])
+            return full[:, :k].to(torch.bfloat16).contiguous(), None
+        assert w.dtype == torch.bfloat16, f"unsupported weight dtype {w.dtype}"
+        return w, None
+
+    def _layer_weights(self, blk):
+        a, f = blk.attention, blk.feed_forward
+        out = {n: self._dense(m) for n, m in (("wqkv", a.wqkv), ("wo", a.wo), ("w1", f.w1),
+                                              ("w3", f.w3), ("w2", f.w2))}
+        s1, s3 = out["w1"][1], out["w3"][1]
+        out["s13"] = None if s1 is None else torch.cat([s1, s3]).contiguous()
+        return out
 
     # ------------------------------------------------------------------ layer pieces
-    def _row_parallel(self, x, w, h, next_norm_w, h_out, x_out):
-        """h_out = h + x @ w^T (summed over TP ranks); x_out = rmsnorm(h_out) * next_norm_w."""
+    def _row_parallel(self, x, ws, h, next_norm_w, h_out, x_out):
+        """h_out = h + x @ w^T (summed over TP ranks); x_out = rmsnorm(h_out) * next_norm_w.
+        ``ws`` = (weight, per-feature scale or None)."""
+        w, sc = ws
         if self.reduce == "local":
-            gemm.linear_residual(x, w, h, out=h_out)
+            gemm.linear_residual(x, w, h, out=h_out, scale=sc)
             Fn.fused_residual_rmsnorm(h_out, next_norm_w, self.eps, x_out=x_out)
             self._count(2)
         elif self.reduce == "nccl":
             part = self.partial[:, : x.shape[0]] if x.shape[0] <= self.B else \
                 torch.empty(1, x.shape[0], self.dim, dtype=torch.float32, device=self.dev)
-            gemm.linear(x, w, out=part[0])
+            gemm.linear(x, w, out=part[0], scale=sc)
             dist.all_reduce(part, group=groups.get_model_parallel_group())
             Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                       x_out=x_out)
@@ -109,7 +141,7 @@ class DecodeEngine:
             T = x.shape[0]
             if T > self.rp.T:  # prefill-sized inputs take the NCCL route
                 part = torch.empty(1, T, self.dim, dtype=torch.float32, device=self.dev)
-                gemm.linear(x, w, out=part[0])
+                gemm.linear(x, w, out=part[0], scale=sc)
                 dist.all_reduce(part, group=groups.get_model_parallel_group())
                 Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                           x_out=x_out)
@@ -117,7 +149,7 @@ class DecodeEngine:
                 rp = self.rp
                 s = rp.slot()
                 gemm.linear(x, w, out=rp.partial_out(s, T), signal=rp.signal_ptrs(s),
-                            ticket=rp.gemm_ticket[s:s + 1])
+                            ticket=rp.gemm_ticket[s:s + 1], scale=sc)
                 Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=rp.partial_ptrs(s),
                                           h_out=h_out, x_out=x_out, flags=rp.flags(s),
                                           use_count=rp.use_count[s:s + 1],
@@ -132,22 +164,23 @@ class DecodeEngine:
     def _layers(self, T: int, sq: int, h, xn, q, att, act, prefill_B: int = 0):
         m = self.model
         for li, blk in enumerate(m.layers):
-            a, f = blk.attention, blk.feed_forward
-            gemm.linear_qkv_rope(xn, a.wqkv.weight, q, freqs=self.freqs, pos_base=self.pos,
+            W = self.W[li]
+            gemm.linear_qkv_rope(xn, W["wqkv"][0], q, freqs=self.freqs, pos_base=self.pos,
                                  sq=sq, n_head=self.n_head, n_kv=self.n_kv, head_dim=self.D,
-                                 kcache=self.kcache[li], vcache=self.vcache[li])
+                                 kcache=self.kcache[li], vcache=self.vcache[li],
+                                 scale=W["wqkv"][1])
             if sq == 1:
                 Fn.attn_decode(q, self.kcache[li], self.vcache[li], self.pos, self.left_pad,
                                self.n_head, out=att, n_split=1 if T * self.n_kv >= 256 else 0)
             else:
                 self._prefill_attention(li, q, att, prefill_B, sq)
             self._count(2)
-            self._row_parallel(att, a.wo.weight, h, blk.ffn_norm.weight, h, xn)
-            gemm.linear_swiglu(xn, f.w1.weight, f.w3.weight, out=act)
+            self._row_parallel(att, W["wo"], h, blk.ffn_norm.weight, h, xn)
+            gemm.linear_swiglu(xn, W["w1"][0], W["w3"][0], out=act, scale=W["s13"])
             self._count(1)
             nxt = (m.layers[li + 1].attention_norm.weight if li + 1 < len(m.layers)
                    else m.norm.weight)
-            self._row_parallel(act, f.w2.weight, h, nxt, h, xn)
+            self._row_parallel(act, W["w2"], h, nxt, h, xn)
 
     def _prefill_attention(self, li, q, att, B, S):
         from ..ops import attention as attn_ops

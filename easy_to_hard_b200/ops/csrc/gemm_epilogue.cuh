@@ -22,6 +22,11 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
     const float s = f_ok ? p.scale[f] : 0.f;
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] *= s;
+    if constexpr (DUAL) {   // second weight matrix: its per-feature scales follow the first F
+      const float s2 = f_ok ? p.scale[p.F + f] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v2[j] *= s2;
+    }
   }
   switch (p.epi) {
     case E2H_EPI_STORE_BF16: {

@@ -288,6 +288,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             ok = mbar_wait(smem_u32(&ctrl->res_full[b]), (cc >> 1) & 1, abort_flag, p.status,
                            kStatusTimeoutFull);
           const float sc = (p.scale != nullptr && f < p.F) ? p.scale[f] : 1.f;
+          const float sc2 = (DUAL && p.scale != nullptr && f < p.F) ? p.scale[p.F + f] : 1.f;
           __nv_bfloat16* so = reinterpret_cast<__nv_bfloat16*>(stage_out + b * kChunkBytes);
           if (staged == 2) {
             // feature-major output (weight gradients): this lane's 32 values are one 64-byte
@@ -320,7 +321,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           for (int j = 0; j < kChunkTok; ++j) {
             float y;
             if constexpr (DUAL) {
-              const float g = bf16_round(v[j]), u = bf16_round(v2[j]);
+              const float g = bf16_round(v[j] * sc), u = bf16_round(v2[j] * sc2);
               y = bf16_round(silu(g)) * u;
             } else {
               y = v[j] * sc;
