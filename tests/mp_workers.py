@@ -27,12 +27,23 @@ def _entry(rank, world, port, fn, out, kwargs):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank),
                       LOCAL_RANK=str(rank), WORLD_SIZE=str(world))
     torch.set_num_threads(1)
+    backend = kwargs.pop("backend", "gloo")
     try:
+        if backend == "nccl":
+            torch.cuda.set_device(rank)
         if world > 1:
-            dist.init_process_group("gloo", rank=rank, world_size=world,
-                                    timeout=datetime.timedelta(seconds=kwargs.pop("pg_timeout", 120)))
+            extra = {"device_id": torch.device("cuda", rank)} if backend == "nccl" else {}
+            dist.init_process_group(backend, rank=rank, world_size=world,
+                                    timeout=datetime.timedelta(seconds=kwargs.pop("pg_timeout", 120)),
+                                    **extra)
         res = fn(rank, world, **kwargs)
         torch.save(res, os.path.join(out, f"rank{rank}.pt"))
+        if backend == "nccl" and world > 1:
+            # communicators referenced by captured CUDA graphs can block in their destructor:
+            # synchronise, then leave the child without tearing NCCL down
+            torch.cuda.synchronize()
+            dist.barrier()
+            os._exit(0)
     except Exception:  # noqa: BLE001 -- the parent only sees files
         with open(os.path.join(out, f"rank{rank}.err"), "w") as f:
             f.write(traceback.format_exc())
@@ -91,7 +102,7 @@ def _merged_state(sdp):
 
 
 def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_parallel=False,
-                          steps=1, micro=None, gen=True):
+                          steps=1, micro=None, gen=True, device="cpu"):
     """One (or more) SFT steps on the tiny model with TP=tp, DP=world/tp, then greedy decode."""
     from easy_to_hard_b200.models import tp as tpm
     from easy_to_hard_b200.parallel import groups
@@ -102,7 +113,8 @@ def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_para
     from easy_to_hard_b200.utils.checkpoint_utils import merge_tp_checkpoint
 
     tpm.initialize_model_parallel(tp)
-    model = tiny_model(vocab_parallel=vocab_parallel)
+    device = torch.device(device if device == "cpu" else f"cuda:{rank}")
+    model = tiny_model(vocab_parallel=vocab_parallel).to(device)
     heads = (model.config.n_head, model.config.n_local_heads)
     if tp > 1:
         tpm.apply_tp(model, requires_grad=True, sequence_parallel=sequence_parallel)
@@ -111,9 +123,9 @@ def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_para
     sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group())
     sdp.train()
     opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=1e-4, weight_decay=0.0,
-                               optim_dtype=torch.float32, optim_device=torch.device("cpu"))
+                               optim_dtype=torch.float32, optim_device=device)
     stepper = SFTStepper(sdp, opt)
-    ids, labels = sft_batch()
+    ids, labels = (t.to(device) for t in sft_batch())
     dp, dp_rank = groups.get_data_parallel_world_size(), groups.get_data_parallel_rank()
     per = ids.shape[0] // dp                       # every data-parallel rank takes its rows
     my_ids, my_lab = ids[dp_rank * per:(dp_rank + 1) * per], labels[dp_rank * per:(dp_rank + 1) * per]
@@ -127,7 +139,7 @@ def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_para
         losses.append(float(l))
         norms.append(float(gn))
     state = _merged_state(sdp)
-    state = {k: v for k, v in state.items() if "layers" in k and k.endswith("weight")
+    state = {k: v.cpu() for k, v in state.items() if "layers" in k and k.endswith("weight")
              and "norm" not in k}
     if tp > 1:   # gather the tensor-parallel shards and merge them to the TP=1 layout
         shards = [None] * tp
@@ -137,14 +149,14 @@ def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_para
     if gen:
         # decode with the updated weights through the plain module path
         for u in sdp.units:
-            u.gather_into(torch.empty(u.padded, dtype=u.shard.dtype))
+            u.gather_into(torch.empty(u.padded, dtype=u.shard_lp.dtype, device=device))
         model.eval()
         g = torch.Generator().manual_seed(11)
-        prompts = torch.randint(0, 1024, (4, 32), generator=g)
+        prompts = torch.randint(0, 1024, (4, 32), generator=g).to(device)
         with torch.no_grad():
             seq = generate_tokens(model, prompts, None, 16, temperature=0.0, top_k=None,
                                   eos_id=None)
-        out["tokens"] = seq
+        out["tokens"] = seq.cpu()
     return out
 
 
