@@ -209,6 +209,8 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
 
 }  // namespace e2h
 
+#include "elementwise_vec.cuh"
+
 using namespace e2h;
 
 extern "C" {
@@ -219,6 +221,21 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
                     int* use_count, unsigned int* ticket, int* status, void* stream) {
   if (dim % 2 || n_part > 8) return -1;
   if (flags != nullptr && (use_count == nullptr || ticket == nullptr)) return -2;
+  // plain row normalisation of many tokens: the vectorised streaming kernel
+  if (T >= 256 && h_in != nullptr && tokens == nullptr && n_part == 0 && h_out == nullptr &&
+      x_out != nullptr && flags == nullptr && dim % 8 == 0 && dim <= 8192 && aligned16(h_in) &&
+      aligned16(x_out) && aligned16(weight)) {
+    const int threads = dim > 4096 ? 256 : 128;
+    const int nv = (dim / 8 + threads - 1) / threads;
+    cudaStream_t st = (cudaStream_t)stream;
+#define E2H_GO(NV)                                                                            \
+  rmsnorm_rows_kernel<NV><<<T, threads, 0, st>>>((const __nv_bfloat16*)h_in,                  \
+                                                 (const __nv_bfloat16*)weight,                \
+                                                 (__nv_bfloat16*)x_out, rstd_out, dim, eps)
+    if (nv <= 1) E2H_GO(1); else if (nv == 2) E2H_GO(2); else if (nv <= 4) E2H_GO(4);
+#undef E2H_GO
+    if (nv <= 4) return (int)cudaGetLastError();
+  }
   PartPtrs parts;
   for (int i = 0; i < 8; ++i)
     parts.p[i] = i < n_part ? static_cast<const float*>(part_ptrs[i]) : nullptr;
@@ -232,6 +249,19 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
 
 int e2h_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const void* dres, void* dx,
                     int T, int dim, float eps, void* stream) {
+  if (dim % 8 == 0 && dim <= 8192 && aligned16(x) && aligned16(dy) && aligned16(dx) &&
+      aligned16(weight) && (dres == nullptr || aligned16(dres))) {
+    const int threads = dim > 4096 ? 256 : 128;
+    const int nv = (dim / 8 + threads - 1) / threads;
+    cudaStream_t st = (cudaStream_t)stream;
+#define E2H_GO(NV)                                                                           \
+  rmsnorm_bwd_rows_kernel<NV><<<T, threads, 0, st>>>(                                        \
+      (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (const __nv_bfloat16*)weight,       \
+      (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, dim, eps)
+    if (nv <= 1) E2H_GO(1); else if (nv == 2) E2H_GO(2); else if (nv <= 4) E2H_GO(4);
+#undef E2H_GO
+    if (nv <= 4) return (int)cudaGetLastError();
+  }
   const int threads = dim >= 2048 ? 512 : 128;
   const size_t smem = (2 * dim + 32) * sizeof(float);
   rmsnorm_bwd_kernel<<<T, threads, smem, (cudaStream_t)stream>>>(
@@ -249,6 +279,14 @@ int e2h_embedding(const int* tokens, const void* table, void* out, int T, int di
 
 int e2h_swiglu_fwd(const void* g, const void* u, void* out, long long n, void* stream) {
   if (n % 2) return -1;
+  if (n % 8 == 0 && aligned16(g) && aligned16(u) && aligned16(out)) {
+    const long long nvec = n / 8;
+    long long vb = (nvec + 255) / 256;
+    if (vb > 148 * 16) vb = 148 * 16;
+    swiglu_fwd_vec_kernel<<<(unsigned)vb, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)out, nvec);
+    return (int)cudaGetLastError();
+  }
   const long long blocks = (n / 2 + 255) / 256;
   swiglu_fwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (__nv_bfloat16*)out, n);
@@ -257,6 +295,16 @@ int e2h_swiglu_fwd(const void* g, const void* u, void* out, long long n, void* s
 
 int e2h_swiglu_bwd(const void* g, const void* u, const void* dact, void* dg, void* du, long long n,
                    void* stream) {
+  if (n % 8 == 0 && aligned16(g) && aligned16(u) && aligned16(dact) && aligned16(dg) &&
+      aligned16(du)) {
+    const long long nvec = n / 8;
+    long long vb = (nvec + 255) / 256;
+    if (vb > 148 * 16) vb = 148 * 16;
+    swiglu_bwd_vec_kernel<<<(unsigned)vb, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (const __nv_bfloat16*)dact,
+        (__nv_bfloat16*)dg, (__nv_bfloat16*)du, nvec);
+    return (int)cudaGetLastError();
+  }
   const long long blocks = (n + 255) / 256;
   swiglu_bwd_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
       (const __nv_bfloat16*)g, (const __nv_bfloat16*)u, (const __nv_bfloat16*)dact,
@@ -266,6 +314,12 @@ int e2h_swiglu_bwd(const void* g, const void* u, const void* dact, void* dg, voi
 
 int e2h_rope(const void* x, void* out, const void* freqs, const int* pos, int T, int n_heads,
              int head_dim, long long ld, int inverse, void* stream) {
+  if (head_dim % 8 == 0 && ld % 8 == 0 && aligned16(x) && aligned16(out) && aligned16(freqs)) {
+    rope_vec_kernel<<<T, 256, 0, (cudaStream_t)stream>>>(
+        (const __nv_bfloat16*)x, (__nv_bfloat16*)out, (const __nv_bfloat16*)freqs, pos, n_heads,
+        head_dim, ld, inverse);
+    return (int)cudaGetLastError();
+  }
   rope_kernel<<<T, 128, 0, (cudaStream_t)stream>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out,
                                                    (const __nv_bfloat16*)freqs, pos, n_heads,
                                                    head_dim, ld, inverse);
