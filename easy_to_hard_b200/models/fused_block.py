@@ -57,6 +57,60 @@ def _sp_reduce_scatter(t: torch.Tensor, shape: BlockShape) -> torch.Tensor:
     return out
 
 
+_ROW_REDUCE: Dict[tuple, object] = {}
+_P2P_REDUCE = {"enabled": None}
+
+
+def p2p_reduce_enabled() -> bool:
+    """The fused row-parallel GEMM -> all-reduce -> residual (+ RMSNorm) over peer memory is used
+    when symmetric memory is available; ``E2H_TP_REDUCE=nccl`` forces the NCCL all-reduce."""
+    if _P2P_REDUCE["enabled"] is None:
+        import os
+        ok = os.environ.get("E2H_TP_REDUCE", "p2p") != "nccl"
+        if ok:
+            try:
+                import torch.distributed._symmetric_memory  # noqa: F401
+            except Exception:  # noqa: BLE001
+                ok = False
+        _P2P_REDUCE["enabled"] = ok
+    return _P2P_REDUCE["enabled"]
+
+
+def _row_reduce(T: int, dim: int):
+    """Symmetric partial-sum buffers for T tokens (two alternating slots), one set per shape.
+    Every rank of the tensor-parallel group creates it at the same point of its first forward."""
+    key = (T, dim)
+    rp = _ROW_REDUCE.get(key)
+    if rp is None:
+        from ..ops import _lib
+        from ..parallel.symm import RowParallelReduce
+        rp = RowParallelReduce(T, dim, groups.get_model_parallel_group(), dtype=torch.bfloat16)
+        # training ranks drift apart (data loading, first-use initialisation): wait up to 2 min
+        _lib.check(_lib.lib().e2h_set_flag_wait_ms(120000), "set_flag_wait_ms")
+        _ROW_REDUCE[key] = rp
+    return rp
+
+
+def _row_parallel_fused(x_in: torch.Tensor, w: torch.Tensor, residual: torch.Tensor,
+                        norm_w: Optional[torch.Tensor], eps: float):
+    """residual + sum over ranks of (x_in @ w^T), and optionally its RMSNorm, without NCCL: the
+    GEMM writes this rank's fp32 partial into symmetric memory and raises a flag on every peer
+    when its grid has finished; the consumer kernel waits (bounded) for all flags and sums the
+    partials straight out of the peers' memory. The partials are bf16 (the GEMM's TMA-store
+    epilogue writes them), summed in fp32."""
+    T, dim = residual.shape
+    rp = _row_reduce(T, dim)
+    s = rp.slot()
+    gemm.linear(x_in, w, out=rp.partial_out(s, T), signal=rp.signal_ptrs(s),
+                ticket=rp.gemm_ticket[s:s + 1])
+    h = torch.empty_like(residual)
+    xn = torch.empty_like(residual) if norm_w is not None else None
+    Fn.reduce_residual_norm_bf16(residual, norm_w, eps, partials=rp.partial_ptrs(s), h_out=h,
+                                 x_out=xn, flags=rp.flags(s), use_count=rp.use_count[s:s + 1],
+                                 ticket=rp.norm_ticket[s:s + 1])
+    return h, xn
+
+
 def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tensor,
                   pos: torch.Tensor, shape: BlockShape, keep: bool = False):
     """x [T, dim] (T = B*S, or B*S/tp rows under sequence parallelism). ``w`` holds bf16
@@ -74,18 +128,24 @@ def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tens
     v = qkv[:, (H + Hkv) * D:].view(shape.B, shape.S, Hkv, D)
     o, lse = flash.flash_fwd(q, k, v, None, return_lse=True)
     o2 = o.view(T, H * D)
+    fused_reduce = shape.tp > 1 and not sp and p2p_reduce_enabled()
     if shape.tp == 1:
         h = gemm.linear_residual(o2, w["wo"], x)
+        xn2 = Fn.rmsnorm(h, w["ffn_norm"], shape.eps)
+    elif fused_reduce:
+        h, xn2 = _row_parallel_fused(o2, w["wo"], x, w["ffn_norm"], shape.eps)
     else:
         part = gemm.linear(o2, w["wo"])
         part = _sp_reduce_scatter(part, shape) if sp else _tp_all_reduce(part, shape)
         h = part.add_(x)
-    xn2 = Fn.rmsnorm(h, w["ffn_norm"], shape.eps)
+        xn2 = Fn.rmsnorm(h, w["ffn_norm"], shape.eps)
     xn2f = _sp_gather(xn2, shape) if sp else xn2
     g, u = gemm.linear_dual(xn2f, w["w1"], w["w3"])
     act = Fn.swiglu(g, u)
     if shape.tp == 1:
         out = gemm.linear_residual(act, w["w2"], h)
+    elif fused_reduce:
+        out, _ = _row_parallel_fused(act, w["w2"], h, None, shape.eps)
     else:
         part = gemm.linear(act, w["w2"])
         part = _sp_reduce_scatter(part, shape) if sp else _tp_all_reduce(part, shape)

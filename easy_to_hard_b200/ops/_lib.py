@@ -62,6 +62,8 @@ _SIGNATURES = {
     "e2h_gemm_persistent": [C.POINTER(GemmParams), _vp],
     "e2h_rmsnorm_fwd": [_vp, _vp, _vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
                         _vp, _vp, _vp, _vp, _vp],
+    "e2h_reduce_residual_norm_bf16": [_vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _i, _i, _f,
+                                      _vp, _vp, _vp, _vp, _vp],
     "e2h_rmsnorm_bwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
     "e2h_embedding": [_vp, _vp, _vp, _i, _i, _vp],
     "e2h_swiglu_fwd": [_vp, _vp, _vp, _ll, _vp],
@@ -75,6 +77,7 @@ _SIGNATURES = {
     "e2h_flash_fwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _vp,
                       _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
     "e2h_set_pdl": [_i],
+    "e2h_set_flag_wait_ms": [_i],
     "e2h_flash_bwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll,
                       _ll, _ll, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _f, _vp,
                       _vp],

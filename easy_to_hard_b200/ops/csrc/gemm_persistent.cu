@@ -357,7 +357,16 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
-    if (staged && et == 0) bulk_wait_group_read<0>();   // smem stays valid until the stores read it
+    if (staged && et == 0) {
+      if (p.n_signal > 0) {
+        // a completion signal follows: the TMA stores must have been written to global memory,
+        // not merely have read their shared-memory source, before peers are told to read
+        asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+        asm volatile("fence.proxy.async;" ::: "memory");
+      } else {
+        bulk_wait_group_read<0>();   // smem stays valid until the stores have read it
+      }
+    }
   }
 
   if (p.n_signal > 0) __threadfence();

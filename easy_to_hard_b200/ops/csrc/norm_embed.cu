@@ -41,6 +41,11 @@ struct PartPtrs {
 //               partial for this use is complete. The kernel waits (bounded) for
 //               flags[i] >= *use_count + 1; the last CTA to finish bumps *use_count, so the
 //               protocol needs no host-side epoch and replays inside a CUDA graph.
+// Limit of the cross-rank flag wait, in SM cycles. The default (about a second) suits the decode
+// loop, where the ranks run in lock step; training raises it (e2h_set_flag_wait_ms) because ranks
+// may drift apart by data loading or first-use initialisation.
+__device__ long long g_flag_wait_cycles = kWaitLimitCycles;
+
 __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
                                    const int* __restrict__ tokens,
                                    const __nv_bfloat16* __restrict__ emb,
@@ -59,7 +64,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
       tokens ? emb + (long long)tokens[t] * dim : (h_in ? h_in + (long long)t * dim : nullptr);
   if (flags != nullptr) {
     const int want = *use_count + 1;
-    if (threadIdx.x < n_part) wait_flag_ge(flags + threadIdx.x, want, status);
+    if (threadIdx.x < n_part)
+      wait_flag_ge(flags + threadIdx.x, want, status, g_flag_wait_cycles);
     __syncthreads();
   }
   float ss = 0.f;
@@ -211,7 +217,143 @@ __global__ void rope_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* 
 
 #include "elementwise_vec.cuh"
 
+namespace e2h {
+
+__device__ __forceinline__ float4 ld_sys_f32x4(const float* p) {
+  float4 v;
+  asm volatile("ld.relaxed.sys.global.v4.f32 {%0, %1, %2, %3}, [%4];"
+               : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// Large-token form of the fused "residual + sum of tensor-parallel partials (+ RMSNorm)": same
+// flag protocol as rmsnorm_fwd_kernel, but every thread moves 8 features per access (two
+// 16-byte system-scope loads per partial) and keeps its part of the row in registers.
+__device__ __forceinline__ uint4 ld_sys_b32x4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// BF16P: the partials are bf16 (written by the GEMM's TMA-store epilogue) instead of fp32.
+template <int NV, bool BF16P>
+__global__ void rmsnorm_parts_rows_kernel(const __nv_bfloat16* __restrict__ h_in,
+                                          const PartPtrs parts, int n_part,
+                                          const __nv_bfloat16* __restrict__ weight,
+                                          __nv_bfloat16* __restrict__ h_out,
+                                          __nv_bfloat16* __restrict__ x_out, int dim, float eps,
+                                          const int* flags, int* use_count, unsigned int* ticket,
+                                          int* status) {
+  __shared__ float red[64];
+  const long long base = (long long)blockIdx.x * dim;
+  const int nvec = dim >> 3;
+  if (flags != nullptr) {
+    const int want = *use_count + 1;
+    if (threadIdx.x < n_part)
+      wait_flag_ge(flags + threadIdx.x, want, status, g_flag_wait_cycles);
+    __syncthreads();
+  }
+  float v[NV][8];
+  float ss = 0.f;
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) {
+      float acc[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int s = 0; s < n_part; ++s) {
+        if constexpr (BF16P) {
+          const __nv_bfloat16* src =
+              reinterpret_cast<const __nv_bfloat16*>(parts.p[s]) + base + 8 * i;
+          BF8 raw;
+          *reinterpret_cast<uint4*>(&raw) =
+              flags ? ld_sys_b32x4(src) : *reinterpret_cast<const uint4*>(src);
+          float f[8];
+          unpack8(raw, f);
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] += f[e];
+        } else {
+          const float* src = parts.p[s] + base + 8 * i;
+          const float4 a = flags ? ld_sys_f32x4(src) : *reinterpret_cast<const float4*>(src);
+          const float4 b =
+              flags ? ld_sys_f32x4(src + 4) : *reinterpret_cast<const float4*>(src + 4);
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+          acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
+      }
+      float r[8];
+      unpack8(*reinterpret_cast<const BF8*>(h_in + base + 8 * i), r);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        // the linear's output is a bf16 tensor in the reference; round before the residual add
+        v[k][e] = bf16_round(r[e] + bf16_round(acc[e]));
+        ss += v[k][e] * v[k][e];
+      }
+      *reinterpret_cast<BF8*>(h_out + base + 8 * i) = pack8(v[k]);
+    }
+  }
+  if (flags != nullptr) {
+    // all reads of this use are done: the last CTA advances the use counter
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+        *ticket = 0;
+        *use_count = *use_count + 1;
+      }
+    }
+  }
+  if (x_out == nullptr) return;
+  ss = block_sum2(ss, 0.f, red).x;
+  const float rstd = rsqrtf(ss / dim + eps);
+#pragma unroll
+  for (int k = 0; k < NV; ++k) {
+    const int i = threadIdx.x + k * blockDim.x;
+    if (i < nvec) {
+      float w[8], o[8];
+      unpack8(*reinterpret_cast<const BF8*>(weight + 8 * i), w);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) o[e] = bf16_round(v[k][e] * rstd) * w[e];
+      *reinterpret_cast<BF8*>(x_out + base + 8 * i) = pack8(o);
+    }
+  }
+}
+
+}  // namespace e2h
+
 using namespace e2h;
+
+// Launches rmsnorm_parts_rows_kernel; returns -100 when the shape / alignment is not covered.
+static int launch_parts_rows(const void* h_in, const PartPtrs& parts, int n_part, bool bf16_parts,
+                             const void* weight, void* h_out, void* x_out, int T, int dim,
+                             float eps, const int* flags, int* use_count, unsigned int* ticket,
+                             int* status, void* stream) {
+  if (dim % 8 || dim > 8192 || !aligned16(h_in) || !aligned16(h_out)) return -100;
+  if (x_out != nullptr && (!aligned16(x_out) || !aligned16(weight))) return -100;
+  for (int i = 0; i < n_part; ++i)
+    if (!aligned16(parts.p[i])) return -100;
+  const int threads = dim > 4096 ? 256 : 128;
+  const int nv = (dim / 8 + threads - 1) / threads;
+  if (nv > 4) return -100;
+  cudaStream_t st = (cudaStream_t)stream;
+#define E2H_GO(NV, BP)                                                                       \
+  rmsnorm_parts_rows_kernel<NV, BP><<<T, threads, 0, st>>>(                                  \
+      (const __nv_bfloat16*)h_in, parts, n_part, (const __nv_bfloat16*)weight,               \
+      (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out, dim, eps, flags, use_count, ticket, status)
+  if (bf16_parts) {
+    if (nv <= 1) E2H_GO(1, true); else if (nv == 2) E2H_GO(2, true); else E2H_GO(4, true);
+  } else {
+    if (nv <= 1) E2H_GO(1, false); else if (nv == 2) E2H_GO(2, false); else E2H_GO(4, false);
+  }
+#undef E2H_GO
+  return (int)cudaGetLastError();
+}
 
 extern "C" {
 
@@ -221,6 +363,16 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
                     int* use_count, unsigned int* ticket, int* status, void* stream) {
   if (dim % 2 || n_part > 8) return -1;
   if (flags != nullptr && (use_count == nullptr || ticket == nullptr)) return -2;
+  PartPtrs parts;
+  for (int i = 0; i < 8; ++i)
+    parts.p[i] = i < n_part ? static_cast<const float*>(part_ptrs[i]) : nullptr;
+  // many tokens with tensor-parallel partials: the vectorised form of the fused reduce
+  if (T >= 256 && h_in != nullptr && tokens == nullptr && n_part > 0 && h_out != nullptr &&
+      rstd_out == nullptr) {
+    const int rc = launch_parts_rows(h_in, parts, n_part, false, weight, h_out, x_out, T, dim,
+                                     eps, flags, use_count, ticket, status, stream);
+    if (rc != -100) return rc;
+  }
   // plain row normalisation of many tokens: the vectorised streaming kernel
   if (T >= 256 && h_in != nullptr && tokens == nullptr && n_part == 0 && h_out == nullptr &&
       x_out != nullptr && flags == nullptr && dim % 8 == 0 && dim <= 8192 && aligned16(h_in) &&
@@ -236,15 +388,28 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
 #undef E2H_GO
     if (nv <= 4) return (int)cudaGetLastError();
   }
-  PartPtrs parts;
-  for (int i = 0; i < 8; ++i)
-    parts.p[i] = i < n_part ? static_cast<const float*>(part_ptrs[i]) : nullptr;
   const int threads = dim >= 2048 ? 512 : 128;
   const size_t smem = (dim + 32) * sizeof(float);
   return (int)launch(rmsnorm_fwd_kernel, dim3(T), dim3(threads), smem, (cudaStream_t)stream,
                      (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, parts, n_part,
                      (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out,
                      rstd_out, dim, eps, flags, use_count, ticket, status);
+}
+
+// h_out = h_in + sum of the bf16 [T, dim] partials (peers' symmetric buffers), optionally
+// x_out = rmsnorm(h_out) * weight; same flag protocol as e2h_rmsnorm_fwd.
+int e2h_reduce_residual_norm_bf16(const void* h_in, const void* const* part_ptrs, int n_part,
+                                  const void* weight, void* h_out, void* x_out, int T, int dim,
+                                  float eps, const int* flags, int* use_count,
+                                  unsigned int* ticket, int* status, void* stream) {
+  if (n_part < 1 || n_part > 8 || h_in == nullptr || h_out == nullptr) return -1;
+  if (flags != nullptr && (use_count == nullptr || ticket == nullptr)) return -2;
+  PartPtrs parts;
+  for (int i = 0; i < 8; ++i)
+    parts.p[i] = i < n_part ? static_cast<const float*>(part_ptrs[i]) : nullptr;
+  const int rc = launch_parts_rows(h_in, parts, n_part, true, weight, h_out, x_out, T, dim, eps,
+                                   flags, use_count, ticket, status, stream);
+  return rc == -100 ? -3 : rc;
 }
 
 int e2h_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const void* dres, void* dx,
@@ -324,6 +489,13 @@ int e2h_rope(const void* x, void* out, const void* freqs, const int* pos, int T,
                                                    (const __nv_bfloat16*)freqs, pos, n_heads,
                                                    head_dim, ld, inverse);
   return (int)cudaGetLastError();
+}
+
+// Sets the cross-rank flag wait limit of this device (milliseconds at ~2 GHz); returns 0 or a
+// cudaError_t.
+int e2h_set_flag_wait_ms(int ms) {
+  const long long cycles = (long long)(ms < 1 ? 1 : ms) * 2000000LL;
+  return (int)cudaMemcpyToSymbol(g_flag_wait_cycles, &cycles, sizeof(cycles));
 }
 
 // Process-wide switch for programmatic dependent launch (see launch.cuh).

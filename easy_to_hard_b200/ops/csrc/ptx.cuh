@@ -313,10 +313,11 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Bounded wait for *p >= want. Returns false (and records kStatusTimeoutFlag) on time-out.
-__device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status) {
+__device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status,
+                                             long long limit = kWaitLimitCycles) {
   const long long t0 = clock64();
   while (ld_acquire_sys(p) < want) {
-    if (clock64() - t0 > kWaitLimitCycles) {
+    if (clock64() - t0 > limit) {
       if (status) atomicCAS(status, 0, kStatusTimeoutFlag);
       return false;
     }

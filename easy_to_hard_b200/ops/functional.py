@@ -75,6 +75,23 @@ def fused_residual_rmsnorm(h: Optional[torch.Tensor], weight: Optional[torch.Ten
     return h_out, x_out
 
 
+def reduce_residual_norm_bf16(h: torch.Tensor, weight: Optional[torch.Tensor], eps: float, *,
+                              partials, h_out: torch.Tensor,
+                              x_out: Optional[torch.Tensor] = None, flags=None, use_count=None,
+                              ticket=None):
+    """h_out = h + sum of bf16 [T, dim] partials given by raw device addresses (this rank's and
+    its tensor-parallel peers' symmetric buffers); x_out = rmsnorm(h_out) * weight when asked.
+    Large-token (T >= 1) form of ``fused_residual_rmsnorm`` with the same flag protocol."""
+    T, dim = h.shape
+    parts = list(partials)
+    rc = _lib.lib().e2h_reduce_residual_norm_bf16(
+        h.data_ptr(), _part_array(parts), len(parts), _lib.ptr(weight), h_out.data_ptr(),
+        _lib.ptr(x_out), T, dim, eps, _lib.ptr(flags), _lib.ptr(use_count), _lib.ptr(ticket),
+        _lib.status_word(h.device).data_ptr(), _s())
+    _lib.check(rc, "reduce_residual_norm_bf16")
+    return h_out, x_out
+
+
 def rmsnorm_bwd(x, dy, weight, eps, dres=None):
     dim = x.shape[-1]
     x2, dy2 = x.reshape(-1, dim), dy.reshape(-1, dim)

@@ -76,9 +76,11 @@ class RowParallelReduce:
     + ``world`` int32 flag words."""
 
     def __init__(self, max_tokens: int, dim: int, group=None, buf: Optional[SymmetricBuffer] = None,
-                 device="cuda"):
-        self.T, self.dim = max_tokens, dim
-        self.part_bytes = max_tokens * dim * 4
+                 device="cuda", dtype: torch.dtype = torch.float32):
+        """``dtype``: element type of the partial sums (fp32 for the decode path, bf16 for the
+        large-token training path, whose GEMM stores through its TMA epilogue)."""
+        self.T, self.dim, self.dtype = max_tokens, dim, dtype
+        self.part_bytes = max_tokens * dim * torch.empty((), dtype=dtype).element_size()
         self.slot_bytes = self.part_bytes + 256
         if buf is None:
             buf = SymmetricBuffer(2 * self.slot_bytes, group)
@@ -96,8 +98,8 @@ class RowParallelReduce:
         return s
 
     def partial_out(self, slot: int, T: int) -> torch.Tensor:
-        """This rank's fp32 [T, dim] partial (the GEMM writes here)."""
-        return self.buf.view(slot * self.slot_bytes, (self.T, self.dim), torch.float32)[:T]
+        """This rank's [T, dim] partial (the GEMM writes here)."""
+        return self.buf.view(slot * self.slot_bytes, (self.T, self.dim), self.dtype)[:T]
 
     def signal_ptrs(self, slot: int) -> List[int]:
         """Address of *this rank's* flag word inside every rank's slot."""

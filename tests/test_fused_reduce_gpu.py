@@ -9,12 +9,12 @@ import torch
 pytestmark = pytest.mark.gpu
 
 
-@pytest.mark.parametrize("world", [2, 4, 8])
-def test_row_parallel_reduce_emulated(world):
+@pytest.mark.parametrize("world,T", [(2, 64), (4, 64), (8, 64), (2, 512), (4, 384)])
+def test_row_parallel_reduce_emulated(world, T):
     from easy_to_hard_b200.ops import _lib, functional as Fn, gemm, reference
     from easy_to_hard_b200.parallel.symm import RowParallelReduce, SymmetricBuffer
     torch.manual_seed(0)
-    T, dim, K = 64, 1024, 512 * world
+    dim, K = 1024, 512 * world   # T >= 256 takes the vectorised consumer kernel
     g = torch.Generator(device="cuda").manual_seed(1)
     x = (torch.randn(T, K, generator=g, device="cuda")).bfloat16()
     w = (torch.randn(dim, K, generator=g, device="cuda") / math.sqrt(K)).bfloat16()
