@@ -76,6 +76,9 @@ _SIGNATURES = {
     "e2h_gae": [_vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "e2h_flash_fwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _vp,
                       _i, _i, _i, _i, _i, _i, _f, _vp, _vp],
+    "e2h_signal_peers": [C.POINTER(C.c_void_p), _i, _vp],
+    "e2h_reduce_scatter_accum": [C.POINTER(C.c_void_p), _i, _vp, _ll, _f, _i, _vp, _vp, _vp, _i,
+                                 _vp, _vp],
     "e2h_set_pdl": [_i],
     "e2h_set_flag_wait_ms": [_i],
     "e2h_flash_bwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll,

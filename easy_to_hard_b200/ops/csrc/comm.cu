@@ -1,0 +1,128 @@
+// Stand-alone collective kernels over peer-mapped (symmetric) memory.
+//
+// e2h_reduce_scatter_accum: the gradient reduce-scatter of sharded data parallelism fused with
+// the bf16 -> fp32 cast, the 1/world averaging and the accumulation into the fp32 gradient
+// shard. Every rank's backward pass leaves a flat bf16 gradient buffer in its own symmetric
+// memory and then raises a flag on every peer (e2h_signal_peers, stream-ordered after the
+// weight-gradient GEMMs). The reduce kernel of rank r waits -- bounded -- for all flags and pulls
+// slice r of every rank's buffer with 16-byte system-scope loads, sums in fp32 and writes (or
+// adds to) its fp32 shard: one pass, no intermediate reduce-scatter output, no NCCL.
+// Two buffer slots alternate between consecutive uses; a slot is only rewritten two uses later,
+// after this rank has itself consumed the peers' flags of the use in between, which the peers
+// raise only after they have finished reading the older slot (same stream order on every rank).
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "ptx.cuh"
+
+namespace e2h {
+
+struct PeerSrc {
+  const __nv_bfloat16* p[8];
+};
+struct PeerFlags {
+  int* p[8];
+};
+
+__global__ void signal_peers_kernel(const PeerFlags flags, int n) {
+  if (threadIdx.x < n) {
+    __threadfence_system();
+    red_release_sys_add(flags.p[threadIdx.x], 1);
+  }
+}
+
+__device__ __forceinline__ uint4 comm_ld_sys_b32x4(const void* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.b32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+// src.p[r] points at element 0 of this rank's slice inside rank r's buffer; n is a multiple of 8.
+__global__ void reduce_scatter_accum_kernel(const PeerSrc src, int n_peer, float* __restrict__ out,
+                                            long long n, float scale, int accumulate,
+                                            const int* flags, int* use_count, unsigned int* ticket,
+                                            long long wait_cycles, int* status) {
+  if (flags != nullptr) {
+    const int want = *use_count + 1;
+    if (threadIdx.x < n_peer) wait_flag_ge(flags + threadIdx.x, want, status, wait_cycles);
+    __syncthreads();
+  }
+  const long long nvec = n >> 3;
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
+       i += (long long)gridDim.x * blockDim.x) {
+    float acc[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+    for (int r = 0; r < n_peer; ++r) {
+      const uint4 raw = flags ? comm_ld_sys_b32x4(src.p[r] + 8 * i)
+                              : *reinterpret_cast<const uint4*>(src.p[r] + 8 * i);
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        acc[2 * e] += __bfloat162float(h[e].x);
+        acc[2 * e + 1] += __bfloat162float(h[e].y);
+      }
+    }
+    float4* dst = reinterpret_cast<float4*>(out + 8 * i);
+    float4 lo = make_float4(acc[0] * scale, acc[1] * scale, acc[2] * scale, acc[3] * scale);
+    float4 hi = make_float4(acc[4] * scale, acc[5] * scale, acc[6] * scale, acc[7] * scale);
+    if (accumulate) {
+      const float4 a = dst[0], b = dst[1];
+      lo.x += a.x; lo.y += a.y; lo.z += a.z; lo.w += a.w;
+      hi.x += b.x; hi.y += b.y; hi.z += b.z; hi.w += b.w;
+    }
+    dst[0] = lo;
+    dst[1] = hi;
+  }
+  if (flags != nullptr) {
+    // all reads of this use are done: the last CTA advances the use counter
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      __threadfence();
+      if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+        *ticket = 0;
+        *use_count = *use_count + 1;
+      }
+    }
+  }
+}
+
+}  // namespace e2h
+
+using namespace e2h;
+
+extern "C" {
+
+// flag_ptrs: n device addresses (this rank's flag word inside every rank's buffer).
+int e2h_signal_peers(const void* const* flag_ptrs, int n, void* stream) {
+  if (n < 1 || n > 8) return -1;
+  PeerFlags f;
+  for (int i = 0; i < 8; ++i) f.p[i] = i < n ? (int*)flag_ptrs[i] : nullptr;
+  signal_peers_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(f, n);
+  return (int)cudaGetLastError();
+}
+
+int e2h_reduce_scatter_accum(const void* const* peer_src, int n_peer, float* out, long long n,
+                             float scale, int accumulate, const int* flags, int* use_count,
+                             unsigned int* ticket, int wait_ms, int* status, void* stream) {
+  if (n_peer < 1 || n_peer > 8 || n <= 0 || (n % 8)) return -1;
+  if (flags != nullptr && (use_count == nullptr || ticket == nullptr)) return -2;
+  if (reinterpret_cast<uintptr_t>(out) & 15) return -3;
+  PeerSrc s;
+  for (int i = 0; i < 8; ++i) {
+    s.p[i] = i < n_peer ? (const __nv_bfloat16*)peer_src[i] : nullptr;
+    if (i < n_peer && (reinterpret_cast<uintptr_t>(s.p[i]) & 15)) return -3;
+  }
+  long long blocks = (n / 8 + 255) / 256;
+  if (blocks > 148 * 8) blocks = 148 * 8;
+  const long long cycles = (long long)(wait_ms < 1 ? 1 : wait_ms) * 2000000LL;
+  reduce_scatter_accum_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(
+      s, n_peer, out, n, scale, accumulate, flags, use_count, ticket, cycles, status);
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

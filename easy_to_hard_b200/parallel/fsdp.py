@@ -125,6 +125,20 @@ class ShardUnit:
         else:
             self.shard.grad.add_(out)
 
+    def reduce_grads_p2p(self, rs, slot: int) -> None:
+        """Same result as ``reduce_grads`` through the fused kernel of ``ops/csrc/comm.cu``: the
+        flat bf16 gradient already sits in slot ``slot`` of the symmetric buffers ``rs``; raise
+        the flags, then pull this rank's slice from every rank, average in fp32 and write (or
+        add to) ``shard.grad`` in one pass."""
+        if self.padded > self.total:
+            rs.grad_buffer(slot)[self.total:self.padded].zero_()
+        rs.signal(slot)
+        fresh = self.shard.grad is None
+        if fresh:
+            self.shard.grad = torch.empty_like(self.shard.data)
+        rs.reduce(slot, self.rank * self.shard_size, self.shard_size, self.shard.grad,
+                  1.0 / self.world, accumulate=not fresh)
+
     def refresh_low_precision(self) -> None:
         """After an update of the master shard that did not write the low-precision copy."""
         self.shard_lp.copy_(self.shard.data)
@@ -224,6 +238,14 @@ class ShardedDataParallel(nn.Module):
         self._param_bufs = [torch.empty(biggest, dtype=self.compute_dtype, device=dev)
                             for _ in range(2)]
         self._grad_buf = torch.empty(biggest, dtype=self.compute_dtype, device=dev)
+        # fused pull-based gradient reduce-scatter over peer memory (falls back to NCCL)
+        self._rs = None
+        if (self.fused and self.world > 1 and param_dtype == torch.float32
+                and self.compute_dtype == torch.bfloat16):
+            from ..models.fused_block import p2p_reduce_enabled
+            if p2p_reduce_enabled():
+                from .symm import GradReduceScatter
+                self._rs = GradReduceScatter(biggest, process_group)
         self._root_buf = (torch.empty(self.root.padded, dtype=self.compute_dtype, device=dev)
                           if self.root else None)
         self._comm_stream = torch.cuda.Stream() if dev.type == "cuda" else None
@@ -300,7 +322,9 @@ class ShardedDataParallel(nn.Module):
         blk = self.backbone.layers[idx]
         if self.fused:
             from ..models import fused_block as fb
-            views = unit.grad_views(self._grad_buf)
+            slot = self._rs.slot() if self._rs is not None else -1
+            gradbuf = self._rs.grad_buffer(slot) if self._rs is not None else self._grad_buf
+            views = unit.grad_views(gradbuf)
             grads = {n.split(".")[-2]: v for n, v in views.items()}
             dx = fb.block_backward(dy, x, self._block_weights(blk, unit), grads, self._freqs,
                                    self._pos, self._shape(blk, B, S))
@@ -317,7 +341,10 @@ class ShardedDataParallel(nn.Module):
                 v.copy_(p.grad if p.grad is not None else torch.zeros_like(v))
                 p.grad = None
         unit.release()
-        unit.reduce_grads(self._grad_buf)
+        if self.fused and self._rs is not None:
+            unit.reduce_grads_p2p(self._rs, slot)
+        else:
+            unit.reduce_grads(self._grad_buf)
         return dx
 
     # ------------------------------------------------------------------ forward

@@ -112,3 +112,66 @@ class RowParallelReduce:
 
     def partial_ptrs(self, slot: int) -> List[int]:
         return [self.buf.peer_ptr(r, slot * self.slot_bytes) for r in range(self.world)]
+
+
+class GradReduceScatter:
+    """Buffers and counters of the fused gradient reduce-scatter of sharded data parallelism
+    (``ops/csrc/comm.cu``): two alternating slots, each a flat bf16 gradient buffer of ``numel``
+    elements followed by ``world`` int32 flag words, in symmetric memory."""
+
+    def __init__(self, numel: int, group=None, buf: Optional[SymmetricBuffer] = None,
+                 wait_ms: int = 120000):
+        self.numel = (numel + 7) // 8 * 8
+        self.grad_bytes = self.numel * 2
+        self.slot_bytes = (self.grad_bytes + 255) // 256 * 256 + 256
+        if buf is None:
+            buf = SymmetricBuffer(2 * self.slot_bytes, group)
+        self.buf = buf
+        self.world, self.rank = buf.world, buf.rank
+        dev = buf.local.device
+        self.use_count = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.ticket = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.wait_ms = wait_ms
+        self.next_slot = 0
+
+    def slot(self) -> int:
+        s = self.next_slot
+        self.next_slot ^= 1
+        return s
+
+    def _flag_off(self, slot: int) -> int:
+        return slot * self.slot_bytes + (self.grad_bytes + 255) // 256 * 256
+
+    def grad_buffer(self, slot: int) -> torch.Tensor:
+        """This rank's flat bf16 gradient buffer of ``slot`` (the weight-gradient GEMMs write
+        views of it)."""
+        return self.buf.view(slot * self.slot_bytes, (self.numel,), torch.bfloat16)
+
+    def flags(self, slot: int) -> torch.Tensor:
+        return self.buf.view(self._flag_off(slot), (self.world,), torch.int32)
+
+    def signal(self, slot: int) -> None:
+        """Tell every rank that this rank's buffer of ``slot`` is complete (stream-ordered after
+        the kernels that wrote it)."""
+        import ctypes as C
+        from ..ops import _lib
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.buf.peer_ptr(r, self._flag_off(slot) + 4 * self.rank)
+        _lib.check(_lib.lib().e2h_signal_peers(arr, self.world, _lib.stream()), "signal_peers")
+
+    def reduce(self, slot: int, offset: int, n: int, out: torch.Tensor, scale: float,
+               accumulate: bool) -> None:
+        """out[:n] (+)= scale * sum over ranks of their buffer[offset : offset + n] (fp32 out)."""
+        import ctypes as C
+        from ..ops import _lib
+        assert out.dtype == torch.float32 and out.is_contiguous() and n % 8 == 0 and offset % 8 == 0
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.buf.peer_ptr(r, slot * self.slot_bytes + 2 * offset)
+        rc = _lib.lib().e2h_reduce_scatter_accum(
+            arr, self.world, out.data_ptr(), n, float(scale), int(accumulate),
+            self.flags(slot).data_ptr(), self.use_count[slot:slot + 1].data_ptr(),
+            self.ticket[slot:slot + 1].data_ptr(), int(self.wait_ms),
+            _lib.status_word(out.device).data_ptr(), _lib.stream())
+        _lib.check(rc, "reduce_scatter_accum")

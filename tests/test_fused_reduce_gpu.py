@@ -70,3 +70,36 @@ def test_wait_times_out_with_error_status():
     assert _lib.read_status() == 105  # kStatusTimeoutFlag
     assert _lib.read_status() == 0    # cleared; the device still works
     assert torch.ones(2, device="cuda").sum().item() == 2
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_gradient_reduce_scatter_emulated(world):
+    """Fused reduce-scatter + cast + average + accumulate (ops/csrc/comm.cu), ranks emulated as
+    buffers of one process: all producers signal before any consumer runs."""
+    from easy_to_hard_b200.ops import _lib
+    from easy_to_hard_b200.parallel.symm import GradReduceScatter, SymmetricBuffer
+    torch.manual_seed(0)
+    shard = 4096 + 8
+    numel = shard * world
+    proto = GradReduceScatter.__new__(GradReduceScatter)
+    slot_bytes = (numel * 2 + 255) // 256 * 256 + 256
+    bufs = SymmetricBuffer.emulated(2 * slot_bytes, world)
+    ranks = [GradReduceScatter(numel, buf=b, wait_ms=1000) for b in bufs]
+    outs = [torch.zeros(shard, device="cuda") for _ in range(world)]
+    total = torch.zeros(numel, device="cuda")
+    for use in range(4):                      # both slots, then both again (accumulating)
+        slots = [r.slot() for r in ranks]
+        s = slots[0]
+        grads = [(torch.randn(numel, device="cuda") * 0.1).bfloat16() for _ in range(world)]
+        for r, rs in enumerate(ranks):        # producers
+            rs.grad_buffer(s).copy_(grads[r])
+            rs.signal(s)
+        for r, rs in enumerate(ranks):        # consumers
+            rs.reduce(s, r * shard, shard, outs[r], 1.0 / world, accumulate=use > 0)
+        torch.cuda.synchronize()
+        assert _lib.read_status() == 0
+        total += sum(g.float() for g in grads) / world
+        for r in range(world):
+            assert torch.allclose(outs[r], total[r * shard:(r + 1) * shard], atol=1e-5, rtol=1e-5)
+        for rs in ranks:
+            assert int(rs.flags(s).min()) == int(rs.use_count[s]) == use // 2 + 1
