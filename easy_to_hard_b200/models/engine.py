@@ -96,13 +96,14 @@ class DecodeEngine:
     def _dense(linear):
         """(bf16 [out, in] weight, per-output-feature fp32 scale or None) as the GEMM kernels
         read them. bf16 modules hand out their own tensor (in-place updates of the model, e.g.
-        the PPO rollout sync, are seen by captured graphs). Weight-only int8 becomes the exact
-        bf16 image of the integers plus its scales, applied in the GEMM epilogue exactly where
-        the reference multiplies (models/quantize.py:397-398); int4-g128 (tinygemm packing) is
-        unpacked and dequantised once."""
+        the PPO rollout sync, are seen by captured graphs). Weight-only int8 stays int8 (the
+        decode GEMM expands it to bf16 inside the SM) with its scales applied in the GEMM
+        epilogue, exactly where the reference multiplies (models/quantize.py:397-398);
+        int4-g128 (tinygemm packing) is unpacked and dequantised once."""
         w = linear.weight
         if w.dtype == torch.int8 and hasattr(linear, "scales"):
-            return w.to(torch.bfloat16).contiguous(), linear.scales.float().contiguous()
+            # stays int8 in memory: ops.gemm streams it through the converting kernel
+            return w.contiguous(), linear.scales.float().contiguous()
         if w.dtype == torch.int32 and hasattr(linear, "scales_and_zeros"):
             from . import quantize as qz
             q = qz.unpack_int4_tinygemm(w, linear.inner_k_tiles)

@@ -60,6 +60,7 @@ _vp, _i, _ll, _f, _ull = C.c_void_p, C.c_int, C.c_longlong, C.c_float, C.c_ulong
 _SIGNATURES = {
     "e2h_gemm_umma": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_persistent": [C.POINTER(GemmParams), _vp],
+    "e2h_gemm_w8": [C.POINTER(GemmParams), _vp],
     "e2h_rmsnorm_fwd": [_vp, _vp, _vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
                         _vp, _vp, _vp, _vp, _vp],
     "e2h_reduce_residual_norm_bf16": [_vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _i, _i, _f,

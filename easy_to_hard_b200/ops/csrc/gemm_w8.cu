@@ -1,0 +1,461 @@
+// Weight-only int8 GEMM for the decode step (few tokens, the weight matrix streams once):
+//   out[t, f] = epilogue( scale[f] * sum_k x[t, k] * w8[f, k] )
+// The int8 weights cross HBM as int8 -- half the bytes of the bf16 GEMM, which is the whole point
+// of the format for a bandwidth-bound decode step -- and are expanded to bf16 inside the SM:
+//
+//   warp 0      TMA producer: per stage one int8 weight tile [128 features x 128 k] (128-byte rows,
+//               128B swizzle: the same row granularity as the bf16 GEMM) and the two matching bf16
+//               activation tiles [BN tokens x 64 k] (one 3-D box);
+//   warps 2-9   converters during the main loop (two threads per feature row, 64 k each):
+//               int8 -> bf16 two values per instruction -- a byte permute drops each byte into the
+//               mantissa of bf16(128) (0x4300 | low 7 bits), and one packed bf16 subtraction of
+//               128 or 256 (chosen by the sign bit) yields the exact integer -- written as the
+//               128-byte-swizzled K-major A tile that tcgen05.mma reads, two alternating buffers;
+//               afterwards warps 2-5 run the epilogue;
+//   warp 1      one thread issues tcgen05.mma (M = 128, N = BN, K = 16) from the converted tile
+//               and the activation tile into the fp32 accumulator in tensor memory.
+//
+// The integers -128..127 are exact in bf16, so the product equals the reference's
+// F.linear(x, w_int8.to(bf16)) * scales (models/quantize.py:397-398) up to accumulation order;
+// the per-feature scales ride in the shared epilogue (p.scale; a dual GEMM carries 2F of them).
+// Split-K over a thread-block cluster with the DSMEM reduce-scatter, the fused epilogues and the
+// completion signal are those of umma_gemm_kernel (gemm_umma.cu).
+//
+// All waits are bounded; a time-out writes a code to p.status and the CTA still reaches every
+// barrier, frees its tensor memory and returns.
+#include <cuda.h>
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <string.h>
+#include <mutex>
+
+#include "gemm_epilogue.cuh"
+#include "gemm_umma.cuh"
+#include "launch.cuh"
+#include "ptx.cuh"
+
+namespace e2h {
+
+constexpr int kW8Threads = 320;     // TMA warp, MMA warp, 8 converter warps (4 of them: epilogue)
+constexpr int kW8MaxStages = 8;
+constexpr int kW8Ctrl = 1024;
+constexpr int kW8Kps = 2;          // 64-wide k-blocks per pipeline stage
+constexpr int kW8ConvMax = 4;      // converted-tile buffers: 4 (2 for a dual GEMM, whose tiles are twice as large)
+constexpr int kA8Bytes = 128 * 64; // int8 bytes of one 64-wide k-block (a stage holds kW8Kps of them
+                                   // as one [128 x 128] tile)
+constexpr int kA16Bytes = 128 * 128;
+
+struct CtrlW8 {
+  uint64_t full[kW8MaxStages];
+  uint64_t empty[kW8MaxStages];
+  uint64_t conv_full[kW8ConvMax];
+  uint64_t conv_empty[kW8ConvMax];
+  uint64_t tmem_full;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+static_assert(sizeof(CtrlW8) <= kW8Ctrl, "control block too large");
+
+__host__ __device__ inline int w8_xchg_bytes(int bn, int splitk, int dual) {
+  if (splitk <= 1) return 0;
+  return (splitk - 1) * (bn / splitk) * 128 * 4 * (dual ? 2 : 1);
+}
+
+// four signed bytes (one 32-bit word) -> two packed bf16x2 words, exactly.
+// For a byte s = low7 - 128 * sign: bf16 bits 0x4300 | low7 are the number 128 + low7; subtracting
+// bf16(128) = 0x4300 (sign clear) or bf16(256) = 0x4380 (sign set) leaves s. All three values
+// are exact in bf16, so is the result.
+__device__ __forceinline__ void cvt4_s8_bf16(uint32_t w, uint32_t& lo, uint32_t& hi) {
+  const uint32_t t01 = __byte_perm(w, 0x43434343u, 0x5140);   // [0x43:s1 | 0x43:s0]
+  const uint32_t t23 = __byte_perm(w, 0x43434343u, 0x5342);   // [0x43:s3 | 0x43:s2]
+  const uint32_t x01 = t01 & 0x437F437Fu, c01 = (t01 & 0x00800080u) | 0x43004300u;
+  const uint32_t x23 = t23 & 0x437F437Fu, c23 = (t23 & 0x00800080u) | 0x43004300u;
+  const __nv_bfloat162 r01 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&x01),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&c01));
+  const __nv_bfloat162 r23 = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&x23),
+                                     *reinterpret_cast<const __nv_bfloat162*>(&c23));
+  lo = *reinterpret_cast<const uint32_t*>(&r01);
+  hi = *reinterpret_cast<const uint32_t*>(&r23);
+}
+
+template <int BN, bool DUAL>
+__global__ void __launch_bounds__(kW8Threads, 1)
+umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
+                    const __grid_constant__ CUtensorMap tmB, const E2hGemmParams p) {
+  constexpr int NMAT = DUAL ? 2 : 1;
+  // the conversion -> MMA -> commit round trip of one buffer takes about 2 us; several buffers
+  // in flight hide it
+  constexpr int kW8Conv = DUAL ? 2 : 4;
+  constexpr int B_BYTES = BN * 128;
+  constexpr int STAGE = kW8Kps * (kA8Bytes * NMAT + B_BYTES);
+  constexpr int CONV = kW8Kps * kA16Bytes * NMAT;
+  constexpr int ACC_COLS = BN * NMAT;
+  constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : 256;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
+                                             ~uintptr_t(1023));
+  CtrlW8* ctrl = reinterpret_cast<CtrlW8*>(smem);
+  uint8_t* tiles = smem + kW8Ctrl;
+  const int stages = p.stages;
+  float* xchg = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE);
+  uint8_t* conv = reinterpret_cast<uint8_t*>(xchg) + w8_xchg_bytes(BN, p.splitk, DUAL);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int S = p.splitk;
+  const int rank = (S > 1) ? (int)cluster_ctarank() : 0;
+  const int f0 = blockIdx.x * 128;
+  const int t0 = blockIdx.y * BN;
+  // the K range is split in units of one int8 tile (128 k = two bf16 k-blocks)
+  const int kb2_total = p.K / 128;
+  const int kb_begin = 2 * (int)((long long)rank * kb2_total / S);
+  const int kb_end = 2 * (int)((long long)(rank + 1) * kb2_total / S);
+  const int n_kb = kb_end - kb_begin;
+  const int n_it = (n_kb + kW8Kps - 1) / kW8Kps;
+  volatile int* abort_flag = &ctrl->abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&ctrl->full[s]), 1);
+      mbar_init(smem_u32(&ctrl->empty[s]), 1);
+    }
+    for (int c = 0; c < kW8Conv; ++c) {
+      mbar_init(smem_u32(&ctrl->conv_full[c]), 8);    // one arrival per converter warp
+      mbar_init(smem_u32(&ctrl->conv_empty[c]), 1);
+    }
+    mbar_init(smem_u32(&ctrl->tmem_full), 1);
+    ctrl->abort_flag = 0;
+    fence_mbar_init();
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+    if (DUAL) tma_prefetch_desc(&tmA2);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(&ctrl->tmem_base), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = ctrl->tmem_base;
+  if (S > 1) cluster_sync_all();
+  pdl_wait_prior();
+  pdl_launch_dependents();
+
+  if (warp == 0 && lane == 0) {
+    // ---------------- TMA producer ----------------
+    const uint64_t pol_a = policy_evict_first();
+    int armed = 0;
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it % stages;
+      const uint32_t ph = (it / stages) & 1;
+      if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, p.status,
+                     kStatusTimeoutEmpty))
+        break;
+      const uint32_t bar = smem_u32(&ctrl->full[s]);
+      const uint32_t st = smem_u32(tiles + (size_t)s * STAGE);
+      const int kb = kb_begin + it * kW8Kps;
+      if (p.debug_mode & 2) {          // timing experiment without the loads
+        mbar_arrive(bar);
+        armed = it + 1;
+        continue;
+      }
+      // boxes are always full size: k-blocks past the matrix are zero filled, k-blocks past this
+      // CTA's range are loaded but never multiplied
+      mbar_expect_tx(bar, STAGE);
+      tma_load_3d_hint(st, &tmA, 0, f0, kb / kW8Kps, bar, pol_a);
+      if (DUAL) tma_load_3d_hint(st + kW8Kps * kA8Bytes, &tmA2, 0, f0, kb / kW8Kps, bar, pol_a);
+      tma_load_3d(st + kW8Kps * kA8Bytes * NMAT, &tmB, 0, t0, kb, bar);
+      armed = it + 1;
+    }
+    if (*abort_flag) {   // bounded wait for the copies still in flight into this CTA's smem
+      for (int it = (armed > stages ? armed - stages : 0); it < armed; ++it) {
+        const long long tq = clock64();
+        while (!mbar_try_wait(smem_u32(&ctrl->full[it % stages]), (it / stages) & 1)) {
+          if (clock64() - tq > kWaitLimitCycles / 8) break;
+        }
+      }
+    }
+  } else if (warp == 1 && lane == 0) {
+    // ---------------- UMMA issuer ----------------
+    const uint32_t idesc = make_idesc_bf16(128, BN, 0, 0);
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; ++it) {
+      const int s = it % stages, c = it % kW8Conv;
+      ok = mbar_wait(smem_u32(&ctrl->full[s]), (it / stages) & 1, abort_flag, p.status,
+                     kStatusTimeoutFull) &&
+           mbar_wait(smem_u32(&ctrl->conv_full[c]), (it / kW8Conv) & 1, abort_flag, p.status,
+                     kStatusTimeoutFull);
+      if (!ok) break;
+      tc_fence_after();
+      const uint32_t st = smem_u32(tiles + (size_t)s * STAGE);
+      const uint32_t cv = smem_u32(conv + (size_t)c * CONV);
+      const int kcount = (p.debug_mode & 4) ? 0 : min(kW8Kps, n_kb - it * kW8Kps);
+      for (int kk = 0; kk < kcount; ++kk) {
+        const uint32_t a_base = cv + kk * kA16Bytes;
+        const uint32_t a2_base = a_base + kW8Kps * kA16Bytes;
+        const uint32_t b_base = st + kW8Kps * kA8Bytes * NMAT + kk * B_BYTES;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const uint64_t bdesc = make_sw128_desc(b_base + k * 32, 16, 1024);
+          const uint32_t acc = (it > 0 || kk > 0 || k > 0) ? 1u : 0u;
+          umma_f16(tmem_base, make_sw128_desc(a_base + k * 32, 16, 1024), bdesc, idesc, acc);
+          if (DUAL)
+            umma_f16(tmem_base + BN, make_sw128_desc(a2_base + k * 32, 16, 1024), bdesc, idesc,
+                     acc);
+        }
+      }
+      umma_commit(smem_u32(&ctrl->empty[s]));        // activation tile (and int8 tile) reusable
+      umma_commit(smem_u32(&ctrl->conv_empty[c]));   // converted tile reusable
+    }
+    umma_commit(smem_u32(&ctrl->tmem_full));
+  }
+
+  const bool is_conv = warp >= 2;
+  const bool is_epi = warp >= 2 && warp < 6;
+  const int q = warp & 3;
+  const int lane_row = q * 32 + lane;                 // feature row = TMEM lane (epilogue warps)
+  if (is_conv) {
+    // ---------------- converters: int8 tile -> swizzled bf16 A tiles ----------------
+    // thread (row, half): the 64 int8 of `row` that make up bf16 k-block `half` of the stage
+    const int ct = threadIdx.x - 64;                  // 0 .. 255
+    const int row = ct & 127, half = ct >> 7;
+    const int sw = row & 7;                           // 128B-swizzle term of this row
+    bool ok = true;
+    for (int it = 0; it < n_it; ++it) {
+      const int s = it % stages, c = it % kW8Conv;
+      // every converter thread waits itself (one polling lane per warp plus a shuffle measured
+      // 10% slower: the acquire has to be re-established for the other lanes anyway)
+      if (ok)
+        ok = mbar_wait(smem_u32(&ctrl->full[s]), (it / stages) & 1, abort_flag, p.status,
+                       kStatusTimeoutFull) &&
+             mbar_wait(smem_u32(&ctrl->conv_empty[c]), ((it / kW8Conv) & 1) ^ 1, abort_flag,
+                       p.status, kStatusTimeoutEmpty);
+      if (ok && !(p.debug_mode & 1)) {   // debug_mode 1: timing experiment without the conversion
+        const uint8_t* st = tiles + (size_t)s * STAGE;
+        uint8_t* cv = conv + (size_t)c * CONV;
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+          const uint8_t* src = st + m * kW8Kps * kA8Bytes + row * 128;
+          uint8_t* dst = cv + (m * kW8Kps + half) * kA16Bytes + row * 128;
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {               // 16 int8 -> two 16-byte bf16 chunks
+            const uint4 raw = *reinterpret_cast<const uint4*>(src + (((4 * half + j) ^ sw) << 4));
+            uint4 o0, o1;
+            cvt4_s8_bf16(raw.x, o0.x, o0.y);
+            cvt4_s8_bf16(raw.y, o0.z, o0.w);
+            cvt4_s8_bf16(raw.z, o1.x, o1.y);
+            cvt4_s8_bf16(raw.w, o1.z, o1.w);
+            *reinterpret_cast<uint4*>(dst + (((2 * j) ^ sw) << 4)) = o0;
+            *reinterpret_cast<uint4*>(dst + (((2 * j + 1) ^ sw) << 4)) = o1;
+          }
+        }
+      }
+      if (!(p.debug_mode & 8)) fence_proxy_async_smem();   // generic writes -> tcgen05.mma
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&ctrl->conv_full[c]));
+    }
+  }
+
+  // ---------------- epilogue: accumulator -> registers -> fused epilogue ----------------
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+  const int slice = BN / S;
+  bool acc_ok = true;
+  if (is_epi) {
+    int ok_i = 1;
+    if (lane == 0)
+      ok_i = mbar_wait_relaxed(smem_u32(&ctrl->tmem_full), 0, abort_flag, p.status,
+                               kStatusTimeoutTmemFull) ? 1 : 0;
+    ok_i = __shfl_sync(0xffffffffu, ok_i, 0);
+    acc_ok = ok_i != 0;
+    tc_fence_after();
+    if (S > 1 && acc_ok && n_kb > 0) {
+      // reduce-scatter over token columns through distributed shared memory
+      for (int peer = 0; peer < S; ++peer) {
+        if (peer == rank) continue;
+        const int slot = rank < peer ? rank : rank - 1;
+        for (int c = 0; c < slice; c += 8) {
+#pragma unroll
+          for (int m = 0; m < NMAT; ++m) {
+            float v[8];
+            tmem_ld_x8(taddr + m * BN + peer * slice + c, v);
+            tmem_ld_wait();
+            const uint32_t base = smem_u32(xchg) +
+                                  ((m * (S - 1) * slice + slot * slice + c) * 128 + lane_row) * 4;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) st_cluster_f32(mapa_shared(base + j * 128 * 4, peer), v[j]);
+          }
+        }
+      }
+    }
+  }
+  __syncwarp();
+  if (S > 1) cluster_sync_all();
+
+  if (is_epi && acc_ok) {
+    const int c_begin = rank * slice;
+    const int f = f0 + lane_row;
+    for (int c = 0; c < slice; c += 8) {
+      float v[8], v2[DUAL ? 8 : 1];
+      if (n_kb > 0) {
+        tmem_ld_x8(taddr + c_begin + c, v);
+        if constexpr (DUAL) tmem_ld_x8(taddr + BN + c_begin + c, v2);
+        tmem_ld_wait();
+      } else {
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          v[j] = 0.f;
+          if constexpr (DUAL) v2[j] = 0.f;
+        }
+      }
+      if (S > 1) {
+        for (int slot = 0; slot < S - 1; ++slot) {
+          const float* src = xchg + (size_t)(slot * slice + c) * 128 + lane_row;
+#pragma unroll
+          for (int j = 0; j < 8; ++j) v[j] += src[j * 128];
+          if constexpr (DUAL) {
+            const float* src2 = src + (size_t)(S - 1) * slice * 128;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v2[j] += src2[j * 128];
+          }
+        }
+      }
+      epilogue8<DUAL>(p, f, t0 + c_begin + c, v, v2);
+    }
+  }
+
+  if (p.n_signal > 0) __threadfence();
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+  if (p.n_signal > 0 && threadIdx.x == 0) {
+    __threadfence();
+    const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
+    if (atomicAdd(p.ticket, 1u) == total - 1) {
+      *p.ticket = 0;
+      __threadfence_system();
+      for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
+typedef CUresult (*W8EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
+                               const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                               const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                               CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static W8EncodeFn w8_encode_fn() {
+  static W8EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &q) ==
+            cudaSuccess && q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<W8EncodeFn>(sym);
+  });
+  return fn;
+}
+
+// K-major operand [rows, K] seen as {inner, rows, K / inner} with `inner` elements = 128 bytes
+// (64 bf16 or 128 int8): one box {inner, box_rows, nblk} lands as nblk consecutive
+// [box_rows x 128 B] tiles with the 128-byte swizzle.
+static int w8_map3d(CUtensorMap* m, const void* base, long long K, long long rows, long long ld,
+                    int box_rows, int nblk, bool int8) {
+  W8EncodeFn fn = w8_encode_fn();
+  if (!fn) return -10;
+  const int es = int8 ? 1 : 2;
+  const int inner = 128 / es;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)rows, (cuuint64_t)(K / inner)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * es, 128u};
+  cuuint32_t box[3] = {(cuuint32_t)inner, (cuuint32_t)box_rows, (cuuint32_t)nblk};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(m, int8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3,
+                  const_cast<void*>(base), dims, strides, box, estr,
+                  CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <int BN, bool DUAL>
+static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
+  constexpr int NMAT = DUAL ? 2 : 1;
+  constexpr int kW8Conv = DUAL ? 2 : 4;
+  constexpr int STAGE = kW8Kps * (kA8Bytes * NMAT + BN * 128);
+  constexpr int CONV = kW8Kps * kA16Bytes * NMAT;
+  const int fixed = 1024 + kW8Ctrl + w8_xchg_bytes(BN, p.splitk, DUAL) + kW8Conv * CONV;
+  int stages = (227 * 1024 - fixed) / STAGE;
+  if (stages > kW8MaxStages) stages = kW8MaxStages;
+  if (p.stages > 0 && p.stages < stages) stages = p.stages;
+  const int n_it = (p.K / 128 + p.splitk - 1) / p.splitk;
+  if (stages > n_it) stages = n_it < 1 ? 1 : n_it;
+  if (stages < 1) return -8;
+  p.stages = stages;
+  CUtensorMap ta, ta2, tb;
+  int r = w8_map3d(&ta, p.a, p.K, p.F, p.lda, 128, 1, true);
+  if (r) return r;
+  if (DUAL) {
+    r = w8_map3d(&ta2, p.a2, p.K, p.F, p.lda2, 128, 1, true);
+    if (r) return r;
+  } else {
+    ta2 = ta;
+  }
+  r = w8_map3d(&tb, p.b, p.K, p.T, p.ldb, BN, kW8Kps, false);
+  if (r) return r;
+  const size_t smem = (size_t)fixed + (size_t)stages * STAGE;
+  auto kern = umma_gemm_w8_kernel<BN, DUAL>;
+  static size_t configured = 0;
+  if (smem > configured) {
+    cudaError_t e =
+        cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    configured = smem;
+  }
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = dim3((p.F + 127) / 128, (p.T + BN - 1) / BN, p.splitk);
+  cfg.blockDim = dim3(kW8Threads, 1, 1);
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  if (p.splitk > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 1;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = p.splitk;
+    ++na;
+  }
+  if (p.pdl || g_pdl) {
+    attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[na].val.programmaticStreamSerializationAllowed = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return (int)cudaLaunchKernelEx(&cfg, kern, ta, ta2, tb, p);
+}
+
+}  // namespace e2h
+
+// Same parameter block as e2h_gemm_umma, with p.a (and p.a2) pointing at int8 [F, K] weights
+// (lda in elements = bytes, a multiple of 16), p.b bf16 [T, K], K % 128 == 0, T-tile bn 64 or 128,
+// and p.scale the fp32 per-feature scales (F of them, or 2F for a dual GEMM).
+extern "C" int e2h_gemm_w8(const E2hGemmParams* pp, void* stream_v) {
+  using namespace e2h;
+  E2hGemmParams p = *pp;
+  if (p.F <= 0 || p.T <= 0 || p.K <= 0 || (p.K % 128)) return -1;
+  if (p.bn != 64 && p.bn != 128) return -2;
+  if (p.dual && p.bn != 64) return -2;
+  if (p.splitk < 1 || p.splitk > 8 || (p.bn % (p.splitk * 8)) != 0) return -3;
+  if ((p.K / 128) < p.splitk) return -4;
+  if (p.a_mn_major || p.b_mn_major || p.a_tiled) return -5;
+  if (p.dual && p.a2 == nullptr) return -5;
+  if ((p.lda % 16) || (p.ldb % 8) || (p.dual && (p.lda2 % 16))) return -6;
+  if (((uintptr_t)p.a & 15) || ((uintptr_t)p.b & 15) || (p.dual && ((uintptr_t)p.a2 & 15)))
+    return -7;
+  if (p.scale == nullptr) return -9;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (p.dual) return w8_launch<64, true>(p, stream);
+  if (p.bn == 64) return w8_launch<64, false>(p, stream);
+  return w8_launch<128, false>(p, stream);
+}

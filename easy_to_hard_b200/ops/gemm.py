@@ -81,8 +81,21 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
          signal=None, ticket: Optional[torch.Tensor] = None,
          persistent: Optional[bool] = None) -> None:
-    """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T])."""
-    assert a.is_cuda and b.is_cuda and a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16
+    """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T]).
+    An int8 ``a`` (weight-only quantisation; ``scale`` holds the per-feature scales) streams as
+    int8 through the converting kernel for up to 128 tokens and is expanded to a scratch bf16
+    matrix first for larger token counts."""
+    assert a.is_cuda and b.is_cuda and b.dtype == torch.bfloat16
+    w8 = a.dtype == torch.int8
+    if w8:
+        assert scale is not None and not a_mn_major and not b_mn_major and tiled_shape is None
+        if a2 is not None:
+            assert a2.dtype == torch.int8
+        if b.shape[0] > 128 or a.shape[1] % 128 or _ld(a) % 16:
+            a = _expand_int8(a, 0)
+            a2 = _expand_int8(a2, 1) if a2 is not None else None
+            w8 = False
+    assert w8 or a.dtype == torch.bfloat16
     if tiled_shape is not None:      # a is a TiledWeight payload: logical shape given
         F, K = tiled_shape
         assert tf is not None, "a tile-major weight fixes the feature-tile height"
@@ -96,6 +109,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         T, Kb = b.shape
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
     dual = a2 is not None
+    if w8 and bn is None:
+        bn = 64 if (T <= 64 or dual) else 128
     bn, splitk, stages, tf, kps = pick_tiles(F, T, K, dual, splitk, bn, stages, tf, kps)
     p = GemmParams()
     p.F, p.T, p.K = F, T, K
@@ -136,6 +151,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     p.status = _lib.status_word(a.device).data_ptr()
     # more than one token tile: the persistent kernel (double-buffered accumulator, TMA-store
     # epilogue); skinny / split-K shapes: the latency-oriented one-tile-per-CTA kernel
+    if w8:
+        _lib.check(_lib.lib().e2h_gemm_w8(C.byref(p), _lib.stream()), "e2h_gemm_w8")
+        return
     big = (persistent if persistent is not None else
            (T > bn and splitk == 1 and tf == 128 and tiled_shape is None and debug_mode == 0
             and bn >= 128))
@@ -144,6 +162,23 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
                    "e2h_gemm_persistent")
     else:
         _lib.check(_lib.lib().e2h_gemm_umma(C.byref(p), _lib.stream()), "e2h_gemm_umma")
+
+
+_INT8_SCRATCH: dict = {}
+
+
+def _expand_int8(w: torch.Tensor, which: int) -> torch.Tensor:
+    """bf16 image of an int8 weight in a per-device scratch buffer (two buffers, so that both
+    matrices of a dual GEMM can be live). Used for token counts where re-converting the weights
+    per token tile would cost more than one expansion pass."""
+    key = (w.device.index, which)
+    buf = _INT8_SCRATCH.get(key)
+    if buf is None or buf.numel() < w.numel():
+        buf = torch.empty(w.numel(), dtype=torch.bfloat16, device=w.device)
+        _INT8_SCRATCH[key] = buf
+    out = buf[: w.numel()].view(w.shape)
+    out.copy_(w)
+    return out
 
 
 def tile_weight(w: torch.Tensor, tf: int = 128) -> torch.Tensor:

@@ -80,6 +80,14 @@ def cases(T: int, B: int, S: int, ctx: int):
     out["decode_gemm_w13_swiglu"] = (lambda: gemm.linear_swiglu(xd, w1, w3), 0, 2 * FFN * DIM * 2)
     xa = _bf(64, FFN)
     out["decode_gemm_w2_residual"] = (lambda: gemm.linear_residual(xa, w2, hd), 0, FFN * DIM * 2)
+    w8 = torch.randint(-128, 128, (3 * DIM, DIM), device="cuda", dtype=torch.int8)
+    s8 = torch.rand(3 * DIM, device="cuda") * 0.01
+    w8b = torch.randint(-128, 128, (DIM, FFN // 64 * 64), device="cuda", dtype=torch.int8)
+    s8b = torch.rand(DIM, device="cuda") * 0.01
+    xa8 = _bf(64, FFN // 64 * 64)
+    out["decode_gemm_w8_wqkv"] = (lambda: gemm.linear(xd, w8, scale=s8), 0, 3 * DIM * DIM)
+    out["decode_gemm_w8_w2_residual"] = (lambda: gemm.linear_residual(xa8, w8b, hd, scale=s8b),
+                                         0, (FFN // 64 * 64) * DIM)
     kc, vc = _bf(64, HEADS, ctx, HEAD_DIM), _bf(64, HEADS, ctx, HEAD_DIM)
     qd = _bf(64, HEADS * HEAD_DIM)
     pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")
