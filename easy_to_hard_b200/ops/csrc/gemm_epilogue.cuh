@@ -48,13 +48,19 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
     case E2H_EPI_RESIDUAL: {
       __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
       const __nv_bfloat16* res = static_cast<const __nv_bfloat16*>(p.aux);
+      // all residual loads first: `out` may alias `res`, so a load placed after a store could
+      // not be moved above it and the eight round trips would run one after another
+      float r[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int t = t0 + j;
-        if (f_ok && t < p.T) {
-          const long long o = (long long)t * p.ldo + f;
-          out[o] = __float2bfloat16_rn(bf16_round(v[j]) + __bfloat162float(res[o]));
-        }
+        r[j] = (f_ok && t < p.T) ? __bfloat162float(res[(long long)t * p.ldo + f]) : 0.f;
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int t = t0 + j;
+        if (f_ok && t < p.T)
+          out[(long long)t * p.ldo + f] = __float2bfloat16_rn(bf16_round(v[j]) + r[j]);
       }
     } break;
     case E2H_EPI_SWIGLU: {
@@ -147,29 +153,38 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
       // one division per 8 tokens: (sequence, offset) advance incrementally
       int b = t0 / p.sq;
       int s = t0 - b * p.sq;
+      // rotation factors first (loads placed after the cache stores could not be hoisted)
+      float cj[8], sj[8];
+      int posj[8], bj[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        posj[j] = pos0 + s;
+        bj[j] = b;
+        if (++s == p.sq) {
+          s = 0;
+          ++b;
+        }
+        cj[j] = 1.f;
+        sj[j] = 0.f;
+        if (!is_v && f_ok && t0 + j < p.T) {
+          const __nv_bfloat162 cs = freqs2[(long long)posj[j] * (D / 2) + (d >> 1)];
+          cj[j] = __bfloat162float(cs.x);
+          sj[j] = __bfloat162float(cs.y);
+        }
+      }
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         const int t = t0 + j;
         const float x = bf16_round(v[j]);
         const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
-        const int pos = pos0 + s;
-        const int bb = b;
-        if (++s == p.sq) {
-          s = 0;
-          ++b;
-        }
         if (!(f_ok && t < p.T)) continue;
         float y = x;
-        if (!is_v) {
-          const __nv_bfloat162 cs = freqs2[(long long)pos * (D / 2) + (d >> 1)];
-          const float c = __bfloat162float(cs.x), sn = __bfloat162float(cs.y);
-          y = (d & 1) ? (x * c + partner * sn) : (x * c - partner * sn);
-        }
+        if (!is_v) y = (d & 1) ? (x * cj[j] + partner * sj[j]) : (x * cj[j] - partner * sj[j]);
         const __nv_bfloat16 yb = __float2bfloat16_rn(y);
         if (is_q) {
           static_cast<__nv_bfloat16*>(p.out)[(long long)t * p.ldo + f] = yb;
-        } else if (pos < p.smax) {
-          cache[(((long long)bb * p.n_kv + hk) * p.smax + pos) * D + d] = yb;
+        } else if (posj[j] < p.smax) {
+          cache[(((long long)bj[j] * p.n_kv + hk) * p.smax + posj[j]) * D + d] = yb;
         }
       }
     } break;

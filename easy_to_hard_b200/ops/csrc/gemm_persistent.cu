@@ -144,23 +144,29 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
-    int it = 0;
+    // stage / phase are running counters: this thread is one dependent scalar chain and an
+    // integer division per k-block is a hundred cycles of it
+    int it = 0, s = 0;
+    uint32_t ph = 0;
+    const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+    const uint32_t tiles0 = smem_u32(tiles);
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
       int ft, tt;
       tile_coords(tile, n_f, n_t, ft, tt);
       const int f0 = ft * 128, t0 = tt * BN;
       for (int kb = 0; kb < n_kb; ++kb, ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
-        if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, p.status,
-                       kStatusTimeoutEmpty)) {
+        if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) {
           ok = false;
           break;
         }
-        const uint32_t bar = smem_u32(&ctrl->full[s]);
+        const uint32_t bar = full0 + 8 * s;
         mbar_expect_tx(bar, STAGE);
-        const uint32_t a_dst = smem_u32(tiles + (size_t)s * STAGE);
+        const uint32_t a_dst = tiles0 + s * STAGE;
+        if (++s == stages) {
+          s = 0;
+          ph ^= 1;
+        }
         const int k0 = kb * 64;
         if (!p.a_mn_major) {
           tma_load_2d(a_dst, &tmA, k0, f0, bar);
@@ -199,7 +205,14 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
     const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u;
     const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
-    int it = 0, tcount = 0;
+    // descriptors: constant high word, base low words once, then one add per instruction
+    const uint32_t d_hi = sw128_desc_hi(1024);
+    const uint32_t a_lo0 = sw128_desc_lo(smem_u32(tiles), a_lbo);
+    const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles) + A_BYTES * (DUAL ? 2 : 1), b_lbo);
+    const uint32_t a_ks = a_kstep >> 4, b_ks = b_kstep >> 4;
+    const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+    int tcount = 0, s = 0;
+    uint32_t ph = 0, st_lo = 0;
     bool ok = true;
     for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
       const int acc = tcount & 1;
@@ -209,26 +222,28 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       if (!ok) break;
       tc_fence_after();
       const uint32_t d0 = tmem_base + acc * ACC_COLS;
-      for (int kb = 0; kb < n_kb; ++kb, ++it) {
-        const int s = it % stages;
-        const uint32_t ph = (it / stages) & 1;
-        ok = mbar_wait(smem_u32(&ctrl->full[s]), ph, abort_flag, p.status, kStatusTimeoutFull);
+      uint32_t accum = 0;   // the first instruction of a tile overwrites the accumulator
+      for (int kb = 0; kb < n_kb; ++kb) {
+        ok = mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, kStatusTimeoutFull);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t a_base = smem_u32(tiles + (size_t)s * STAGE);
-        const uint32_t b_base = a_base + A_BYTES * (DUAL ? 2 : 1);
+        const uint32_t a_lo = a_lo0 + st_lo, b_lo = b_lo0 + st_lo;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t bdesc = make_sw128_desc(b_base + k * b_kstep, b_lbo, 1024);
-          const uint64_t adesc = make_sw128_desc(a_base + k * a_kstep, a_lbo, 1024);
-          const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
-          umma_f16(d0, adesc, bdesc, idesc, accum);
-          if (DUAL) {
-            const uint64_t a2desc = make_sw128_desc(a_base + A_BYTES + k * a_kstep, a_lbo, 1024);
-            umma_f16(d0 + BN, a2desc, bdesc, idesc, accum);
-          }
+          umma_f16_lohi(d0, a_lo + k * a_ks, d_hi, b_lo + k * b_ks, d_hi, idesc, accum);
+          if (DUAL)
+            umma_f16_lohi(d0 + BN, a_lo + (A_BYTES >> 4) + k * a_ks, d_hi, b_lo + k * b_ks, d_hi,
+                          idesc, accum);
+          accum = 1;
         }
-        umma_commit(smem_u32(&ctrl->empty[s]));
+        umma_commit(empty0 + 8 * s);
+        if (++s == stages) {
+          s = 0;
+          st_lo = 0;
+          ph ^= 1;
+        } else {
+          st_lo += STAGE >> 4;
+        }
       }
       if (ok) umma_commit(smem_u32(&ctrl->tmem_full[acc]));
     }

@@ -56,6 +56,14 @@ struct E2hGemmParams {
   int* signal[8];        // flag words (local or peer-GPU memory), one per tensor-parallel rank
   unsigned int* ticket;  // grid completion counter (local, zero between launches)
   int a_tiled;           // A (and A2) stored tile-major: [F/tf][ceil(K/64)][tf][64], zero padded
+  // work-split ("stream-K") skinny GEMM only
+  int sk_ctas;           // CTAs the (feature tile x k-group) units are divided over (0: one per SM)
+  int sk_smem_kb;        // shared-memory budget per CTA in KiB (0: half an SM, two CTAs resident)
+  float* sk_ws;          // fp32 partial-tile workspace
+  long long sk_ws_bytes; // its capacity
+  unsigned int* sk_count;  // one arrival counter per feature tile, zero between launches
+  int sk_count_len;
+  int sk_slots;          // partial-tile slots reserved per feature tile (set by the entry point)
 };
 
 #ifdef __cplusplus
@@ -63,6 +71,7 @@ extern "C" {
 #endif
 // Returns 0 on success, a cudaError_t / negative code otherwise. Launches on `stream`.
 int e2h_gemm_umma(const E2hGemmParams* p, void* stream);
+int e2h_gemm_streamk(const E2hGemmParams* p, void* stream);
 #ifdef __cplusplus
 }
 #endif

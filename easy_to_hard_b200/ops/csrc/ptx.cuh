@@ -195,6 +195,27 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// Same with the two 64-bit shared-memory descriptors given as (low, high) words. The single
+// issuing thread runs a dependent scalar chain, so every instruction it spends on building a
+// descriptor is ~5 cycles the tensor pipe may sit idle for: kernels keep the high word (layout
+// constants) and a base low word (address >> 4 | LBO) in registers and only add the tile /
+// k-step offset (in 16-byte units) to the low word per instruction. The 14-bit address field
+// cannot carry into the LBO field while addresses stay inside the 228 KiB of shared memory.
+__device__ __forceinline__ void umma_f16_lohi(uint32_t d_tmem, uint32_t a_lo, uint32_t a_hi,
+                                              uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      ".reg .b64 da, db;\n"
+      "setp.ne.b32 p, %6, 0;\n"
+      "mov.b64 da, {%1, %2};\n"
+      "mov.b64 db, {%3, %4};\n"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n"
+      "}\n"
+      ::"r"(d_tmem), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
 // Arrive on an mbarrier of this CTA once every UMMA issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
@@ -244,6 +265,13 @@ __device__ __forceinline__ uint64_t make_sw128_desc(uint32_t saddr, uint32_t lbo
   d |= static_cast<uint64_t>(1) << 46;  // descriptor version of sm_100
   d |= static_cast<uint64_t>(2) << 61;  // SWIZZLE_128B
   return d;
+}
+// The two words of the same descriptor, for umma_f16_lohi.
+__device__ __forceinline__ uint32_t sw128_desc_lo(uint32_t saddr, uint32_t lbo_bytes) {
+  return ((saddr & 0x3FFFF) >> 4) | (((lbo_bytes >> 4) & 0x3FFF) << 16);
+}
+__device__ __forceinline__ uint32_t sw128_desc_hi(uint32_t sbo_bytes) {
+  return ((sbo_bytes >> 4) & 0x3FFF) | (1u << 14) | (2u << 29);
 }
 // Instruction descriptor for kind::f16 with bf16 A/B and fp32 D.
 __host__ __device__ constexpr uint32_t make_idesc_bf16(int m, int n, int a_mn_major,

@@ -8,6 +8,7 @@ natural call for any token count.
 from __future__ import annotations
 
 import ctypes as C
+import os
 from typing import Optional
 
 import torch
@@ -80,7 +81,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          rope: Optional[dict] = None, pdl: bool = False, tf: Optional[int] = None,
          tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
          signal=None, ticket: Optional[torch.Tensor] = None,
-         persistent: Optional[bool] = None) -> None:
+         persistent: Optional[bool] = None, streamk: Optional[bool] = None, sk_ctas: int = 0,
+         sk_smem_kb: int = 0) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T]).
     An int8 ``a`` (weight-only quantisation; ``scale`` holds the per-feature scales) streams as
     int8 through the converting kernel for up to 128 tokens and is expanded to a scratch bf16
@@ -111,6 +113,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     dual = a2 is not None
     if w8 and bn is None:
         bn = 64 if (T <= 64 or dual) else 128
+    sk_ok = (not w8 and not a_mn_major and not b_mn_major and tiled_shape is None and T <= 128
+             and K % 64 == 0 and splitk is None and tf is None)
+    use_sk = sk_ok and (streamk if streamk is not None else STREAMK_DEFAULT)
+    if use_sk:
+        sk_bn = bn if bn in (32, 64, 128) and bn >= T else (32 if T <= 32 else 64 if T <= 64 else 128)
+        sk_kps, sk_stages = kps, stages
     bn, splitk, stages, tf, kps = pick_tiles(F, T, K, dual, splitk, bn, stages, tf, kps)
     p = GemmParams()
     p.F, p.T, p.K = F, T, K
@@ -154,6 +162,14 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     if w8:
         _lib.check(_lib.lib().e2h_gemm_w8(C.byref(p), _lib.stream()), "e2h_gemm_w8")
         return
+    if use_sk:
+        ws, count = _sk_workspace(a.device)
+        p.bn, p.kps, p.stages, p.splitk, p.tf = sk_bn, sk_kps, sk_stages, 1, 128
+        p.sk_ctas, p.sk_smem_kb = sk_ctas, sk_smem_kb
+        p.sk_ws, p.sk_ws_bytes = ws.data_ptr(), ws.numel() * 4
+        p.sk_count, p.sk_count_len = count.data_ptr(), count.numel()
+        _lib.check(_lib.lib().e2h_gemm_streamk(C.byref(p), _lib.stream()), "e2h_gemm_streamk")
+        return
     big = (persistent if persistent is not None else
            (T > bn and splitk == 1 and tf == 128 and tiled_shape is None and debug_mode == 0
             and bn >= 128))
@@ -165,6 +181,24 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
 
 
 _INT8_SCRATCH: dict = {}
+_SK_WS: dict = {}
+# skinny GEMMs (one token tile of at most 128 tokens, K-major operands) may take the work-split
+# kernel (``streamk=True`` per call, or E2H_STREAMK=1 for every eligible call)
+STREAMK_DEFAULT = os.environ.get("E2H_STREAMK", "0") == "1"
+
+
+def _sk_workspace(device):
+    """Per-device partial-tile workspace (fp32, stays in L2) and per-tile arrival counters of the
+    work-split GEMM. One launch at a time may use them: all launches of a device go to one
+    stream (the decode engine's), which orders them."""
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    v = _SK_WS.get(key)
+    if v is None:
+        v = (torch.empty(16 << 20, dtype=torch.float32, device=device),
+             torch.zeros(4096, dtype=torch.int32, device=device))
+        _SK_WS[key] = v
+    return v
+
 
 
 def _expand_int8(w: torch.Tensor, which: int) -> torch.Tensor:
