@@ -235,8 +235,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t o = (kk / 4) * kHalfBytes + (kk % 4) * 32;
-        umma_f16(tmem_s, make_sw128_desc(qa + o, 16, 1024), make_sw128_desc(ka + o, 16, 1024),
-                 idesc_s, kk > 0 ? 1u : 0u);
+        umma_f16_lohi(tmem_s, sw128_desc_lo(qa, 16) + ((o) >> 4), sw128_desc_hi(1024), sw128_desc_lo(ka, 16) + ((o) >> 4), sw128_desc_hi(1024),
+                      idesc_s, kk > 0 ? 1u : 0u);
       }
       umma_commit(smem_u32(&ctrl->k_empty[s]));
       umma_commit(smem_u32(&ctrl->s_full));
@@ -261,10 +261,9 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
       const uint32_t va = smem_u32(v_s + s * kTileBytes);
 #pragma unroll
       for (int kk = 0; kk < kBK / 16; ++kk) {
-        const uint64_t adesc =
-            make_sw128_desc(pa + (kk / 4) * kHalfBytes + (kk % 4) * 32, 16, 1024);
-        const uint64_t bdesc = make_sw128_desc(va + kk * 2048, kHalfBytes, 1024);
-        umma_f16(tmem_o, adesc, bdesc, idesc_o, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_f16_lohi(tmem_o, sw128_desc_lo(pa, 16) + (((kk / 4) * kHalfBytes + (kk % 4) * 32) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(va, kHalfBytes) + ((kk * 2048) >> 4), sw128_desc_hi(1024), idesc_o,
+                      (it > 0 || kk > 0) ? 1u : 0u);
       }
       umma_commit(smem_u32(&ctrl->v_empty[s]));
       umma_commit(smem_u32(&ctrl->p_empty[it & 1]));
@@ -571,13 +570,15 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
-        umma_f16(tm_s, make_sw128_desc(qa + o, 16, 1024), make_sw128_desc(ka + o, 16, 1024), id_kk,
+        umma_f16_lohi(tm_s, sw128_desc_lo(qa, 16) + ((o) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(ka, 16) + ((o) >> 4), sw128_desc_hi(1024), id_kk,
                  kk > 0 ? 1u : 0u);
       }
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
-        umma_f16(tm_dp, make_sw128_desc(da + o, 16, 1024), make_sw128_desc(va + o, 16, 1024), id_kk,
+        umma_f16_lohi(tm_dp, sw128_desc_lo(da, 16) + ((o) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(va, 16) + ((o) >> 4), sw128_desc_hi(1024), id_kk,
                  kk > 0 ? 1u : 0u);
       }
       umma_commit(smem_u32(&ctrl->sdp_full));
@@ -588,10 +589,10 @@ flash_bwd_dkdv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_cons
 #pragma unroll
       for (int kk = 0; kk < kBQ / 16; ++kk) {   // contraction over the 128 queries
         const uint32_t acc = (it > 0 || kk > 0) ? 1u : 0u;
-        umma_f16(tm_dv, make_sw128_desc(pa + kk * 2048, kHalf, 1024),
-                 make_sw128_desc(da + kk * 2048, kHalf, 1024), id_mm, acc);
-        umma_f16(tm_dk, make_sw128_desc(sa + kk * 2048, kHalf, 1024),
-                 make_sw128_desc(qa + kk * 2048, kHalf, 1024), id_mm, acc);
+        umma_f16_lohi(tm_dv, sw128_desc_lo(pa, kHalf) + ((kk * 2048) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(da, kHalf) + ((kk * 2048) >> 4), sw128_desc_hi(1024), id_mm, acc);
+        umma_f16_lohi(tm_dk, sw128_desc_lo(sa, kHalf) + ((kk * 2048) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(qa, kHalf) + ((kk * 2048) >> 4), sw128_desc_hi(1024), id_mm, acc);
       }
       umma_commit(smem_u32(&ctrl->it_empty));
     }
@@ -776,13 +777,15 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
-        umma_f16(tm_s, make_sw128_desc(qa + o, 16, 1024), make_sw128_desc(ka + o, 16, 1024), id_kk,
+        umma_f16_lohi(tm_s, sw128_desc_lo(qa, 16) + ((o) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(ka, 16) + ((o) >> 4), sw128_desc_hi(1024), id_kk,
                  kk > 0 ? 1u : 0u);
       }
 #pragma unroll
       for (int kk = 0; kk < D / 16; ++kk) {
         const uint32_t o = (kk / 4) * kHalf + (kk % 4) * 32;
-        umma_f16(tm_dp, make_sw128_desc(da + o, 16, 1024), make_sw128_desc(va + o, 16, 1024), id_kk,
+        umma_f16_lohi(tm_dp, sw128_desc_lo(da, 16) + ((o) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(va, 16) + ((o) >> 4), sw128_desc_hi(1024), id_kk,
                  kk > 0 ? 1u : 0u);
       }
       umma_commit(smem_u32(&ctrl->sdp_full));
@@ -792,8 +795,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
       const uint32_t sa = smem_u32(ds_s);
 #pragma unroll
       for (int kk = 0; kk < kBK / 16; ++kk) {   // contraction over the 128 keys
-        umma_f16(tm_dq, make_sw128_desc(sa + (kk / 4) * kHalf + (kk % 4) * 32, 16, 1024),
-                 make_sw128_desc(ka + kk * 2048, kHalf, 1024), id_dq, (it > 0 || kk > 0) ? 1u : 0u);
+        umma_f16_lohi(tm_dq, sw128_desc_lo(sa, 16) + (((kk / 4) * kHalf + (kk % 4) * 32) >> 4), sw128_desc_hi(1024),
+                      sw128_desc_lo(ka, kHalf) + ((kk * 2048) >> 4), sw128_desc_hi(1024), id_dq, (it > 0 || kk > 0) ? 1u : 0u);
       }
       umma_commit(smem_u32(&ctrl->it_empty));
     }

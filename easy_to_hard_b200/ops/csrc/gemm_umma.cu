@@ -128,13 +128,21 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     // ---------------- TMA producer ----------------
     const uint64_t pol_a = policy_evict_first();
     int armed = 0;
+    // stage / phase as running counters: this thread is one dependent scalar chain, a division
+    // per iteration costs it on the order of a hundred cycles
+    int s = 0;
+    uint32_t ph = 0;
+    const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+    const uint32_t tiles0 = smem_u32(tiles);
+    const uint32_t stage_sz = kps * Plan::stage_bytes;
     for (int it = 0; it < n_it; ++it) {
-      const int s = it % stages;
-      const uint32_t ph = (it / stages) & 1;
-      if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, p.status,
-                     kStatusTimeoutEmpty))
-        break;
-      const uint32_t bar = smem_u32(&ctrl->full[s]);
+      if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+      const uint32_t bar = full0 + 8 * s;
+      const uint32_t st0 = tiles0 + s * stage_sz;
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1;
+      }
       if (p.debug_mode == 2 || p.debug_mode == 4) {  // timing experiment: no loads
         mbar_arrive(bar);
         armed = it + 1;
@@ -145,9 +153,8 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // one 3-D box per operand brings kps k-blocks (rows x 64 x kps): two TMA instructions
         // per stage instead of 2*kps. The box is always full size (out-of-range k-blocks are
         // zero filled), k-blocks past this CTA's range are loaded but never multiplied.
-        uint8_t* st = tiles + (size_t)s * kps * Plan::stage_bytes;
         const int kb = kb_begin + it * kps;
-        const uint32_t a_dst = smem_u32(st);
+        const uint32_t a_dst = st0;
         mbar_expect_tx(bar, kps * Plan::stage_bytes);
         tma_load_3d_hint(a_dst, &tmA, 0, f0, kb, bar, pol_a);
         if (DUAL) tma_load_3d_hint(a_dst + kps * Plan::a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
@@ -157,10 +164,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       mbar_expect_tx(bar, kcount * Plan::stage_bytes);
       for (int kk = 0; kk < kcount; ++kk) {
-        uint8_t* st = tiles + ((size_t)s * kps + kk) * Plan::stage_bytes;
         const int kb = kb_begin + it * kps + kk;
         const int k0 = kb * kTileK;
-        const uint32_t a_dst = smem_u32(st);
+        const uint32_t a_dst = st0 + kk * Plan::stage_bytes;
         if (p.a_tiled) {
           // tile-major weight: tile (feature tile, k block) is one contiguous TF x 64 block
           const int row = (blockIdx.x * kb_total + kb) * TF;
@@ -200,40 +206,53 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
     const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u;
     const uint32_t b_lbo = p.b_mn_major ? 8192u : 16u;
-    constexpr int NACC = Plan::nacc;
+    static_assert(Plan::nacc == 1, "one accumulation chain");
+    // descriptors: constant high word, base low words once, one add per instruction; stage and
+    // phase are running counters (no division in this dependent scalar chain)
+    const uint32_t d_hi = sw128_desc_hi(1024);
+    const uint32_t a_lo0 = sw128_desc_lo(smem_u32(tiles), a_lbo);
+    const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles), b_lbo);
+    const uint32_t a_ks = a_kstep >> 4, b_ks = b_kstep >> 4;
+    const uint32_t a2_off = (kps * Plan::a_bytes) >> 4;
+    const uint32_t b_off = (kps * Plan::a_bytes * (DUAL ? 2 : 1)) >> 4;
+    const uint32_t stage_step = (kps * Plan::stage_bytes) >> 4;
+    const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     bool ok = true;
+    int s = 0;
+    uint32_t ph = 0, st_lo = 0, accf = 0;
     for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it % stages;
-      const uint32_t ph = (it / stages) & 1;
-      ok = mbar_wait(smem_u32(&ctrl->full[s]), ph, abort_flag, p.status, kStatusTimeoutFull);
+      ok = mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, kStatusTimeoutFull);
       if (!ok) break;
       tc_fence_after();
+      const uint32_t e_bar = empty0 + 8 * s;
+      const uint32_t cur_lo = st_lo;
+      if (++s == stages) {
+        s = 0;
+        st_lo = 0;
+        ph ^= 1;
+      } else {
+        st_lo += stage_step;
+      }
       if (p.debug_mode == 1 || p.debug_mode == 4) {  // timing experiment: no tensor-core work
-        mbar_arrive(smem_u32(&ctrl->empty[s]));
+        mbar_arrive(e_bar);
         continue;
       }
       const int kcount = min(kps, n_kb - it * kps);
+      // kps == 1: stage = [A][A2][B]; kps > 1: stage = [A x kps][A2 x kps][B x kps]
+      uint32_t a_lo = a_lo0 + cur_lo, b_lo = b_lo0 + cur_lo + b_off;
       for (int kk = 0; kk < kcount; ++kk) {
-        // kps == 1: stage = [A][A2][B]; kps > 1: stage = [A x kps][A2 x kps][B x kps]
-        const uint32_t st_base = smem_u32(tiles + (size_t)s * kps * Plan::stage_bytes);
-        const uint32_t a_base = st_base + kk * Plan::a_bytes;
-        const uint32_t a2_base = a_base + kps * Plan::a_bytes;
-        const uint32_t b_base =
-            st_base + kps * Plan::a_bytes * (DUAL ? 2 : 1) + kk * Plan::b_bytes;
 #pragma unroll
         for (int k = 0; k < kTileK / kUmmaK; ++k) {
-          const uint64_t bdesc = make_sw128_desc(b_base + k * b_kstep, b_lbo, 1024);
-          const uint64_t adesc = make_sw128_desc(a_base + k * a_kstep, a_lbo, 1024);
-          const int chain = k % NACC;
-          const uint32_t acc = (it > 0 || kk > 0 || k >= NACC) ? 1u : 0u;
-          umma_f16(tmem_base + chain * BN, adesc, bdesc, idesc, acc);
-          if (DUAL) {
-            const uint64_t a2desc = make_sw128_desc(a2_base + k * a_kstep, a_lbo, 1024);
-            umma_f16(tmem_base + (NACC + chain) * BN, a2desc, bdesc, idesc, acc);
-          }
+          umma_f16_lohi(tmem_base, a_lo + k * a_ks, d_hi, b_lo + k * b_ks, d_hi, idesc, accf);
+          if (DUAL)
+            umma_f16_lohi(tmem_base + BN, a_lo + a2_off + k * a_ks, d_hi, b_lo + k * b_ks, d_hi,
+                          idesc, accf);
+          accf = 1;
         }
+        a_lo += Plan::a_bytes >> 4;
+        b_lo += Plan::b_bytes >> 4;
       }
-      umma_commit(smem_u32(&ctrl->empty[s]));  // stage reusable once these UMMAs have read it
+      umma_commit(e_bar);  // stage reusable once these UMMAs have read it
     }
     umma_commit(smem_u32(&ctrl->tmem_full));
   }

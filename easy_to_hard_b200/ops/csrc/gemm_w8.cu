@@ -145,14 +145,18 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // ---------------- TMA producer ----------------
     const uint64_t pol_a = policy_evict_first();
     int armed = 0;
+    int s = 0;
+    uint32_t ph = 0;
+    const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
+    const uint32_t tiles0 = smem_u32(tiles);
     for (int it = 0; it < n_it; ++it) {
-      const int s = it % stages;
-      const uint32_t ph = (it / stages) & 1;
-      if (!mbar_wait(smem_u32(&ctrl->empty[s]), ph ^ 1, abort_flag, p.status,
-                     kStatusTimeoutEmpty))
-        break;
-      const uint32_t bar = smem_u32(&ctrl->full[s]);
-      const uint32_t st = smem_u32(tiles + (size_t)s * STAGE);
+      if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
+      const uint32_t bar = full0 + 8 * s;
+      const uint32_t st = tiles0 + s * STAGE;
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1;
+      }
       const int kb = kb_begin + it * kW8Kps;
       if (p.debug_mode & 2) {          // timing experiment without the loads
         mbar_arrive(bar);
@@ -178,34 +182,45 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   } else if (warp == 1 && lane == 0) {
     // ---------------- UMMA issuer ----------------
     const uint32_t idesc = make_idesc_bf16(128, BN, 0, 0);
+    // descriptors: constant high word, base low words once, one add per instruction; stage and
+    // phase are running counters (no division in this dependent scalar chain)
+    const uint32_t d_hi = sw128_desc_hi(1024);
+    const uint32_t a_lo0 = sw128_desc_lo(smem_u32(conv), 16);
+    const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles) + kW8Kps * kA8Bytes * NMAT, 16);
+    const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     bool ok = true;
+    int s = 0;
+    uint32_t ph = 0, st_lo = 0, accf = 0;
     for (int it = 0; it < n_it && ok; ++it) {
-      const int s = it % stages, c = it % kW8Conv;
-      ok = mbar_wait(smem_u32(&ctrl->full[s]), (it / stages) & 1, abort_flag, p.status,
-                     kStatusTimeoutFull) &&
+      const int c = it % kW8Conv;
+      ok = mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, kStatusTimeoutFull) &&
            mbar_wait(smem_u32(&ctrl->conv_full[c]), (it / kW8Conv) & 1, abort_flag, p.status,
                      kStatusTimeoutFull);
       if (!ok) break;
       tc_fence_after();
-      const uint32_t st = smem_u32(tiles + (size_t)s * STAGE);
-      const uint32_t cv = smem_u32(conv + (size_t)c * CONV);
       const int kcount = (p.debug_mode & 4) ? 0 : min(kW8Kps, n_kb - it * kW8Kps);
+      uint32_t a_lo = a_lo0 + c * (CONV >> 4), b_lo = b_lo0 + st_lo;
       for (int kk = 0; kk < kcount; ++kk) {
-        const uint32_t a_base = cv + kk * kA16Bytes;
-        const uint32_t a2_base = a_base + kW8Kps * kA16Bytes;
-        const uint32_t b_base = st + kW8Kps * kA8Bytes * NMAT + kk * B_BYTES;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          const uint64_t bdesc = make_sw128_desc(b_base + k * 32, 16, 1024);
-          const uint32_t acc = (it > 0 || kk > 0 || k > 0) ? 1u : 0u;
-          umma_f16(tmem_base, make_sw128_desc(a_base + k * 32, 16, 1024), bdesc, idesc, acc);
+          umma_f16_lohi(tmem_base, a_lo + 2 * k, d_hi, b_lo + 2 * k, d_hi, idesc, accf);
           if (DUAL)
-            umma_f16(tmem_base + BN, make_sw128_desc(a2_base + k * 32, 16, 1024), bdesc, idesc,
-                     acc);
+            umma_f16_lohi(tmem_base + BN, a_lo + ((kW8Kps * kA16Bytes) >> 4) + 2 * k, d_hi,
+                          b_lo + 2 * k, d_hi, idesc, accf);
+          accf = 1;
         }
+        a_lo += kA16Bytes >> 4;
+        b_lo += B_BYTES >> 4;
       }
-      umma_commit(smem_u32(&ctrl->empty[s]));        // activation tile (and int8 tile) reusable
+      umma_commit(empty0 + 8 * s);                   // activation tile (and int8 tile) reusable
       umma_commit(smem_u32(&ctrl->conv_empty[c]));   // converted tile reusable
+      if (++s == stages) {
+        s = 0;
+        st_lo = 0;
+        ph ^= 1;
+      } else {
+        st_lo += STAGE >> 4;
+      }
     }
     umma_commit(smem_u32(&ctrl->tmem_full));
   }
@@ -221,17 +236,25 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     const int row = ct & 127, half = ct >> 7;
     const int sw = row & 7;                           // 128B-swizzle term of this row
     bool ok = true;
+    int s = 0;
+    uint32_t ph = 0;
     for (int it = 0; it < n_it; ++it) {
-      const int s = it % stages, c = it % kW8Conv;
+      const int c = it % kW8Conv;
+      const int s_cur = s;
+      const uint32_t ph_cur = ph;
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1;
+      }
       // every converter thread waits itself (one polling lane per warp plus a shuffle measured
       // 10% slower: the acquire has to be re-established for the other lanes anyway)
       if (ok)
-        ok = mbar_wait(smem_u32(&ctrl->full[s]), (it / stages) & 1, abort_flag, p.status,
+        ok = mbar_wait(smem_u32(&ctrl->full[s_cur]), ph_cur, abort_flag, p.status,
                        kStatusTimeoutFull) &&
              mbar_wait(smem_u32(&ctrl->conv_empty[c]), ((it / kW8Conv) & 1) ^ 1, abort_flag,
                        p.status, kStatusTimeoutEmpty);
       if (ok && !(p.debug_mode & 1)) {   // debug_mode 1: timing experiment without the conversion
-        const uint8_t* st = tiles + (size_t)s * STAGE;
+        const uint8_t* st = tiles + (size_t)s_cur * STAGE;
         uint8_t* cv = conv + (size_t)c * CONV;
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {

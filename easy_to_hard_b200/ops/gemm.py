@@ -165,7 +165,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     if use_sk:
         ws, count = _sk_workspace(a.device)
         p.bn, p.kps, p.stages, p.splitk, p.tf = sk_bn, sk_kps, sk_stages, 1, 128
-        p.sk_ctas, p.sk_smem_kb = sk_ctas, sk_smem_kb
+        p.sk_ctas, p.sk_smem_kb = sk_ctas, sk_smem_kb or STREAMK_SMEM_KB
         p.sk_ws, p.sk_ws_bytes = ws.data_ptr(), ws.numel() * 4
         p.sk_count, p.sk_count_len = count.data_ptr(), count.numel()
         _lib.check(_lib.lib().e2h_gemm_streamk(C.byref(p), _lib.stream()), "e2h_gemm_streamk")
@@ -185,6 +185,7 @@ _SK_WS: dict = {}
 # skinny GEMMs (one token tile of at most 128 tokens, K-major operands) may take the work-split
 # kernel (``streamk=True`` per call, or E2H_STREAMK=1 for every eligible call)
 STREAMK_DEFAULT = os.environ.get("E2H_STREAMK", "0") == "1"
+STREAMK_SMEM_KB = int(os.environ.get("E2H_STREAMK_SMEM_KB", "0"))   # 0: half an SM per CTA
 
 
 def _sk_workspace(device):
