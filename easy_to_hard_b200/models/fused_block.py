@@ -234,10 +234,11 @@ def can_fuse(model, idx: torch.Tensor) -> bool:
 
 
 @torch.no_grad()
-def transformer_hidden(model, idx: torch.Tensor) -> torch.Tensor:
+def transformer_hidden(model, idx: torch.Tensor, final_norm: bool = True) -> torch.Tensor:
     """Fully-causal forward of the whole stack without a KV cache (scoring, log-probs of given
-    sequences): token ids [B, S] -> final-norm hidden states [B, S, dim] bf16. Right padding is
-    harmless under the causal mask; the caller ignores padded positions."""
+    sequences): token ids [B, S] -> final-norm hidden states [B, S, dim] bf16 (the residual
+    stream before the final norm with ``final_norm=False``, for heads that fuse the norm). Right
+    padding is harmless under the causal mask; the caller ignores padded positions."""
     B, S = idx.shape
     if model.freqs_cis is None or model.max_seq_length < S or model.max_batch_size < B:
         model.setup_caches(B, S, kv_cache=False)
@@ -248,5 +249,6 @@ def transformer_hidden(model, idx: torch.Tensor) -> torch.Tensor:
     x = model.embed(idx).to(torch.bfloat16).reshape(B * S, -1)
     for blk in model.layers:
         x, _ = block_forward(x, block_weights(blk), model.freqs_cis, pos, shape)
-    x = Fn.rmsnorm(x, model.norm.weight.to(torch.bfloat16), model.config.norm_eps)
+    if final_norm:
+        x = Fn.rmsnorm(x, model.norm.weight.to(torch.bfloat16), model.config.norm_eps)
     return x.view(B, S, -1)

@@ -55,8 +55,38 @@ class RewardModel(nn.Module):
         head = self.backbone_model.output
         return tp_mod.reward_head_forward(head, hidden).float().mean(dim=-1)
 
+    def _fused_rewards(self, idx: Tensor, eos_pos: Optional[Tensor]) -> Optional[Tensor]:
+        """Scoring on CUDA without autograd: the fused block stack, then ONE kernel for the final
+        norm, the 2-row head, the mean and the gather at ``eos_pos`` (only those rows are
+        normalised and multiplied). A head sharded over its input dimension contributes fp32
+        partial dots that are summed over the tensor-parallel group before the rounding."""
+        from . import fused_block
+        from ..ops import functional as Fn
+        bb = self.backbone_model
+        head = bb.output
+        w = getattr(head, "weight", None)
+        if (torch.is_grad_enabled() or not idx.is_cuda or not isinstance(w, Tensor)
+                or w.dtype != torch.bfloat16 or w.shape[0] != 2 or not fused_block.can_fuse(bb, idx)):
+            return None
+        B, S = idx.shape
+        hidden = fused_block.transformer_hidden(bb, idx, final_norm=False).view(B * S, -1)
+        index = None
+        if eos_pos is not None:
+            index = (torch.arange(B, device=idx.device) * S + eos_pos.to(idx.device).long()).int()
+        sharded = getattr(head, "tp_row_parallel", False)
+        k0 = tp_mod.groups.get_model_parallel_rank() * w.shape[1] if sharded else 0
+        reward, dots, _ = Fn.reward_head(hidden, bb.norm.weight, w, bb.config.norm_eps,
+                                         index=index, k0=k0, finalize=not sharded)
+        if sharded:
+            dots = tp_mod.coll.reduce_from_tp(dots)
+            reward = dots.to(torch.bfloat16).float().mean(dim=-1)
+        return reward if eos_pos is not None else reward.view(B, S)
+
     def forward(self, idx: Tensor, eos_pos: Optional[Tensor] = None) -> Tensor:
         bb = self.backbone_model
+        fused = self._fused_rewards(idx, eos_pos)
+        if fused is not None:
+            return fused
         if bb.freqs_cis is None or bb.max_seq_length < idx.size(-1) \
                 or bb.max_batch_size < idx.size(0):
             bb.setup_caches(idx.size(0), idx.size(-1), kv_cache=False)

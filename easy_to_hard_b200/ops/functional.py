@@ -182,3 +182,39 @@ def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int], se
         _lib.ptr(n_unfinished), _lib.ptr(ticket), _s())
     _lib.check(rc, "sample")
     return next_tok
+
+
+def reward_head(x: torch.Tensor, norm_weight: torch.Tensor, head_weight: torch.Tensor, eps: float,
+                *, index: Optional[torch.Tensor] = None, k0: int = 0, finalize: bool = True,
+                labels: Optional[torch.Tensor] = None, weights: Optional[torch.Tensor] = None):
+    """Final RMSNorm + 2-row reward head + mean (+ weighted BCE-with-logits) in one kernel.
+
+    ``x`` [rows, dim] bf16 is the residual stream BEFORE the final norm; ``head_weight`` [2, klen]
+    holds columns ``[k0, k0 + klen)`` of the head (the whole head when unsharded). ``index``
+    (int32 [n]) picks the rows to score. Returns ``(reward [n] fp32, dots [n, 2] fp32,
+    loss_acc [2] fp32 or None)``: with ``finalize=False`` (a tensor-parallel slice) only ``dots``
+    (fp32 partial sums) is meaningful and the caller reduces it over the ranks.
+    Reference semantics: models/reward_model.py:80-88, train_rm_pointwise.py:101-110."""
+    assert x.is_cuda and x.dtype == torch.bfloat16 and x.dim() == 2 and x.stride(1) == 1
+    dim = x.shape[1]
+    head_weight = head_weight.to(torch.bfloat16)
+    if head_weight.stride(1) != 1:
+        head_weight = head_weight.contiguous()
+    klen = head_weight.shape[1]
+    n = int(index.numel()) if index is not None else x.shape[0]
+    if index is not None:
+        index = index.to(torch.int32).contiguous()
+    reward = torch.empty(n, dtype=torch.float32, device=x.device)
+    dots = torch.empty(n, 2, dtype=torch.float32, device=x.device)
+    acc = None
+    if labels is not None:
+        acc = torch.zeros(2, dtype=torch.float32, device=x.device)
+        labels = labels.to(torch.float32).contiguous()
+        weights = weights.to(torch.float32).contiguous() if weights is not None else None
+    nw = norm_weight.to(torch.bfloat16).contiguous()
+    rc = _lib.lib().e2h_reward_head(
+        x.data_ptr(), x.stride(0), nw.data_ptr(), head_weight.data_ptr(), head_weight.stride(0),
+        dim, k0, klen, eps, _lib.ptr(index), n, dots.data_ptr(), reward.data_ptr(),
+        int(finalize), _lib.ptr(labels), _lib.ptr(weights), _lib.ptr(acc), _s())
+    _lib.check(rc, "reward_head")
+    return reward, dots, acc
