@@ -54,7 +54,9 @@ class DecodeEngine:
         blk0 = model.layers[0].attention
         self.n_head, self.n_kv, self.D = blk0.n_head, blk0.n_local_heads, blk0.head_dim
         self.dim = model.tok_embeddings.weight.shape[1]
-        self.ffn = model.layers[0].feed_forward.w2.weight.shape[1]
+        w2 = model.layers[0].feed_forward.w2          # packed int4 weights are not [out, in]
+        self.ffn = getattr(w2, "origin_in_features", None) or getattr(w2, "in_features", None) \
+            or w2.weight.shape[1]
         self.vocab = model.output.weight.shape[0]
         self.eps = cfg.norm_eps
         if reduce == "auto":
@@ -98,8 +100,10 @@ class DecodeEngine:
         read them. bf16 modules hand out their own tensor (in-place updates of the model, e.g.
         the PPO rollout sync, are seen by captured graphs). Weight-only int8 stays int8 (the
         decode GEMM expands it to bf16 inside the SM) with its scales applied in the GEMM
-        epilogue, exactly where the reference multiplies (models/quantize.py:397-398);
-        int4-g128 (tinygemm packing) is unpacked and dequantised once."""
+        epilogue, exactly where the reference multiplies (models/quantize.py:397-398).
+        Group-wise int4 (tinygemm packing in the checkpoint) is re-packed once into the
+        row-major nibble layout of ``ops.gemm.Int4Weight`` and streams as int4; group sizes the
+        kernel does not take (below 64) are dequantised once instead."""
         w = linear.weight
         if w.dtype == torch.int8 and hasattr(linear, "scales"):
             # stays int8 in memory: ops.gemm streams it through the converting kernel
@@ -107,11 +111,17 @@ class DecodeEngine:
         if w.dtype == torch.int32 and hasattr(linear, "scales_and_zeros"):
             from . import quantize as qz
             q = qz.unpack_int4_tinygemm(w, linear.inner_k_tiles)
-            full = qz.group_dequantize_tensor(q, linear.scales_and_zeros, 4, linear.groupsize)
-            k = getattr(linear, "origin_in_features", full.shape[1])
+            k = getattr(linear, "origin_in_features", q.shape[1])
+            g = linear.groupsize
+            if k % 128 == 0 and k % g == 0 and g >= 64 and (g & (g - 1)) == 0:
+                # input columns added by the checkpoint's padding multiply zeros: dropped
+                return gemm.Int4Weight.from_int(q[:, :k].contiguous(),
+                                                linear.scales_and_zeros[: k // g], g), None
+            full = qz.group_dequantize_tensor(q, linear.scales_and_zeros, 4, g)
             return full[:, :k].to(torch.bfloat16).contiguous(), None
         assert w.dtype == torch.bfloat16, f"unsupported weight dtype {w.dtype}"
         return w, None
+
 
     def _layer_weights(self, blk):
         a, f = blk.attention, blk.feed_forward

@@ -46,6 +46,7 @@ class GemmParams(C.Structure):
         ("sk_ctas", C.c_int), ("sk_smem_kb", C.c_int),
         ("sk_ws", C.c_void_p), ("sk_ws_bytes", C.c_longlong),
         ("sk_count", C.c_void_p), ("sk_count_len", C.c_int), ("sk_slots", C.c_int),
+        ("groupsize", C.c_int), ("qsz", C.c_void_p), ("qsz2", C.c_void_p),
     ]
 
 
@@ -65,6 +66,7 @@ _SIGNATURES = {
     "e2h_gemm_persistent": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_w8": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_streamk": [C.POINTER(GemmParams), _vp],
+    "e2h_gemm_w4": [C.POINTER(GemmParams), _vp],
     "e2h_rmsnorm_fwd": [_vp, _vp, _vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
                         _vp, _vp, _vp, _vp, _vp],
     "e2h_reduce_residual_norm_bf16": [_vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _i, _i, _f,

@@ -64,6 +64,10 @@ struct E2hGemmParams {
   unsigned int* sk_count;  // one arrival counter per feature tile, zero between launches
   int sk_count_len;
   int sk_slots;          // partial-tile slots reserved per feature tile (set by the entry point)
+  // weight-only int4 (e2h_gemm_w4) only
+  int groupsize;         // k per (scale, zero) pair
+  const void* qsz;       // bf16 [K / groupsize][F][2] (scale, zero) of A
+  const void* qsz2;      // same for A2 of a dual GEMM
 };
 
 #ifdef __cplusplus
@@ -72,6 +76,8 @@ extern "C" {
 // Returns 0 on success, a cudaError_t / negative code otherwise. Launches on `stream`.
 int e2h_gemm_umma(const E2hGemmParams* p, void* stream);
 int e2h_gemm_streamk(const E2hGemmParams* p, void* stream);
+int e2h_gemm_w8(const E2hGemmParams* p, void* stream);
+int e2h_gemm_w4(const E2hGemmParams* p, void* stream);
 #ifdef __cplusplus
 }
 #endif

@@ -41,8 +41,6 @@ constexpr int kW8MaxStages = 8;
 constexpr int kW8Ctrl = 1024;
 constexpr int kW8Kps = 2;          // 64-wide k-blocks per pipeline stage
 constexpr int kW8ConvMax = 4;      // converted-tile buffers: 4 (2 for a dual GEMM, whose tiles are twice as large)
-constexpr int kA8Bytes = 128 * 64; // int8 bytes of one 64-wide k-block (a stage holds kW8Kps of them
-                                   // as one [128 x 128] tile)
 constexpr int kA16Bytes = 128 * 128;
 
 struct CtrlW8 {
@@ -78,7 +76,24 @@ __device__ __forceinline__ void cvt4_s8_bf16(uint32_t w, uint32_t& lo, uint32_t&
   hi = *reinterpret_cast<const uint32_t*>(&r23);
 }
 
-template <int BN, bool DUAL>
+// four unsigned nibbles -> exact bf16 (q - 8) * scale + zero with a rounding after every step,
+// the arithmetic of the reference's int4 linear ((q - 8) * scales + zeros in bf16,
+// models/quantize.py:108-116). The packed word holds 8 consecutive k as
+// sum_j q[2j] << 4j | q[2j+1] << (16 + 4j), so (w >> 4j) & 0x000F000F is the pair (2j, 2j+1)
+// already in bf16x2 position: OR-ing 0x4300 makes each half the bf16 number 128 + q.
+__device__ __forceinline__ uint32_t cvt2_u4_bf16(uint32_t w, int j, __nv_bfloat162 scale,
+                                                 __nv_bfloat162 zero) {
+  const uint32_t t = ((w >> (4 * j)) & 0x000F000Fu) | 0x43004300u;
+  const uint32_t c136 = 0x43084308u;                       // bf16(136) = 128 + 8, twice
+  __nv_bfloat162 v = __hsub2(*reinterpret_cast<const __nv_bfloat162*>(&t),
+                             *reinterpret_cast<const __nv_bfloat162*>(&c136));
+  v = __hadd2_rn(__hmul2_rn(v, scale), zero);   // _rn: never contracted into one fused op
+  return *reinterpret_cast<const uint32_t*>(&v);
+}
+
+// QB = 8: int8 weights with per-feature scales in the epilogue; QB = 4: packed int4 weights with
+// group-wise (scale, zero) pairs applied by the converters.
+template <int BN, bool DUAL, int QB>
 __global__ void __launch_bounds__(kW8Threads, 1)
 umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmA2,
                     const __grid_constant__ CUtensorMap tmB, const E2hGemmParams p) {
@@ -87,7 +102,8 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // in flight hide it
   constexpr int kW8Conv = DUAL ? 2 : 4;
   constexpr int B_BYTES = BN * 128;
-  constexpr int STAGE = kW8Kps * (kA8Bytes * NMAT + B_BYTES);
+  constexpr int AQ_BYTES = 128 * 16 * QB;   // quantised weight tile of one stage: 128 rows x 128 k
+  constexpr int STAGE = AQ_BYTES * NMAT + kW8Kps * B_BYTES;
   constexpr int CONV = kW8Kps * kA16Bytes * NMAT;
   constexpr int ACC_COLS = BN * NMAT;
   constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : 256;
@@ -167,8 +183,8 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       // CTA's range are loaded but never multiplied
       mbar_expect_tx(bar, STAGE);
       tma_load_3d_hint(st, &tmA, 0, f0, kb / kW8Kps, bar, pol_a);
-      if (DUAL) tma_load_3d_hint(st + kW8Kps * kA8Bytes, &tmA2, 0, f0, kb / kW8Kps, bar, pol_a);
-      tma_load_3d(st + kW8Kps * kA8Bytes * NMAT, &tmB, 0, t0, kb, bar);
+      if (DUAL) tma_load_3d_hint(st + AQ_BYTES, &tmA2, 0, f0, kb / kW8Kps, bar, pol_a);
+      tma_load_3d(st + AQ_BYTES * NMAT, &tmB, 0, t0, kb, bar);
       armed = it + 1;
     }
     if (*abort_flag) {   // bounded wait for the copies still in flight into this CTA's smem
@@ -186,7 +202,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // phase are running counters (no division in this dependent scalar chain)
     const uint32_t d_hi = sw128_desc_hi(1024);
     const uint32_t a_lo0 = sw128_desc_lo(smem_u32(conv), 16);
-    const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles) + kW8Kps * kA8Bytes * NMAT, 16);
+    const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles) + AQ_BYTES * NMAT, 16);
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     bool ok = true;
     int s = 0;
@@ -238,6 +254,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     bool ok = true;
     int s = 0;
     uint32_t ph = 0;
+    const int gshift = QB == 4 ? __ffs(p.groupsize) - 1 : 0;   // group size is a power of two
     for (int it = 0; it < n_it; ++it) {
       const int c = it % kW8Conv;
       const int s_cur = s;
@@ -258,18 +275,50 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         uint8_t* cv = conv + (size_t)c * CONV;
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {
-          const uint8_t* src = st + m * kW8Kps * kA8Bytes + row * 128;
           uint8_t* dst = cv + (m * kW8Kps + half) * kA16Bytes + row * 128;
+          if constexpr (QB == 8) {
+            const uint8_t* src = st + m * AQ_BYTES + row * 128;
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {               // 16 int8 -> two 16-byte bf16 chunks
-            const uint4 raw = *reinterpret_cast<const uint4*>(src + (((4 * half + j) ^ sw) << 4));
-            uint4 o0, o1;
-            cvt4_s8_bf16(raw.x, o0.x, o0.y);
-            cvt4_s8_bf16(raw.y, o0.z, o0.w);
-            cvt4_s8_bf16(raw.z, o1.x, o1.y);
-            cvt4_s8_bf16(raw.w, o1.z, o1.w);
-            *reinterpret_cast<uint4*>(dst + (((2 * j) ^ sw) << 4)) = o0;
-            *reinterpret_cast<uint4*>(dst + (((2 * j + 1) ^ sw) << 4)) = o1;
+            for (int j = 0; j < 4; ++j) {             // 16 int8 -> two 16-byte bf16 chunks
+              const uint4 raw =
+                  *reinterpret_cast<const uint4*>(src + (((4 * half + j) ^ sw) << 4));
+              uint4 o0, o1;
+              cvt4_s8_bf16(raw.x, o0.x, o0.y);
+              cvt4_s8_bf16(raw.y, o0.z, o0.w);
+              cvt4_s8_bf16(raw.z, o1.x, o1.y);
+              cvt4_s8_bf16(raw.w, o1.z, o1.w);
+              *reinterpret_cast<uint4*>(dst + (((2 * j) ^ sw) << 4)) = o0;
+              *reinterpret_cast<uint4*>(dst + (((2 * j + 1) ^ sw) << 4)) = o1;
+            }
+          } else {
+            // int4 tile: 128 rows x 64 bytes, 64-byte swizzle (16-byte chunk c of a row sits at
+            // c ^ ((row >> 1) & 3)); this thread's 64 k are chunks 2*half and 2*half + 1.
+            // One (scale, zero) pair per feature and group: [K / g][F][2] bf16.
+            const uint8_t* src = st + m * AQ_BYTES + row * 64;
+            const int f = f0 + row;
+            const int kglob = (kb_begin + it * kW8Kps + half) * 64;
+            const __nv_bfloat162* szp =
+                static_cast<const __nv_bfloat162*>(m == 0 ? p.qsz : p.qsz2);
+            __nv_bfloat162 pair = __floats2bfloat162_rn(0.f, 0.f);
+            if (f < p.F) pair = szp[(long long)(kglob >> gshift) * p.F + f];
+            const __nv_bfloat162 sc2 = __bfloat162bfloat162(pair.x);
+            const __nv_bfloat162 zr2 = __bfloat162bfloat162(pair.y);
+            const int sw4 = (row >> 1) & 3;
+#pragma unroll
+            for (int cc = 0; cc < 2; ++cc) {          // 16 bytes = 32 nibbles -> four bf16 chunks
+              const uint4 raw =
+                  *reinterpret_cast<const uint4*>(src + (((2 * half + cc) ^ sw4) << 4));
+              const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+              for (int wi = 0; wi < 4; ++wi) {
+                uint4 o;
+                o.x = cvt2_u4_bf16(wds[wi], 0, sc2, zr2);
+                o.y = cvt2_u4_bf16(wds[wi], 1, sc2, zr2);
+                o.z = cvt2_u4_bf16(wds[wi], 2, sc2, zr2);
+                o.w = cvt2_u4_bf16(wds[wi], 3, sc2, zr2);
+                *reinterpret_cast<uint4*>(dst + (((4 * cc + wi) ^ sw) << 4)) = o;
+              }
+            }
           }
         }
       }
@@ -399,11 +448,27 @@ static int w8_map3d(CUtensorMap* m, const void* base, long long K, long long row
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-template <int BN, bool DUAL>
+// Packed int4 operand [rows, K / 2 bytes] seen as {64 bytes, rows, K / 128}: one box
+// {64, 128, 1} is the [128 rows x 128 k] tile of a stage, 64-byte swizzle.
+static int w4_map3d(CUtensorMap* m, const void* base, long long K, long long rows,
+                    long long ld_bytes) {
+  W8EncodeFn fn = w8_encode_fn();
+  if (!fn) return -10;
+  cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(K / 128)};
+  cuuint64_t strides[2] = {(cuuint64_t)ld_bytes, 64u};
+  cuuint32_t box[3] = {64u, 128u, 1u};
+  cuuint32_t estr[3] = {1u, 1u, 1u};
+  CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
+                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? 0 : -11;
+}
+
+template <int BN, bool DUAL, int QB>
 static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
   constexpr int NMAT = DUAL ? 2 : 1;
   constexpr int kW8Conv = DUAL ? 2 : 4;
-  constexpr int STAGE = kW8Kps * (kA8Bytes * NMAT + BN * 128);
+  constexpr int STAGE = 128 * 16 * QB * NMAT + kW8Kps * BN * 128;
   constexpr int CONV = kW8Kps * kA16Bytes * NMAT;
   const int fixed = 1024 + kW8Ctrl + w8_xchg_bytes(BN, p.splitk, DUAL) + kW8Conv * CONV;
   int stages = (227 * 1024 - fixed) / STAGE;
@@ -414,10 +479,12 @@ static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
   if (stages < 1) return -8;
   p.stages = stages;
   CUtensorMap ta, ta2, tb;
-  int r = w8_map3d(&ta, p.a, p.K, p.F, p.lda, 128, 1, true);
+  int r = QB == 8 ? w8_map3d(&ta, p.a, p.K, p.F, p.lda, 128, 1, true)
+                  : w4_map3d(&ta, p.a, p.K, p.F, p.lda);
   if (r) return r;
   if (DUAL) {
-    r = w8_map3d(&ta2, p.a2, p.K, p.F, p.lda2, 128, 1, true);
+    r = QB == 8 ? w8_map3d(&ta2, p.a2, p.K, p.F, p.lda2, 128, 1, true)
+                : w4_map3d(&ta2, p.a2, p.K, p.F, p.lda2);
     if (r) return r;
   } else {
     ta2 = ta;
@@ -425,7 +492,7 @@ static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
   r = w8_map3d(&tb, p.b, p.K, p.T, p.ldb, BN, kW8Kps, false);
   if (r) return r;
   const size_t smem = (size_t)fixed + (size_t)stages * STAGE;
-  auto kern = umma_gemm_w8_kernel<BN, DUAL>;
+  auto kern = umma_gemm_w8_kernel<BN, DUAL, QB>;
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e =
@@ -478,7 +545,35 @@ extern "C" int e2h_gemm_w8(const E2hGemmParams* pp, void* stream_v) {
     return -7;
   if (p.scale == nullptr) return -9;
   cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
-  if (p.dual) return w8_launch<64, true>(p, stream);
-  if (p.bn == 64) return w8_launch<64, false>(p, stream);
-  return w8_launch<128, false>(p, stream);
+  if (p.dual) return w8_launch<64, true, 8>(p, stream);
+  if (p.bn == 64) return w8_launch<64, false, 8>(p, stream);
+  return w8_launch<128, false, 8>(p, stream);
+}
+
+// Weight-only int4, group-wise: p.a (and p.a2) point at packed nibbles [F, K / 2] bytes (lda =
+// row pitch in bytes, a multiple of 16) where every 32-bit word holds 8 consecutive k as
+// sum_j q[2j] << 4j | q[2j+1] << (16 + 4j); p.qsz (and p.qsz2) the [K / g][F][2] bf16
+// (scale, zero) pairs of the reference's checkpoint format; p.groupsize a power of two >= 64
+// that divides K; K % 128 == 0. out = epilogue( sum_k x[t,k] * bf16((q-8) * scale + zero) ).
+extern "C" int e2h_gemm_w4(const E2hGemmParams* pp, void* stream_v) {
+  using namespace e2h;
+  E2hGemmParams p = *pp;
+  if (p.F <= 0 || p.T <= 0 || p.K <= 0 || (p.K % 128)) return -1;
+  if (p.bn != 64 && p.bn != 128) return -2;
+  if (p.dual && p.bn != 64) return -2;
+  if (p.splitk < 1 || p.splitk > 8 || (p.bn % (p.splitk * 8)) != 0) return -3;
+  if ((p.K / 128) < p.splitk) return -4;
+  if (p.a_mn_major || p.b_mn_major || p.a_tiled) return -5;
+  if (p.dual && (p.a2 == nullptr || p.qsz2 == nullptr)) return -5;
+  if ((p.lda % 16) || (p.ldb % 8) || (p.dual && (p.lda2 % 16))) return -6;
+  if (((uintptr_t)p.a & 15) || ((uintptr_t)p.b & 15) || (p.dual && ((uintptr_t)p.a2 & 15)))
+    return -7;
+  if (p.qsz == nullptr || p.groupsize < 64 || (p.groupsize & (p.groupsize - 1)) ||
+      (p.K % p.groupsize))
+    return -9;
+  p.scale = nullptr;
+  cudaStream_t stream = static_cast<cudaStream_t>(stream_v);
+  if (p.dual) return w8_launch<64, true, 4>(p, stream);
+  if (p.bn == 64) return w8_launch<64, false, 4>(p, stream);
+  return w8_launch<128, false, 4>(p, stream);
 }

@@ -88,7 +88,17 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     int8 through the converting kernel for up to 128 tokens and is expanded to a scratch bf16
     matrix first for larger token counts."""
     assert a.is_cuda and b.is_cuda and b.dtype == torch.bfloat16
-    w8 = a.dtype == torch.int8
+    w4 = isinstance(a, Int4Weight)
+    if w4:
+        assert not a_mn_major and not b_mn_major and tiled_shape is None and scale is None
+        assert a2 is None or isinstance(a2, Int4Weight)
+        K4 = a.shape[1]
+        if (b.shape[0] > 128 or K4 % 128 or a.groupsize < 64 or a.groupsize & (a.groupsize - 1)
+                or (K4 // 2) % 16):
+            a = _expand_int4(a, 0)            # many tokens: one dequantisation pass, then bf16
+            a2 = _expand_int4(a2, 1) if a2 is not None else None
+            w4 = False
+    w8 = not w4 and a.dtype == torch.int8
     if w8:
         assert scale is not None and not a_mn_major and not b_mn_major and tiled_shape is None
         if a2 is not None:
@@ -97,8 +107,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
             a = _expand_int8(a, 0)
             a2 = _expand_int8(a2, 1) if a2 is not None else None
             w8 = False
-    assert w8 or a.dtype == torch.bfloat16
-    if tiled_shape is not None:      # a is a TiledWeight payload: logical shape given
+    assert w8 or w4 or a.dtype == torch.bfloat16
+    if w4:
+        F, K = a.shape
+    elif tiled_shape is not None:      # a is a TiledWeight payload: logical shape given
         F, K = tiled_shape
         assert tf is not None, "a tile-major weight fixes the feature-tile height"
     elif a_mn_major:
@@ -111,9 +123,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         T, Kb = b.shape
     assert K == Kb, f"contraction mismatch {K} vs {Kb}"
     dual = a2 is not None
-    if w8 and bn is None:
+    if (w8 or w4) and bn is None:
         bn = 64 if (T <= 64 or dual) else 128
-    sk_ok = (not w8 and not a_mn_major and not b_mn_major and tiled_shape is None and T <= 128
+    sk_ok = (not w8 and not w4 and not a_mn_major and not b_mn_major and tiled_shape is None and T <= 128
              and K % 64 == 0 and splitk is None and tf is None)
     use_sk = sk_ok and (streamk if streamk is not None else STREAMK_DEFAULT)
     if use_sk:
@@ -135,11 +147,19 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         p.ticket = ticket.data_ptr()
     p.kps = kps
     p.a_tiled = int(tiled_shape is not None)
-    p.lda, p.ldb = (64 if tiled_shape is not None else _ld(a)), _ld(b)
-    p.a, p.b = a.data_ptr(), b.data_ptr()
-    if dual:
-        assert a2.shape == a.shape
-        p.a2, p.lda2 = a2.data_ptr(), (64 if tiled_shape is not None else _ld(a2))
+    if w4:
+        p.lda, p.ldb = _ld(a.q), _ld(b)
+        p.a, p.b = a.q.data_ptr(), b.data_ptr()
+        p.qsz, p.groupsize = a.sz.data_ptr(), a.groupsize
+        if dual:
+            assert a2.shape == a.shape and a2.groupsize == a.groupsize
+            p.a2, p.lda2, p.qsz2 = a2.q.data_ptr(), _ld(a2.q), a2.sz.data_ptr()
+    else:
+        p.lda, p.ldb = (64 if tiled_shape is not None else _ld(a)), _ld(b)
+        p.a, p.b = a.data_ptr(), b.data_ptr()
+        if dual:
+            assert a2.shape == a.shape
+            p.a2, p.lda2 = a2.data_ptr(), (64 if tiled_shape is not None else _ld(a2))
     if out is not None:
         p.out, p.ldo = out.data_ptr(), out.stride(0)
     if out2 is not None:
@@ -162,6 +182,9 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     if w8:
         _lib.check(_lib.lib().e2h_gemm_w8(C.byref(p), _lib.stream()), "e2h_gemm_w8")
         return
+    if w4:
+        _lib.check(_lib.lib().e2h_gemm_w4(C.byref(p), _lib.stream()), "e2h_gemm_w4")
+        return
     if use_sk:
         ws, count = _sk_workspace(a.device)
         p.bn, p.kps, p.stages, p.splitk, p.tf = sk_bn, sk_kps, sk_stages, 1, 128
@@ -178,6 +201,47 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
                    "e2h_gemm_persistent")
     else:
         _lib.check(_lib.lib().e2h_gemm_umma(C.byref(p), _lib.stream()), "e2h_gemm_umma")
+
+
+class Int4Weight:
+    """Group-wise int4 weight as the decode GEMM streams it: ``q`` uint8 ``[F, K / 2]`` where each
+    32-bit word holds 8 consecutive k as ``sum_j q[2j] << 4j | q[2j+1] << (16 + 4j)`` (the pair
+    (2j, 2j+1) then sits in bf16x2 position after one shift and mask), and ``sz`` bf16
+    ``[K / g, F, 2]`` (scale, zero) exactly as the reference's checkpoints store it
+    (models/quantize.py:60-70 of the reference). ``from_int`` builds it from integer codes
+    ``[F, K]`` in 0..15 (``models.quantize.unpack_int4_tinygemm`` yields those)."""
+
+    def __init__(self, q: torch.Tensor, sz: torch.Tensor, groupsize: int, shape):
+        self.q, self.sz, self.groupsize, self.shape = q, sz, groupsize, tuple(shape)
+        self.dtype, self.device, self.is_cuda = torch.uint8, q.device, q.is_cuda
+
+    @classmethod
+    def from_int(cls, codes: torch.Tensor, sz: torch.Tensor, groupsize: int) -> "Int4Weight":
+        F, K = codes.shape
+        assert K % 8 == 0
+        c = codes.to(torch.int32).view(F, K // 8, 4, 2)
+        sh = torch.arange(4, device=codes.device, dtype=torch.int32) * 4
+        word = ((c[..., 0] << sh) | (c[..., 1] << (sh + 16))).sum(-1, dtype=torch.int64)
+        word = word.to(torch.int32)                      # bit 31 may be set: wraps as intended
+        q = word.view(torch.uint8).view(F, K // 2).contiguous()
+        return cls(q, sz.to(torch.bfloat16).contiguous(), groupsize, (F, K))
+
+    def codes(self) -> torch.Tensor:
+        """Integer codes [F, K] (inverse of ``from_int``)."""
+        F, K = self.shape
+        w = self.q.view(torch.int32).view(F, K // 8, 1)
+        sh = torch.arange(4, device=self.q.device, dtype=torch.int32) * 4
+        lo, hi = (w >> sh) & 15, (w >> (sh + 16)) & 15
+        return torch.stack([lo, hi], -1).view(F, K)
+
+    def dequant(self) -> torch.Tensor:
+        """bf16 [F, K]: ((q - 8) * scale + zero), each step rounded to bf16 as the reference does."""
+        F, K = self.shape
+        g = self.groupsize
+        x = (self.codes() - 8).to(torch.bfloat16).view(F, K // g, g)
+        s = self.sz[..., 0].t().unsqueeze(-1)            # [F, K/g, 1]
+        z = self.sz[..., 1].t().unsqueeze(-1)
+        return (x * s + z).view(F, K)
 
 
 _INT8_SCRATCH: dict = {}
@@ -213,6 +277,19 @@ def _expand_int8(w: torch.Tensor, which: int) -> torch.Tensor:
         _INT8_SCRATCH[key] = buf
     out = buf[: w.numel()].view(w.shape)
     out.copy_(w)
+    return out
+
+
+def _expand_int4(w: "Int4Weight", which: int) -> torch.Tensor:
+    """bf16 image of an int4 weight in the per-device scratch buffers of ``_expand_int8``."""
+    key = (w.device.index, which)
+    n = w.shape[0] * w.shape[1]
+    buf = _INT8_SCRATCH.get(key)
+    if buf is None or buf.numel() < n:
+        buf = torch.empty(n, dtype=torch.bfloat16, device=w.device)
+        _INT8_SCRATCH[key] = buf
+    out = buf[:n].view(w.shape)
+    out.copy_(w.dequant())
     return out
 
 

@@ -88,6 +88,10 @@ def cases(T: int, B: int, S: int, ctx: int):
     out["decode_gemm_w8_wqkv"] = (lambda: gemm.linear(xd, w8, scale=s8), 0, 3 * DIM * DIM)
     out["decode_gemm_w8_w2_residual"] = (lambda: gemm.linear_residual(xa8, w8b, hd, scale=s8b),
                                          0, (FFN // 64 * 64) * DIM)
+    codes = torch.randint(0, 16, (3 * DIM, DIM), device="cuda", dtype=torch.int32)
+    sz = (torch.rand(DIM // 128, 3 * DIM, 2, device="cuda") * 0.01).bfloat16()
+    w4 = gemm.Int4Weight.from_int(codes, sz, 128)
+    out["decode_gemm_w4_wqkv"] = (lambda: gemm.linear(xd, w4), 0, 3 * DIM * DIM // 2)
     kc, vc = _bf(64, HEADS, ctx, HEAD_DIM), _bf(64, HEADS, ctx, HEAD_DIM)
     qd = _bf(64, HEADS * HEAD_DIM)
     pos = torch.tensor([ctx - 1], dtype=torch.int32, device="cuda")

@@ -91,10 +91,31 @@ def test_int4_weights_are_unpacked_exactly():
     lin.weight.copy_(packed)
     lin.scales_and_zeros.copy_(sz)
     lin = lin.cuda()
-    dense, scale = DecodeEngine._dense(lin)
+    from easy_to_hard_b200.ops.gemm import Int4Weight
+    packed4, scale = DecodeEngine._dense(lin)
     q, sz_again = qz.group_quantize_tensor(w, 4, 128)
     assert torch.equal(sz_again, sz)
     want = qz.group_dequantize_tensor(q, sz, 4, 128).bfloat16()
-    assert scale is None and dense.shape == (256, 1024)
+    # the engine keeps the weight as packed nibbles (streamed as int4 by the decode GEMM)
+    assert scale is None and isinstance(packed4, Int4Weight) and packed4.shape == (256, 1024)
+    assert packed4.q.shape == (256, 512) and packed4.q.dtype == torch.uint8
+    assert torch.equal(packed4.codes().cpu(), q)
+    dense = packed4.dequant()
     assert torch.equal(dense.cpu(), want)
     assert float((dense.cpu().float() - w.float()).abs().max()) < 0.03
+
+
+def test_int4_weight_only_engine_matches_module_path():
+    from easy_to_hard_b200.models.quantize import WeightOnlyInt4QuantHandler
+    from easy_to_hard_b200.ops.gemm import Int4Weight
+    model = _model()
+    h = WeightOnlyInt4QuantHandler(copy.deepcopy(model).cpu(), groupsize=128, inner_k_tiles=8)
+    sd = h.create_quantized_state_dict()
+    q4 = h.convert_for_runtime()
+    q4.load_state_dict(sd, strict=False)
+    q4 = q4.to("cuda").eval()
+    prompt = torch.randint(1, 1024, (2, 20), device="cuda", dtype=torch.int32)
+    want = _module_logits(copy.deepcopy(q4), prompt, None)
+    got, eng = _engine_logits(q4, prompt, None)
+    assert isinstance(eng.W[0]["wqkv"][0], Int4Weight)
+    assert torch.allclose(got, want, atol=0.1, rtol=0.05), float((got - want).abs().max())
