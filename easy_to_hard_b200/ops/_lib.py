@@ -88,6 +88,9 @@ _SIGNATURES = {
     "e2h_signal_peers": [C.POINTER(C.c_void_p), _i, _vp],
     "e2h_reduce_scatter_accum": [C.POINTER(C.c_void_p), _i, _vp, _ll, _f, _i, _vp, _vp, _vp, _i,
                                  _vp, _vp],
+    "e2h_wait_flags": [_vp, _i, _vp, _i, _i, _vp, _vp],
+    "e2h_p2p_all_gather": [C.POINTER(C.c_void_p), _i, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp],
+    "e2h_p2p_reduce_bf16": [C.POINTER(C.c_void_p), _i, _vp, _ll, _f, _vp, _vp, _vp, _i, _vp, _vp],
     "e2h_set_pdl": [_i],
     "e2h_set_flag_wait_ms": [_i],
     "e2h_flash_bwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll,

@@ -175,3 +175,134 @@ class GradReduceScatter:
             self.ticket[slot:slot + 1].data_ptr(), int(self.wait_ms),
             _lib.status_word(out.device).data_ptr(), _lib.stream())
         _lib.check(rc, "reduce_scatter_accum")
+
+
+class P2PChannel:
+    """Stand-alone collectives over peer memory with the flag protocol of the fused kernels
+    (``ops/csrc/comm.cu``): all-gather (pull), one-shot all-reduce, reduce-scatter, two-shot
+    all-reduce (reduce-scatter + all-gather) and a barrier, each wait bounded by ``wait_ms``
+    (a time-out lands in the device status word, ``ops._lib.read_status``).
+
+    Every use is ``post`` (copy the payload into this rank's slot, then raise this rank's flag
+    on every peer, stream-ordered) followed by one consuming kernel that waits for all flags and
+    pulls from the peers. Two slots alternate; all ranks must issue the same sequence of uses.
+    The split into ``post`` / ``*_posted`` lets a single process play several ranks on one GPU
+    (all posts first, then the consumers), which is how the single-GPU tests run it."""
+
+    def __init__(self, nbytes: int, group=None, buf: Optional[SymmetricBuffer] = None,
+                 wait_ms: int = 120000):
+        self.nbytes = (nbytes + 255) // 256 * 256
+        self.slot_bytes = self.nbytes + 256
+        if buf is None:
+            buf = SymmetricBuffer(2 * self.slot_bytes, group)
+        self.buf = buf
+        self.world, self.rank = buf.world, buf.rank
+        dev = buf.local.device
+        self.use_count = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.ticket = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.wait_ms = wait_ms
+        self.next_slot = 0
+        self._second: Optional["P2PChannel"] = None
+        self._group = group
+
+    # ---- building blocks
+    def _flag_off(self, slot: int) -> int:
+        return slot * self.slot_bytes + self.nbytes
+
+    def flags(self, slot: int) -> torch.Tensor:
+        return self.buf.view(self._flag_off(slot), (self.world,), torch.int32)
+
+    def payload(self, slot: int, shape, dtype) -> torch.Tensor:
+        return self.buf.view(slot * self.slot_bytes, shape, dtype)
+
+    def _ptr_array(self, slot: int, byte_offset: int = 0):
+        import ctypes as C
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.buf.peer_ptr(r, slot * self.slot_bytes + byte_offset)
+        return arr
+
+    def _ctl(self, slot: int):
+        from ..ops import _lib
+        return (self.flags(slot).data_ptr(), self.use_count[slot:slot + 1].data_ptr(),
+                self.ticket[slot:slot + 1].data_ptr(), int(self.wait_ms),
+                _lib.status_word(self.buf.local.device).data_ptr(), _lib.stream())
+
+    def post(self, x: Optional[torch.Tensor]) -> int:
+        """Stage ``x`` (any dtype, contiguous) in the next slot and signal every rank."""
+        import ctypes as C
+        from ..ops import _lib
+        slot = self.next_slot
+        self.next_slot ^= 1
+        if x is not None:
+            nb = x.numel() * x.element_size()
+            assert x.is_contiguous() and nb <= self.nbytes
+            self.payload(slot, tuple(x.shape), x.dtype).copy_(x)
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.buf.peer_ptr(r, self._flag_off(slot) + 4 * self.rank)
+        _lib.check(_lib.lib().e2h_signal_peers(arr, self.world, _lib.stream()), "signal_peers")
+        return slot
+
+    def gather_posted(self, slot: int, like: torch.Tensor) -> torch.Tensor:
+        from ..ops import _lib
+        nb = like.numel() * like.element_size()
+        assert nb % 16 == 0, "payloads are moved as 16-byte vectors"
+        out = torch.empty((self.world,) + tuple(like.shape), dtype=like.dtype, device=like.device)
+        rc = _lib.lib().e2h_p2p_all_gather(self._ptr_array(slot), self.world, out.data_ptr(), nb,
+                                           *self._ctl(slot))
+        _lib.check(rc, "p2p_all_gather")
+        return out
+
+    def reduce_posted(self, slot: int, offset: int, n: int, out: torch.Tensor,
+                      scale: float = 1.0) -> torch.Tensor:
+        """out[:n] = bf16(scale * sum over ranks of their payload[offset : offset + n])."""
+        from ..ops import _lib
+        assert out.dtype == torch.bfloat16 and n % 8 == 0 and offset % 8 == 0
+        rc = _lib.lib().e2h_p2p_reduce_bf16(self._ptr_array(slot, 2 * offset), self.world,
+                                            out.data_ptr(), n, float(scale), *self._ctl(slot))
+        _lib.check(rc, "p2p_reduce_bf16")
+        return out
+
+    def wait_posted(self, slot: int) -> None:
+        from ..ops import _lib
+        flags, use, _, wait_ms, status, stream = self._ctl(slot)
+        _lib.check(_lib.lib().e2h_wait_flags(flags, self.world, use, 1, wait_ms, status, stream),
+                   "wait_flags")
+
+    def second(self) -> "P2PChannel":
+        """Channel of the second phase of a two-shot all-reduce (the reduced slices)."""
+        if self._second is None:
+            self._second = P2PChannel(self.nbytes // self.world + 256, self._group,
+                                      wait_ms=self.wait_ms)
+        return self._second
+
+    # ---- collectives (one rank per process)
+    def all_gather(self, x: torch.Tensor) -> torch.Tensor:
+        """[world, *x.shape]: every rank's ``x`` (same shape and dtype on all ranks)."""
+        return self.gather_posted(self.post(x), x)
+
+    def reduce_scatter(self, x: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+        """This rank's slice (numel / world elements) of the element-wise sum of bf16 ``x``."""
+        n = x.numel() // self.world
+        assert x.dtype == torch.bfloat16 and x.numel() % (8 * self.world) == 0
+        slot = self.post(x.reshape(-1))
+        out = torch.empty(n, dtype=torch.bfloat16, device=x.device)
+        return self.reduce_posted(slot, self.rank * n, n, out, scale)
+
+    def all_reduce(self, x: torch.Tensor, algo: str = "one_shot", scale: float = 1.0) -> torch.Tensor:
+        """Element-wise sum of bf16 ``x`` over the ranks. ``one_shot``: every rank pulls and adds
+        all payloads (latency-optimal, world x traffic); ``two_shot``: each rank reduces one
+        slice, then the reduced slices are all-gathered (bandwidth-optimal)."""
+        assert x.dtype == torch.bfloat16 and x.numel() % 8 == 0
+        if algo == "one_shot" or self.world == 1:
+            slot = self.post(x.reshape(-1))
+            out = torch.empty_like(x)
+            self.reduce_posted(slot, 0, x.numel(), out.view(-1), scale)
+            return out
+        assert algo == "two_shot" and x.numel() % (8 * self.world) == 0
+        part = self.reduce_scatter(x, scale)
+        return self.second().all_gather(part).view(x.shape)
+
+    def barrier(self) -> None:
+        self.wait_posted(self.post(None))

@@ -255,3 +255,31 @@ def rank_never_joins(rank, world):
         return "completed"
     except Exception as e:  # noqa: BLE001
         return f"error:{type(e).__name__}"
+
+
+def p2p_channel_ops(rank, world, device="cuda"):
+    """Stand-alone peer-memory collectives (parallel/symm.P2PChannel) against NCCL."""
+    from easy_to_hard_b200.ops import _lib
+    from easy_to_hard_b200.parallel.symm import P2PChannel
+    torch.manual_seed(100 + rank)
+    n = 1 << 16
+    ch = P2PChannel(n * 2, wait_ms=20000)
+    res = {}
+    for rep in range(3):
+        x = torch.randn(n, device="cuda").bfloat16()
+        ref = [torch.empty_like(x) for _ in range(world)]
+        dist.all_gather(ref, x)
+        got = ch.all_gather(x)
+        res[f"gather{rep}"] = bool(torch.equal(got, torch.stack(ref)))
+        want = torch.stack(ref).float().sum(0)
+        one = ch.all_reduce(x, "one_shot")
+        two = ch.all_reduce(x, "two_shot")
+        res[f"one{rep}"] = float((one.float() - want).abs().max() / want.abs().max())
+        res[f"two{rep}"] = float((two.float() - want).abs().max() / want.abs().max())
+        res[f"same{rep}"] = bool(torch.equal(one, two))
+        rs = ch.reduce_scatter(x)
+        res[f"rs{rep}"] = bool(torch.equal(rs, one.view(world, -1)[rank]))
+        ch.barrier()
+    torch.cuda.synchronize()
+    res["status"] = _lib.read_status()
+    return res

@@ -39,3 +39,13 @@ def test_two_gpu_sft_step_matches_single_gpu(single, tmp_path, kw):
     # greedy tokens of a random tiny model can flip on bf16 noise; most must agree
     agree = (res[0]["tokens"] == single["tokens"]).float().mean()
     assert float(agree) > 0.8, float(agree)
+
+
+def test_two_gpu_p2p_channel_collectives_match_nccl(tmp_path):
+    _need_two()
+    res = W.run(W.p2p_channel_ops, 2, str(tmp_path), device="cuda", backend="nccl")
+    for r in res:
+        assert r["status"] == 0
+        for rep in range(3):
+            assert r[f"gather{rep}"] and r[f"same{rep}"] and r[f"rs{rep}"]
+            assert r[f"one{rep}"] < 0.01 and r[f"two{rep}"] < 0.01

@@ -1,0 +1,80 @@
+"""Stand-alone peer-memory collectives (ops/csrc/comm.cu, parallel/symm.P2PChannel) on one GPU:
+``world`` emulated ranks post first and consume afterwards, so no launch waits on a later one.
+A wait whose flag nobody raises must time out into the status word and leave the context usable."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _channels(world, nbytes):
+    from easy_to_hard_b200.parallel.symm import P2PChannel, SymmetricBuffer
+    slot_bytes = (nbytes + 255) // 256 * 256 + 256
+    bufs = SymmetricBuffer.emulated(2 * slot_bytes, world)
+    return [P2PChannel(nbytes, buf=b, wait_ms=2000) for b in bufs]
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_all_gather_and_one_shot_all_reduce(world):
+    from easy_to_hard_b200.ops import _lib
+    n = 4096 + 64
+    ch = _channels(world, n * 2)
+    xs = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
+    for rep in range(3):                                   # slots alternate and are reused
+        slots = [c.post(x) for c, x in zip(ch, xs)]
+        for c in ch:
+            got = c.gather_posted(slots[c.rank], xs[0])
+            assert torch.equal(got, torch.stack(xs))
+        slots = [c.post(x) for c, x in zip(ch, xs)]
+        want = torch.stack(xs).float().sum(0)
+        outs = []
+        for c in ch:
+            out = torch.empty(n, dtype=torch.bfloat16, device="cuda")
+            c.reduce_posted(slots[c.rank], 0, n, out, 1.0)
+            outs.append(out)
+        assert all(torch.equal(o, outs[0]) for o in outs)  # same order of additions everywhere
+        assert float((outs[0].float() - want).abs().max()) <= 0.02 * float(want.abs().max())
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+
+
+def test_reduce_scatter_slices_and_two_shot():
+    from easy_to_hard_b200.ops import _lib
+    world, n = 4, 8192
+    ch = _channels(world, n * 2)
+    ch2 = _channels(world, n * 2 // world)
+    xs = [torch.randn(n, device="cuda").bfloat16() for _ in range(world)]
+    want = torch.stack(xs).float().sum(0)
+    slots = [c.post(x) for c, x in zip(ch, xs)]
+    parts = []
+    for c in ch:
+        out = torch.empty(n // world, dtype=torch.bfloat16, device="cuda")
+        parts.append(c.reduce_posted(slots[c.rank], c.rank * (n // world), n // world, out, 0.5))
+    got = torch.cat(parts).float()
+    assert float((got - 0.5 * want).abs().max()) <= 0.02 * float(want.abs().max())
+    # second shot: all-gather of the reduced slices
+    slots2 = [c.post(p) for c, p in zip(ch2, parts)]
+    for c in ch2:
+        full = c.gather_posted(slots2[c.rank], parts[0]).view(-1)
+        assert torch.equal(full, torch.cat(parts))
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+
+
+def test_barrier_and_a_wait_that_runs_out():
+    from easy_to_hard_b200.ops import _lib
+    ch = _channels(2, 256)
+    slots = [c.post(None) for c in ch]
+    for c in ch:
+        c.wait_posted(slots[c.rank])
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    assert [int(c.use_count[slots[c.rank]]) for c in ch] == [1, 1]
+    # only rank 0 posts: rank 1's flag on rank 0 never rises -> bounded wait, status code, no hang
+    ch[0].wait_ms = 20
+    s0 = ch[0].post(None)
+    ch[0].wait_posted(s0)
+    torch.cuda.synchronize()
+    assert _lib.read_status() != 0
+    x = torch.ones(8, device="cuda")
+    assert float((x + 1).sum()) == 16.0                    # the context still works
