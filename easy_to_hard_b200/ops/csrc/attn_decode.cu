@@ -54,8 +54,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   const bool lane_active = hl < LPK;
   const int slot = warp * 2 + half;
 
+  pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
   pdl_wait_prior();
-  pdl_launch_dependents();
   const int pos = *pos_ptr;              // index of the newest token (already in the cache)
   int start = left_pad ? left_pad[b] : 0;
   if (start > pos) start = pos;
@@ -194,8 +194,8 @@ template <int D>
 __global__ void attn_decode_merge_kernel(const float* __restrict__ partial,
                                          __nv_bfloat16* __restrict__ out, int n_split) {
   const long long bh = blockIdx.x;
+  pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
   pdl_wait_prior();
-  pdl_launch_dependents();
   const float* pp = partial + bh * n_split * (D + 2);
   float mm = -FLT_MAX;
   for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, pp[s * (D + 2) + D]);

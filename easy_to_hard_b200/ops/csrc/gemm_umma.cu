@@ -121,8 +121,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const uint32_t tmem_base = ctrl->tmem_base;
   if (S > 1) cluster_sync_all();  // every CTA of the cluster is resident before DSMEM traffic
 
-  pdl_wait_prior();         // inputs written by the previous kernel are visible from here
-  pdl_launch_dependents();  // the next kernel may begin its own prologue
+  // Programmatic dependent launch: the next kernel may begin its prologue now. This kernel's
+  // own wait for its predecessor is taken per role: the producer first streams the opening
+  // weight tiles (weights are never written by a preceding kernel of a PDL chain), the epilogue
+  // warps wait before they touch the outputs, the MMA thread touches no global memory.
+  pdl_launch_dependents();
+  const bool early_weights = kps > 1 && !p.debug_mode;
+  if (!(warp == 0 && lane == 0 && early_weights) && !(warp == 1 && lane == 0)) pdl_wait_prior();
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
@@ -135,7 +140,29 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     const uint32_t tiles0 = smem_u32(tiles);
     const uint32_t stage_sz = kps * Plan::stage_bytes;
-    for (int it = 0; it < n_it; ++it) {
+    int it0 = 0;
+    if (early_weights) {
+      // the ring is empty: fill every stage's weight part before waiting for the predecessor,
+      // then add the activation part (the stage completes when both have landed)
+      const int n_pre = n_it < stages ? n_it : stages;
+      for (int it = 0; it < n_pre; ++it) {
+        const uint32_t bar = full0 + 8 * it;
+        const uint32_t a_dst = tiles0 + it * stage_sz;
+        const int kb = kb_begin + it * kps;
+        mbar_expect_tx(bar, kps * Plan::stage_bytes);
+        tma_load_3d_hint(a_dst, &tmA, 0, f0, kb, bar, pol_a);
+        if (DUAL) tma_load_3d_hint(a_dst + kps * Plan::a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
+      }
+      pdl_wait_prior();
+      for (int it = 0; it < n_pre; ++it)
+        tma_load_3d(tiles0 + it * stage_sz + kps * Plan::a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0,
+                    kb_begin + it * kps, full0 + 8 * it);
+      armed = n_pre;
+      it0 = n_pre;
+      s = n_pre == stages ? 0 : n_pre;
+      ph = n_pre == stages ? 1 : 0;
+    }
+    for (int it = it0; it < n_it; ++it) {
       if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
       const uint32_t bar = full0 + 8 * s;
       const uint32_t st0 = tiles0 + s * stage_sz;

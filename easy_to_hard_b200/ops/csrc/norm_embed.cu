@@ -58,8 +58,8 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
   extern __shared__ float row[];  // dim floats + 32
   float* red = row + dim;
   const int t = blockIdx.x;
+  pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
   pdl_wait_prior();
-  pdl_launch_dependents();
   const __nv_bfloat16* src =
       tokens ? emb + (long long)tokens[t] * dim : (h_in ? h_in + (long long)t * dim : nullptr);
   if (flags != nullptr) {
