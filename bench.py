@@ -309,10 +309,13 @@ def run_ours_sft(a):
     status = _lib.read_status()
     toks = SFT_GLOBAL_BATCH * SFT_SEQ * a.steps
     n_micro = -(-(per_rank * a.tp) // micro)
-    # per block and micro batch: forward 9 kernels, backward recompute 9 + 17; plus CE chunks
-    launches = (cfg.n_layer * (9 + 26) * n_micro + cfg.n_layer * 2 + 40) * a.steps
+    # per block and micro batch: forward 9 kernels, backward 17 (+ 9 where the block is
+    # recomputed; blocks whose intermediates fit the activation budget are not); plus CE chunks
+    kept = int(getattr(sdp, "_keep_budget", 0) > 0)
+    launches = (cfg.n_layer * (9 + 17 + (0 if kept else 9)) * n_micro + cfg.n_layer * 2 + 40) \
+        * a.steps
     if rank == 0:
-        flops = 6 * 6.74e9 * SFT_GLOBAL_BATCH * SFT_SEQ * (4.0 / 3.0)   # with recomputation
+        flops = 6 * 6.74e9 * SFT_GLOBAL_BATCH * SFT_SEQ     # model FLOPs, recomputation not counted
         out = {
             "metric": "sft_train_tokens_per_s", "value": toks / (ms / 1e3), "unit": "tokens/s",
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
@@ -324,6 +327,8 @@ def run_ours_sft(a):
                        "optimizer": "AdamW lr 2e-5 betas 0.9/0.95, fp32 master, bf16 moments",
                        "loss": "cross-entropy on response tokens (prompt 64..384 masked)",
                        "l2": "inputs larger than L2 (13 GB of bf16 weights per pass)",
+                       "activations": ("block intermediates kept within %.0f GiB, rest recomputed"
+                                       % (getattr(sdp, "_keep_budget", 0) / 2 ** 30)),
                        "model_tflops_per_gpu": flops / (ms / a.steps / 1e3) / 1e12 / world},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",

@@ -158,12 +158,21 @@ def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tens
 
 def block_backward(dy: torch.Tensor, x: torch.Tensor, w: Dict[str, torch.Tensor],
                    grads: Dict[str, torch.Tensor], freqs: torch.Tensor, pos: torch.Tensor,
-                   shape: BlockShape, accumulate: bool = False) -> torch.Tensor:
-    """Recompute the block from its input ``x``, then back-propagate ``dy``. Weight gradients go
-    to ``grads[name]`` (``[out, in]`` bf16 or fp32; added to when ``accumulate``). Returns dx."""
+                   shape: BlockShape, accumulate: bool = False,
+                   saved: Optional[Dict[str, torch.Tensor]] = None) -> torch.Tensor:
+    """Back-propagate ``dy`` through the block. The intermediates come from ``saved`` (what
+    ``block_forward(..., keep=True)`` returned for the same input; ``act`` may be left out and is
+    then rebuilt from ``g`` and ``u``) or, without it, from re-running the block on its input
+    ``x``. Weight gradients go to ``grads[name]`` (``[out, in]`` bf16 or fp32; added to when
+    ``accumulate``). Returns dx."""
     H, Hkv, D = shape.n_head, shape.n_kv, shape.head_dim
     sp = shape.sequence_parallel and shape.tp > 1
-    _, a = block_forward(x, w, freqs, pos, shape, keep=True)
+    if saved is None:
+        _, a = block_forward(x, w, freqs, pos, shape, keep=True)
+    else:
+        a = dict(saved)
+        if "act" not in a:
+            a["act"] = Fn.swiglu(a["g"], a["u"])
     T = a["xn1f"].shape[0]
 
     def wgrad(name, d_out, inp):

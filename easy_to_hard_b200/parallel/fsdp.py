@@ -181,14 +181,17 @@ class _BlockFn(torch.autograd.Function):
         ctx.tables = (sdp._input_pos, sdp._freqs_pos, sdp._freqs, sdp._pos)
         ctx.save_for_backward(x)
         with torch.no_grad():
-            return sdp._run_block(idx, x, B, S)
+            # the budget is zero for forwards that need no backward (set in hidden_states)
+            out, ctx.acts = sdp._run_block(idx, x, B, S, keep=True)
+        return out
 
     @staticmethod
     def backward(ctx, dy):
         (x,) = ctx.saved_tensors
         sdp = ctx.sdp
         sdp._input_pos, sdp._freqs_pos, sdp._freqs, sdp._pos = ctx.tables
-        dx = ctx.sdp._backward_block(ctx.idx, x, dy.contiguous(), *ctx.BS)
+        acts, ctx.acts = ctx.acts, None
+        dx = ctx.sdp._backward_block(ctx.idx, x, dy.contiguous(), *ctx.BS, saved=acts)
         return dx, None, None, None, None
 
 
@@ -250,6 +253,9 @@ class ShardedDataParallel(nn.Module):
                           if self.root else None)
         self._comm_stream = torch.cuda.Stream() if dev.type == "cuda" else None
         self._pending: Dict[int, "torch.cuda.Event"] = {}
+        self._keep_budget = 0          # bytes of block intermediates kept per forward (0: recompute)
+        self._keep_left = 0
+        self._keep_planned = False
         self.micro_step = 0
         if self.root is not None:
             self.root.gather_into(self._root_buf)   # small: stays gathered
@@ -305,19 +311,32 @@ class ShardedDataParallel(nn.Module):
                           tp=getattr(a, "tp_size", 1),
                           sequence_parallel=getattr(a, "sequence_parallel", False))
 
-    def _run_block(self, idx: int, x: torch.Tensor, B: int, S: int) -> torch.Tensor:
+    def _run_block(self, idx: int, x: torch.Tensor, B: int, S: int, keep: bool = False):
+        """One block forward. With ``keep`` (a training forward) the block's intermediates are
+        kept for the backward while the activation budget lasts, instead of being recomputed:
+        returns ``(out, saved or None)``."""
         unit = self._acquire(idx, idx + 1)
         blk = self.backbone.layers[idx]
+        saved = None
         if self.fused:
             from ..models import fused_block as fb
-            out, _ = fb.block_forward(x, self._block_weights(blk, unit), self._freqs, self._pos,
-                                      self._shape(blk, B, S))
+            want = keep and self._keep_left > 0
+            out, saved = fb.block_forward(x, self._block_weights(blk, unit), self._freqs,
+                                          self._pos, self._shape(blk, B, S), keep=want)
+            if saved is not None:
+                saved = {k: v for k, v in saved.items() if k not in ("act", "q", "k", "v")}
+                nbytes = sum(t.numel() * t.element_size() for t in saved.values())
+                if nbytes <= self._keep_left:
+                    self._keep_left -= nbytes
+                else:                      # does not fit: this block is recomputed instead
+                    saved, self._keep_left = None, 0
         else:
             out = blk(x, self._input_pos, self._freqs_pos, None, True)
         unit.release()
-        return out
+        return out, saved
 
-    def _backward_block(self, idx: int, x: torch.Tensor, dy: torch.Tensor, B: int, S: int):
+    def _backward_block(self, idx: int, x: torch.Tensor, dy: torch.Tensor, B: int, S: int,
+                        saved=None):
         unit = self._acquire(idx, idx - 1)
         blk = self.backbone.layers[idx]
         if self.fused:
@@ -326,8 +345,15 @@ class ShardedDataParallel(nn.Module):
             gradbuf = self._rs.grad_buffer(slot) if self._rs is not None else self._grad_buf
             views = unit.grad_views(gradbuf)
             grads = {n.split(".")[-2]: v for n, v in views.items()}
+            if saved is not None:          # q, k, v are views of the kept qkv
+                shp = self._shape(blk, B, S)
+                H, Hkv, D = shp.n_head, shp.n_kv, shp.head_dim
+                qkv = saved["qkv"]
+                saved["q"] = qkv[:, : H * D].view(B, S, H, D)
+                saved["k"] = qkv[:, H * D: (H + Hkv) * D].view(B, S, Hkv, D)
+                saved["v"] = qkv[:, (H + Hkv) * D:].view(B, S, Hkv, D)
             dx = fb.block_backward(dy, x, self._block_weights(blk, unit), grads, self._freqs,
-                                   self._pos, self._shape(blk, B, S))
+                                   self._pos, self._shape(blk, B, S), saved=saved)
         else:
             for p in unit.params:
                 p.grad = None
@@ -361,6 +387,7 @@ class ShardedDataParallel(nn.Module):
         self._freqs = bb.freqs_cis
         self._pos = torch.arange(S, device=dev, dtype=torch.int32).repeat(B)
         self._pending.clear()
+        self._keep_left = self._keep_budget if (torch.is_grad_enabled() and self.fused) else 0
         x = bb.embed(idx)
         sp = bb.sequence_parallel and bb.tp_size > 1 and self.training
         if sp:                       # rows of the batch are split over the tensor-parallel ranks
@@ -426,8 +453,35 @@ class ShardedDataParallel(nn.Module):
             p.grad = None
         self.root.reduce_grads(self._grad_buf)
 
+    def plan_activation_budget(self, margin_bytes: int = 14 << 30) -> int:
+        """How many bytes of block intermediates a training forward may keep for its backward
+        instead of recomputing them (the reference always recomputes,
+        models/model.py:233-243; with 180 GB per GPU the 7B model's 0.6 GB per block and
+        micro-batch fit beside weights, gradients and optimizer state). Measured between steps,
+        when only the static state is resident: free device memory plus what the caching
+        allocator holds unused, minus ``margin_bytes`` for the transient buffers of a step.
+        ``E2H_KEEP_ACTIVATIONS=0`` keeps the always-recompute behaviour, a number sets the
+        budget in GiB."""
+        import os
+        env = os.environ.get("E2H_KEEP_ACTIVATIONS", "auto")
+        dev = self.backbone.output.weight.device
+        if not self.fused or dev.type != "cuda" or env == "0":
+            self._keep_budget = 0
+        elif env not in ("auto", "1", ""):
+            self._keep_budget = int(float(env) * (1 << 30))
+        else:
+            free, _ = torch.cuda.mem_get_info(dev)
+            cached = torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
+            self._keep_budget = max(0, int(free + cached - margin_bytes))
+        return self._keep_budget
+
     def after_optimizer_step(self, lp_written: bool = False) -> None:
         """``lp_written``: the optimizer kernel already refreshed the low-precision shards."""
+        if not self._keep_planned:
+            # first optimizer step done: every piece of static state (moments, master weights,
+            # gradient shards) now exists, so the memory left over can be measured
+            self._keep_planned = True
+            self.plan_activation_budget()
         if not lp_written:
             for u in self._all_units():
                 u.refresh_low_precision()
