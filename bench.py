@@ -45,6 +45,8 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="decode", choices=["decode", "sft"],
                     help="decode: batched generation (headline); sft: full-parameter SFT step")
+    ap.add_argument("--quant", default="none", choices=["none", "int8", "int4"],
+                    help="decode: weight-only quantisation of the linears (int4: groups of 128)")
     ap.add_argument("--micro", type=int, default=8, help="sft: sequences per micro batch")
     ap.add_argument("--tp", type=int, default=1, help="sft: tensor-parallel size (rest is FSDP)")
     ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine")
@@ -169,6 +171,19 @@ def run_ours(a):
     if world > 1:
         tp.apply_tp(model)
         torch.cuda.empty_cache()
+    if a.quant == "int8":
+        from easy_to_hard_b200.models.quantize import WeightOnlyInt8QuantHandler
+        model = WeightOnlyInt8QuantHandler(model).convert_for_runtime_on_the_fly()
+    elif a.quant == "int4":
+        from easy_to_hard_b200.models.quantize import WeightOnlyInt4QuantHandler
+        h = WeightOnlyInt4QuantHandler(model, groupsize=128, inner_k_tiles=8)
+        sd = h.create_quantized_state_dict()
+        model = h.convert_for_runtime()
+        model.load_state_dict(sd, strict=False)
+        del sd
+    if a.quant != "none":
+        model = model.cuda()
+        torch.cuda.empty_cache()
     model.eval()
     eng = get_engine(model, BATCH, PROMPT + NEW, reduce=a.reduce, use_pdl=bool(a.pdl))
 
@@ -206,7 +221,8 @@ def run_ours(a):
             "metric": "batched_decode_tokens_per_s", "value": toks / (ms / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16",
+            "vs_baseline": None,
+            "dtype": "bf16" if a.quant == "none" else f"bf16 activations, {a.quant} weights",
             "data": "synthetic (random token ids, random-init weights)",
             "impl": "ours",
             "config": {"model": "Llemma-7B architecture (llemma-7b-32016)",
