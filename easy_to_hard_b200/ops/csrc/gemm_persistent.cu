@@ -86,7 +86,13 @@ __device__ __forceinline__ void tile_coords(int id, int n_f, int n_t, int& ft, i
   tt = band * kGroupT + r % tb;
 }
 
-template <int BN, bool DUAL>
+// PAIR: two CTAs of a cluster share one 256 (features) x 256 (tokens) tile with cta_group::2
+// instructions: CTA r of the pair owns features [128 r, 128 r + 128) of the tile (its A rows, its
+// accumulator lanes, its epilogue) and stages the B rows of tokens [128 r, 128 r + 128); the
+// leader (rank 0) issues every tcgen05.mma for both. The full barriers of the leader count the
+// TMA bytes of both CTAs, the commits are multicast to the barriers of both, and the peer's
+// epilogue warps hand the accumulator back on the leader's barrier.
+template <int BN, bool DUAL, bool PAIR>
 __global__ void __launch_bounds__(kPThreads, 1)
 umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                             const __grid_constant__ CUtensorMap tmA2,
@@ -94,8 +100,10 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                             const __grid_constant__ CUtensorMap tmOut,
                             const __grid_constant__ CUtensorMap tmRes, const E2hGemmParams p,
                             const int staged, const int mn3d) {
+  static_assert(!PAIR || (BN == 256 && !DUAL), "pair tiles are 2 x 128 features x 256 tokens");
   constexpr int A_BYTES = 128 * 128;                  // 128 features x 64 k, bf16
-  constexpr int B_BYTES = BN * 128;
+  constexpr int BROWS = PAIR ? BN / 2 : BN;           // B rows staged by this CTA
+  constexpr int B_BYTES = BROWS * 128;
   constexpr int STAGE = A_BYTES * (DUAL ? 2 : 1) + B_BYTES;
   constexpr int ACC_COLS = BN * (DUAL ? 2 : 1);
   static_assert(ACC_COLS <= 256, "two accumulator buffers must fit in 512 TMEM columns");
@@ -109,7 +117,11 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   uint8_t* stage_res = stage_out + 2 * kChunkBytes;         // 2 x kChunkBytes
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_f = (p.F + 127) / 128, n_t = (p.T + BN - 1) / BN;
+  const int crank = PAIR ? (int)cluster_ctarank() : 0;          // 0: leader of the pair
+  const int worker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;   // tile walker id
+  const int n_workers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  constexpr int TILE_F = PAIR ? 256 : 128;
+  const int n_f = (p.F + TILE_F - 1) / TILE_F, n_t = (p.T + BN - 1) / BN;
   const int n_tiles = n_f * n_t;
   const int n_kb = (p.K + 63) / 64;
   volatile int* abort_flag = &ctrl->abort_flag;
@@ -121,7 +133,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(smem_u32(&ctrl->tmem_full[a]), 1);
-      mbar_init(smem_u32(&ctrl->tmem_empty[a]), 4);   // one arrival per epilogue warp
+      mbar_init(smem_u32(&ctrl->tmem_empty[a]), PAIR ? 8 : 4);   // one arrival per epilogue warp
       mbar_init(smem_u32(&ctrl->res_full[a]), 1);
     }
     ctrl->abort_flag = 0;
@@ -132,13 +144,19 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     if (staged) tma_prefetch_desc(&tmOut);
   }
   if (warp == 1) {
-    tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
-    tmem_relinquish();
+    if constexpr (PAIR) {
+      tmem_alloc_pair(smem_u32(&ctrl->tmem_base), 512);
+      tmem_relinquish_pair();
+    } else {
+      tmem_alloc(smem_u32(&ctrl->tmem_base), 512);
+      tmem_relinquish();
+    }
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
+  if constexpr (PAIR) cluster_sync_all();   // the peer's barriers exist before anything signals them
   pdl_wait_prior();
   pdl_launch_dependents();
 
@@ -151,18 +169,41 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     const uint32_t tiles0 = smem_u32(tiles);
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+    const uint32_t full_lead0 = PAIR ? mapa_shared(full0, 0) : full0;   // leader's full barriers
+    for (int tile = worker; tile < n_tiles && ok; tile += n_workers) {
       int ft, tt;
       tile_coords(tile, n_f, n_t, ft, tt);
-      const int f0 = ft * 128, t0 = tt * BN;
+      const int f0 = ft * TILE_F + crank * 128, t0 = tt * BN + crank * BROWS * (PAIR ? 1 : 0);
       for (int kb = 0; kb < n_kb; ++kb, ++it) {
         if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) {
           ok = false;
           break;
         }
+        const uint32_t a_dst = tiles0 + s * STAGE;
+        if constexpr (PAIR) {
+          // the leader arms its barrier for the bytes of both CTAs; each CTA's copies complete
+          // on that barrier (the arrival count keeps the phase open until the leader has armed)
+          const uint32_t bar = full_lead0 + 8 * s;
+          if (crank == 0) mbar_expect_tx(full0 + 8 * s, 2 * STAGE);
+          const int k0p = kb * 64;
+          if (!p.a_mn_major) {
+            tma_load_2d_pair(a_dst, &tmA, k0p, f0, bar);
+          } else {
+            tma_load_3d_pair(a_dst, &tmA, 0, k0p, f0 >> 6, bar);
+          }
+          if (!p.b_mn_major) {
+            tma_load_2d_pair(a_dst + A_BYTES, &tmB, k0p, t0, bar);
+          } else {
+            tma_load_3d_pair(a_dst + A_BYTES, &tmB, 0, k0p, t0 >> 6, bar);
+          }
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1;
+          }
+          continue;
+        }
         const uint32_t bar = full0 + 8 * s;
         mbar_expect_tx(bar, STAGE);
-        const uint32_t a_dst = tiles0 + s * STAGE;
         if (++s == stages) {
           s = 0;
           ph ^= 1;
@@ -198,9 +239,9 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         }
       }
     }
-  } else if (warp == 1 && lane == 0) {
-    // ---------------- UMMA issuer ----------------
-    const uint32_t idesc = make_idesc_bf16(128, BN, p.a_mn_major, p.b_mn_major);
+  } else if (warp == 1 && lane == 0 && crank == 0) {
+    // ---------------- UMMA issuer (the leader's for a pair) ----------------
+    const uint32_t idesc = make_idesc_bf16(PAIR ? 256 : 128, BN, p.a_mn_major, p.b_mn_major);
     const uint32_t a_kstep = p.a_mn_major ? 2048u : 32u;
     const uint32_t b_kstep = p.b_mn_major ? 2048u : 32u;
     const uint32_t a_lbo = p.a_mn_major ? 8192u : 16u;
@@ -214,7 +255,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     int tcount = 0, s = 0;
     uint32_t ph = 0, st_lo = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++tcount) {
+    for (int tile = worker; tile < n_tiles && ok; tile += n_workers, ++tcount) {
       const int acc = tcount & 1;
       const uint32_t accph = (tcount >> 1) & 1;
       ok = mbar_wait(smem_u32(&ctrl->tmem_empty[acc]), accph ^ 1, abort_flag, p.status,
@@ -230,13 +271,18 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         const uint32_t a_lo = a_lo0 + st_lo, b_lo = b_lo0 + st_lo;
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_f16_lohi(d0, a_lo + k * a_ks, d_hi, b_lo + k * b_ks, d_hi, idesc, accum);
-          if (DUAL)
-            umma_f16_lohi(d0 + BN, a_lo + (A_BYTES >> 4) + k * a_ks, d_hi, b_lo + k * b_ks, d_hi,
-                          idesc, accum);
+          if constexpr (PAIR) {
+            umma_f16_lohi_pair(d0, a_lo + k * a_ks, d_hi, b_lo + k * b_ks, d_hi, idesc, accum);
+          } else {
+            umma_f16_lohi(d0, a_lo + k * a_ks, d_hi, b_lo + k * b_ks, d_hi, idesc, accum);
+            if (DUAL)
+              umma_f16_lohi(d0 + BN, a_lo + (A_BYTES >> 4) + k * a_ks, d_hi, b_lo + k * b_ks,
+                            d_hi, idesc, accum);
+          }
           accum = 1;
         }
-        umma_commit(empty0 + 8 * s);
+        if constexpr (PAIR) umma_commit_pair(empty0 + 8 * s);
+        else umma_commit(empty0 + 8 * s);
         if (++s == stages) {
           s = 0;
           st_lo = 0;
@@ -245,7 +291,10 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           st_lo += STAGE >> 4;
         }
       }
-      if (ok) umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+      if (ok) {
+        if constexpr (PAIR) umma_commit_pair(smem_u32(&ctrl->tmem_full[acc]));
+        else umma_commit(smem_u32(&ctrl->tmem_full[acc]));
+      }
     }
   } else if (warp >= 2) {
     // ---------------- epilogue warps ----------------
@@ -256,10 +305,13 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     const bool with_res = staged && p.epi == E2H_EPI_RESIDUAL;
     int tcount = 0, cc = 0;
     bool ok = true;
-    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++tcount) {
+    // the accumulator goes back to the MMA thread of the pair's leader
+    const uint32_t tmem_empty0 = PAIR ? mapa_shared(smem_u32(&ctrl->tmem_empty[0]), 0)
+                                      : smem_u32(&ctrl->tmem_empty[0]);
+    for (int tile = worker; tile < n_tiles; tile += n_workers, ++tcount) {
       int ft, tt;
       tile_coords(tile, n_f, n_t, ft, tt);
-      const int f0 = ft * 128, t0 = tt * BN;
+      const int f0 = ft * TILE_F + crank * 128, t0 = tt * BN;
       const int f = f0 + lane_row;
       const int acc = tcount & 1;
       const uint32_t accph = (tcount >> 1) & 1;
@@ -297,7 +349,10 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           if (c + 1 == BN / kChunkTok) {   // accumulator fully read: hand it back to the MMA
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(tmem_empty0 + 8 * acc);
+              else mbar_arrive(tmem_empty0 + 8 * acc);
+            }
           }
           if (with_res && ok)
             ok = mbar_wait(smem_u32(&ctrl->res_full[b]), (cc >> 1) & 1, abort_flag, p.status,
@@ -362,7 +417,10 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           if (c + 32 == BN) {
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) mbar_arrive(smem_u32(&ctrl->tmem_empty[acc]));
+            if (lane == 0) {
+              if constexpr (PAIR) mbar_arrive_cluster(tmem_empty0 + 8 * acc);
+              else mbar_arrive(tmem_empty0 + 8 * acc);
+            }
           }
           if (ok) {
 #pragma unroll
@@ -387,7 +445,14 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   if (p.n_signal > 0) __threadfence();
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_base, 512);
+  if constexpr (PAIR) {
+    // neither CTA may leave (or free tensor memory) while the other can still read its shared
+    // memory through an instruction in flight or signal one of its barriers
+    cluster_sync_all();
+    if (warp == 1) tmem_dealloc_pair(tmem_base, 512);
+  } else {
+    if (warp == 1) tmem_dealloc(tmem_base, 512);
+  }
   if (p.n_signal > 0 && threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(p.ticket, 1u) == gridDim.x - 1) {
@@ -449,9 +514,10 @@ static int p_map_mn3d(CUtensorMap* m, const void* base, long long mn, long long 
   return r == CUDA_SUCCESS ? 0 : -11;
 }
 
-template <int BN, bool DUAL>
+template <int BN, bool DUAL, bool PAIR>
 static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
-  constexpr int STAGE = 128 * 128 * (DUAL ? 2 : 1) + BN * 128;
+  constexpr int BROWS = PAIR ? BN / 2 : BN;
+  constexpr int STAGE = 128 * 128 * (DUAL ? 2 : 1) + BROWS * 128;
   CUtensorMap ta, ta2, tb, to, tr;
   int r;
   int mn3d = 0;
@@ -471,10 +537,10 @@ static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
   }
   if (p.b_mn_major && p.T % 64 == 0) {
     mn3d |= 2;
-    r = p_map_mn3d(&tb, p.b, p.T, p.K, p.ldb, BN / 64);
+    r = p_map_mn3d(&tb, p.b, p.T, p.K, p.ldb, BROWS / 64);
   } else {
     r = p.b_mn_major ? p_map(&tb, p.b, p.T, p.K, p.ldb, 64, 64, true)
-                     : p_map(&tb, p.b, p.K, p.T, p.ldb, 64, BN, true);
+                     : p_map(&tb, p.b, p.K, p.T, p.ldb, 64, BROWS, true);
   }
   if (r) return r;
   int staged = (p.epi == E2H_EPI_STORE_BF16 || p.epi == E2H_EPI_RESIDUAL ||
@@ -507,7 +573,7 @@ static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
   if (stages < 2) return -8;
   p.stages = stages;
   const size_t smem = 2048 + (size_t)stages * STAGE + 4 * kChunkBytes;
-  auto kern = umma_gemm_persistent_kernel<BN, DUAL>;
+  auto kern = umma_gemm_persistent_kernel<BN, DUAL, PAIR>;
   static size_t configured = 0;
   if (smem > configured) {
     cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -524,6 +590,32 @@ static int p_launch(E2hGemmParams& p, cudaStream_t stream) {
       cudaDeviceGetAttribute(&cached, cudaDevAttrMultiProcessorCount, dev);
     }
     if (cached > 0) n_sm = cached;
+  }
+  if constexpr (PAIR) {
+    // one cluster of two CTAs per 256 x 256 tile walker
+    const int n_tiles = (p.F / 256) * ((p.T + BN - 1) / BN);
+    const int pairs = n_tiles < n_sm / 2 ? n_tiles : n_sm / 2;
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * pairs, 1, 1);
+    cfg.blockDim = dim3(kPThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attrs[2];
+    int na = 0;
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = 2;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+    if (p.pdl || g_pdl) {
+      attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attrs[na].val.programmaticStreamSerializationAllowed = 1;
+      ++na;
+    }
+    cfg.attrs = attrs;
+    cfg.numAttrs = na;
+    return (int)cudaLaunchKernelEx(&cfg, kern, ta, ta2, tb, to, tr, p, staged, mn3d);
   }
   const int n_tiles = ((p.F + 127) / 128) * ((p.T + BN - 1) / BN);
   const int grid = n_tiles < n_sm ? n_tiles : n_sm;
@@ -543,7 +635,12 @@ extern "C" int e2h_gemm_persistent(const E2hGemmParams* pp, void* stream_v) {
   if (p.dual && (p.a_mn_major || p.a2 == nullptr)) return -5;
   if ((p.lda % 8) || (p.ldb % 8) || (p.dual && (p.lda2 % 8))) return -6;
   if (((uintptr_t)p.a & 15) || ((uintptr_t)p.b & 15)) return -7;
-  if (p.dual) return p_launch<128, true>(p, stream);
-  if (p.bn == 128) return p_launch<128, false>(p, stream);
-  return p_launch<256, false>(p, stream);
+  if (p.dual) return p_launch<128, true, false>(p, stream);
+  if (p.bn == 128) return p_launch<128, false, false>(p, stream);
+  // tf == 256 asks for CTA-pair tiles (cta_group::2): 256-feature tiles, operands that the 3-D
+  // boxes can address
+  if (p.tf == 256 && (p.F % 256) == 0 && p.T > 256 && (p.K % 64) == 0 &&
+      (!p.b_mn_major || (p.T % 64) == 0))
+    return p_launch<256, false, true>(p, stream);
+  return p_launch<256, false, false>(p, stream);
 }

@@ -82,7 +82,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
          signal=None, ticket: Optional[torch.Tensor] = None,
          persistent: Optional[bool] = None, streamk: Optional[bool] = None, sk_ctas: int = 0,
-         sk_smem_kb: int = 0) -> None:
+         sk_smem_kb: int = 0, pair: Optional[bool] = None) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T]).
     An int8 ``a`` (weight-only quantisation; ``scale`` holds the per-feature scales) streams as
     int8 through the converting kernel for up to 128 tokens and is expanded to a scratch bf16
@@ -197,6 +197,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
            (T > bn and splitk == 1 and tf == 128 and tiled_shape is None and debug_mode == 0
             and bn >= 128))
     if big:
+        if (pair if pair is not None else PAIR_DEFAULT) and not dual and bn == 256:
+            p.tf = 256      # CTA-pair (cta_group::2) tiles where the shape allows them
         _lib.check(_lib.lib().e2h_gemm_persistent(C.byref(p), _lib.stream()),
                    "e2h_gemm_persistent")
     else:
@@ -249,6 +251,8 @@ _SK_WS: dict = {}
 # skinny GEMMs (one token tile of at most 128 tokens, K-major operands) may take the work-split
 # kernel (``streamk=True`` per call, or E2H_STREAMK=1 for every eligible call)
 STREAMK_DEFAULT = os.environ.get("E2H_STREAMK", "0") == "1"
+# large GEMMs on CTA pairs (cta_group::2, 256 x 256 tiles): E2H_GEMM_PAIR=0 keeps single-CTA tiles
+PAIR_DEFAULT = os.environ.get("E2H_GEMM_PAIR", "1") != "0"
 STREAMK_SMEM_KB = int(os.environ.get("E2H_STREAMK_SMEM_KB", "0"))   # 0: half an SM per CTA
 
 

@@ -133,3 +133,36 @@ def test_qkv_rope_kv(sq, B, n_head, n_kv, D, tf):
     _close(kc[:B, :, pos0:pos0 + sq].transpose(1, 2), kr)
     _close(vc[:B, :, pos0:pos0 + sq].transpose(1, 2), vr)
     assert kc[B].abs().sum().item() == 0 and kc[:, :, :pos0].abs().sum().item() == 0
+
+
+@pytest.mark.parametrize("T,F,K", [(512, 512, 256), (700, 768, 1024), (1536, 1024, 2048 + 64),
+                                   (3000, 256, 512)])
+def test_cta_pair_tiles_match_fp32(T, F, K):
+    """256 x 256 tiles on CTA pairs (cta_group::2): forward, dgrad, wgrad (bf16 and accumulated
+    fp32), residual epilogue, ragged token counts, against fp32 PyTorch."""
+    from easy_to_hard_b200.ops import _lib, gemm
+    g = torch.Generator(device="cuda").manual_seed(T + F)
+    x = (torch.randn(T, K, device="cuda", generator=g) * 0.5).bfloat16()
+    w = (torch.randn(F, K, device="cuda", generator=g) * 0.05).bfloat16()
+    dy = (torch.randn(T, F, device="cuda", generator=g) * 0.5).bfloat16()
+    res = torch.randn(T, F, device="cuda", generator=g).bfloat16()
+
+    def rel(got, want):
+        return float((got.float() - want).abs().max() / want.abs().max())
+
+    y = x.float() @ w.float().T
+    assert rel(gemm.linear(x, w, pair=True), y) < 1e-2
+    assert rel(gemm.linear(x, w, out_dtype=torch.float32, pair=True), y) < 2e-3
+    assert rel(gemm.linear_residual(x, w, res, pair=True), res.float() + y.bfloat16().float()) < 1e-2
+    assert rel(gemm.linear_dgrad(dy, w, pair=True), dy.float() @ w.float()) < 1e-2
+    dw = dy.float().T @ x.float()
+    if T % 64 == 0:
+        out16 = torch.empty(F, K, device="cuda", dtype=torch.bfloat16)
+        assert rel(gemm.linear_wgrad(dy, x, out=out16, pair=True), dw) < 1e-2
+        acc = torch.ones(F, K, device="cuda")
+        gemm.linear_wgrad(dy, x, out=acc, accumulate=True, pair=True)
+        assert rel(acc, dw + 1.0) < 2e-3
+    # same numbers as the single-CTA tiles up to accumulation order
+    assert rel(gemm.linear(x, w, pair=True), gemm.linear(x, w, pair=False).float()) < 1e-2
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
