@@ -47,7 +47,7 @@ def parse():
                     help="decode: batched generation (headline); sft: full-parameter SFT step")
     ap.add_argument("--quant", default="none", choices=["none", "int8", "int4"],
                     help="decode: weight-only quantisation of the linears (int4: groups of 128)")
-    ap.add_argument("--micro", type=int, default=8, help="sft: sequences per micro batch")
+    ap.add_argument("--micro", type=int, default=16, help="sft: sequences per micro batch")
     ap.add_argument("--tp", type=int, default=1, help="sft: tensor-parallel size (rest is FSDP)")
     ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch in the "
@@ -299,7 +299,7 @@ def run_ours_sft(a):
     host = sft_batches(a.steps + a.warmup, cfg.vocab_size, per_rank, rank)
     dev = [(i.cuda(), l.cuda()) for i, l in host]
     host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
-    micro = a.micro
+    micro = max(1, min(a.micro, per_rank * a.tp))     # sequences per forward/backward pass
 
     def step_device(i):
         ids, labels = prepare_batch(*dev[i % len(dev)], -1, 0, a.tp > 1)
