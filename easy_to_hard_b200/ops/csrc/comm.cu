@@ -135,12 +135,23 @@ __global__ void p2p_gather_kernel(const PeerBytes src, int n_peer, uint8_t* __re
                                   unsigned int* ticket, long long wait_cycles, int* status) {
   comm_wait_all(flags, n_peer, use_count, status, wait_cycles);
   const long long nvec = nbytes >> 4;
+  // always system-scope loads: the peers rewrite these buffers between uses (between optimizer
+  // steps for parameter shards), a line kept in this SM's L1 from an earlier use must not serve
+  const long long stride = (long long)gridDim.x * blockDim.x;
   for (int r = 0; r < n_peer; ++r) {
     uint4* dst = reinterpret_cast<uint4*>(out + (long long)r * nbytes);
-    for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < nvec;
-         i += (long long)gridDim.x * blockDim.x)
-      dst[i] = flags ? comm_ld_sys_b32x4(src.p[r] + 16 * i)
-                     : *reinterpret_cast<const uint4*>(src.p[r] + 16 * i);
+    long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+    for (; i + 3 * stride < nvec; i += 4 * stride) {      // four loads in flight per thread
+      const uint4 a = comm_ld_sys_b32x4(src.p[r] + 16 * i);
+      const uint4 b = comm_ld_sys_b32x4(src.p[r] + 16 * (i + stride));
+      const uint4 c = comm_ld_sys_b32x4(src.p[r] + 16 * (i + 2 * stride));
+      const uint4 d = comm_ld_sys_b32x4(src.p[r] + 16 * (i + 3 * stride));
+      dst[i] = a;
+      dst[i + stride] = b;
+      dst[i + 2 * stride] = c;
+      dst[i + 3 * stride] = d;
+    }
+    for (; i < nvec; i += stride) dst[i] = comm_ld_sys_b32x4(src.p[r] + 16 * i);
   }
   comm_done(flags, use_count, ticket);
 }
@@ -242,7 +253,9 @@ int e2h_p2p_all_gather(const void* const* peer_src, int n_peer, void* out, long 
     s.p[i] = i < n_peer ? (const uint8_t*)peer_src[i] : nullptr;
     if (i < n_peer && (reinterpret_cast<uintptr_t>(s.p[i]) & 15)) return -3;
   }
-  p2p_gather_kernel<<<comm_blocks(nbytes / 16), 256, 0, (cudaStream_t)stream>>>(
+  unsigned blocks = comm_blocks(nbytes / 16);
+  if (blocks > 296) blocks = 296;   // two CTAs per SM keep NVLink busy and leave the SMs to the GEMMs
+  p2p_gather_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>(
       s, n_peer, (uint8_t*)out, nbytes, flags, use_count, ticket, comm_cycles(wait_ms), status);
   return (int)cudaGetLastError();
 }

@@ -81,12 +81,37 @@ class ShardUnit:
         for p in self.params:             # the full tensors only exist while gathered
             p.data = torch.empty(0, dtype=compute_dtype, device=dev)
         self.gathered_in: Optional[torch.Tensor] = None
+        self.lp_symm = None        # (SymmetricBuffer, byte offset) once shard_lp lives in one
+
+    def move_lp_to(self, sbuf, offset: int) -> None:
+        """Re-home the low-precision shard into symmetric memory (peers read it directly)."""
+        view = sbuf.view(offset, (self.shard_size,), self.compute_dtype)
+        view.copy_(self.shard_lp)
+        self.shard_lp = view
+        if hasattr(self.shard, "_lp_copy"):
+            self.shard._lp_copy = view
+        self.lp_symm = (sbuf, offset)
 
     # -------------------------------------------------------------- parameters
     def gather_into(self, buf: torch.Tensor) -> None:
         """All-gather the bf16 shards into ``buf`` and point the parameters at views of it."""
         full = buf[: self.padded]
-        if self.world > 1:
+        if self.world > 1 and self.lp_symm is not None:
+            # pull every rank's bf16 shard straight out of its symmetric memory (NVLink loads in
+            # our own kernel); the shards only change at optimizer steps, which are fenced by
+            # barriers on both sides (ShardedDataParallel.finish_backward / after_optimizer_step)
+            import ctypes as C
+            from ..ops import _lib
+            sbuf, off = self.lp_symm
+            arr = (C.c_void_p * 8)()
+            for r in range(self.world):
+                arr[r] = sbuf.peer_ptr(r, off)
+            rc = _lib.lib().e2h_p2p_all_gather(arr, self.world, full.data_ptr(),
+                                               self.shard_size * 2, None, None, None, 0,
+                                               _lib.status_word(full.device).data_ptr(),
+                                               _lib.stream())
+            _lib.check(rc, "p2p_all_gather")
+        elif self.world > 1:
             dist.all_gather_into_tensor(full, self.shard_lp, group=self.group)
         else:
             full.copy_(self.shard_lp)
@@ -243,12 +268,23 @@ class ShardedDataParallel(nn.Module):
         self._grad_buf = torch.empty(biggest, dtype=self.compute_dtype, device=dev)
         # fused pull-based gradient reduce-scatter over peer memory (falls back to NCCL)
         self._rs = None
+        self._lp_bar = None
         if (self.fused and self.world > 1 and param_dtype == torch.float32
                 and self.compute_dtype == torch.bfloat16):
             from ..models.fused_block import p2p_reduce_enabled
             if p2p_reduce_enabled():
-                from .symm import GradReduceScatter
+                from .symm import GradReduceScatter, P2PChannel, SymmetricBuffer
                 self._rs = GradReduceScatter(biggest, process_group)
+                # parameter all-gather as a pull over peer memory: every unit's bf16 shard lives
+                # in one symmetric allocation
+                sizes = [(u.shard_size * 2 + 255) // 256 * 256 for u in self._all_units()]
+                self._lp_buf = SymmetricBuffer(sum(sizes), process_group)
+                off = 0
+                for u, nb in zip(self._all_units(), sizes):
+                    u.move_lp_to(self._lp_buf, off)
+                    off += nb
+                self._lp_bar = P2PChannel(256, process_group)
+                self._lp_bar.barrier()      # every rank's shards are in place
         self._root_buf = (torch.empty(self.root.padded, dtype=self.compute_dtype, device=dev)
                           if self.root else None)
         self._comm_stream = torch.cuda.Stream() if dev.type == "cuda" else None
@@ -444,7 +480,11 @@ class ShardedDataParallel(nn.Module):
             u.shard.grad = None
 
     def finish_backward(self) -> None:
-        """Reduce the root unit's gradients (tensors outside the block stack)."""
+        """Reduce the root unit's gradients (tensors outside the block stack). With parameter
+        shards in peer-readable memory this is also the point where every rank has finished
+        reading them for this step: a barrier before the optimizer may overwrite them."""
+        if self._lp_bar is not None:
+            self._lp_bar.barrier()
         if self.root is None:
             return
         views = self.root.grad_views(self._grad_buf)
@@ -485,8 +525,14 @@ class ShardedDataParallel(nn.Module):
         if not lp_written:
             for u in self._all_units():
                 u.refresh_low_precision()
+        self._lp_fence()
         if self.root is not None:
             self.root.gather_into(self._root_buf)
+
+    def _lp_fence(self) -> None:
+        """Every rank has written its low-precision shards before any rank pulls them."""
+        if self._lp_bar is not None:
+            self._lp_bar.barrier()
 
     # ------------------------------------------------------------------ checkpoints
     def full_state_dict(self, rank0_only: bool = True) -> Optional[Dict[str, torch.Tensor]]:
@@ -510,6 +556,7 @@ class ShardedDataParallel(nn.Module):
         for k, v in state.items():
             if k in bufs and bufs[k].shape == v.shape:
                 bufs[k].data.copy_(v)
+        self._lp_fence()
         if self.root is not None:
             self.root.gather_into(self._root_buf)
         if strict and missing:
