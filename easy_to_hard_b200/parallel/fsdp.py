@@ -221,10 +221,14 @@ class _BlockFn(torch.autograd.Function):
 
 
 class ShardedDataParallel(nn.Module):
+    _instances: List = []          # weak references, for sharing the activation budget
+
     def __init__(self, model: nn.Module, process_group=None, param_dtype=torch.float32,
                  compute_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16,
                  fused: Optional[bool] = None):
         super().__init__()
+        import weakref
+        ShardedDataParallel._instances.append(weakref.ref(self))
         self.module = model
         backbone = getattr(model, "backbone_model", model)
         self.backbone = backbone
@@ -357,8 +361,17 @@ class ShardedDataParallel(nn.Module):
         if self.fused:
             from ..models import fused_block as fb
             want = keep and self._keep_left > 0
-            out, saved = fb.block_forward(x, self._block_weights(blk, unit), self._freqs,
-                                          self._pos, self._shape(blk, B, S), keep=want)
+            try:
+                out, saved = fb.block_forward(x, self._block_weights(blk, unit), self._freqs,
+                                              self._pos, self._shape(blk, B, S), keep=want)
+            except torch.cuda.OutOfMemoryError:
+                if not want or self.world > 1 or getattr(blk.attention, "tp_size", 1) > 1:
+                    raise      # with peers, a one-sided retry would re-issue collectives
+                # the budget was too optimistic: back to recomputation from here on
+                self._keep_budget = self._keep_left = 0
+                torch.cuda.empty_cache()
+                out, saved = fb.block_forward(x, self._block_weights(blk, unit), self._freqs,
+                                              self._pos, self._shape(blk, B, S), keep=False)
             if saved is not None:
                 saved = {k: v for k, v in saved.items() if k not in ("act", "q", "k", "v")}
                 nbytes = sum(t.numel() * t.element_size() for t in saved.values())
@@ -512,7 +525,16 @@ class ShardedDataParallel(nn.Module):
         else:
             free, _ = torch.cuda.mem_get_info(dev)
             cached = torch.cuda.memory_reserved(dev) - torch.cuda.memory_allocated(dev)
-            self._keep_budget = max(0, int(free + cached - margin_bytes))
+            # several wrapped models in one process (PPO: policy and value) share what is left
+            live = max(1, sum(1 for m in ShardedDataParallel._instances
+                              if m() is not None and m().fused))
+            self._keep_budget = max(0, int(free + cached - margin_bytes)) // live
+        if dist.is_available() and dist.is_initialized() and dev.type == "cuda":
+            # the same decision on every rank: a block that one tensor-parallel rank recomputes
+            # (issuing its collectives again) must be recomputed by all of them
+            t = torch.tensor([self._keep_budget], dtype=torch.int64, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            self._keep_budget = int(t.item())
         return self._keep_budget
 
     def after_optimizer_step(self, lp_written: bool = False) -> None:
