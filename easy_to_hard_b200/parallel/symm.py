@@ -23,6 +23,9 @@ import torch.distributed as dist
 
 
 class SymmetricBuffer:
+    GUARD = 256        # bytes of canary after the payload
+    CANARY = 0xA5
+
     def __init__(self, nbytes: int, group=None, device=None):
         import torch.distributed._symmetric_memory as symm_mem
         assert dist.is_initialized(), "SymmetricBuffer needs an initialised process group"
@@ -31,9 +34,13 @@ class SymmetricBuffer:
         self.rank = dist.get_rank(group)
         dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
         nbytes = (nbytes + 255) // 256 * 256
-        self.local = symm_mem.empty(nbytes, dtype=torch.uint8, device=dev)
-        self.local.zero_()
-        self.handle = symm_mem.rendezvous(self.local, group)
+        # one guard block after the payload: peers write into this allocation with raw
+        # pointers, so an overrun would otherwise go unnoticed (see check_canary)
+        self._raw = symm_mem.empty(nbytes + self.GUARD, dtype=torch.uint8, device=dev)
+        self._raw.zero_()
+        self._raw[nbytes:].fill_(self.CANARY)
+        self.local = self._raw[:nbytes]
+        self.handle = symm_mem.rendezvous(self._raw, group)
         self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
         try:
             self.multicast_ptr = int(self.handle.multicast_ptr)
@@ -46,15 +53,25 @@ class SymmetricBuffer:
     def emulated(cls, nbytes: int, world: int, device="cuda") -> List["SymmetricBuffer"]:
         """``world`` buffers in one process; buffer r plays rank r's copy."""
         nbytes = (nbytes + 255) // 256 * 256
-        locals_ = [torch.zeros(nbytes, dtype=torch.uint8, device=device) for _ in range(world)]
+        raws = [torch.zeros(nbytes + cls.GUARD, dtype=torch.uint8, device=device)
+                for _ in range(world)]
+        for t in raws:
+            t[nbytes:].fill_(cls.CANARY)
+        locals_ = [t[:nbytes] for t in raws]
         out = []
         for r in range(world):
             b = cls.__new__(cls)
-            b.world, b.rank, b.local = world, r, locals_[r]
+            b.world, b.rank, b.local, b._raw = world, r, locals_[r], raws[r]
             b.handle, b.multicast_ptr = None, 0
             b.ptrs = [t.data_ptr() for t in locals_]
             out.append(b)
         return out
+
+    def check_canary(self) -> bool:
+        """True while nothing (this rank's kernels or a peer's stores) has written past the end
+        of the payload. Synchronises the device; meant for tests and post-mortems."""
+        guard = self._raw[self.local.numel():]
+        return bool((guard == self.CANARY).all().item())
 
     def view(self, offset: int, shape, dtype) -> torch.Tensor:
         """Typed view of the local copy at a byte offset."""

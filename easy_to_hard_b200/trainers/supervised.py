@@ -160,6 +160,8 @@ def run(args, task: Task) -> Dict:
         return record
     _log(rank0, "Starting training ...")
     t0 = time.time()
+    from ..utils.tracing import StepProfiler
+    profiler = StepProfiler(getattr(args, "profile", None))   # --profile: trace of a few steps
     try:
         for epoch in range(args.num_train_epochs):
             if sampler is not None:
@@ -173,6 +175,7 @@ def run(args, task: Task) -> Dict:
                 if task.prepare is not None:
                     tensors = task.prepare(tensors, tokenizer)
                 tensors = gather_tp_batch(tensors, use_tp)
+                profiler.step()
                 loss, grad_norm = guarded_step(monitor, stepper.step, *tensors,
                                                micro_batch_size=micro_global)
                 if it % task.log_every == 0:
@@ -203,6 +206,7 @@ def run(args, task: Task) -> Dict:
                         epoch_length, use_fsdp=use_fsdp,
                         trainable_param_names=trainable_param_names)
     finally:
+        profiler.close()
         if monitor is not None:
             monitor.stop()
     _log(rank0, f"Time to train: {time.time() - t0:.02f} seconds")

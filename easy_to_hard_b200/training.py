@@ -134,13 +134,20 @@ class TrainStepper:
         mb = micro_batch_size or n
         scale = 1.0 / (-(-n // mb))
         loss = None
+        nvtx = torch.cuda.nvtx if torch.cuda.is_available() else None
         for a in range(0, n, mb):
+            if nvtx:
+                nvtx.range_push("forward_backward")
             out = self.loss_fn(model, *[t[a:a + mb] for t in tensors])
             if isinstance(out, tuple):
                 loss, self.metrics = out
             else:
                 loss = out
             (loss * scale).backward()
+            if nvtx:
+                nvtx.range_pop()
+        if nvtx:
+            nvtx.range_push("clip_and_optimizer")
         if self.sharded:
             model.finish_backward()
         if self.clipper is not None:
@@ -153,6 +160,8 @@ class TrainStepper:
             model.after_optimizer_step(lp_written=hasattr(self.optimizer, "clip_coef"))
         if self.scheduler is not None:
             self.scheduler.step()
+        if nvtx:
+            nvtx.range_pop()
         return loss.detach(), grad_norm
 
 

@@ -92,8 +92,11 @@ def test_train_rm_pointwise_end_to_end(workspace, tmp_path):
     import train_rm_pointwise
     save = tmp_path / "prm"
     rec = train_rm_pointwise.main(_args(workspace, save, dataset=str(workspace / "prm.json"),
-                                        dataset_format="prm-v2"))
+                                        dataset_format="prm-v2",
+                                        profile=str(tmp_path / "trace")))
     assert 0.3 < rec["loss"] < 1.5
+    # --profile: a chrome trace of the steps after the first one
+    assert any(f.startswith("trace") and f.endswith(".json") for f in os.listdir(tmp_path))
     ck = torch.load(save / "epoch_1_step_2_rank_0.pt", weights_only=False)
     assert "backbone_model.output.weight" in ck["model"]
     assert ck["model"]["backbone_model.output.weight"].shape == (2, 256)

@@ -36,6 +36,9 @@ def test_all_gather_and_one_shot_all_reduce(world):
         assert float((outs[0].float() - want).abs().max()) <= 0.02 * float(want.abs().max())
     torch.cuda.synchronize()
     assert _lib.read_status() == 0
+    assert all(c.buf.check_canary() for c in ch)            # nothing wrote past a payload
+    ch[0].buf._raw[-1] = 0                                  # and the check does see an overrun
+    assert not ch[0].buf.check_canary()
 
 
 def test_reduce_scatter_slices_and_two_shot():
