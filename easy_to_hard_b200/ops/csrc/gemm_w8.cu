@@ -154,8 +154,12 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
   if (S > 1) cluster_sync_all();
-  pdl_wait_prior();
+  // programmatic dependent launch: the successor may start its prologue; this kernel's producer
+  // streams the opening weight tiles (never written by a preceding kernel of the chain) before
+  // it waits for the predecessor, every other thread that touches global memory waits first
   pdl_launch_dependents();
+  const bool early_weights = !p.debug_mode;
+  if (!(warp == 0 && lane == 0 && early_weights) && !(warp == 1 && lane == 0)) pdl_wait_prior();
 
   if (warp == 0 && lane == 0) {
     // ---------------- TMA producer ----------------
@@ -165,7 +169,26 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     uint32_t ph = 0;
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     const uint32_t tiles0 = smem_u32(tiles);
-    for (int it = 0; it < n_it; ++it) {
+    int it0 = 0;
+    if (early_weights) {
+      const int n_pre = n_it < stages ? n_it : stages;
+      for (int it = 0; it < n_pre; ++it) {
+        const uint32_t bar = full0 + 8 * it;
+        const uint32_t st = tiles0 + it * STAGE;
+        const int kb = kb_begin + it * kW8Kps;
+        mbar_expect_tx(bar, STAGE);
+        tma_load_3d_hint(st, &tmA, 0, f0, kb / kW8Kps, bar, pol_a);
+        if (DUAL) tma_load_3d_hint(st + AQ_BYTES, &tmA2, 0, f0, kb / kW8Kps, bar, pol_a);
+      }
+      pdl_wait_prior();
+      for (int it = 0; it < n_pre; ++it)
+        tma_load_3d(tiles0 + it * STAGE + AQ_BYTES * NMAT, &tmB, 0, t0, kb_begin + it * kW8Kps,
+                    full0 + 8 * it);
+      armed = it0 = n_pre;
+      s = n_pre == stages ? 0 : n_pre;
+      ph = n_pre == stages ? 1 : 0;
+    }
+    for (int it = it0; it < n_it; ++it) {
       if (!mbar_wait(empty0 + 8 * s, ph ^ 1, abort_flag, p.status, kStatusTimeoutEmpty)) break;
       const uint32_t bar = full0 + 8 * s;
       const uint32_t st = tiles0 + s * STAGE;
