@@ -149,7 +149,8 @@ flash_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant_
   uint8_t* p_s = v_s + 2 * kTileBytes;       // 2 buffers
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // the last query tiles meet the most key tiles: launch them first (longest work first)
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
   const int q0 = qb * kBQ;
   const int off = p.Sk - p.Sq;                        // query i sits at key position i + off
@@ -716,7 +717,8 @@ flash_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_consta
   uint8_t* ds_s = v_s + kTile;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int qb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  // the last query tiles meet the most key tiles: launch them first (longest work first)
+  const int qb = gridDim.x - 1 - blockIdx.x, h = blockIdx.y, b = blockIdx.z;
   const int hk = h / (p.H / p.Hkv);
   const int q0 = qb * kBQ;
   const int off = p.Sk - p.Sq;
