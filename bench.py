@@ -364,7 +364,8 @@ def run_reference(a):
 
     if not os.path.isdir(os.path.join(ref_dir, "models")):
         return unavailable("reference is not installed under baseline/_ref "
-                           "(no setup.py/pyproject in the reference; see DESIGN.md)")
+                           "(the reference ships neither setup.py nor pyproject.toml: install it from a copy "
+                           "with a minimal setup.py, --no-deps)")
     try:
         from baseline import reference_runner
     except Exception as e:  # noqa: BLE001
