@@ -225,8 +225,13 @@ class ShardedDataParallel(nn.Module):
 
     def __init__(self, model: nn.Module, process_group=None, param_dtype=torch.float32,
                  compute_dtype=torch.bfloat16, reduce_dtype=torch.bfloat16,
-                 fused: Optional[bool] = None):
+                 fused: Optional[bool] = None, keep_params: bool = False):
+        """``keep_params``: the gathered low-precision parameters of every block stay resident
+        between optimizer steps (gradients and optimizer state remain sharded): one all-gather
+        per block and step instead of one per use. This is the reference's ``SHARD_GRAD_OP``
+        choice for ``--slow_cross_node_comm`` (trainers/ppo_trainer.py:1384-1388)."""
         super().__init__()
+        self.keep_params = keep_params
         import weakref
         ShardedDataParallel._instances.append(weakref.ref(self))
         self.module = model
@@ -267,8 +272,14 @@ class ShardedDataParallel(nn.Module):
                                   reduce_dtype if self.fused else param_dtype)
         self._shards = nn.ParameterList([u.shard for u in self._all_units()])
         biggest = max(u.padded for u in self._all_units())
-        self._param_bufs = [torch.empty(biggest, dtype=self.compute_dtype, device=dev)
-                            for _ in range(2)]
+        if keep_params:      # one resident buffer per block
+            self._param_bufs = [torch.empty(u.padded, dtype=self.compute_dtype, device=dev)
+                                for u in self.units]
+        else:                # two rotating buffers: the block in use and the prefetched one
+            self._param_bufs = [torch.empty(biggest, dtype=self.compute_dtype, device=dev)
+                                for _ in range(2)]
+        self._resident = [False] * len(self.units)
+        self.gathers = 0     # block all-gathers issued (what keep_params saves)
         self._grad_buf = torch.empty(biggest, dtype=self.compute_dtype, device=dev)
         # fused pull-based gradient reduce-scatter over peer memory (falls back to NCCL)
         self._rs = None
@@ -316,7 +327,13 @@ class ShardedDataParallel(nn.Module):
     def _prefetch(self, idx: int) -> None:
         if not (0 <= idx < len(self.units)) or idx in self._pending:
             return
-        unit, buf = self.units[idx], self._param_bufs[idx % 2]
+        if self.keep_params and self._resident[idx]:
+            self._pending[idx] = None       # still gathered from an earlier use of this step
+            return
+        unit = self.units[idx]
+        buf = self._param_bufs[idx if self.keep_params else idx % 2]
+        self._resident[idx] = self.keep_params
+        self.gathers += 1
         if self._comm_stream is None:
             unit.gather_into(buf)
             self._pending[idx] = None
@@ -381,7 +398,8 @@ class ShardedDataParallel(nn.Module):
                     saved, self._keep_left = None, 0
         else:
             out = blk(x, self._input_pos, self._freqs_pos, None, True)
-        unit.release()
+        if not self.keep_params:
+            unit.release()
         return out, saved
 
     def _backward_block(self, idx: int, x: torch.Tensor, dy: torch.Tensor, B: int, S: int,
@@ -415,7 +433,8 @@ class ShardedDataParallel(nn.Module):
             for (n, v), p in zip(unit.grad_views(self._grad_buf).items(), unit.params):
                 v.copy_(p.grad if p.grad is not None else torch.zeros_like(v))
                 p.grad = None
-        unit.release()
+        if not self.keep_params:
+            unit.release()
         if self.fused and self._rs is not None:
             unit.reduce_grads_p2p(self._rs, slot)
         else:
@@ -547,6 +566,7 @@ class ShardedDataParallel(nn.Module):
         if not lp_written:
             for u in self._all_units():
                 u.refresh_low_precision()
+        self._resident = [False] * len(self.units)     # resident copies are stale now
         self._lp_fence()
         if self.root is not None:
             self.root.gather_into(self._root_buf)
@@ -578,6 +598,7 @@ class ShardedDataParallel(nn.Module):
         for k, v in state.items():
             if k in bufs and bufs[k].shape == v.shape:
                 bufs[k].data.copy_(v)
+        self._resident = [False] * len(self.units)
         self._lp_fence()
         if self.root is not None:
             self.root.gather_into(self._root_buf)

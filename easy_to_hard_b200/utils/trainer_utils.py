@@ -39,7 +39,8 @@ def create_fsdp_model_for_finetune(args, model: torch.nn.Module, bf16_all_reduce
     reduce_dtype = torch.float32 if dp >= bf16_all_reduce_upper_bound else args.compute_dtype
     return ShardedDataParallel(model, process_group=groups.get_data_parallel_group(),
                                param_dtype=args.param_dtype, compute_dtype=args.compute_dtype,
-                               reduce_dtype=reduce_dtype)
+                               reduce_dtype=reduce_dtype,
+                               keep_params=bool(getattr(args, "slow_cross_node_comm", False)))
 
 
 def _cosine_with_warmup(step: int, *, warmup: int, total: int, warmup_start_ratio: float,

@@ -102,7 +102,7 @@ def _merged_state(sdp):
 
 
 def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_parallel=False,
-                          steps=1, micro=None, gen=True, device="cpu"):
+                          steps=1, micro=None, gen=True, device="cpu", keep_params=False):
     """One (or more) SFT steps on the tiny model with TP=tp, DP=world/tp, then greedy decode."""
     from easy_to_hard_b200.models import tp as tpm
     from easy_to_hard_b200.parallel import groups
@@ -120,7 +120,8 @@ def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_para
         tpm.apply_tp(model, requires_grad=True, sequence_parallel=sequence_parallel)
     for n, p in model.named_parameters():
         p.requires_grad_(True)
-    sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group())
+    sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group(),
+                              keep_params=keep_params)
     sdp.train()
     opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=1e-4, weight_decay=0.0,
                                optim_dtype=torch.float32, optim_device=device)
@@ -145,7 +146,7 @@ def sft_step_and_generate(rank, world, tp=1, sequence_parallel=False, vocab_para
         shards = [None] * tp
         dist.all_gather_object(shards, state, group=groups.get_model_parallel_group())
         state = merge_tp_checkpoint(shards, heads=heads)
-    out = {"loss": losses, "grad_norm": norms, "state": state}
+    out = {"loss": losses, "grad_norm": norms, "state": state, "gathers": sdp.gathers}
     if gen:
         # decode with the updated weights through the plain module path
         for u in sdp.units:

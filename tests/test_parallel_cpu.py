@@ -47,6 +47,22 @@ def test_sharded_data_parallel_matches_single(single, tmp_path):
         _compare(single, r)
 
 
+def test_resident_parameters_match_and_gather_once_per_step(tmp_path):
+    """``keep_params`` (the reference's SHARD_GRAD_OP choice for --slow_cross_node_comm): same
+    two training steps as full re-sharding, one all-gather per block and step instead of one per
+    forward / backward use of every micro batch."""
+    kw = dict(tp=1, steps=2, micro=1, gen=False)
+    a = W.run(W.sft_step_and_generate, 2, str(tmp_path / "reshard"), **kw)
+    b = W.run(W.sft_step_and_generate, 2, str(tmp_path / "resident"), keep_params=True, **kw)
+    for ra, rb in zip(a, b):
+        assert ra["loss"] == rb["loss"] and ra["grad_norm"] == rb["grad_norm"]
+        for k, v in ra["state"].items():
+            assert torch.equal(v, rb["state"][k]), k
+        # tiny model: 2 blocks; 2 rows per rank -> 2 micro batches per step, 2 steps
+        assert rb["gathers"] == 2 * 2
+        assert ra["gathers"] >= 2 * 2 * 2 * 2            # forward + backward of every micro batch
+
+
 def test_micro_batches_match_full_batch(single, tmp_path):
     res = W.run(W.sft_step_and_generate, 1, str(tmp_path), tp=1, micro=2, gen=False)[0]
     # the last micro batch's loss differs from the full-batch loss; the update must not
