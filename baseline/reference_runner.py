@@ -135,12 +135,10 @@ def run(a, wl, ClockSampler):
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
             "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (random token ids, random-init weights)", "impl": "reference",
-            "config": {"model": "Llemma-7B architecture (reference Transformer)",
-                       "global_batch": B, "seq_len": T + NEW, "prompt_len": T, "new_tokens": NEW,
-                       "temperature": wl["temperature"], "top_k": wl["top_k"],
-                       "parallelism": f"tp{world}", "block_size": model.config.block_size,
-                       "note": note,
-                       "step": "one batched generation: prefill + 511 decode steps"},
+            "config": wl["config"](world),
+            "impl_notes": {"kv_cache": f"sized to block_size {model.config.block_size} and read "
+                           "in full every step (the reference's stock generate)",
+                           "decode_mode": note},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": B * T * 4, "d2h_bytes_per_step": B * (T + NEW) * 4},

@@ -37,6 +37,18 @@ TEMPERATURE, TOP_K = 0.7, 50
 MODEL = "llemma-7b-32016"
 
 
+def decode_config(world: int, quant: str = "none") -> dict:
+    """The workload description both arms print (identical keys and values for one N)."""
+    return {"model": "Llemma-7B architecture (32 layers, dim 4096, 32 heads, ffn 11008, "
+                     "vocab 32016, rope 1e6)",
+            "global_batch": BATCH, "seq_len": PROMPT + NEW, "prompt_len": PROMPT,
+            "new_tokens": NEW, "temperature": TEMPERATURE, "top_k": TOP_K,
+            "weights": "bf16" if quant == "none" else quant,
+            "parallelism": f"tp{world}",
+            "step": "one batched generation: prefill + 511 decode steps",
+            "l2": "inputs larger than L2 (weights 13.5 GB + KV cache stream per step)"}
+
+
 def parse():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -225,12 +237,9 @@ def run_ours(a):
             "dtype": "bf16" if a.quant == "none" else f"bf16 activations, {a.quant} weights",
             "data": "synthetic (random token ids, random-init weights)",
             "impl": "ours",
-            "config": {"model": "Llemma-7B architecture (llemma-7b-32016)",
-                       "global_batch": BATCH, "seq_len": PROMPT + NEW, "prompt_len": PROMPT,
-                       "new_tokens": NEW, "temperature": TEMPERATURE, "top_k": TOP_K,
-                       "parallelism": f"tp{world}", "tp_reduce": eng.reduce,
-                       "step": "one batched generation: prefill + 511 decode steps",
-                       "l2": "inputs larger than L2 (weights 13.5 GB + KV cache stream per step)"},
+            "config": decode_config(world, a.quant),
+            "impl_notes": {"tp_reduce": eng.reduce, "kv_cache": "sized to prompt + new tokens, "
+                           "only the live range is read"},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": BATCH * PROMPT * 4,
@@ -238,6 +247,42 @@ def run_ours(a):
             "gpu_launches": launches, "kernel_status": status,
         }
         print(json.dumps(out), flush=True)
+    eng._graphs.clear()
+
+
+def finish():
+    """Ends the process. The result line is out and every rank has synchronised. CUDA graphs are
+    dropped first (they may hold collective kernels), then the interpreter's exit callbacks run
+    (so that anything registered with ``atexit``, e.g. a hook that records which shared libraries
+    this process mapped, still sees a live process), then the process leaves without running the
+    static destructors of the communication libraries: tearing a communicator down at
+    interpreter exit has blocked on this stack before. A watchdog bounds the whole sequence."""
+    import atexit
+
+    def _bail():
+        time.sleep(90)
+        os._exit(0)
+
+    threading.Thread(target=_bail, daemon=True).start()
+    try:
+        import torch
+        import torch.distributed as dist
+        if torch.cuda.is_available():
+            torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()
+            torch.cuda.synchronize()
+    except Exception:  # noqa: BLE001
+        pass
+    sys.stdout.flush()
+    sys.stderr.flush()
+    try:
+        atexit._run_exitfuncs()
+    except Exception:  # noqa: BLE001
+        pass
+    sys.stdout.flush()
+    sys.stderr.flush()
+    os._exit(0)
 
 
 SFT_SEQ, SFT_GLOBAL_BATCH = 768, 64
@@ -372,7 +417,7 @@ def run_reference(a):
         return unavailable(f"reference runner import failed: {type(e).__name__}: {e}")
     try:
         reference_runner.run(a, dict(batch=BATCH, prompt=PROMPT, new=NEW, temperature=TEMPERATURE,
-                                     top_k=TOP_K), ClockSampler)
+                                     top_k=TOP_K, config=decode_config), ClockSampler)
     except Exception as e:  # noqa: BLE001
         unavailable(f"reference failed: {type(e).__name__}: {str(e)[:300]}")
 
@@ -385,18 +430,4 @@ if __name__ == "__main__":
         run_ours_sft(args)
     else:
         run_ours(args)
-    # Leave without tearing NCCL down: destroying a communicator whose kernels sit in captured
-    # CUDA graphs can block at interpreter exit. Every rank has synchronised and the result
-    # line is flushed, so a hard exit is safe.
-    try:
-        import torch
-        import torch.distributed as dist
-        if torch.cuda.is_available():
-            torch.cuda.synchronize()
-        if dist.is_initialized():
-            dist.barrier()
-    except Exception:
-        pass
-    sys.stdout.flush()
-    sys.stderr.flush()
-    os._exit(0)
+    finish()

@@ -20,11 +20,23 @@ Position, current tokens, EOS flags and the output sequence all live on the devi
 needs no per-token host synchronisation (the reference syncs every token through
 ``eos_flag.all()``, rl_model.py:441).
 
-With tensor parallelism the row-parallel GEMMs (wo, w2) write fp32 partial sums and the following
-norm kernel adds the partials of all ranks; how the partials travel is the ``reduce`` strategy:
-``"nccl"`` (all-reduce between the two kernels, the baseline) or ``"p2p"`` (the GEMM epilogue
-pushes its partial tile straight into every peer's buffer over NVLink and raises a flag that the
-norm kernel waits on, see ``parallel.symm``).
+With tensor parallelism the ``reduce`` strategy says how the partial sums of the row-parallel
+GEMMs (wo, w2) meet:
+
+``"fused"`` (default for TP > 1)
+    the GEMM writes its bf16 partial into symmetric memory and its last CTA raises a flag on
+    every peer; one kernel (``ops/csrc/tp_reduce.cu``) then sums the rows this rank owns over
+    NVLink (plain peer loads, or ``multimem.ld_reduce`` through the NVSwitch where the group
+    has a multicast mapping), adds the residual, normalises and writes the rows into every
+    rank's activation buffer. No NCCL call sits in the decode graph.
+``"nccl"``
+    fp32 partial, ``dist.all_reduce``, then the local residual + norm kernel (the baseline).
+
+A vocabulary-parallel model (``Transformer(vocab_parallel=True)`` under TP, the reference's
+``--vocab_parallel`` flag: sharded embedding table and LM head, models/tp.py:85-119 and
+models/rl_model.py:366-379 of the reference) runs on the fused strategy only: the embedding is a
+masked lookup whose partial rows go through the same reduce kernel, and the ranks' logit shards
+are gathered over peer memory before the (replicated, same-seed) sampler.
 """
 from __future__ import annotations
 
@@ -57,10 +69,29 @@ class DecodeEngine:
         w2 = model.layers[0].feed_forward.w2          # packed int4 weights are not [out, in]
         self.ffn = getattr(w2, "origin_in_features", None) or getattr(w2, "in_features", None) \
             or w2.weight.shape[1]
-        self.vocab = model.output.weight.shape[0]
+        self.vocab_parallel = bool(getattr(model, "vocab_parallel", False)) and self.tp > 1
+        self.vocab_local = model.output.weight.shape[0]
+        self.vocab = self.vocab_local * (self.tp if self.vocab_parallel else 1)
+        self.tp_rank = groups.get_model_parallel_rank() if self.tp > 1 else 0
         self.eps = cfg.norm_eps
-        if reduce == "auto":
-            reduce = "local" if self.tp == 1 else "nccl"
+        if reduce in ("auto", "p2p"):
+            reduce = "local"
+            if self.tp > 1:     # peer memory reaches every rank of a one-host group only
+                from ..parallel.symm import peer_memory_usable
+                reduce = ("fused" if peer_memory_usable(groups.get_model_parallel_group())
+                          else "nccl")
+        if self.tp == 1:
+            reduce = "local"
+        if reduce not in ("local", "nccl", "fused"):
+            raise ValueError(f"unknown reduce strategy {reduce!r}")
+        if self.vocab_parallel and reduce != "fused":
+            raise ValueError("a vocabulary-parallel model needs reduce='fused': its token ids "
+                             "index a sharded embedding table and its logits are sharded")
+        emb_rows = model.tok_embeddings.weight.shape[0]
+        if not self.vocab_parallel and self.tp > 1 and emb_rows != cfg.vocab_size \
+                and emb_rows * self.tp == cfg.vocab_size:
+            raise ValueError("the embedding table is vocabulary-sharded but model.vocab_parallel "
+                             "is off: global token ids would index past its end")
         self.reduce = reduce
         dev, bf = self.dev, torch.bfloat16
         B, S = self.B, self.S
@@ -71,17 +102,25 @@ class DecodeEngine:
                        for _ in model.layers]
         # decode-step buffers
         self.h = torch.empty(B, self.dim, dtype=bf, device=dev)
-        self.xn = torch.empty(B, self.dim, dtype=bf, device=dev)
+        self.n_points = 2 * len(model.layers) + 2      # embedding, wo / w2 per layer, logits
+        self.sync = self.sync_prefill = None
+        if self.reduce == "fused":
+            from ..parallel.symm import TPReduceSync
+            self.sync = TPReduceSync(
+                B, self.dim, self.n_points, groups.get_model_parallel_group(),
+                extra_bytes=B * self.vocab_local * 4 if self.vocab_parallel else 0)
+            self.xn = self.sync.xn
+        else:
+            self.xn = torch.empty(B, self.dim, dtype=bf, device=dev)
         self.q = torch.empty(B, self.n_head * self.D, dtype=bf, device=dev)
         self.att = torch.empty(B, self.n_head * self.D, dtype=bf, device=dev)
         self.act = torch.empty(B, self.ffn, dtype=bf, device=dev)
         self.logits = torch.empty(B, self.vocab, dtype=torch.float32, device=dev)
         self.partial = (torch.empty(1, B, self.dim, dtype=torch.float32, device=dev)
                         if self.reduce == "nccl" else None)
-        self.rp = None
-        if self.reduce == "p2p":
-            from ..parallel.symm import RowParallelReduce
-            self.rp = RowParallelReduce(B, self.dim, groups.get_model_parallel_group())
+        self.logits_shard = (self.sync.extra((B, self.vocab_local), torch.float32)
+                             if self.vocab_parallel else None)
+        self.seed_dev = torch.zeros(1, dtype=torch.int64, device=dev)
         self.pos = torch.zeros(1, dtype=torch.int32, device=dev)
         self.next_tok = torch.zeros(B, dtype=torch.int32, device=dev)
         self.left_pad = torch.zeros(B, dtype=torch.int32, device=dev)
@@ -132,47 +171,65 @@ class DecodeEngine:
         return out
 
     # ------------------------------------------------------------------ layer pieces
-    def _row_parallel(self, x, ws, h, next_norm_w, h_out, x_out):
+    def _row_parallel(self, x, ws, h, next_norm_w, h_out, x_out, point: int = 0, sync=None):
         """h_out = h + x @ w^T (summed over TP ranks); x_out = rmsnorm(h_out) * next_norm_w.
-        ``ws`` = (weight, per-feature scale or None)."""
+        ``ws`` = (weight, per-feature scale or None). On the fused strategy ``x_out`` is the
+        activation buffer of ``sync`` and only the token rows this rank owns are kept in
+        ``h_out`` (the residual stream of a row lives on its owner)."""
         w, sc = ws
+        T = x.shape[0]
         if self.reduce == "local":
             gemm.linear_residual(x, w, h, out=h_out, scale=sc)
             Fn.fused_residual_rmsnorm(h_out, next_norm_w, self.eps, x_out=x_out)
-            self._count(2)
         elif self.reduce == "nccl":
-            part = self.partial[:, : x.shape[0]] if x.shape[0] <= self.B else \
-                torch.empty(1, x.shape[0], self.dim, dtype=torch.float32, device=self.dev)
+            part = self.partial[:, :T] if T <= self.B else \
+                torch.empty(1, T, self.dim, dtype=torch.float32, device=self.dev)
             gemm.linear(x, w, out=part[0], scale=sc)
             dist.all_reduce(part, group=groups.get_model_parallel_group())
             Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                       x_out=x_out)
-            self._count(2)
-        elif self.reduce == "p2p":
-            T = x.shape[0]
-            if T > self.rp.T:  # prefill-sized inputs take the NCCL route
-                part = torch.empty(1, T, self.dim, dtype=torch.float32, device=self.dev)
-                gemm.linear(x, w, out=part[0], scale=sc)
-                dist.all_reduce(part, group=groups.get_model_parallel_group())
-                Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
-                                          x_out=x_out)
-            else:
-                rp = self.rp
-                s = rp.slot()
-                gemm.linear(x, w, out=rp.partial_out(s, T), signal=rp.signal_ptrs(s),
-                            ticket=rp.gemm_ticket[s:s + 1], scale=sc)
-                Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=rp.partial_ptrs(s),
-                                          h_out=h_out, x_out=x_out, flags=rp.flags(s),
-                                          use_count=rp.use_count[s:s + 1],
-                                          ticket=rp.norm_ticket[s:s + 1], T=T, dim=self.dim)
+        else:
+            gemm.linear(x, w, out=sync.partial[:T], signal=sync.flag_a_remote(point),
+                        ticket=sync.gemm_ticket[point:point + 1], scale=sc)
+            sync.reduce_norm(point, h, h_out, next_norm_w, self.eps, T)
+        self._count(2)
+
+    def _embed_norm(self, tok, h, xn, sync):
+        """h = embedding(tok); xn = rmsnorm(h) * first attention norm."""
+        m = self.model
+        w0 = m.layers[0].attention_norm.weight
+        if self.vocab_parallel:
+            sync.embed_partial(0, tok, m.tok_embeddings.weight, self.tp_rank * self.vocab_local)
+            sync.reduce_norm(0, None, h, w0, self.eps, tok.numel())
             self._count(2)
         else:
-            raise ValueError(self.reduce)
+            Fn.fused_residual_rmsnorm(None, w0, self.eps, tokens=tok, emb=m.tok_embeddings.weight,
+                                      h_out=h, x_out=xn)
+            self._count(1)
+
+    def _head_sample(self, x, B, temperature, top_k, eos_id):
+        """LM head on ``x`` [B, dim] and the fused sampler (advances the position)."""
+        m = self.model
+        logits = self.logits[:B]
+        if self.vocab_parallel:
+            pt = self.n_points - 1
+            gemm.linear(x, m.output.weight, out=self.logits_shard[:B],
+                        signal=self.sync.flag_a_remote(pt),
+                        ticket=self.sync.gemm_ticket[pt:pt + 1])
+            self.sync.gather_logits(pt, B, self.vocab_local, logits)
+            self._count(1)
+        else:
+            gemm.linear(x, m.output.weight, out=logits)
+        Fn.sample(logits, temperature=temperature, top_k=top_k, seed=0, seed_dev=self.seed_dev,
+                  pos=self.pos, next_tok=self.next_tok[:B], seq=self.seq[:B], eos_id=eos_id,
+                  eos_flag=self.eos_flag[:B], n_unfinished=self.n_unfinished, ticket=self.ticket,
+                  advance_pos=True)
+        self._count(2)
 
     def _count(self, n):
         self.launches_per_step += n
 
-    def _layers(self, T: int, sq: int, h, xn, q, att, act, prefill_B: int = 0):
+    def _layers(self, T: int, sq: int, h, xn, q, att, act, prefill_B: int = 0, sync=None):
         m = self.model
         for li, blk in enumerate(m.layers):
             W = self.W[li]
@@ -186,12 +243,12 @@ class DecodeEngine:
             else:
                 self._prefill_attention(li, q, att, prefill_B, sq)
             self._count(2)
-            self._row_parallel(att, W["wo"], h, blk.ffn_norm.weight, h, xn)
+            self._row_parallel(att, W["wo"], h, blk.ffn_norm.weight, h, xn, 1 + 2 * li, sync)
             gemm.linear_swiglu(xn, W["w1"][0], W["w3"][0], out=act, scale=W["s13"])
             self._count(1)
             nxt = (m.layers[li + 1].attention_norm.weight if li + 1 < len(m.layers)
                    else m.norm.weight)
-            self._row_parallel(act, W["w2"], h, nxt, h, xn)
+            self._row_parallel(act, W["w2"], h, nxt, h, xn, 2 + 2 * li, sync)
 
     def _prefill_attention(self, li, q, att, B, S):
         from ..ops import attention as attn_ops
@@ -199,26 +256,16 @@ class DecodeEngine:
                                    self.vcache[li], self.left_pad[:B], att.view(B, S, -1))
 
     # ------------------------------------------------------------------ decode
-    def _decode_step(self, B, temperature, top_k, seed, eos_id):
-        m = self.model
+    def _decode_step(self, B, temperature, top_k, eos_id):
         h, xn, q, att, act = (t[:B] for t in (self.h, self.xn, self.q, self.att, self.act))
-        Fn.fused_residual_rmsnorm(None, m.layers[0].attention_norm.weight, self.eps,
-                                  tokens=self.next_tok[:B], emb=m.tok_embeddings.weight,
-                                  h_out=h, x_out=xn)
-        self._count(1)
-        self._layers(B, 1, h, xn, q, att, act)
-        logits = self.logits[:B]
-        gemm.linear(xn, m.output.weight, out=logits)
-        Fn.sample(logits, temperature=temperature, top_k=top_k, seed=seed, pos=self.pos,
-                  next_tok=self.next_tok[:B], seq=self.seq[:B], eos_id=eos_id,
-                  eos_flag=self.eos_flag[:B], n_unfinished=self.n_unfinished, ticket=self.ticket,
-                  advance_pos=True)
-        self._count(2)
+        self._embed_norm(self.next_tok[:B], h, xn, self.sync)
+        self._layers(B, 1, h, xn, q, att, act, sync=self.sync)
+        self._head_sample(xn, B, temperature, top_k, eos_id)
 
     def _graph_for(self, key):
         if key in self._graphs:
             return self._graphs[key]
-        B, temperature, top_k, seed, eos_id = key
+        B, temperature, top_k, eos_id = key
         # warm up on a side stream (module loading, attribute setting), then capture
         saved = [t.clone() for t in (self.pos, self.next_tok, self.seq, self.eos_flag,
                                      self.n_unfinished)]
@@ -263,26 +310,39 @@ class DecodeEngine:
         else:
             self.left_pad[:B] = left_pad_mask_pos.to(device=dev, dtype=torch.int32)
         self.pos.zero_()
+        self.seed_dev.fill_(int(seed) & (2 ** 63 - 1))
         n = B * T
+        sync = None
+        if self.reduce == "fused":
+            sync = self._prefill_sync(n)
+            xn = sync.xn[:n]
+        else:
+            xn = torch.empty(n, self.dim, dtype=bf, device=dev)
         h = torch.empty(n, self.dim, dtype=bf, device=dev)
-        xn = torch.empty(n, self.dim, dtype=bf, device=dev)
         q = torch.empty(n, self.n_head * self.D, dtype=bf, device=dev)
         att = torch.empty(n, self.n_head * self.D, dtype=bf, device=dev)
         act = torch.empty(n, self.ffn, dtype=bf, device=dev)
         self.launches_per_step = 0
-        Fn.fused_residual_rmsnorm(None, m.layers[0].attention_norm.weight, self.eps,
-                                  tokens=tok.view(-1), emb=m.tok_embeddings.weight, h_out=h,
-                                  x_out=xn)
-        self._layers(n, T, h, xn, q, att, act, prefill_B=B)
+        self._embed_norm(tok.view(-1), h, xn, sync)
+        self._layers(n, T, h, xn, q, att, act, prefill_B=B, sync=sync)
         last = xn.view(B, T, self.dim)[:, -1].contiguous()
-        logits = self.logits[:B]
-        gemm.linear(last, m.output.weight, out=logits)
         self.pos.fill_(T - 1)
-        Fn.sample(logits, temperature=temperature, top_k=top_k, seed=seed, pos=self.pos,
-                  next_tok=self.next_tok[:B], seq=self.seq[:B], eos_id=eos_id,
-                  eos_flag=self.eos_flag[:B], n_unfinished=self.n_unfinished, ticket=self.ticket,
-                  advance_pos=True)
+        self._head_sample(last, B, temperature, top_k, eos_id)
         self.prefill_launches = self.launches_per_step + 3
+
+    def _prefill_sync(self, n_tokens: int):
+        """Symmetric buffers of the prompt pass, grown on demand (a collective: every rank
+        prefills the same shape). They are separate from the decode buffers, whose addresses
+        sit inside captured graphs."""
+        sp = self.sync_prefill
+        if sp is None or sp.T < n_tokens:
+            from ..parallel.symm import TPReduceSync
+            self.sync_prefill = sp = None
+            torch.cuda.empty_cache()
+            cap = 1 << max(10, (n_tokens - 1).bit_length())
+            sp = TPReduceSync(cap, self.dim, self.n_points, groups.get_model_parallel_group())
+            self.sync_prefill = sp
+        return sp
 
     # ------------------------------------------------------------------ generate
     @torch.no_grad()
@@ -297,7 +357,7 @@ class DecodeEngine:
         eos = -1 if eos_id is None else int(eos_id)
         self.prefill(prompt, left_pad_mask_pos, temperature, top_k, seed, eos)
         steps = 0
-        key = (B, float(temperature), int(top_k) if top_k else 0, int(seed), eos)
+        key = (B, float(temperature), int(top_k) if top_k else 0, eos)
         n_dec = min(max_new_tokens - 1, self.S - T - 1)
         if self.use_graph:
             g, _ = self._graph_for(key)
@@ -309,7 +369,17 @@ class DecodeEngine:
             steps += 1
             if eos >= 0 and (i + 1) % check_eos_every == 0 and self.n_unfinished.item() <= 0:
                 break
+        if self.reduce == "fused":
+            self.check_status()
         return self.seq[:B, : T + max_new_tokens], steps
+
+    def check_status(self) -> None:
+        """Raises when a kernel of this device recorded a time-out (a tensor-parallel peer that
+        never signalled): the tokens of that generation are not to be trusted."""
+        code = _lib.read_status(self.dev)
+        if code != 0:
+            raise RuntimeError(f"decode engine: a device-side wait timed out (status {code}); "
+                               "a tensor-parallel peer did not reach the same step")
 
     def decode_launches(self, key=None) -> int:
         if key is None and self._graphs:

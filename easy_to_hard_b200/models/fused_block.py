@@ -61,19 +61,18 @@ _ROW_REDUCE: Dict[tuple, object] = {}
 _P2P_REDUCE = {"enabled": None}
 
 
-def p2p_reduce_enabled() -> bool:
-    """The fused row-parallel GEMM -> all-reduce -> residual (+ RMSNorm) over peer memory is used
-    when symmetric memory is available; ``E2H_TP_REDUCE=nccl`` forces the NCCL all-reduce."""
+def p2p_reduce_enabled(group=None) -> bool:
+    """The fused collectives over peer memory are used when symmetric memory is available and
+    every rank of ``group`` (default: the tensor-parallel group) is on this host; groups that
+    span hosts, and ``E2H_TP_REDUCE=nccl``, take the NCCL collectives. Collective on first use
+    per group."""
     if _P2P_REDUCE["enabled"] is None:
         import os
-        ok = os.environ.get("E2H_TP_REDUCE", "p2p") != "nccl"
-        if ok:
-            try:
-                import torch.distributed._symmetric_memory  # noqa: F401
-            except Exception:  # noqa: BLE001
-                ok = False
-        _P2P_REDUCE["enabled"] = ok
-    return _P2P_REDUCE["enabled"]
+        _P2P_REDUCE["enabled"] = os.environ.get("E2H_TP_REDUCE", "p2p") != "nccl"
+    if not _P2P_REDUCE["enabled"]:
+        return False
+    from ..parallel.symm import peer_memory_usable
+    return peer_memory_usable(group if group is not None else groups.get_model_parallel_group())
 
 
 def _row_reduce(T: int, dim: int):
@@ -85,8 +84,9 @@ def _row_reduce(T: int, dim: int):
         from ..ops import _lib
         from ..parallel.symm import RowParallelReduce
         rp = RowParallelReduce(T, dim, groups.get_model_parallel_group(), dtype=torch.bfloat16)
-        # training ranks drift apart (data loading, first-use initialisation): wait up to 2 min
-        _lib.check(_lib.lib().e2h_set_flag_wait_ms(120000), "set_flag_wait_ms")
+        # training ranks drift apart (data loading, first-use initialisation) by seconds
+        from ..parallel.symm import peer_wait_ms
+        _lib.check(_lib.lib().e2h_set_flag_wait_ms(peer_wait_ms()), "set_flag_wait_ms")
         _ROW_REDUCE[key] = rp
     return rp
 

@@ -219,7 +219,11 @@ def _copy_tp_attrs(old: nn.Module, new: nn.Module) -> None:
 
 
 class WeightOnlyInt8QuantHandler:
-    """Quantise every block linear of a model to int8 (the LM / reward head stays as is)."""
+    """Weight-only int8. The state dict covers every ``nn.Linear`` of the model, the LM head
+    included when it is one, as the reference's files do (models/quantize.py:383-394 there);
+    the runtime conversion swaps the block linears only, and a quantised head found in a file
+    is expanded to bf16 at load time (``dequantize_head_in_state_dict``), because the head of an
+    inference model is a frozen bf16 buffer."""
 
     def __init__(self, mod: nn.Module):
         self.mod = mod
@@ -228,7 +232,7 @@ class WeightOnlyInt8QuantHandler:
     def create_quantized_state_dict(self) -> Dict[str, torch.Tensor]:
         sd = self.mod.state_dict()
         for fqn, m in self.mod.named_modules():
-            if isinstance(m, nn.Linear) and not fqn.endswith("output"):
+            if isinstance(m, nn.Linear):
                 q, scales, _ = dynamically_quantize_per_channel(m.weight.float(), -128, 127,
                                                                 torch.int8)
                 sd[f"{fqn}.weight"] = q
@@ -268,15 +272,16 @@ class WeightOnlyInt4QuantHandler:
     def create_quantized_state_dict(self) -> Dict[str, torch.Tensor]:
         sd = self.mod.state_dict()
         for fqn, m in self.mod.named_modules():
-            if not isinstance(m, nn.Linear) or fqn.endswith("output"):
+            if not isinstance(m, nn.Linear):
                 continue
             assert m.out_features % 8 == 0, "int4 needs out_features divisible by 8"
             w = m.weight.data
+            # input features are padded to a multiple of 1024 only when the plain layout does
+            # not fit (models/quantize.py:513-535 of the reference): the 7B / 13B / 34B FFN
+            # widths (11008, 13824, 22016) pass the check and are stored unpadded
             if not _check_linear_int4_k(m.in_features, self.groupsize, self.inner_k_tiles):
                 if not self.padding:
                     continue
-                w = F.pad(w, pad=(0, find_multiple(m.in_features, 1024) - m.in_features))
-            elif self.padding and m.in_features % 1024:
                 w = F.pad(w, pad=(0, find_multiple(m.in_features, 1024) - m.in_features))
             packed, sz = prepare_int4_weight_and_scales_and_zeros(
                 w.to(torch.bfloat16), self.groupsize, self.inner_k_tiles)
@@ -285,10 +290,38 @@ class WeightOnlyInt4QuantHandler:
         return sd
 
     def convert_for_runtime(self) -> nn.Module:
-        _swap_linears(self.mod, lambda lin, fqn: WeightOnlyInt4Linear(
-            lin.in_features, lin.out_features, device=lin.weight.device,
-            groupsize=self.groupsize, inner_k_tiles=self.inner_k_tiles, padding=self.padding))
+        """Block linears become ``WeightOnlyInt4Linear``: unpadded where the input width fits
+        the packed layout, padded otherwise (or left alone when padding is off), exactly the
+        choice of the reference's ``replace_linear_int4`` (models/quantize.py:460-490)."""
+        def make(lin, fqn):
+            fits = _check_linear_int4_k(lin.in_features, self.groupsize, self.inner_k_tiles)
+            if not fits and not self.padding:
+                return lin
+            return WeightOnlyInt4Linear(lin.in_features, lin.out_features,
+                                        device=lin.weight.device, groupsize=self.groupsize,
+                                        inner_k_tiles=self.inner_k_tiles, padding=not fits)
+        _swap_linears(self.mod, make)
         return self.mod
+
+
+def dequantize_head_in_state_dict(state: Dict[str, torch.Tensor], groupsize: int = 128,
+                                  name: str = "output") -> Dict[str, torch.Tensor]:
+    """Quantised checkpoints written from a model whose LM head is an ``nn.Linear`` carry the
+    head as int8 (+ ``scales``) or packed int4 (+ ``scales_and_zeros``). Inference models keep
+    the head as a frozen bf16 buffer, so it is expanded here, in place, before
+    ``load_state_dict``; files without a quantised head pass through unchanged."""
+    w = state.get(f"{name}.weight")
+    if w is None:
+        return state
+    if f"{name}.scales" in state and w.dtype == torch.int8:
+        sc = state.pop(f"{name}.scales").float()
+        state[f"{name}.weight"] = (w.float() * sc.unsqueeze(-1)).to(torch.bfloat16)
+    elif f"{name}.scales_and_zeros" in state and w.dtype == torch.int32:
+        sz = state.pop(f"{name}.scales_and_zeros")
+        q = unpack_int4_tinygemm(w, w.shape[-1] * 2)
+        state[f"{name}.weight"] = group_dequantize_tensor(
+            q, sz, 4, groupsize).to(torch.bfloat16)
+    return state
 
 
 def quantize(checkpoint_path: Path, mode: str = "int8", groupsize: int = 128,

@@ -67,12 +67,12 @@ _SIGNATURES = {
     "e2h_gemm_w8": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_streamk": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_w4": [C.POINTER(GemmParams), _vp],
-    "e2h_rmsnorm_fwd": [_vp, _vp, _vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
+    "e2h_rmsnorm_fwd": [_vp, _vp, _vp, _i, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
                         _vp, _vp, _vp, _vp, _vp],
     "e2h_reduce_residual_norm_bf16": [_vp, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _i, _i, _f,
                                       _vp, _vp, _vp, _vp, _vp],
     "e2h_rmsnorm_bwd": [_vp, _vp, _vp, _vp, _vp, _i, _i, _f, _vp],
-    "e2h_embedding": [_vp, _vp, _vp, _i, _i, _vp],
+    "e2h_embedding": [_vp, _vp, _i, _vp, _i, _i, _vp, _vp],
     "e2h_swiglu_fwd": [_vp, _vp, _vp, _ll, _vp],
     "e2h_swiglu_bwd": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "e2h_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp],
@@ -91,6 +91,12 @@ _SIGNATURES = {
     "e2h_wait_flags": [_vp, _i, _vp, _i, _i, _vp, _vp],
     "e2h_p2p_all_gather": [C.POINTER(C.c_void_p), _i, _vp, _ll, _vp, _vp, _vp, _i, _vp, _vp],
     "e2h_p2p_reduce_bf16": [C.POINTER(C.c_void_p), _i, _vp, _ll, _f, _vp, _vp, _vp, _i, _vp, _vp],
+    "e2h_tp_reduce_norm": [_vp, _vp, _vp, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                           C.POINTER(C.c_void_p), _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
+                           _i, _vp, _vp],
+    "e2h_tp_embed_partial": [_vp, _vp, _i, _i, _vp, _i, _i, C.POINTER(C.c_void_p), _i, _vp, _vp],
+    "e2h_tp_gather_logits": [C.POINTER(C.c_void_p), _i, _i, _i, _vp, _ll, _vp, _vp, _vp, _i, _vp,
+                             _vp],
     "e2h_set_pdl": [_i],
     "e2h_set_flag_wait_ms": [_i],
     "e2h_flash_bwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll,
@@ -99,7 +105,7 @@ _SIGNATURES = {
     "e2h_ce_stats": [_vp, _ll, _i, _i, _vp, _i, _f, _vp, _vp],
     "e2h_ce_grad": [_vp, _ll, _i, _i, _vp, _i, _f, _vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "e2h_sample": [_vp, _ll, _i, _i, _f, _i, _ull, _vp, _i, _vp, _vp, _ll, _i, _i, _vp, _vp,
-                   _vp, _vp],
+                   _vp, _vp, _vp],
 }
 
 

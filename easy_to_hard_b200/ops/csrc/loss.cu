@@ -35,6 +35,7 @@ ce_stats_kernel(const float* __restrict__ logits, long long ld, int vocab,
                 const long long* __restrict__ targets, int vocab_start, float inv_temp,
                 float4* __restrict__ stats) {
   __shared__ float red[32];
+  pdl_wait_prior();  // launched through the PDL-capable helper: wait before any global access
   const int row = blockIdx.x;
   const float* x = logits + (long long)row * ld;
   float m = -FLT_MAX;
@@ -64,6 +65,7 @@ ce_grad_kernel(const float* __restrict__ logits, long long ld, int vocab,
                const float* __restrict__ lse, const float* __restrict__ ent,
                const float* __restrict__ g_lp, const float* __restrict__ g_ent,
                __nv_bfloat16* __restrict__ dlogits, long long ldd) {
+  pdl_wait_prior();  // launched through the PDL-capable helper: wait before any global access
   const int row = blockIdx.x;
   const float* x = logits + (long long)row * ld;
   __nv_bfloat16* d = dlogits + (long long)row * ldd;

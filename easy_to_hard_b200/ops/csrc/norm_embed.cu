@@ -31,7 +31,8 @@ struct PartPtrs {
 
 // One CTA per token row.
 //   h_in      : bf16 [T, dim]  residual stream (or nullptr when `tokens` is given)
-//   tokens    : int32 [T]      when set, the row is gathered from `emb` instead of h_in
+//   tokens    : int32 [T]      when set, the row is gathered from `emb` ([emb_rows, dim]) instead
+//                              of h_in; ids outside the table give a zero row and status 106
 //   parts     : n_part fp32 [T, dim] partial sums of a row-parallel linear (one per
 //               tensor-parallel rank; the pointers may be peer-GPU addresses, read with
 //               system-scope loads over NVLink); added to the row when n_part > 0
@@ -48,7 +49,7 @@ __device__ long long g_flag_wait_cycles = kWaitLimitCycles;
 
 __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
                                    const int* __restrict__ tokens,
-                                   const __nv_bfloat16* __restrict__ emb,
+                                   const __nv_bfloat16* __restrict__ emb, int emb_rows,
                                    const PartPtrs parts, int n_part,
                                    const __nv_bfloat16* __restrict__ weight,
                                    __nv_bfloat16* __restrict__ h_out,
@@ -60,8 +61,17 @@ __global__ void rmsnorm_fwd_kernel(const __nv_bfloat16* __restrict__ h_in,
   const int t = blockIdx.x;
   pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
   pdl_wait_prior();
-  const __nv_bfloat16* src =
-      tokens ? emb + (long long)tokens[t] * dim : (h_in ? h_in + (long long)t * dim : nullptr);
+  const __nv_bfloat16* src = h_in ? h_in + (long long)t * dim : nullptr;
+  if (tokens) {
+    // an id outside the table reads as a zero row and is reported, never dereferenced
+    const int id = tokens[t];
+    if (id >= 0 && id < emb_rows) {
+      src = emb + (long long)id * dim;
+    } else {
+      src = nullptr;
+      if (threadIdx.x == 0 && status) atomicCAS(status, 0, kStatusBadArgs);
+    }
+  }
   if (flags != nullptr) {
     const int want = *use_count + 1;
     if (threadIdx.x < n_part)
@@ -154,13 +164,18 @@ __global__ void rmsnorm_bwd_kernel(const __nv_bfloat16* __restrict__ x,
 }
 
 // out[t, :] = table[tokens[t], :]
+// (ids outside [0, rows) give a zero row and status 106)
 __global__ void embedding_kernel(const int* __restrict__ tokens,
-                                 const __nv_bfloat16* __restrict__ table,
-                                 __nv_bfloat16* __restrict__ out, int dim) {
+                                 const __nv_bfloat16* __restrict__ table, int rows,
+                                 __nv_bfloat16* __restrict__ out, int dim, int* status) {
   const int t = blockIdx.x;
-  const uint4* src = reinterpret_cast<const uint4*>(table + (long long)tokens[t] * dim);
+  const int id = tokens[t];
+  const bool ok = id >= 0 && id < rows;
+  if (!ok && threadIdx.x == 0 && status) atomicCAS(status, 0, kStatusBadArgs);
+  const uint4* src = reinterpret_cast<const uint4*>(table + (long long)(ok ? id : 0) * dim);
   uint4* dst = reinterpret_cast<uint4*>(out + (long long)t * dim);
-  for (int i = threadIdx.x; i < dim / 8; i += blockDim.x) dst[i] = src[i];
+  for (int i = threadIdx.x; i < dim / 8; i += blockDim.x)
+    dst[i] = ok ? src[i] : make_uint4(0u, 0u, 0u, 0u);
 }
 
 // act = bf16(bf16(silu(g)) * u)
@@ -357,11 +372,12 @@ static int launch_parts_rows(const void* h_in, const PartPtrs& parts, int n_part
 
 extern "C" {
 
-int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
+int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb, int emb_rows,
                     const void* const* part_ptrs, int n_part, const void* weight, void* h_out,
                     void* x_out, float* rstd_out, int T, int dim, float eps, const int* flags,
                     int* use_count, unsigned int* ticket, int* status, void* stream) {
   if (dim % 2 || n_part > 8) return -1;
+  if (tokens != nullptr && (emb == nullptr || emb_rows < 1)) return -1;
   if (flags != nullptr && (use_count == nullptr || ticket == nullptr)) return -2;
   PartPtrs parts;
   for (int i = 0; i < 8; ++i)
@@ -391,7 +407,8 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb,
   const int threads = dim >= 2048 ? 512 : 128;
   const size_t smem = (dim + 32) * sizeof(float);
   return (int)launch(rmsnorm_fwd_kernel, dim3(T), dim3(threads), smem, (cudaStream_t)stream,
-                     (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, parts, n_part,
+                     (const __nv_bfloat16*)h_in, tokens, (const __nv_bfloat16*)emb, emb_rows, parts,
+                     n_part,
                      (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out, (__nv_bfloat16*)x_out,
                      rstd_out, dim, eps, flags, use_count, ticket, status);
 }
@@ -435,10 +452,11 @@ int e2h_rmsnorm_bwd(const void* x, const void* dy, const void* weight, const voi
   return (int)cudaGetLastError();
 }
 
-int e2h_embedding(const int* tokens, const void* table, void* out, int T, int dim, void* stream) {
-  if (dim % 8) return -1;
-  embedding_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(tokens, (const __nv_bfloat16*)table,
-                                                        (__nv_bfloat16*)out, dim);
+int e2h_embedding(const int* tokens, const void* table, int rows, void* out, int T, int dim,
+                  int* status, void* stream) {
+  if (dim % 8 || rows < 1) return -1;
+  embedding_kernel<<<T, 128, 0, (cudaStream_t)stream>>>(tokens, (const __nv_bfloat16*)table, rows,
+                                                        (__nv_bfloat16*)out, dim, status);
   return (int)cudaGetLastError();
 }
 

@@ -50,7 +50,7 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
               int top_k, unsigned long long seed, int* pos_ptr, int advance_pos,
               int* __restrict__ next_tok, int* __restrict__ seq, long long seq_ld, int seq_len,
               int eos_id, int* __restrict__ eos_flag, int* __restrict__ n_unfinished,
-              unsigned int* ticket) {
+              unsigned int* ticket, const unsigned long long* __restrict__ seed_ptr) {
   __shared__ unsigned int hist[256];
   __shared__ uint32_t sh_prefix, sh_remaining;
   __shared__ float red_v[kSampThreads / 32];
@@ -60,6 +60,8 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
   pdl_wait_prior();
   pdl_launch_dependents();
   const int pos = *pos_ptr;
+  // a seed kept in device memory lets one captured graph serve every generation call
+  if (seed_ptr != nullptr) seed = *seed_ptr;
   const bool greedy = temperature <= 0.f;
 
   uint32_t pivot_key = 0;  // keep everything
@@ -157,10 +159,11 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
 extern "C" int e2h_sample(const float* logits, long long ld, int B, int vocab, float temperature,
                           int top_k, unsigned long long seed, int* pos_ptr, int advance_pos,
                           int* next_tok, int* seq, long long seq_ld, int seq_len, int eos_id,
-                          int* eos_flag, int* n_unfinished, unsigned int* ticket, void* stream) {
+                          int* eos_flag, int* n_unfinished, unsigned int* ticket,
+                          const unsigned long long* seed_ptr, void* stream) {
   using namespace e2h;
   if (advance_pos && ticket == nullptr) return -1;
   return (int)launch(sample_kernel, dim3(B), dim3(kSampThreads), 0, (cudaStream_t)stream, logits,
                      ld, vocab, temperature, top_k, seed, pos_ptr, advance_pos, next_tok, seq,
-                     seq_ld, seq_len, eos_id, eos_flag, n_unfinished, ticket);
+                     seq_ld, seq_len, eos_id, eos_flag, n_unfinished, ticket, seed_ptr);
 }

@@ -32,7 +32,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float,
     assert x2.is_contiguous() and x.dtype == torch.bfloat16
     if out is None:
         out = torch.empty_like(x2)
-    rc = _lib.lib().e2h_rmsnorm_fwd(x2.data_ptr(), None, None, _part_array([]), 0,
+    rc = _lib.lib().e2h_rmsnorm_fwd(x2.data_ptr(), None, None, 0, _part_array([]), 0,
                                     weight.data_ptr(), None, out.data_ptr(), None, x2.shape[0],
                                     dim, eps, None, None, None,
                                     _lib.status_word(x.device).data_ptr(), _s())
@@ -68,7 +68,7 @@ def fused_residual_rmsnorm(h: Optional[torch.Tensor], weight: Optional[torch.Ten
     dev = ref.device
     rc = _lib.lib().e2h_rmsnorm_fwd(
         _lib.ptr(h) if tokens is None else None, _lib.ptr(tokens), _lib.ptr(emb),
-        _part_array(parts), len(parts), _lib.ptr(weight), _lib.ptr(h_out), _lib.ptr(x_out), None,
+        0 if emb is None else emb.shape[0], _part_array(parts), len(parts), _lib.ptr(weight), _lib.ptr(h_out), _lib.ptr(x_out), None,
         T, dim, eps, _lib.ptr(flags), _lib.ptr(use_count), _lib.ptr(ticket),
         _lib.status_word(dev).data_ptr(), _s())
     _lib.check(rc, "rmsnorm_fwd")
@@ -107,8 +107,10 @@ def embedding(tokens: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
         return torch.nn.functional.embedding(tokens.long(), table)
     tk = tokens.reshape(-1).to(torch.int32)
     out = torch.empty(tk.numel(), table.shape[1], dtype=table.dtype, device=table.device)
-    _lib.check(_lib.lib().e2h_embedding(tk.data_ptr(), table.data_ptr(), out.data_ptr(),
-                                        tk.numel(), table.shape[1], _s()), "embedding")
+    _lib.check(_lib.lib().e2h_embedding(tk.data_ptr(), table.data_ptr(), table.shape[0],
+                                        out.data_ptr(), tk.numel(), table.shape[1],
+                                        _lib.status_word(table.device).data_ptr(), _s()),
+               "embedding")
     return out.view(*tokens.shape, table.shape[1])
 
 
@@ -170,8 +172,11 @@ def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int], se
            pos: torch.Tensor, next_tok: torch.Tensor, advance_pos: bool = True,
            seq: Optional[torch.Tensor] = None, eos_id: int = -1,
            eos_flag: Optional[torch.Tensor] = None, n_unfinished: Optional[torch.Tensor] = None,
-           ticket: Optional[torch.Tensor] = None, vocab: Optional[int] = None) -> torch.Tensor:
-    """Fused top-k / temperature / exponential-race sampler (fp32 logits [B, ld])."""
+           ticket: Optional[torch.Tensor] = None, vocab: Optional[int] = None,
+           seed_dev: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Fused top-k / temperature / exponential-race sampler (fp32 logits [B, ld]). With
+    ``seed_dev`` (int64 device scalar) the kernel reads the seed from device memory, so a
+    captured graph does not bake it in."""
     B = logits.shape[0]
     vocab = vocab or logits.shape[1]
     rc = _lib.lib().e2h_sample(
@@ -179,7 +184,7 @@ def sample(logits: torch.Tensor, *, temperature: float, top_k: Optional[int], se
         int(top_k) if top_k else 0, int(seed) & (2 ** 64 - 1), pos.data_ptr(), int(advance_pos),
         next_tok.data_ptr(), _lib.ptr(seq), 0 if seq is None else seq.stride(0),
         0 if seq is None else seq.shape[1], int(eos_id), _lib.ptr(eos_flag),
-        _lib.ptr(n_unfinished), _lib.ptr(ticket), _s())
+        _lib.ptr(n_unfinished), _lib.ptr(ticket), _lib.ptr(seed_dev), _s())
     _lib.check(rc, "sample")
     return next_tok
 

@@ -287,7 +287,7 @@ class ShardedDataParallel(nn.Module):
         if (self.fused and self.world > 1 and param_dtype == torch.float32
                 and self.compute_dtype == torch.bfloat16):
             from ..models.fused_block import p2p_reduce_enabled
-            if p2p_reduce_enabled():
+            if p2p_reduce_enabled(process_group):
                 from .symm import GradReduceScatter, P2PChannel, SymmetricBuffer
                 self._rs = GradReduceScatter(biggest, process_group)
                 # parameter all-gather as a pull over peer memory: every unit's bf16 shard lives

@@ -22,6 +22,39 @@ import torch
 import torch.distributed as dist
 
 
+def peer_wait_ms() -> int:
+    """Limit of one cross-rank device wait of the training kernels. Ranks of a training job can
+    drift apart by seconds (data loading, first-use initialisation), not by minutes: ten
+    seconds by default, ``E2H_PEER_WAIT_MS`` overrides."""
+    import os
+    return int(os.environ.get("E2H_PEER_WAIT_MS", "10000"))
+
+
+def peer_memory_usable(group=None) -> bool:
+    """True when every rank of ``group`` sits on the same host, i.e. when peer-mapped
+    (symmetric) memory can reach all of them; groups that span hosts keep the NCCL collectives.
+    A collective call (one small object all-gather), cached per group."""
+    if not dist.is_initialized():
+        return False
+    key = id(group) if group is not None else 0
+    hit = _PEER_OK.get(key)
+    if hit is not None:
+        return hit
+    import socket
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+        names = [None] * dist.get_world_size(group)
+        dist.all_gather_object(names, socket.gethostname(), group=group)
+        ok = len(set(names)) == 1
+    except Exception:  # noqa: BLE001
+        ok = False
+    _PEER_OK[key] = ok
+    return ok
+
+
+_PEER_OK: dict = {}
+
+
 class SymmetricBuffer:
     GUARD = 256        # bytes of canary after the payload
     CANARY = 0xA5
@@ -137,7 +170,8 @@ class GradReduceScatter:
     elements followed by ``world`` int32 flag words, in symmetric memory."""
 
     def __init__(self, numel: int, group=None, buf: Optional[SymmetricBuffer] = None,
-                 wait_ms: int = 120000):
+                 wait_ms: Optional[int] = None):
+        wait_ms = peer_wait_ms() if wait_ms is None else wait_ms
         self.numel = (numel + 7) // 8 * 8
         self.grad_bytes = self.numel * 2
         self.slot_bytes = (self.grad_bytes + 255) // 256 * 256 + 256
@@ -207,7 +241,8 @@ class P2PChannel:
     (all posts first, then the consumers), which is how the single-GPU tests run it."""
 
     def __init__(self, nbytes: int, group=None, buf: Optional[SymmetricBuffer] = None,
-                 wait_ms: int = 120000):
+                 wait_ms: Optional[int] = None):
+        wait_ms = peer_wait_ms() if wait_ms is None else wait_ms
         self.nbytes = (nbytes + 255) // 256 * 256
         self.slot_bytes = self.nbytes + 256
         if buf is None:
@@ -323,3 +358,129 @@ class P2PChannel:
 
     def barrier(self) -> None:
         self.wait_posted(self.post(None))
+
+
+class TPReduceSync:
+    """Buffers, flag words and use counters of the decode engine's fused tensor-parallel
+    reductions (``ops/csrc/tp_reduce.cu``): the row-parallel GEMMs write bf16 partials into
+    ``partial`` and raise flag A of their call site ("point") on every rank; ``reduce_norm``
+    sums the rows this rank owns, adds the residual, normalises, writes the rows into every
+    rank's ``xn`` and hand-shakes on flag B. One symmetric allocation holds
+
+        partial [T, dim] bf16 | xn [T, dim] bf16 | extra bytes | flags A [points, 8] | flags B
+
+    and the per-point use counters and tickets live in local memory. With an NVSwitch multicast
+    mapping of the allocation (``multicast=True`` and the group has one) the reduction is one
+    ``multimem.ld_reduce`` and the write-out one ``multimem.st`` per 16 bytes.
+
+    All ranks must issue the same sequence of uses. ``emulated`` builds the ``world`` ranks'
+    objects inside one process for single-GPU tests."""
+
+    def __init__(self, max_tokens: int, dim: int, n_points: int, group=None, extra_bytes: int = 0,
+                 multicast: bool = True, wait_ms: int = 2000, buf: Optional[SymmetricBuffer] = None):
+        self.T, self.dim, self.n_points = max_tokens, dim, n_points
+        self.part_bytes = (max_tokens * dim * 2 + 255) // 256 * 256
+        self.extra_off = 2 * self.part_bytes
+        self.extra_bytes = (extra_bytes + 255) // 256 * 256
+        self.flag_a_off = self.extra_off + self.extra_bytes
+        self.flag_b_off = self.flag_a_off + n_points * 32
+        total = self.flag_b_off + n_points * 32
+        if buf is None:
+            buf = SymmetricBuffer(total, group)
+        self.buf = buf
+        self.world, self.rank = buf.world, buf.rank
+        dev = buf.local.device
+        self.count = torch.zeros(n_points, dtype=torch.int32, device=dev)
+        self.ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
+        self.gemm_ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
+        self.multicast = bool(multicast and buf.multicast_ptr)
+        self.wait_ms = wait_ms
+        self.partial = buf.view(0, (max_tokens, dim), torch.bfloat16)
+        self.xn = buf.view(self.part_bytes, (max_tokens, dim), torch.bfloat16)
+
+    @classmethod
+    def emulated(cls, max_tokens: int, dim: int, n_points: int, world: int, extra_bytes: int = 0,
+                 wait_ms: int = 50, device="cuda") -> List["TPReduceSync"]:
+        part = (max_tokens * dim * 2 + 255) // 256 * 256
+        total = 2 * part + (extra_bytes + 255) // 256 * 256 + 2 * n_points * 32
+        bufs = SymmetricBuffer.emulated(total, world, device)
+        return [cls(max_tokens, dim, n_points, extra_bytes=extra_bytes, multicast=False,
+                    wait_ms=wait_ms, buf=b) for b in bufs]
+
+    # ---- addresses
+    def _ptrs(self, offset: int):
+        import ctypes as C
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.buf.peer_ptr(r, offset)
+        return arr
+
+    def flag_a_remote(self, point: int) -> List[int]:
+        """Address of this rank's flag-A word of ``point`` in every rank's buffer (what a
+        producer bumps when its partial is complete)."""
+        off = self.flag_a_off + point * 32 + 4 * self.rank
+        return [self.buf.peer_ptr(r, off) for r in range(self.world)]
+
+    def flag_a(self, point: int) -> torch.Tensor:
+        return self.buf.view(self.flag_a_off + point * 32, (8,), torch.int32)
+
+    def flag_b(self, point: int) -> torch.Tensor:
+        return self.buf.view(self.flag_b_off + point * 32, (8,), torch.int32)
+
+    def extra(self, shape, dtype) -> torch.Tensor:
+        return self.buf.view(self.extra_off, shape, dtype)
+
+    def extra_ptrs(self):
+        return self._ptrs(self.extra_off)
+
+    # ---- kernels
+    def reduce_norm(self, point: int, h_in: Optional[torch.Tensor], h_out: torch.Tensor,
+                    weight: torch.Tensor, eps: float, T: int, wait_b: bool = True) -> None:
+        """Rows owned by this rank: h_out = h_in + sum of all ranks' ``partial``; every rank's
+        ``xn`` rows = rmsnorm(h_out) * weight. Returns once (on the stream) every rank's rows
+        have arrived in the local ``xn`` unless ``wait_b`` is off (single-process emulation,
+        where the other ranks' kernels only run later in stream order)."""
+        import ctypes as C
+        from ..ops import _lib
+        assert T <= self.T and h_out.dtype == torch.bfloat16 and h_out.stride(0) == self.dim
+        if self.multicast:
+            parts, xn = (C.c_void_p * 8)(), (C.c_void_p * 8)()
+            parts[0] = self.buf.multicast_ptr
+            xn[0] = self.buf.multicast_ptr + self.part_bytes
+        else:
+            parts, xn = self._ptrs(0), self._ptrs(self.part_bytes)
+        fb = self._ptrs(self.flag_b_off + point * 32 + 4 * self.rank)
+        rc = _lib.lib().e2h_tp_reduce_norm(
+            _lib.ptr(h_in), h_out.data_ptr(), weight.data_ptr(), parts, xn, fb,
+            self.flag_a(point).data_ptr(), self.flag_b(point).data_ptr(),
+            self.count[point:point + 1].data_ptr(), self.ticket[point:point + 1].data_ptr(),
+            self.world, self.rank, T, self.dim, float(eps), int(self.multicast), int(wait_b),
+            int(self.wait_ms), _lib.status_word(h_out.device).data_ptr(), _lib.stream())
+        _lib.check(rc, "tp_reduce_norm")
+
+    def embed_partial(self, point: int, tokens: torch.Tensor, table: torch.Tensor, v0: int) -> None:
+        """partial[t] = table[tokens[t] - v0] for ids this rank's vocabulary shard holds, zeros
+        otherwise; raises flag A of ``point`` on every rank."""
+        import ctypes as C
+        from ..ops import _lib
+        T = tokens.numel()
+        assert T <= self.T and tokens.dtype == torch.int32 and table.shape[1] == self.dim
+        fa = (C.c_void_p * 8)()
+        for r, p in enumerate(self.flag_a_remote(point)):
+            fa[r] = p
+        rc = _lib.lib().e2h_tp_embed_partial(
+            tokens.data_ptr(), table.data_ptr(), int(v0), table.shape[0], self.partial.data_ptr(),
+            T, self.dim, fa, self.world, self.gemm_ticket[point:point + 1].data_ptr(),
+            _lib.stream())
+        _lib.check(rc, "tp_embed_partial")
+
+    def gather_logits(self, point: int, B: int, vs: int, out: torch.Tensor) -> None:
+        """out[b, r * vs:(r + 1) * vs] = rank r's fp32 shard [B, vs] (in ``extra``), for all r."""
+        from ..ops import _lib
+        assert out.dtype == torch.float32 and out.shape[1] >= self.world * vs
+        rc = _lib.lib().e2h_tp_gather_logits(
+            self.extra_ptrs(), self.world, B, vs, out.data_ptr(), out.stride(0),
+            self.flag_a(point).data_ptr(), self.count[point:point + 1].data_ptr(),
+            self.ticket[point:point + 1].data_ptr(), int(self.wait_ms),
+            _lib.status_word(out.device).data_ptr(), _lib.stream())
+        _lib.check(rc, "tp_gather_logits")

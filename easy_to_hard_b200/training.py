@@ -110,6 +110,11 @@ class GradClipper:
         return self.norm
 
 
+class DeviceWaitTimeout(RuntimeError):
+    """A bounded device-side wait (a peer's flag, a pipeline barrier) ran out during the step:
+    what the kernels computed afterwards is not to be trusted."""
+
+
 class TrainStepper:
     """zero_grad -> micro-batch forward/backward -> clip -> optimizer -> scheduler, for any
     ``loss_fn(model, *tensors)`` returning a loss or ``(loss, metrics)``."""
@@ -150,6 +155,7 @@ class TrainStepper:
             nvtx.range_push("clip_and_optimizer")
         if self.sharded:
             model.finish_backward()
+        self.check_device_status()
         if self.clipper is not None:
             grad_norm = self.clipper(list(model.grad_shards()), self.max_grad_norm)
             self.optimizer.clip_coef = self.clipper.coef
@@ -163,6 +169,22 @@ class TrainStepper:
         if nvtx:
             nvtx.range_pop()
         return loss.detach(), grad_norm
+
+
+    def check_device_status(self) -> None:
+        """Reads the kernels' status word (4 bytes, once per optimizer step, before the
+        update is applied). The fused gradient reduce-scatter and the peer-memory barriers
+        carry on after a time-out with whatever bytes sit in the peers' buffers, so a
+        non-zero status means the gradients of this step are corrupt: raise instead of
+        stepping. Callers that run under a ``HealthMonitor`` (``parallel.health.guarded_step``)
+        publish the exception to the other ranks."""
+        dev = next(iter(self.model.parameters())).device
+        if dev.type != "cuda":
+            return
+        code = _lib.read_status(dev)
+        if code != 0:
+            raise DeviceWaitTimeout(f"a device-side wait timed out during the step (status "
+                                    f"{code}); the optimizer update was not applied")
 
 
 class SFTStepper(TrainStepper):

@@ -75,6 +75,10 @@ def _load_model(checkpoint_path: Path, device, precision, use_tp: bool) -> Trans
         assert group.startswith("g"), f"cannot parse the group size from {name}"
         model = WeightOnlyInt4QuantHandler(model, int(group[1:])).convert_for_runtime()
     state = torch.load(str(checkpoint_path), mmap=True, weights_only=True)
+    if "int8" in name or "int4" in name:
+        from easy_to_hard_b200.models.quantize import dequantize_head_in_state_dict
+        g = int(name.split(".")[-2][1:]) if "int4" in name else 128
+        state = dequantize_head_in_state_dict(dict(state), g)
     model.load_state_dict(state, assign=True)
     if use_tp:
         apply_tp(model)

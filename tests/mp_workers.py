@@ -284,3 +284,36 @@ def p2p_channel_ops(rank, world, device="cuda"):
     torch.cuda.synchronize()
     res["status"] = _lib.read_status()
     return res
+
+
+def decode_engine_tp(rank, world, vocab_parallel=False, reduce="fused", dim_name="tiny-llama",
+                     new_tokens=24):
+    """Batched generation on the CUDA decode engine with TP = world: greedy and sampled tokens,
+    the device status word, and whether the multicast (NVLS) form of the reduce was used."""
+    from easy_to_hard_b200.models import tp as tpm
+    from easy_to_hard_b200.models.engine import DecodeEngine
+    from easy_to_hard_b200.ops import _lib
+
+    tpm.initialize_model_parallel(world)
+    dev = torch.device(f"cuda:{rank}")
+    model = tiny_model(dtype=torch.bfloat16, vocab_parallel=vocab_parallel, name=dim_name).to(dev)
+    if world > 1:
+        tpm.apply_tp(model)
+    model.eval()
+    eng = DecodeEngine(model, 8, 96, reduce=reduce)
+    g = torch.Generator().manual_seed(21)
+    prompts = torch.randint(0, 1024, (8, 32), generator=g).to(dev)
+    left_pad = torch.tensor([0, 3, 0, 7, 1, 0, 0, 12], device=dev)
+    out = {"reduce": eng.reduce, "multicast": bool(eng.sync.multicast) if eng.sync else False}
+    seq, _ = eng.generate(prompts, left_pad, new_tokens, temperature=0.0, top_k=None)
+    out["greedy"] = seq.cpu().clone()
+    seq, _ = eng.generate(prompts, left_pad, new_tokens, temperature=0.8, top_k=20, seed=5)
+    out["sampled5"] = seq.cpu().clone()
+    n_graphs = len(eng._graphs)
+    seq, _ = eng.generate(prompts, left_pad, new_tokens, temperature=0.8, top_k=20, seed=6)
+    out["sampled6"] = seq.cpu().clone()
+    out["graphs_reused"] = len(eng._graphs) == n_graphs
+    torch.cuda.synchronize()
+    out["status"] = _lib.read_status()
+    eng._graphs.clear()
+    return out

@@ -66,6 +66,35 @@ def test_greedy_generation_is_reproducible_and_in_range():
     assert torch.equal(a[:, :16], prompt) and int(a.max()) < 1024 and int(a.min()) >= 0
 
 
+def test_new_seed_reuses_the_captured_graph_and_changes_the_samples():
+    """The sampler's seed lives in device memory: generation calls with different seeds replay
+    one captured graph (no capture per call, no growth of the graph cache) and still differ."""
+    from easy_to_hard_b200.models.engine import DecodeEngine
+    model = _model()
+    eng = DecodeEngine(model, 4, 64)
+    prompt = torch.randint(1, 1024, (4, 16), device="cuda", dtype=torch.int32)
+    outs = []
+    for seed in (1, 2, 3, 1):
+        seq, _ = eng.generate(prompt, None, 24, temperature=1.0, top_k=50, seed=seed)
+        outs.append(seq.clone())
+    torch.cuda.synchronize()
+    assert len(eng._graphs) == 1
+    assert torch.equal(outs[0], outs[3])
+    assert not torch.equal(outs[0], outs[1]) and not torch.equal(outs[1], outs[2])
+
+
+def test_vocab_sharded_embedding_without_the_flag_is_refused():
+    """An embedding table with V / tp rows indexed by global ids would read past its end: the
+    engine refuses the combination instead of launching."""
+    from easy_to_hard_b200.models.engine import DecodeEngine
+    model = _model()
+    model.tp_size = 2
+    model.tok_embeddings.register_buffer("weight",
+                                         model.tok_embeddings.weight[:512].contiguous())
+    with pytest.raises((ValueError, RuntimeError, AssertionError)):
+        DecodeEngine(model, 4, 64, reduce="nccl")
+
+
 def test_int8_weight_only_engine_matches_module_path():
     from easy_to_hard_b200.models.quantize import WeightOnlyInt8QuantHandler
     model = _model()

@@ -129,3 +129,31 @@ def test_kept_activations_give_the_recomputed_gradients():
     for a, b, c in zip(recomputed, kept_all, one_block):
         assert torch.equal(a, b) and torch.equal(a, c)
     assert float(sum(g.abs().sum() for g in recomputed)) > 0
+
+
+def test_step_raises_when_a_device_wait_timed_out():
+    """A kernel status left by a bounded wait that ran out (here written by the test, no wait is
+    made to expire) stops the step before the optimizer applies the update."""
+    from easy_to_hard_b200.parallel.fsdp import ShardedDataParallel
+    from easy_to_hard_b200.training import DeviceWaitTimeout, SFTStepper
+    from easy_to_hard_b200.utils.memory_efficient_adam import MemoryEfficientAdamW
+    from easy_to_hard_b200.ops import _lib
+    dev = torch.device("cuda:0")
+    model = _tiny(dev)
+    sdp = ShardedDataParallel(model, process_group=None)
+    sdp.train()
+    opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=1e-3,
+                               optim_dtype=torch.float32, optim_device=dev)
+    stepper = SFTStepper(sdp, opt)
+    ids = torch.randint(0, 1024, (2, 128), device=dev)
+    before = [p.detach().clone() for p in sdp.optimizer_parameters()]
+    _lib.read_status()
+    _lib.status_word(dev).fill_(105)
+    with pytest.raises(DeviceWaitTimeout):
+        stepper.step(ids, ids.clone())
+    torch.cuda.synchronize()
+    for a, b in zip(before, sdp.optimizer_parameters()):
+        assert torch.equal(a, b.detach())
+    assert _lib.read_status() == 0          # reading the status cleared it
+    loss, _ = stepper.step(ids, ids.clone())
+    assert torch.isfinite(loss)
