@@ -74,11 +74,19 @@ class SymmetricBuffer:
         self._raw[nbytes:].fill_(self.CANARY)
         self.local = self._raw[:nbytes]
         self.handle = symm_mem.rendezvous(self._raw, group)
-        self.ptrs: List[int] = [int(p) for p in self.handle.buffer_ptrs]
-        try:
-            self.multicast_ptr = int(self.handle.multicast_ptr)
-        except Exception:  # no NVLS multicast on this system
-            self.multicast_ptr = 0
+        # the handle's addresses are those of the allocation block; the tensor may sit at an
+        # offset inside it
+        shift = self._raw.data_ptr() - int(self.handle.buffer_ptrs[self.rank])
+        assert 0 <= shift and shift % 16 == 0
+        self.ptrs: List[int] = [int(p) + shift for p in self.handle.buffer_ptrs]
+        self.multicast_ptr = 0
+        import os
+        if os.environ.get("E2H_MULTIMEM", "1") != "0":
+            try:
+                mc = int(self.handle.multicast_ptr)
+                self.multicast_ptr = mc + shift if mc else 0
+            except Exception:  # noqa: BLE001 -- no NVSwitch multicast on this system
+                self.multicast_ptr = 0
         torch.cuda.synchronize()
         dist.barrier(group)
 
