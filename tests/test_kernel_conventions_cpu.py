@@ -37,10 +37,3 @@ def test_every_kernel_given_to_the_pdl_launch_helper_waits_for_its_predecessor()
             assert "pdl_wait_prior()" in bodies[name], f"{src.name}: {name}"
             checked += 1
     assert checked >= 8
-
-
-def test_no_tma_load_instruction_uses_cluster_multicast():
-    for src in list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")) + list(CSRC.glob("*.h")):
-        for line in src.read_text().splitlines():
-            if '"cp.async.bulk' in line and not line.lstrip().startswith("//"):
-                assert "multicast" not in line, f"{src.name}: {line.strip()}"
