@@ -82,6 +82,11 @@ class DecodeEngine:
                           else "nccl")
         if self.tp == 1:
             reduce = "local"
+        # "fused_oneshot" / "fused_twophase" pin the form of the fused reduce (measurements);
+        # plain "fused" picks by size (see parallel.symm.TPReduceSync)
+        self.reduce_form = {"fused_oneshot": True, "fused_twophase": False}.get(reduce)
+        if reduce.startswith("fused_"):
+            reduce = "fused"
         if reduce not in ("local", "nccl", "fused"):
             raise ValueError(f"unknown reduce strategy {reduce!r}")
         if self.vocab_parallel and reduce != "fused":
@@ -108,7 +113,9 @@ class DecodeEngine:
             from ..parallel.symm import TPReduceSync
             self.sync = TPReduceSync(
                 B, self.dim, self.n_points, groups.get_model_parallel_group(),
-                extra_bytes=B * self.vocab_local * 4 if self.vocab_parallel else 0)
+                extra_bytes=B * self.vocab_local * 4 if self.vocab_parallel else 0,
+                oneshot=self.reduce_form)
+        if self.sync is not None and not self.sync.oneshot:
             self.xn = self.sync.xn
         else:
             self.xn = torch.empty(B, self.dim, dtype=bf, device=dev)
@@ -189,9 +196,9 @@ class DecodeEngine:
             Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                       x_out=x_out)
         else:
-            gemm.linear(x, w, out=sync.partial[:T], signal=sync.flag_a_remote(point),
+            gemm.linear(x, w, out=sync.partial_out(point, T), signal=sync.flag_a_remote(point),
                         ticket=sync.gemm_ticket[point:point + 1], scale=sc)
-            sync.reduce_norm(point, h, h_out, next_norm_w, self.eps, T)
+            sync.reduce_norm(point, h, h_out, next_norm_w, self.eps, T, xn_out=x_out)
         self._count(2)
 
     def _embed_norm(self, tok, h, xn, sync):
@@ -200,7 +207,7 @@ class DecodeEngine:
         w0 = m.layers[0].attention_norm.weight
         if self.vocab_parallel:
             sync.embed_partial(0, tok, m.tok_embeddings.weight, self.tp_rank * self.vocab_local)
-            sync.reduce_norm(0, None, h, w0, self.eps, tok.numel())
+            sync.reduce_norm(0, None, h, w0, self.eps, tok.numel(), xn_out=xn)
             self._count(2)
         else:
             Fn.fused_residual_rmsnorm(None, w0, self.eps, tokens=tok, emb=m.tok_embeddings.weight,
@@ -315,7 +322,8 @@ class DecodeEngine:
         sync = None
         if self.reduce == "fused":
             sync = self._prefill_sync(n)
-            xn = sync.xn[:n]
+            xn = (torch.empty(n, self.dim, dtype=bf, device=dev) if sync.oneshot
+                  else sync.xn[:n])
         else:
             xn = torch.empty(n, self.dim, dtype=bf, device=dev)
         h = torch.empty(n, self.dim, dtype=bf, device=dev)

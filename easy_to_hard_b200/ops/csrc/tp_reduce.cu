@@ -20,6 +20,15 @@
 // activations (which keeps their samplers in lock step), and a rank moves 2 * T/n rows over
 // NVLink instead of pulling n - 1 whole partials.
 //
+// For decode-sized inputs (a few hundred KB per partial) latency, not bytes, is the cost, and
+// the same kernel runs in its ONE-SHOT form: every rank sums all rows itself, pulling the
+// peers' partials with plain 16-byte loads in the same rank order (so the results are still
+// bit-identical), writes only its own activation buffer and needs neither the gather nor phase
+// B: one NVLink round trip per use instead of three. The partial buffers then alternate
+// between two slots, so that a rank's next GEMM never overwrites a partial a slower peer is
+// still reading (a slot is rewritten two uses later, after this rank has seen the peers' flags
+// of the use in between, which they raise only after their reads of the older use).
+//
 // Flags count uses: flag words only ever grow (red.add 1 per use), and the kernel compares them
 // with its own per-call-site use counter in local memory, which the last CTA advances. Nothing is
 // reset between uses, so the sequence replays inside a CUDA graph. All waits are bounded; a
@@ -131,12 +140,16 @@ struct TpReduceArgs {
   int* status;
   long long wait_cycles;
   int n, rank, dim, row0, rows, wait_b;
+  int n_xn;      // activation buffers written (n: every rank's; 1: only p[0], the local one)
+  int signal_b;  // 0: one-shot form, no gather hand-shake
   float eps;
 };
 
 // One CTA per owned row (at least one CTA, which then only takes part in the hand-shakes).
 // NV 16-byte vectors per thread hold the row between the reduction and the write.
-template <int NV, bool MC>
+// LDMC: the sum is one multimem.ld_reduce on parts.p[0]; STMC: the rows go out as one multimem.st
+// on xn.p[0].
+template <int NV, bool LDMC, bool STMC>
 __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
   __shared__ float red[32];
   pdl_launch_dependents();
@@ -156,7 +169,7 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
       if (i < nvec) {
         const long long off = base + 8 * i;
         float acc[8];
-        if constexpr (MC) {
+        if constexpr (LDMC) {
           bf8_unpack(multimem_ld_reduce_bf8(static_cast<const __nv_bfloat16*>(a.parts.p[0]) + off),
                      acc);
         } else {
@@ -197,10 +210,12 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) o[e] = bf16_round(v[k][e] * rstd) * w[e];
         const Bf8 ob = bf8_pack(o);
-        if constexpr (MC) {
+        if constexpr (STMC) {
           multimem_st_bf8(static_cast<__nv_bfloat16*>(a.xn.p[0]) + off, ob);
+        } else if (a.n_xn == 1) {
+          *reinterpret_cast<Bf8*>(static_cast<__nv_bfloat16*>(a.xn.p[0]) + off) = ob;
         } else {
-          for (int s = 0; s < a.n; ++s)
+          for (int s = 0; s < a.n_xn; ++s)
             st_sys_bf8(static_cast<__nv_bfloat16*>(a.xn.p[s]) + off, ob);
         }
       }
@@ -208,14 +223,14 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
   }
 
   // The last CTA to get here tells every rank that this rank's rows are out, waits for the
-  // other ranks' rows and advances the use counter.
-  __threadfence_system();
+  // other ranks' rows and advances the use counter (one-shot form: only the counter).
+  if (a.signal_b) __threadfence_system();
   __syncthreads();
   __shared__ int is_last;
   if (threadIdx.x == 0) is_last = (atomicAdd(a.ticket, 1u) == gridDim.x - 1) ? 1 : 0;
   __syncthreads();
   if (!is_last) return;
-  if (threadIdx.x < a.n) {
+  if (a.signal_b && threadIdx.x < a.n) {
     __threadfence_system();
     red_release_sys_add(static_cast<int*>(a.flag_b_remote.p[threadIdx.x]), 1);
     if (a.wait_b) tp_wait_ge(a.flag_b + threadIdx.x, want, a.status, a.wait_cycles);
@@ -304,16 +319,20 @@ using namespace e2h;
 
 extern "C" {
 
-// h_out[rows of this rank] = h_in + sum_r parts[r];  xn[every rank][those rows] = rmsnorm * w.
-// part_ptrs / xn_ptrs / flag_b_remote: n device addresses (index = rank). With `multicast` the
-// first entry of part_ptrs and xn_ptrs is the multicast address of the respective buffer.
+// Two-phase form (oneshot = 0):
+//   h_out[rows of this rank] = h_in + sum_r parts[r];  xn[every rank][those rows] = rmsnorm * w.
+//   part_ptrs / xn_ptrs / flag_b_remote: n device addresses (index = rank). `multicast` bit 0:
+//   part_ptrs[0] is the multicast address of the partial buffers (multimem.ld_reduce); bit 1:
+//   xn_ptrs[0] is the multicast address of the activation buffers (multimem.st).
+// One-shot form (oneshot = 1): all T rows, xn_ptrs[0] is the local activation buffer,
+//   flag_b_remote / flag_b are unused.
 // Returns 0, a negative argument error, or a cudaError_t.
 int e2h_tp_reduce_norm(const void* h_in, void* h_out, const void* weight,
                        const void* const* part_ptrs, const void* const* xn_ptrs,
                        const void* const* flag_b_remote, const int* flag_a, const int* flag_b,
                        int* count, unsigned int* ticket, int n, int rank, int T, int dim,
-                       float eps, int multicast, int wait_b, int wait_ms, int* status,
-                       void* stream) {
+                       float eps, int multicast, int wait_b, int oneshot, int wait_ms,
+                       int* status, void* stream) {
   if (n < 1 || n > 8 || rank < 0 || rank >= n || T < 1 || dim % 8) return -1;
   if (h_out == nullptr || weight == nullptr || count == nullptr || ticket == nullptr) return -2;
   const int threads = dim >= 4096 ? 512 : (dim >= 1024 ? 128 : 64);
@@ -326,7 +345,8 @@ int e2h_tp_reduce_norm(const void* h_in, void* h_out, const void* weight,
   for (int i = 0; i < 8; ++i) {
     a.parts.p[i] = i < n ? const_cast<void*>(part_ptrs[i]) : nullptr;
     a.xn.p[i] = i < n ? const_cast<void*>(xn_ptrs[i]) : nullptr;
-    a.flag_b_remote.p[i] = i < n ? const_cast<void*>(flag_b_remote[i]) : nullptr;
+    a.flag_b_remote.p[i] =
+        (i < n && flag_b_remote != nullptr) ? const_cast<void*>(flag_b_remote[i]) : nullptr;
   }
   a.flag_a = flag_a;
   a.flag_b = flag_b;
@@ -337,15 +357,21 @@ int e2h_tp_reduce_norm(const void* h_in, void* h_out, const void* weight,
   a.n = n;
   a.rank = rank;
   a.dim = dim;
-  a.row0 = (int)((long long)rank * T / n);
-  a.rows = (int)((long long)(rank + 1) * T / n) - a.row0;
-  a.wait_b = wait_b;
+  a.row0 = oneshot ? 0 : (int)((long long)rank * T / n);
+  a.rows = oneshot ? T : (int)((long long)(rank + 1) * T / n) - a.row0;
+  a.wait_b = oneshot ? 0 : wait_b;
+  a.signal_b = oneshot ? 0 : 1;
+  a.n_xn = oneshot ? 1 : n;
   a.eps = eps;
+  if (!oneshot && flag_b_remote == nullptr) return -2;
+  const bool ldmc = (multicast & 1) != 0, stmc = !oneshot && (multicast & 2) != 0;
   const dim3 grid(a.rows > 0 ? a.rows : 1), block(threads);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define E2H_GO(NV)                                                                     \
-  return (int)(multicast ? launch(tp_reduce_norm_kernel<NV, true>, grid, block, 0, st, a) \
-                         : launch(tp_reduce_norm_kernel<NV, false>, grid, block, 0, st, a))
+#define E2H_GO(NV)                                                                          \
+  return (int)(ldmc ? (stmc ? launch(tp_reduce_norm_kernel<NV, true, true>, grid, block, 0, st, a)    \
+                            : launch(tp_reduce_norm_kernel<NV, true, false>, grid, block, 0, st, a))  \
+                    : (stmc ? launch(tp_reduce_norm_kernel<NV, false, true>, grid, block, 0, st, a)   \
+                            : launch(tp_reduce_norm_kernel<NV, false, false>, grid, block, 0, st, a)))
   if (nv <= 1) E2H_GO(1);
   if (nv == 2) E2H_GO(2);
   E2H_GO(4);

@@ -370,22 +370,29 @@ class P2PChannel:
 
 class TPReduceSync:
     """Buffers, flag words and use counters of the decode engine's fused tensor-parallel
-    reductions (``ops/csrc/tp_reduce.cu``): the row-parallel GEMMs write bf16 partials into
-    ``partial`` and raise flag A of their call site ("point") on every rank; ``reduce_norm``
-    sums the rows this rank owns, adds the residual, normalises, writes the rows into every
-    rank's ``xn`` and hand-shakes on flag B. One symmetric allocation holds
+    reductions (``ops/csrc/tp_reduce.cu``). The row-parallel GEMM of call site ``point`` writes
+    its bf16 partial into ``partial_out(point)`` and raises flag A of that point on every rank;
+    ``reduce_norm`` is the consumer. One symmetric allocation holds
 
-        partial [T, dim] bf16 | xn [T, dim] bf16 | extra bytes | flags A [points, 8] | flags B
+        region 0 [T, dim] bf16 | region 1 [T, dim] bf16 | extra | flags A [points, 8] | flags B
 
-    and the per-point use counters and tickets live in local memory. With an NVSwitch multicast
-    mapping of the allocation (``multicast=True`` and the group has one) the reduction is one
-    ``multimem.ld_reduce`` and the write-out one ``multimem.st`` per 16 bytes.
+    and the per-point use counters and tickets live in local memory. Two forms:
+
+    ``oneshot`` (decode-sized inputs, latency-bound): both regions are partial slots, taken in
+        turn by consecutive points; every rank pulls all partials with plain loads, sums them
+        in rank order and writes its own local activations. One NVLink round trip per use.
+    two-phase (large inputs, bandwidth-bound): region 0 is the partial, region 1 the
+        activation buffer ``xn`` that the owners of the token rows write into on every rank
+        (reduce-scatter + all-gather by rows). With an NVSwitch multicast mapping of the
+        allocation the sum is one ``multimem.ld_reduce`` and the write-out one ``multimem.st``
+        per 16 bytes.
 
     All ranks must issue the same sequence of uses. ``emulated`` builds the ``world`` ranks'
     objects inside one process for single-GPU tests."""
 
     def __init__(self, max_tokens: int, dim: int, n_points: int, group=None, extra_bytes: int = 0,
-                 multicast: bool = True, wait_ms: int = 2000, buf: Optional[SymmetricBuffer] = None):
+                 multicast: bool = True, wait_ms: int = 5000, oneshot: Optional[bool] = None,
+                 buf: Optional[SymmetricBuffer] = None, world: Optional[int] = None):
         self.T, self.dim, self.n_points = max_tokens, dim, n_points
         self.part_bytes = (max_tokens * dim * 2 + 255) // 256 * 256
         self.extra_off = 2 * self.part_bytes
@@ -397,23 +404,29 @@ class TPReduceSync:
             buf = SymmetricBuffer(total, group)
         self.buf = buf
         self.world, self.rank = buf.world, buf.rank
+        if oneshot is None:      # every rank pulls world x the partial: fine while that is small
+            oneshot = self.world * self.part_bytes <= self.ONESHOT_MAX_BYTES
+        self.oneshot = bool(oneshot)
         dev = buf.local.device
         self.count = torch.zeros(n_points, dtype=torch.int32, device=dev)
         self.ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
         self.gemm_ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
-        self.multicast = bool(multicast and buf.multicast_ptr)
+        self.multicast = bool(multicast and buf.multicast_ptr and not self.oneshot)
         self.wait_ms = wait_ms
-        self.partial = buf.view(0, (max_tokens, dim), torch.bfloat16)
-        self.xn = buf.view(self.part_bytes, (max_tokens, dim), torch.bfloat16)
+        self._regions = [buf.view(0, (max_tokens, dim), torch.bfloat16),
+                         buf.view(self.part_bytes, (max_tokens, dim), torch.bfloat16)]
+        self.xn = None if self.oneshot else self._regions[1]
+
+    ONESHOT_MAX_BYTES = 16 << 20
 
     @classmethod
     def emulated(cls, max_tokens: int, dim: int, n_points: int, world: int, extra_bytes: int = 0,
-                 wait_ms: int = 50, device="cuda") -> List["TPReduceSync"]:
+                 wait_ms: int = 50, oneshot: bool = False, device="cuda") -> List["TPReduceSync"]:
         part = (max_tokens * dim * 2 + 255) // 256 * 256
         total = 2 * part + (extra_bytes + 255) // 256 * 256 + 2 * n_points * 32
         bufs = SymmetricBuffer.emulated(total, world, device)
         return [cls(max_tokens, dim, n_points, extra_bytes=extra_bytes, multicast=False,
-                    wait_ms=wait_ms, buf=b) for b in bufs]
+                    wait_ms=wait_ms, oneshot=oneshot, buf=b) for b in bufs]
 
     # ---- addresses
     def _ptrs(self, offset: int):
@@ -422,6 +435,13 @@ class TPReduceSync:
         for r in range(self.world):
             arr[r] = self.buf.peer_ptr(r, offset)
         return arr
+
+    def _region(self, point: int) -> int:
+        return (point & 1) if self.oneshot else 0
+
+    def partial_out(self, point: int, T: int) -> torch.Tensor:
+        """Where this rank's producer of ``point`` writes its [T, dim] bf16 partial."""
+        return self._regions[self._region(point)][:T]
 
     def flag_a_remote(self, point: int) -> List[int]:
         """Address of this rank's flag-A word of ``point`` in every rank's buffer (what a
@@ -443,26 +463,35 @@ class TPReduceSync:
 
     # ---- kernels
     def reduce_norm(self, point: int, h_in: Optional[torch.Tensor], h_out: torch.Tensor,
-                    weight: torch.Tensor, eps: float, T: int, wait_b: bool = True) -> None:
-        """Rows owned by this rank: h_out = h_in + sum of all ranks' ``partial``; every rank's
-        ``xn`` rows = rmsnorm(h_out) * weight. Returns once (on the stream) every rank's rows
-        have arrived in the local ``xn`` unless ``wait_b`` is off (single-process emulation,
-        where the other ranks' kernels only run later in stream order)."""
+                    weight: torch.Tensor, eps: float, T: int, wait_b: bool = True,
+                    xn_out: Optional[torch.Tensor] = None) -> None:
+        """h_out = h_in + sum of all ranks' partials of ``point``; activations = rmsnorm(h_out)
+        * weight. One-shot form: all rows, activations into the local ``xn_out``. Two-phase
+        form: the rows this rank owns, written into every rank's ``xn``; returns once (on the
+        stream) every rank's rows have arrived in the local ``xn`` unless ``wait_b`` is off
+        (single-process emulation, where the other ranks' kernels only run later)."""
         import ctypes as C
         from ..ops import _lib
         assert T <= self.T and h_out.dtype == torch.bfloat16 and h_out.stride(0) == self.dim
-        if self.multicast:
-            parts, xn = (C.c_void_p * 8)(), (C.c_void_p * 8)()
-            parts[0] = self.buf.multicast_ptr
-            xn[0] = self.buf.multicast_ptr + self.part_bytes
+        mc = 0
+        parts = self._ptrs(self._region(point) * self.part_bytes)
+        fb = None
+        if self.oneshot:
+            assert xn_out is not None and xn_out.stride(0) == self.dim
+            xn = (C.c_void_p * 8)()
+            xn[0] = xn_out.data_ptr()
         else:
-            parts, xn = self._ptrs(0), self._ptrs(self.part_bytes)
-        fb = self._ptrs(self.flag_b_off + point * 32 + 4 * self.rank)
+            xn = self._ptrs(self.part_bytes)
+            fb = self._ptrs(self.flag_b_off + point * 32 + 4 * self.rank)
+            if self.multicast:
+                mc = 3
+                parts[0] = self.buf.multicast_ptr
+                xn[0] = self.buf.multicast_ptr + self.part_bytes
         rc = _lib.lib().e2h_tp_reduce_norm(
             _lib.ptr(h_in), h_out.data_ptr(), weight.data_ptr(), parts, xn, fb,
             self.flag_a(point).data_ptr(), self.flag_b(point).data_ptr(),
             self.count[point:point + 1].data_ptr(), self.ticket[point:point + 1].data_ptr(),
-            self.world, self.rank, T, self.dim, float(eps), int(self.multicast), int(wait_b),
+            self.world, self.rank, T, self.dim, float(eps), mc, int(wait_b), int(self.oneshot),
             int(self.wait_ms), _lib.status_word(h_out.device).data_ptr(), _lib.stream())
         _lib.check(rc, "tp_reduce_norm")
 
@@ -477,9 +506,9 @@ class TPReduceSync:
         for r, p in enumerate(self.flag_a_remote(point)):
             fa[r] = p
         rc = _lib.lib().e2h_tp_embed_partial(
-            tokens.data_ptr(), table.data_ptr(), int(v0), table.shape[0], self.partial.data_ptr(),
-            T, self.dim, fa, self.world, self.gemm_ticket[point:point + 1].data_ptr(),
-            _lib.stream())
+            tokens.data_ptr(), table.data_ptr(), int(v0), table.shape[0],
+            self.partial_out(point, T).data_ptr(), T, self.dim, fa, self.world,
+            self.gemm_ticket[point:point + 1].data_ptr(), _lib.stream())
         _lib.check(rc, "tp_embed_partial")
 
     def gather_logits(self, point: int, B: int, vs: int, out: torch.Tensor) -> None:

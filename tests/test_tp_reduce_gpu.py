@@ -34,39 +34,46 @@ def _signal(sync, point):
 
 @pytest.mark.parametrize("world,T,dim", [(2, 64, 4096), (4, 64, 512), (8, 64, 4096), (8, 5, 256),
                                          (2, 300, 1024), (4, 7, 8192)])
-def test_reduce_norm_matches_reference_and_replays(world, T, dim):
+@pytest.mark.parametrize("oneshot", [False, True], ids=["two_phase", "one_shot"])
+def test_reduce_norm_matches_reference_and_replays(world, T, dim, oneshot):
     from easy_to_hard_b200.ops import _lib
     from easy_to_hard_b200.parallel.symm import TPReduceSync
     torch.manual_seed(world * 1000 + T)
     dev = "cuda"
-    syncs = TPReduceSync.emulated(T, dim, 3, world)
+    syncs = TPReduceSync.emulated(T, dim, 3, world, oneshot=oneshot)
     w = (torch.randn(dim, device=dev) * 0.5 + 1).bfloat16()
     _lib.read_status()
     for use in range(3):
         point = use % 2 + 1
         parts = [(torch.randn(T, dim, device=dev) * 0.3).bfloat16() for _ in range(world)]
         hs = [torch.randn(T, dim, device=dev).bfloat16() for _ in range(world)] if use != 1 else None
+        if oneshot and hs is not None:       # every rank keeps the whole residual stream
+            hs = [hs[0]] * world
         for r, s in enumerate(syncs):
-            s.partial[:T].copy_(parts[r])
-            s.xn.zero_()
+            s.partial_out(point, T).copy_(parts[r])
+            if not oneshot:
+                s.xn.zero_()
             _signal(s, point)
-        outs = []
+        outs, xns = [], []
         for r, s in enumerate(syncs):
             h_out = torch.zeros(T, dim, dtype=torch.bfloat16, device=dev)
-            s.reduce_norm(point, None if hs is None else hs[r], h_out, w, 1e-5, T, wait_b=False)
+            xn = torch.zeros(T, dim, dtype=torch.bfloat16, device=dev) if oneshot else None
+            s.reduce_norm(point, None if hs is None else hs[r], h_out, w, 1e-5, T, wait_b=False,
+                          xn_out=xn)
             outs.append(h_out)
+            xns.append(xn if oneshot else s.xn[:T])
         torch.cuda.synchronize()
         assert _lib.read_status() == 0
         h_ref, xn_ref = _ref(hs, parts, w, 1e-5, world)
         for r, s in enumerate(syncs):
-            r0, r1 = r * T // world, (r + 1) * T // world
+            r0, r1 = (0, T) if oneshot else (r * T // world, (r + 1) * T // world)
             assert torch.equal(outs[r][r0:r1], h_ref[r0:r1]), (use, r)
-            # every rank holds every row, bit-identical to what the owner computed
-            torch.testing.assert_close(s.xn[:T].float(), xn_ref.float(), atol=2e-2, rtol=2e-2)
-            assert torch.equal(s.xn[:T], syncs[0].xn[:T])
+            # every rank holds every row, bit-identical on all ranks
+            torch.testing.assert_close(xns[r].float(), xn_ref.float(), atol=2e-2, rtol=2e-2)
+            assert torch.equal(xns[r], xns[0])
             n_use = {0: 1, 1: 1, 2: 2}[use]       # uses of this point so far
             assert int(s.count[point]) == n_use
-            assert s.flag_b(point)[:world].tolist() == [n_use] * world
+            assert s.flag_b(point)[:world].tolist() == [0 if oneshot else n_use] * world
             assert s.flag_a(point)[:world].tolist() == [n_use] * world
             assert s.buf.check_canary()
 
@@ -82,6 +89,11 @@ def test_wait_runs_out_sets_status_and_returns():
     _lib.read_status()
     _signal(syncs[0], 0)                      # rank 1 never signals
     syncs[0].reduce_norm(0, h, h, w, 1e-5, 8, wait_b=True)
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 105
+    one = TPReduceSync.emulated(8, 256, 2, 2, wait_ms=20, oneshot=True)
+    _signal(one[0], 1)
+    one[0].reduce_norm(1, h, h, w, 1e-5, 8, xn_out=torch.empty_like(h))
     torch.cuda.synchronize()
     assert _lib.read_status() == 105
     assert float((torch.ones(4, device="cuda") * 2).sum()) == 8.0
