@@ -61,7 +61,11 @@ def parse():
                     help="decode: weight-only quantisation of the linears (int4: groups of 128)")
     ap.add_argument("--micro", type=int, default=16, help="sft: sequences per micro batch")
     ap.add_argument("--tp", type=int, default=1, help="sft: tensor-parallel size (rest is FSDP)")
-    ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine")
+    ap.add_argument("--reduce", default="auto", help="TP reduce strategy of the engine: auto | "
+                    "fused | fused_oneshot | fused_twophase | nccl")
+    ap.add_argument("--vocab_parallel", type=int, default=1, help="decode, N > 1: shard the "
+                    "embedding table and the LM head over the ranks (the reference's "
+                    "--vocab_parallel flag, which its own model ignores)")
     ap.add_argument("--pdl", type=int, default=1, help="programmatic dependent launch in the "
                     "decode graph (1) or plain stream order (0)")
     return ap.parse_args()
@@ -173,9 +177,11 @@ def run_ours(a):
     tp.initialize_model_parallel(world)
     cfg = ModelArgs.from_name(MODEL)
     torch.manual_seed(0)
+    vocab_parallel = bool(a.vocab_parallel) and world > 1 and a.reduce != "nccl" \
+        and cfg.vocab_size % world == 0
     with torch.device("cuda"):
         model = Transformer(cfg, freeze_tok_embeddings=True, freeze_output=True,
-                            freeze_norm=True).to(torch.bfloat16)
+                            freeze_norm=True, vocab_parallel=vocab_parallel).to(torch.bfloat16)
     g = torch.Generator(device="cuda").manual_seed(1234)
     for name, t in list(model.named_parameters()) + list(model.named_buffers()):
         if t.dim() == 2:
@@ -225,6 +231,16 @@ def run_ours(a):
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(lambda i: step_e2e(a.warmup + i), a.steps)
     status = _lib.read_status()
+    # every rank must have produced the same tokens (same seed, bit-identical activations)
+    agree = True
+    if world > 1:
+        import torch.distributed as dist
+        seq, _ = api.generate(model, dev_prompts[0], None, 32, temperature=TEMPERATURE,
+                              top_k=TOP_K, seed=123)
+        digest = (seq.long() * torch.arange(1, seq.shape[1] + 1, device="cuda")).sum().reshape(1)
+        every = [torch.zeros_like(digest) for _ in range(world)]
+        dist.all_gather(every, digest)
+        agree = all(int(e) == int(every[0]) for e in every)
     toks = BATCH * NEW * a.steps
     key = next(iter(eng._graphs)) if eng._graphs else None
     launches = (eng.prefill_launches + (NEW - 1) * eng.decode_launches(key)) * a.steps
@@ -238,8 +254,13 @@ def run_ours(a):
             "data": "synthetic (random token ids, random-init weights)",
             "impl": "ours",
             "config": decode_config(world, a.quant),
-            "impl_notes": {"tp_reduce": eng.reduce, "kv_cache": "sized to prompt + new tokens, "
-                           "only the live range is read"},
+            "impl_notes": {"tp_reduce": eng.reduce,
+                           "tp_reduce_form": (None if eng.sync is None else
+                                              "one-shot pull" if eng.sync.oneshot else
+                                              "two-phase" + (" (multimem)" if eng.sync.multicast
+                                                             else "")),
+                           "vocab_parallel": eng.vocab_parallel, "ranks_agree": agree,
+                           "kv_cache": "sized to prompt + new tokens, only the live range is read"},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": BATCH * PROMPT * 4,

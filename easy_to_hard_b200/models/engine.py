@@ -246,7 +246,7 @@ class DecodeEngine:
                                  scale=W["wqkv"][1])
             if sq == 1:
                 Fn.attn_decode(q, self.kcache[li], self.vcache[li], self.pos, self.left_pad,
-                               self.n_head, out=att, n_split=1 if T * self.n_kv >= 256 else 0)
+                               self.n_head, out=att)
             else:
                 self._prefill_attention(li, q, att, prefill_B, sq)
             self._count(2)

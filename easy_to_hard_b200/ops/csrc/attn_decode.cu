@@ -9,8 +9,9 @@
 //
 // Layouts: q [B, n_head*D] bf16, caches [max_batch, n_kv, smax, D] bf16, out [B, n_head*D] bf16.
 // Grid: (n_kv * B, n_split). Each CTA has 4 warps; a half-warp (16 lanes x 8 elements) owns
-// one key row at a time. With n_split > 1 the CTA writes (m, l, acc) partials and a second
-// kernel merges them.
+// one key row at a time. With n_split > 1 the CTA writes (m, l, acc) partials; they are merged
+// either by the last CTA of each (sequence, kv head) to arrive (a ticket counter per pair, no
+// extra launch) or, when no ticket array is given, by a second kernel.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <float.h>
@@ -41,7 +42,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ vcache, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ partial, const int* __restrict__ pos_ptr,
                    const int* __restrict__ left_pad, int n_head, int n_kv, int smax, float scale,
-                   int n_split) {
+                   int n_split, unsigned int* __restrict__ tickets) {
   constexpr int R = D / 128 > 0 ? D / 128 : 1;       // 8-element groups per lane (D=128 -> 1)
   constexpr int LPK = D >= 128 ? 16 : D / 8;          // lanes per key row
   static_assert(D == 64 || D == 128 || D == 256, "head_dim must be 64, 128 or 256");
@@ -188,6 +189,35 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
       }
     }
   }
+  if (n_split == 1 || tickets == nullptr) return;
+  // merge in place of a second launch: the last split of this (sequence, kv head) to finish
+  // combines all of them (the ticket word returns to zero for the next launch)
+  __shared__ int is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned int t = atomicAdd(&tickets[blockIdx.x], 1u);
+    is_last = (t == (unsigned int)n_split - 1) ? 1 : 0;
+    if (is_last) tickets[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx - g * D;
+    const int h = hk * G + g;
+    const float* pp = partial + ((long long)b * n_head + h) * n_split * (D + 2);
+    float mm = -FLT_MAX;
+    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(pp + s * (D + 2) + D));
+    float ll = 0.f, a = 0.f;
+    for (int s = 0; s < n_split; ++s) {
+      const float ms = __ldcg(pp + s * (D + 2) + D);
+      const float w = (ms == -FLT_MAX) ? 0.f : __expf(ms - mm);
+      ll += __ldcg(pp + s * (D + 2) + D + 1) * w;
+      a += __ldcg(pp + s * (D + 2) + d) * w;
+    }
+    out[((long long)b * n_head + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+  }
 }
 
 template <int D>
@@ -214,13 +244,14 @@ __global__ void attn_decode_merge_kernel(const float* __restrict__ partial,
 template <int D, int G>
 static int launch_decode(const void* q, const void* k, const void* v, void* out, float* partial,
                          const int* pos, const int* left_pad, int B, int n_head, int n_kv, int smax,
-                         float scale, int n_split, cudaStream_t stream) {
+                         float scale, int n_split, cudaStream_t stream,
+                         unsigned int* tickets = nullptr) {
   dim3 grid(n_kv * B, n_split);
   cudaError_t e = launch(attn_decode_kernel<D, G>, grid, dim3(kWarps * 32), 0, stream,
                          (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
                          (const __nv_bfloat16*)v, (__nv_bfloat16*)out, partial, pos, left_pad,
-                         n_head, n_kv, smax, scale, n_split);
-  if (e == cudaSuccess && n_split > 1)
+                         n_head, n_kv, smax, scale, n_split, tickets);
+  if (e == cudaSuccess && n_split > 1 && tickets == nullptr)
     e = launch(attn_decode_merge_kernel<D>, dim3(B * n_head), dim3(128), 0, stream,
                (const float*)partial, (__nv_bfloat16*)out, n_split);
   return (int)e;
@@ -229,10 +260,12 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
 }  // namespace e2h
 
 // partial: fp32 scratch of B*n_head*n_split*(D+2) floats, needed only when n_split > 1.
+// tickets: optional uint32 [B*n_kv], zero before the first launch (every launch leaves it zero):
+// with it the splits are merged inside the kernel, without it by a second launch.
 extern "C" int e2h_attn_decode(const void* q, const void* kcache, const void* vcache, void* out,
                                float* partial, const int* pos, const int* left_pad, int B,
                                int n_head, int n_kv, int head_dim, int smax, float scale,
-                               int n_split, void* stream_v) {
+                               int n_split, unsigned int* tickets, void* stream_v) {
   using namespace e2h;
   cudaStream_t stream = (cudaStream_t)stream_v;
   if (n_head % n_kv) return -1;
@@ -240,7 +273,7 @@ extern "C" int e2h_attn_decode(const void* q, const void* kcache, const void* vc
   const int G = n_head / n_kv;
 #define E2H_GO(D_, G_)                                                                          \
   return launch_decode<D_, G_>(q, kcache, vcache, out, partial, pos, left_pad, B, n_head, n_kv, \
-                               smax, scale, n_split, stream)
+                               smax, scale, n_split, stream, tickets)
   if (head_dim == 128) {
     if (G == 1) E2H_GO(128, 1);
     if (G == 4) E2H_GO(128, 4);

@@ -87,6 +87,24 @@ def test_attn_decode(B, n_head, n_kv, D, pos, n_split):
     assert torch.allclose(o.view(B, n_head, 1, D).float(), want.float(), rtol=2e-2, atol=2e-2)
 
 
+def test_attn_decode_in_kernel_merge_matches_the_two_launch_form_and_replays():
+    """Split-KV partials merged by the last CTA of each (sequence, kv head) to finish: same
+    result as the separate merge launch, and the ticket words return to zero, so a second call
+    (and a graph replay) works without any reset."""
+    from easy_to_hard_b200.ops import functional as Fn
+    B, n_head, n_kv, D, smax, pos = 6, 8, 2, 128, 512, 411
+    q = _mk(B, n_head * D, seed=31)
+    kc, vc = _mk(B, n_kv, smax, D, seed=32), _mk(B, n_kv, smax, D, seed=33)
+    p = torch.tensor([pos], dtype=torch.int32, device="cuda")
+    two = Fn.attn_decode(q, kc, vc, p, None, n_head, n_split=8, fused_merge=False)
+    for _ in range(3):
+        one = Fn.attn_decode(q, kc, vc, p, None, n_head, n_split=8)
+        assert torch.equal(one, two)
+    auto = Fn.attn_decode(q, kc, vc, p, None, n_head)           # split count picked by size
+    assert torch.allclose(auto.float(), two.float(), rtol=2e-2, atol=2e-2)
+    _status_ok()
+
+
 def test_sampler_greedy_topk_and_bookkeeping():
     from easy_to_hard_b200.ops import functional as Fn
     B, V = 16, 32016
