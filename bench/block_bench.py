@@ -1,6 +1,6 @@
 """Event-timed breakdown of one transformer block at the SFT micro-batch shape of the 7B model.
 
-    python -m easy_to_hard_b200.models.blockbench [--batch 8] [--seq 768]
+    python bench/block_bench.py [--batch 8] [--seq 768]
 
 Prints the forward, the backward from kept intermediates and the backward that recomputes the
 block, then every kernel of the block on its own (CUDA events, five back-to-back launches after
@@ -11,8 +11,13 @@ import argparse
 
 import torch
 
-from ..ops import flash, functional as Fn, gemm, reference
-from . import fused_block as fb
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from easy_to_hard_b200.ops import flash, functional as Fn, gemm, reference  # noqa: E402
+from easy_to_hard_b200.models import fused_block as fb  # noqa: E402
 
 
 def main():

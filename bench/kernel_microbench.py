@@ -1,7 +1,7 @@
 """Event-timed micro-benchmarks of the sm_100a kernels on the shapes of the 7B model.
 
-    python -m easy_to_hard_b200.ops.microbench --case all
-    python -m easy_to_hard_b200.ops.microbench --case gemm_wgrad --tokens 6144 --iters 20
+    python bench/kernel_microbench.py --case all
+    python bench/kernel_microbench.py --case gemm_wgrad --tokens 6144 --iters 20
 
 Each case prints one JSON line: duration (CUDA events on the launching stream, after warm-up,
 L2 flushed between iterations by writing a 256 MB buffer), algorithmic FLOPs or bytes per
@@ -16,12 +16,16 @@ import json
 import math
 import os
 
+import sys
+
 import torch
 
-from . import flash, functional as Fn, gemm, reference
+_ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, _ROOT)
+
+from easy_to_hard_b200.ops import flash, functional as Fn, gemm, reference  # noqa: E402
 
 DIM, FFN, HEADS, HEAD_DIM, VOCAB = 4096, 11008, 32, 128, 32016
-_ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
 
 def _peaks():

@@ -22,6 +22,7 @@ from typing import List, Optional, Union
 import torch
 import torch.distributed as dist
 import torch.nn as nn
+import torch.nn.functional as F
 
 from ..parallel import collectives as coll
 from ..parallel.groups import (  # noqa: F401  (re-exported API)
@@ -81,6 +82,43 @@ def shard_linear(linear: nn.Module, style: str, weight_splits: Optional[List[int
     setattr(linear, attr, getattr(linear, attr) // world)
 
 
+def pad_int4_ffn_for_tp(ffn: nn.Module, world: int) -> bool:
+    """Widen the intermediate dimension of a weight-only int4 feed-forward so that ``w2``'s packed
+    K tiles and (scale, zero) groups divide evenly over ``world`` ranks. The reference asserts
+    divisibility instead (models/tp.py:143-145, 171-181), which rules out int4 at TP 4 and 8
+    for the 7B / 13B FFN widths (11008 = 86 groups of 128). The added features carry code 0 with
+    scale 0 and zero 0, i.e. weights that dequantise to exactly 0: ``w1`` / ``w3`` produce 0 for
+    them, ``silu(0) * 0 = 0``, and ``w2`` multiplies that by 0, so the function of the layer is
+    unchanged. This is an extension of this framework, applied to the in-memory model only; the
+    checkpoint format is not touched. Returns True when anything was padded."""
+    from .quantize import WeightOnlyInt4Linear
+    w1, w2, w3 = ffn.w1, ffn.w2, ffn.w3
+    if not all(isinstance(m, WeightOnlyInt4Linear) for m in (w1, w2, w3)):
+        return False
+    unit = math.lcm(w2.inner_k_tiles * 16, w2.groupsize, 8) * world
+    k_old = w2.in_features
+    k_new = -(-k_old // unit) * unit
+    if k_new == k_old:
+        return False
+    assert w1.out_features == w3.out_features and w1.out_features <= k_old
+    for m in (w1, w3):     # more output features: rows of the packed weight, columns of the qparams
+        n_new = k_new - (k_old - m.out_features)
+        m.register_buffer("weight", F.pad(m.weight, (0, 0, 0, 0, 0, 0, 0, n_new // 8 - m.weight.shape[0])))
+        m.register_buffer("scales_and_zeros",
+                          F.pad(m.scales_and_zeros, (0, 0, 0, n_new - m.scales_and_zeros.shape[1])))
+        m.out_features = n_new
+    kt = w2.inner_k_tiles * 16
+    w2.register_buffer("weight", F.pad(w2.weight, (0, 0, 0, 0, 0, k_new // kt - w2.weight.shape[1])))
+    w2.register_buffer("scales_and_zeros",
+                       F.pad(w2.scales_and_zeros,
+                             (0, 0, 0, 0, 0, k_new // w2.groupsize - w2.scales_and_zeros.shape[0])))
+    if getattr(w2, "padding", False):
+        # the checkpoint's own padding already added zero inputs after origin_in_features
+        w2.origin_in_features = k_new - (k_old - w2.origin_in_features)
+    w2.in_features = k_new
+    return True
+
+
 def apply_tp(model, requires_grad: bool = False, sequence_parallel: bool = False) -> None:
     """Shard ``model`` over the tensor-parallel group in place."""
     world = groups.get_model_parallel_world_size()
@@ -99,6 +137,7 @@ def apply_tp(model, requires_grad: bool = False, sequence_parallel: bool = False
         att.n_head //= world
         att.n_local_heads //= world
         att.dim //= world
+        pad_int4_ffn_for_tp(ffn, world)
         for name, style in (("w1", "colwise"), ("w3", "colwise"), ("w2", "rowwise")):
             shard_linear(getattr(ffn, name), style, None, requires_grad)
         for m in (att, ffn):

@@ -13,8 +13,9 @@ calls them directly:
 As in the reference, "sequence parallel" shards dim 0 of ``[B, S, D]``: every trainer first
 gathers the batch over the tensor-parallel group, so dim 0 holds ``tp`` ranks' samples and each
 rank keeps its own between the parallel regions. All functions are no-ops for a group of one.
-On CUDA these are the NCCL baseline; the fused GEMM+collective kernels of ``parallel.fused``
-replace them on the hot paths.
+On CUDA these are the NCCL form of the collectives; the hot paths use the peer-memory kernels
+instead where they exist (``parallel.symm`` with ``ops/csrc/tp_reduce.cu``, ``ops/csrc/comm.cu``
+and the fused consumers in ``ops/csrc/norm_embed.cu``).
 """
 from __future__ import annotations
 

@@ -246,9 +246,8 @@ class PPOTrainer(RLTrainer):
                 full.copy_(unit.shard_lp)
             for name, o, n, shp in zip(unit.names, unit.offsets, unit.numels, unit.shapes):
                 dst_params[name].data.copy_(full[o:o + n].view(shp))
-        eng = getattr(dst, "_decode_engine", None)
-        if eng is not None and hasattr(eng, "refresh_weights"):
-            eng.refresh_weights()
+        # the decode engine reads the rollout model's own tensors (updated in place above), so
+        # its captured graphs see the new weights without any refresh
 
     @staticmethod
     def sub_batched_outputs(model, rollouts_batch: Dict[str, torch.Tensor],

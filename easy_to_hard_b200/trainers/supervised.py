@@ -71,7 +71,7 @@ def run(args, task: Task) -> Dict:
         tokenizer_path = checkpoint_path.parent
     set_global_compile_mode(args.compile)
 
-    device_id = groups.maybe_init_dist()
+    device_id = groups.maybe_init_dist(timeout_s=args.dist_timeout_s)
     use_tp = device_id is not None
     rank0 = (not use_tp) or dist.get_rank() == 0
     if use_tp:

@@ -153,7 +153,6 @@ _FIELDS += [
     ("rollout_top_k", int, 50, "top-k used when sampling PPO rollouts (hard-coded to 50 upstream)"),
     ("rollout_tensor_parallel_size", Optional[int], None,
      "tensor-parallel degree of the rollout engine when it differs from training"),
-    ("fused_kernels", bool, True, "run the sm_100a fused kernels on CUDA (False: PyTorch oracle path)"),
     ("dist_timeout_s", float, 1800.0, "process-group timeout; a hung peer ends the job with an error"),
 ]
 

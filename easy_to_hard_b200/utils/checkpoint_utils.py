@@ -119,6 +119,24 @@ def save_checkpoint(checkpoint_path: str, model, optimizer, scheduler, epoch: in
             os.remove(victim)
 
 
+class CheckpointError(RuntimeError):
+    """A checkpoint shard is missing or unreadable (truncated, corrupt)."""
+
+
+def read_checkpoint_file(path: str, **load_kwargs):
+    """``torch.load`` with errors a user can act on: which shard is missing, or which file is
+    damaged. Training writes each shard to a temporary name and renames it, so a damaged file
+    means the storage lost data after the write, not that a save was interrupted."""
+    if not os.path.isfile(path):
+        raise CheckpointError(f"checkpoint shard {path} does not exist (every tensor-parallel "
+                              "rank reads its own *_rank_<k>.pt)")
+    try:
+        return torch.load(path, **load_kwargs)
+    except Exception as e:  # noqa: BLE001 -- zip / pickle / EOF errors of a damaged file
+        raise CheckpointError(f"checkpoint shard {path} cannot be read ({type(e).__name__}: "
+                              f"{str(e)[:200]}); the file is truncated or corrupt") from e
+
+
 def _checkpoint_tp_size(checkpoint_path: str, load_rank: int) -> Tuple[str, int]:
     pattern = checkpoint_path.replace(f"_rank_{load_rank}", "_rank_*")
     return pattern, len(glob.glob(pattern))
@@ -132,7 +150,8 @@ def load_checkpoint(checkpoint_path: str, model, optimizer=None, scheduler=None,
     if ckpt_world != world:
         raise ValueError("The model parallel setting of resuming training does not match the "
                          f"current setting: {ckpt_world} (train) vs {world} (resume)")
-    state = torch.load(checkpoint_path, map_location="cpu", mmap=True, weights_only=False)
+    state = read_checkpoint_file(checkpoint_path, map_location="cpu", mmap=True,
+                                 weights_only=False)
     if use_fsdp or _is_sharded(model):
         model.load_full_state_dict(state["model"], strict=False)
         if optimizer is not None and state.get("optimizer") is not None:
@@ -223,7 +242,8 @@ def load_inference_checkpoint(checkpoint_path: str, model: torch.nn.Module):
     """Load the ``model`` part of a training checkpoint into ``model``, resharding when the
     checkpoint was written with a different tensor-parallel degree."""
     if not dist.is_initialized():
-        state = torch.load(checkpoint_path, map_location="cpu", weights_only=False)["model"]
+        state = read_checkpoint_file(checkpoint_path, map_location="cpu",
+                                     weights_only=False)["model"]
     else:
         rank, world = get_model_parallel_rank(), get_model_parallel_world_size()
         if f"_rank_{rank}" not in checkpoint_path:
@@ -232,8 +252,8 @@ def load_inference_checkpoint(checkpoint_path: str, model: torch.nn.Module):
         assert ckpt_world > 0, f"No checkpoint found: '{pattern}'"
 
         def read(i):
-            sd = torch.load(pattern.replace("*", str(i)), map_location="cpu", mmap=True,
-                            weights_only=False)["model"]
+            sd = read_checkpoint_file(pattern.replace("*", str(i)), map_location="cpu",
+                                      mmap=True, weights_only=False)["model"]
             return {k: v.cpu() for k, v in sd.items()}
 
         if ckpt_world == world:

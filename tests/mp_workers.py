@@ -317,3 +317,16 @@ def decode_engine_tp(rank, world, vocab_parallel=False, reduce="fused", dim_name
     out["status"] = _lib.read_status()
     eng._graphs.clear()
     return out
+
+
+def generate_main(rank, world, checkpoint=None, prompt_file=None, output_file=None,
+                  resume=False, tp=1, num_samples=2):
+    """``inference_generate.main`` as one rank of a gloo job (data-parallel batches, shared
+    output file under flock)."""
+    from pathlib import Path
+    import inference_generate
+    inference_generate.main(seed=3, prompt_file=Path(prompt_file), output_file=Path(output_file),
+                            batch_size=2, num_samples=num_samples, max_new_tokens=6, top_k=20,
+                            temperature=0.8, checkpoint_path=Path(checkpoint), compile=False,
+                            resume_generation=resume, tensor_parallel_size=tp)
+    return {"rank": rank}

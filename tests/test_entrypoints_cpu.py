@@ -120,3 +120,46 @@ def test_train_rl_dpo_end_to_end(workspace, tmp_path, variant):
     if variant == "dpo":       # policy == reference at the start: loss starts at ln 2
         assert abs(rec["loss"] - 0.693) < 0.1
     assert (save / "epoch_1_step_2_rank_0.pt").exists()
+
+
+def _read_jsonl(path):
+    with open(path) as fh:
+        return [json.loads(ln) for ln in fh if ln.strip()]
+
+
+def test_inference_generate_main_two_dp_ranks_and_resume(workspace, tmp_path):
+    """The batched-generation entry point end to end: prompts sorted by length and repeated per
+    sample, batches dealt round-robin to two data-parallel (gloo) ranks, both appending to one
+    jsonl under flock; --resume_generation only produces what is missing."""
+    import mp_workers as W
+    g = torch.Generator().manual_seed(4)
+    prompts = [{"prompt": _sentence(g, 3 + i)} for i in range(5)]
+    pfile = tmp_path / "prompts.json"
+    pfile.write_text(json.dumps(prompts))
+    out = tmp_path / "gen" / "out.jsonl"
+    kw = dict(checkpoint=str(workspace / "tiny-llama" / "model.pth"), prompt_file=str(pfile),
+              output_file=str(out))
+    W.run(W.generate_main, 2, str(tmp_path / "r1"), **kw)
+    rows = _read_jsonl(out)
+    # 5 prompts x 2 samples = 10, padded to a multiple of the batch size by repeating the first
+    assert len(rows) == 10
+    assert all(set(r) == {"idx", "sample_idx", "prompt", "output"} for r in rows)
+    per_idx = {}
+    for r in rows:
+        per_idx.setdefault(r["idx"], []).append(r["sample_idx"])
+        assert r["prompt"] == prompts[r["idx"]]["prompt"] and isinstance(r["output"], str)
+    assert sorted(per_idx) == [0, 1, 2, 3, 4]
+    assert all(sorted(v) == [0, 1] for v in per_idx.values())
+    # drop three finished lines, then resume: exactly the missing samples are regenerated
+    kept = rows[:7]
+    out.write_text("".join(json.dumps(r) + "\n" for r in kept))
+    W.run(W.generate_main, 2, str(tmp_path / "r2"), resume=True, **kw)
+    rows2 = _read_jsonl(out)
+    assert rows2[:7] == kept and len(rows2) >= 10
+    count = {}
+    for r in rows2:
+        count[r["idx"]] = count.get(r["idx"], 0) + 1
+    assert all(count[i] >= 2 for i in range(5))
+    # nothing left: a further resume appends nothing
+    W.run(W.generate_main, 2, str(tmp_path / "r3"), resume=True, **kw)
+    assert len(_read_jsonl(out)) == len(rows2)

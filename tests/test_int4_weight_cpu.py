@@ -1,5 +1,6 @@
 """Packed int4 runtime layout (ops.gemm.Int4Weight) on CPU: codes survive the packing, and the
 dequantised weight equals the checkpoint format's definition (models.quantize)."""
+import pytest
 import torch
 
 
@@ -81,3 +82,36 @@ def test_quantised_lm_head_in_a_file_is_expanded_at_load():
     out = qz.dequantize_head_in_state_dict(dict(sd4), 128)
     assert "output.scales_and_zeros" not in out and tuple(out["output.weight"].shape) == (64, 256)
     assert float((out["output.weight"].float() - w).abs().max()) < 0.1 * float(w.abs().max())
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_int4_feed_forward_shards_at_every_tp_degree(world):
+    """11008 input features of w2 are 86 int4 groups: not divisible by 4 or 8. The intermediate
+    dimension is padded with zero-weight features before sharding, so the summed partial
+    outputs of the ranks equal the unsharded int4 layer."""
+    import copy
+    import torch.nn as nn
+    from easy_to_hard_b200.models import quantize as qz, tp as tpm
+    from easy_to_hard_b200.models.model import FeedForward, ModelArgs
+
+    torch.manual_seed(0)
+    cfg = ModelArgs(block_size=64, vocab_size=64, n_layer=1, n_head=2, dim=256,
+                    intermediate_size=11008)
+    holder = nn.Module()
+    holder.ffn = FeedForward(cfg).to(torch.bfloat16)
+    h = qz.WeightOnlyInt4QuantHandler(holder, 128, 8)
+    sd = h.create_quantized_state_dict()
+    h.convert_for_runtime()
+    holder.load_state_dict(sd)
+    x = (torch.randn(5, 256) * 0.5).to(torch.bfloat16)
+    want = holder.ffn(x).float()
+    total = torch.zeros_like(want)
+    for rank in range(world):
+        ffn = copy.deepcopy(holder.ffn)
+        padded = tpm.pad_int4_ffn_for_tp(ffn, world)
+        assert padded == (world in (4, 8))
+        for name, style in (("w1", "colwise"), ("w3", "colwise"), ("w2", "rowwise")):
+            tpm.shard_linear(getattr(ffn, name), style, world=world, rank=rank)
+        assert ffn.w2.in_features == ffn.w1.out_features
+        total += ffn(x).float()
+    torch.testing.assert_close(total, want, atol=0.05, rtol=0.05)

@@ -46,7 +46,7 @@ def main(args: TrainingArguments):
     tokenizer_path = base.parent / "tokenizer.model"
     if not tokenizer_path.is_file():
         tokenizer_path = base.parent
-    device_id = groups.maybe_init_dist()
+    device_id = groups.maybe_init_dist(timeout_s=args.dist_timeout_s)
     use_tp = device_id is not None
     if use_tp:
         groups.initialize_model_parallel(args.tensor_parallel_size or dist.get_world_size())
