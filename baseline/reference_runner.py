@@ -43,7 +43,22 @@ def run(a, wl, ClockSampler):
                 t.data.normal_(0.0, 0.02, generator=g)
         if use_tp:
             apply_tp(m)
-        return m.to(device="cuda", dtype=torch.bfloat16).eval()
+        m = m.to(device="cuda", dtype=torch.bfloat16).eval()
+        quant = wl.get("quant", "none")
+        if quant == "int8":
+            # the reference's own on-the-fly path (inference_generate.py:319-326 there)
+            from models.quantize import WeightOnlyInt8QuantHandler
+            m = WeightOnlyInt8QuantHandler(m).convert_for_runtime_on_the_fly()
+            m = m.to(device="cuda").eval()
+        elif quant == "int4":
+            # its offline path, run in memory: quantised state dict, runtime modules, load
+            from models.quantize import WeightOnlyInt4QuantHandler
+            h = WeightOnlyInt4QuantHandler(m, 128)
+            sd = h.create_quantized_state_dict()
+            m = h.convert_for_runtime()
+            m.load_state_dict(sd, assign=True)
+            m = m.to(device="cuda").eval()
+        return m
 
     eager_decode = ref.decode_one_token
     gen = torch.Generator().manual_seed(7)
@@ -87,6 +102,11 @@ def run(a, wl, ClockSampler):
                 torch.cuda.synchronize()
                 notes.append(f"ran with {label}, block_size {block_size}")
                 break
+            except (NotImplementedError, ImportError, ModuleNotFoundError, AttributeError) as e:
+                if model is None:      # the quantised model itself could not be built
+                    raise RuntimeError(f"{type(e).__name__}: {str(e)[:200]}") from e
+                notes.append(f"{label}: {type(e).__name__}: {str(e)[:120]}")
+                continue
             except torch.cuda.OutOfMemoryError:
                 notes.append(f"{label}, block_size {block_size}: out of memory")
                 model = None
@@ -133,9 +153,11 @@ def run(a, wl, ClockSampler):
             "metric": "batched_decode_tokens_per_s", "value": toks / (ms / 1e3),
             "unit": "tokens/s", "n_gpus": world, "steps": a.steps, "warmup": a.warmup,
             "ms_per_step": ms / a.steps, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16",
+            "vs_baseline": None,
+            "dtype": "bf16" if wl.get("quant", "none") == "none"
+            else f"bf16 activations, {wl['quant']} weights",
             "data": "synthetic (random token ids, random-init weights)", "impl": "reference",
-            "config": wl["config"](world),
+            "config": wl["config"](world, wl.get("quant", "none")),
             "impl_notes": {"kv_cache": f"sized to block_size {model.config.block_size} and read "
                            "in full every step (the reference's stock generate)",
                            "decode_mode": note},

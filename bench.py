@@ -309,6 +309,20 @@ def finish():
 SFT_SEQ, SFT_GLOBAL_BATCH = 768, 64
 
 
+def sft_config(world: int, tp: int) -> dict:
+    """The SFT workload description both arms print."""
+    return {"model": "Llemma-7B architecture (32 layers, dim 4096, 32 heads, ffn 11008, "
+                     "vocab 32016, rope 1e6)",
+            "global_batch": SFT_GLOBAL_BATCH, "seq_len": SFT_SEQ,
+            "parallelism": f"tp{tp}xfsdp{world // tp}",
+            "sequence_parallel": tp > 1,
+            "optimizer": "AdamW lr 2e-5 betas 0.9/0.95, fp32 master weights, fp32 moments, "
+                         "bf16 compute, gradient clipping at 1.0",
+            "loss": "cross-entropy on response tokens (prompt 64..384 masked)",
+            "step": "one optimizer step over the global batch",
+            "l2": "inputs larger than L2 (13 GB of bf16 weights per pass)"}
+
+
 def sft_batches(n, vocab, per_rank, rank):
     """Random token ids; per sequence a prompt of 64..384 tokens whose labels are ignored
     (cross-entropy on the response tokens only). Pinned host tensors."""
@@ -326,8 +340,9 @@ def sft_batches(n, vocab, per_rank, rank):
 
 def run_ours_sft(a):
     """Full-parameter SFT step of the 7B architecture: fp32 master weights, bf16 compute, AdamW
-    with bf16 moments (lr 2e-5, betas 0.9/0.95), global batch 64 x 768 tokens, TP=a.tp x
-    sharded data parallel over the rest. value = trained tokens/s of the whole job."""
+    with fp32 moments (lr 2e-5, betas 0.9/0.95), global batch 64 x 768 tokens, TP=a.tp
+    (sequence parallel) x sharded data parallel over the rest. value = trained tokens/s of the
+    whole job."""
     import torch
     rank, local, world = dist_setup(a.gpus)
     from easy_to_hard_b200.models.model import ModelArgs, Transformer
@@ -350,7 +365,7 @@ def run_ours_sft(a):
         if t.dim() == 2:
             t.data.normal_(0.0, 0.02, generator=g)
     if a.tp > 1:
-        tp.apply_tp(model, requires_grad=True)
+        tp.apply_tp(model, requires_grad=True, sequence_parallel=True)
     model.requires_grad_(True)
     sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group(),
                               param_dtype=torch.float32, compute_dtype=torch.bfloat16,
@@ -358,7 +373,7 @@ def run_ours_sft(a):
     sdp.train()
     torch.cuda.empty_cache()
     opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=2e-5, betas=(0.9, 0.95),
-                               weight_decay=0.0, optim_dtype=torch.bfloat16,
+                               weight_decay=0.0, optim_dtype=torch.float32,
                                optim_device=torch.device("cuda"))
     stepper = SFTStepper(sdp, opt)
     per_rank = SFT_GLOBAL_BATCH // world            # rows each rank loads; a TP group pools them
@@ -403,15 +418,12 @@ def run_ours_sft(a):
             "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (random token ids, random-init weights)", "impl": "ours",
-            "config": {"model": "Llemma-7B architecture (llemma-7b-32016)",
-                       "global_batch": SFT_GLOBAL_BATCH, "seq_len": SFT_SEQ,
-                       "micro_batch": micro, "parallelism": f"tp{a.tp}xfsdp{dp}",
-                       "optimizer": "AdamW lr 2e-5 betas 0.9/0.95, fp32 master, bf16 moments",
-                       "loss": "cross-entropy on response tokens (prompt 64..384 masked)",
-                       "l2": "inputs larger than L2 (13 GB of bf16 weights per pass)",
-                       "activations": ("block intermediates kept within %.0f GiB, rest recomputed"
-                                       % (getattr(sdp, "_keep_budget", 0) / 2 ** 30)),
-                       "model_tflops_per_gpu": flops / (ms / a.steps / 1e3) / 1e12 / world},
+            "config": sft_config(world, a.tp),
+            "impl_notes": {"micro_batch": micro,
+                           "activations": ("block intermediates kept within %.0f GiB, rest "
+                                           "recomputed" % (getattr(sdp, "_keep_budget", 0) / 2 ** 30)),
+                           "model_tflops_per_gpu": flops / (ms / a.steps / 1e3) / 1e12 / world,
+                           "peak_memory_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
                     "h2d_bytes_per_step": 2 * per_rank * SFT_SEQ * 8, "d2h_bytes_per_step": 4},
@@ -421,7 +433,8 @@ def run_ours_sft(a):
 
 
 def run_reference(a):
-    """The unmodified reference on the same workload, through its own generate()."""
+    """The unmodified reference on the same workload: its own generate() for decode, its own
+    training step (FSDP1, its AdamW, its tensor-parallel hooks) for SFT."""
     ref_dir = os.path.join(ROOT, "baseline", "_ref")
 
     def unavailable(why):
@@ -433,12 +446,18 @@ def run_reference(a):
                            "(the reference ships neither setup.py nor pyproject.toml: install it from a copy "
                            "with a minimal setup.py, --no-deps)")
     try:
-        from baseline import reference_runner
+        from baseline import reference_runner, reference_sft_runner
     except Exception as e:  # noqa: BLE001
         return unavailable(f"reference runner import failed: {type(e).__name__}: {e}")
     try:
-        reference_runner.run(a, dict(batch=BATCH, prompt=PROMPT, new=NEW, temperature=TEMPERATURE,
-                                     top_k=TOP_K, config=decode_config), ClockSampler)
+        if a.workload == "sft":
+            reference_sft_runner.run(a, dict(seq=SFT_SEQ, global_batch=SFT_GLOBAL_BATCH,
+                                             sequence_parallel=True, config=sft_config),
+                                     ClockSampler)
+        else:
+            reference_runner.run(a, dict(batch=BATCH, prompt=PROMPT, new=NEW,
+                                         temperature=TEMPERATURE, top_k=TOP_K, quant=a.quant,
+                                         config=decode_config), ClockSampler)
     except Exception as e:  # noqa: BLE001
         unavailable(f"reference failed: {type(e).__name__}: {str(e)[:300]}")
 

@@ -58,7 +58,33 @@ def _sp_reduce_scatter(t: torch.Tensor, shape: BlockShape) -> torch.Tensor:
 
 
 _ROW_REDUCE: Dict[tuple, object] = {}
+_SP_SYNC: Dict[tuple, object] = {}
 _P2P_REDUCE = {"enabled": None}
+
+# call sites of the sequence-parallel collectives of one block (parallel.symm.SequenceParallelSync)
+_PT_ENTRY, _PT_WO, _PT_W2, _PT_DY, _PT_DXN2, _PT_DH, _PT_DXN1 = range(7)
+
+
+def _sp_sync(T: int, dim: int):
+    """Symmetric buffers of the fused sequence-parallel collectives for T tokens per
+    tensor-parallel group, one set per shape, created by every rank of the group at the same
+    point of its first forward."""
+    key = (T, dim)
+    sp = _SP_SYNC.get(key)
+    if sp is None:
+        from ..parallel.symm import SequenceParallelSync
+        sp = SequenceParallelSync(T, dim, 8, groups.get_model_parallel_group())
+        _SP_SYNC[key] = sp
+    return sp
+
+
+def _row_parallel_sp(sync, point: int, x_in: torch.Tensor, w: torch.Tensor, T: int):
+    """Row-parallel GEMM into the next partial slot of ``sync``; its last CTA raises the flag of
+    ``point`` on every rank. Returns the slot for the consuming collective."""
+    slot, part = sync.next_partial(T)
+    gemm.linear(x_in, w, out=part, signal=sync.signal_ptrs(point),
+                ticket=sync.gemm_ticket[point:point + 1])
+    return slot
 
 
 def p2p_reduce_enabled(group=None) -> bool:
@@ -118,8 +144,17 @@ def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tens
     intermediates the backward needs."""
     H, Hkv, D = shape.n_head, shape.n_kv, shape.head_dim
     sp = shape.sequence_parallel and shape.tp > 1
-    xn1 = Fn.rmsnorm(x, w["attention_norm"], shape.eps)
-    xn1f = _sp_gather(xn1, shape) if sp else xn1
+    fused_sp = sp and p2p_reduce_enabled()
+    if fused_sp:
+        # rmsnorm of this rank's rows and the all-gather in one kernel over peer memory
+        T = x.shape[0] * shape.tp
+        sync = _sp_sync(T, x.shape[1])
+        xn1f = sync.gather(_PT_ENTRY, x, T, w["attention_norm"], shape.eps)
+        if keep:
+            xn1f = xn1f.clone()      # the gather buffer is reused by the next collective
+    else:
+        xn1 = Fn.rmsnorm(x, w["attention_norm"], shape.eps)
+        xn1f = _sp_gather(xn1, shape) if sp else xn1
     T = xn1f.shape[0]
     qkv = gemm.linear(xn1f, w["wqkv"])
     Fn.rope(qkv, freqs, pos, H + Hkv, D, out=qkv)          # q and k heads, in place
@@ -129,9 +164,16 @@ def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tens
     o, lse = flash.flash_fwd(q, k, v, None, return_lse=True)
     o2 = o.view(T, H * D)
     fused_reduce = shape.tp > 1 and not sp and p2p_reduce_enabled()
+    xn2f = None
     if shape.tp == 1:
         h = gemm.linear_residual(o2, w["wo"], x)
         xn2 = Fn.rmsnorm(h, w["ffn_norm"], shape.eps)
+    elif fused_sp:
+        # reduce-scatter + residual + RMSNorm + all-gather as the consumer of the wo GEMM
+        slot = _row_parallel_sp(sync, _PT_WO, o2, w["wo"], T)
+        h, xn2f = sync.reduce_norm_gather(_PT_WO, slot, x, w["ffn_norm"], shape.eps, T)
+        if keep:
+            xn2f = xn2f.clone()
     elif fused_reduce:
         h, xn2 = _row_parallel_fused(o2, w["wo"], x, w["ffn_norm"], shape.eps)
     else:
@@ -139,11 +181,15 @@ def block_forward(x: torch.Tensor, w: Dict[str, torch.Tensor], freqs: torch.Tens
         part = _sp_reduce_scatter(part, shape) if sp else _tp_all_reduce(part, shape)
         h = part.add_(x)
         xn2 = Fn.rmsnorm(h, w["ffn_norm"], shape.eps)
-    xn2f = _sp_gather(xn2, shape) if sp else xn2
+    if xn2f is None:
+        xn2f = _sp_gather(xn2, shape) if sp else xn2
     g, u = gemm.linear_dual(xn2f, w["w1"], w["w3"])
     act = Fn.swiglu(g, u)
     if shape.tp == 1:
         out = gemm.linear_residual(act, w["w2"], h)
+    elif fused_sp:
+        slot = _row_parallel_sp(sync, _PT_W2, act, w["w2"], T)
+        out = sync.reduce(_PT_W2, slot, h, T)
     elif fused_reduce:
         out, _ = _row_parallel_fused(act, w["w2"], h, None, shape.eps)
     else:
@@ -178,20 +224,46 @@ def block_backward(dy: torch.Tensor, x: torch.Tensor, w: Dict[str, torch.Tensor]
     def wgrad(name, d_out, inp):
         gemm.linear_wgrad(d_out, inp, out=grads[name], accumulate=accumulate)
 
+    fused_sp = sp and p2p_reduce_enabled()
+    sync = _sp_sync(T, x.shape[1]) if fused_sp else None
+
+    def dgrad_reduce(point, make_partial):
+        """Sum of the ranks' input-gradient partials: all-reduce (tensor parallel) or
+        reduce-scatter to this rank's rows (sequence parallel, fused: the dgrad GEMMs write
+        into a symmetric partial slot and the consumer kernel pulls this rank's rows)."""
+        if fused_sp:
+            slot, part = sync.next_partial(T)
+            make_partial(part, sync.signal_ptrs(point), sync.gemm_ticket[point:point + 1])
+            return sync.reduce(point, slot, None, T)
+        part = make_partial(None, None, None)
+        if shape.tp > 1:
+            part = _sp_reduce_scatter(part, shape) if sp else _tp_all_reduce(part, shape)
+        return part
+
     # ---- feed-forward: out = h + w2(act) ----
-    dyf = _sp_gather(dy, shape) if sp else dy
+    if fused_sp:
+        dyf = sync.gather(_PT_DY, dy.contiguous(), T)
+    else:
+        dyf = _sp_gather(dy, shape) if sp else dy
     d_act = gemm.linear_dgrad(dyf, w["w2"])
     wgrad("w2", dyf, a["act"])
     dg, du = Fn.swiglu_bwd(a["g"], a["u"], d_act)
-    d_xn2 = gemm.linear_dgrad(dg, w["w1"])
-    gemm.gemm(w["w3"], du, epi=gemm.EPI_RESIDUAL, out=d_xn2, aux=d_xn2, a_mn_major=True)
+
+    def d_xn2_partial(out, signal, ticket):
+        out = gemm.linear_dgrad(dg, w["w1"], out=out)
+        kw = dict(signal=signal, ticket=ticket) if signal else {}
+        gemm.gemm(w["w3"], du, epi=gemm.EPI_RESIDUAL, out=out, aux=out, a_mn_major=True, **kw)
+        return out
+
+    d_xn2 = dgrad_reduce(_PT_DXN2, d_xn2_partial)
     wgrad("w1", dg, a["xn2f"])
     wgrad("w3", du, a["xn2f"])
-    if shape.tp > 1:
-        d_xn2 = _sp_reduce_scatter(d_xn2, shape) if sp else _tp_all_reduce(d_xn2, shape)
     dh = Fn.rmsnorm_bwd(a["h"], d_xn2, w["ffn_norm"], shape.eps, dres=dy)
     # ---- attention: h = x + wo(o) ----
-    dhf = _sp_gather(dh, shape) if sp else dh
+    if fused_sp:
+        dhf = sync.gather(_PT_DH, dh, T)
+    else:
+        dhf = _sp_gather(dh, shape) if sp else dh
     d_o = gemm.linear_dgrad(dhf, w["wo"])
     wgrad("wo", dhf, a["o"].view(T, H * D))
     dqkv = torch.empty_like(a["qkv"])   # dq | dk | dv written in place by the attention backward
@@ -200,10 +272,12 @@ def block_backward(dy: torch.Tensor, x: torch.Tensor, w: Dict[str, torch.Tensor]
                     dk=dqkv[:, H * D: (H + Hkv) * D].view(shape.B, shape.S, Hkv, D),
                     dv=dqkv[:, (H + Hkv) * D:].view(shape.B, shape.S, Hkv, D))
     Fn.rope(dqkv, freqs, pos, H + Hkv, D, inverse=True, out=dqkv)
-    d_xn1 = gemm.linear_dgrad(dqkv, w["wqkv"])
+    def d_xn1_partial(out, signal, ticket):
+        kw = dict(signal=signal, ticket=ticket) if signal else {}
+        return gemm.linear_dgrad(dqkv, w["wqkv"], out=out, **kw)
+
+    d_xn1 = dgrad_reduce(_PT_DXN1, d_xn1_partial)
     wgrad("wqkv", dqkv, a["xn1f"])
-    if shape.tp > 1:
-        d_xn1 = _sp_reduce_scatter(d_xn1, shape) if sp else _tp_all_reduce(d_xn1, shape)
     return Fn.rmsnorm_bwd(x, d_xn1, w["attention_norm"], shape.eps, dres=dh)
 
 

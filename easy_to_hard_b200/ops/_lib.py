@@ -94,6 +94,9 @@ _SIGNATURES = {
     "e2h_tp_reduce_norm": [_vp, _vp, _vp, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
                            C.POINTER(C.c_void_p), _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _i, _i,
                            _i, _i, _vp, _vp],
+    "e2h_tp_rows": [_i, _vp, _vp, _vp, C.POINTER(C.c_void_p), C.POINTER(C.c_void_p),
+                    C.POINTER(C.c_void_p), C.POINTER(C.c_void_p), _vp, _vp, _vp, _vp, _i, _i, _i,
+                    _i, _f, _i, _i, _i, _vp, _vp],
     "e2h_tp_embed_partial": [_vp, _vp, _i, _i, _vp, _i, _i, C.POINTER(C.c_void_p), _i, _vp, _vp],
     "e2h_tp_gather_logits": [C.POINTER(C.c_void_p), _i, _i, _i, _vp, _ll, _vp, _vp, _vp, _i, _vp,
                              _vp],

@@ -62,10 +62,24 @@ def needs_build() -> bool:
 
 
 def build(force: bool = False, verbose: bool = False) -> Path:
-    """Compile and link; returns the path of the shared library."""
+    """Compile and link; returns the path of the shared library. Processes that start together
+    (one per GPU under torchrun) take a file lock, so one of them builds and the others find the
+    finished library."""
     if not force and not needs_build():
         return lib_path()
     OUT_DIR.mkdir(parents=True, exist_ok=True)
+    import fcntl
+    with open(OUT_DIR / "build.lock", "w") as lock:
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            if not force and not needs_build():     # another process built it meanwhile
+                return lib_path()
+            return _build_locked(verbose)
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
+
+
+def _build_locked(verbose: bool) -> Path:
     nvcc = _nvcc()
     srcs = sources()
     extra = ["-Xptxas", "-v"] if verbose else []

@@ -140,8 +140,17 @@ struct TpReduceArgs {
   int* status;
   long long wait_cycles;
   int n, rank, dim, row0, rows, wait_b;
-  int n_xn;      // activation buffers written (n: every rank's; 1: only p[0], the local one)
-  int signal_b;  // 0: one-shot form, no gather hand-shake
+  int n_xn;      // activation buffers written (n: every rank's; 1: only p[0], the local one;
+                 // 0: none, a plain reduce-scatter)
+  int signal_b;  // 0: no gather hand-shake (one-shot form, reduce-scatter only)
+  int do_reduce;    // 0: nothing to sum, the rows are h_in as it is (a pure gather)
+  int do_norm;      // 0: the gathered rows are the (summed) rows themselves, not their RMSNorm
+  int self_signal;  // 1: no producer kernel raises flag A for this use; the kernel raises it
+                    // itself when it starts (everything earlier on this rank's stream is
+                    // done), which makes phase A a barrier: peers may write into this rank's
+                    // activation buffer only once its earlier readers have finished
+  int h_compact;    // 1: h_in / h_out hold only this rank's rows (row 0 = global row row0)
+  TpPtrs flag_a_remote;  // self_signal: this rank's flag-A word on every rank
   float eps;
 };
 
@@ -155,12 +164,17 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
   pdl_launch_dependents();
   pdl_wait_prior();
   const int want = *a.count + 1;
+  if (a.self_signal && blockIdx.x == 0 && threadIdx.x < a.n) {
+    __threadfence_system();
+    red_release_sys_add(static_cast<int*>(a.flag_a_remote.p[threadIdx.x]), 1);
+  }
   if (threadIdx.x < a.n) tp_wait_ge(a.flag_a + threadIdx.x, want, a.status, a.wait_cycles);
   __syncthreads();
 
   const int nvec = a.dim >> 3;
   if ((int)blockIdx.x < a.rows) {
     const long long base = (long long)(a.row0 + blockIdx.x) * a.dim;
+    const long long hbase = a.h_compact ? (long long)blockIdx.x * a.dim : base;
     float v[NV][8];
     float ss = 0.f;
 #pragma unroll
@@ -168,8 +182,12 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
       const int i = threadIdx.x + k * blockDim.x;
       if (i < nvec) {
         const long long off = base + 8 * i;
+        const long long hoff = hbase + 8 * i;
         float acc[8];
-        if constexpr (LDMC) {
+        if (!a.do_reduce) {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+        } else if constexpr (LDMC) {
           bf8_unpack(multimem_ld_reduce_bf8(static_cast<const __nv_bfloat16*>(a.parts.p[0]) + off),
                      acc);
         } else {
@@ -184,7 +202,7 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
         }
         float r[8];
         if (a.h_in != nullptr) {
-          bf8_unpack(*reinterpret_cast<const Bf8*>(a.h_in + off), r);
+          bf8_unpack(*reinterpret_cast<const Bf8*>(a.h_in + hoff), r);
         } else {
 #pragma unroll
           for (int e = 0; e < 8; ++e) r[e] = 0.f;
@@ -192,23 +210,32 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
 #pragma unroll
         for (int e = 0; e < 8; ++e) {
           // the linear's output is a bf16 tensor in the reference: round, then the residual add
-          v[k][e] = bf16_round(r[e] + bf16_round(acc[e]));
+          v[k][e] = a.do_reduce ? bf16_round(r[e] + bf16_round(acc[e])) : r[e];
           ss += v[k][e] * v[k][e];
         }
-        *reinterpret_cast<Bf8*>(a.h_out + off) = bf8_pack(v[k]);
+        if (a.h_out != nullptr) *reinterpret_cast<Bf8*>(a.h_out + hoff) = bf8_pack(v[k]);
       }
     }
-    ss = block_sum_f(ss, red);
-    const float rstd = rsqrtf(ss / a.dim + a.eps);
+    float rstd = 1.f;
+    if (a.do_norm) {
+      ss = block_sum_f(ss, red);
+      rstd = rsqrtf(ss / a.dim + a.eps);
+    }
 #pragma unroll
     for (int k = 0; k < NV; ++k) {
       const int i = threadIdx.x + k * blockDim.x;
-      if (i < nvec) {
+      if (i < nvec && a.n_xn > 0) {
         const long long off = base + 8 * i;
-        float w[8], o[8];
-        bf8_unpack(*reinterpret_cast<const Bf8*>(a.weight + 8 * i), w);
+        float o[8];
+        if (a.do_norm) {
+          float w[8];
+          bf8_unpack(*reinterpret_cast<const Bf8*>(a.weight + 8 * i), w);
 #pragma unroll
-        for (int e = 0; e < 8; ++e) o[e] = bf16_round(v[k][e] * rstd) * w[e];
+          for (int e = 0; e < 8; ++e) o[e] = bf16_round(v[k][e] * rstd) * w[e];
+        } else {
+#pragma unroll
+          for (int e = 0; e < 8; ++e) o[e] = v[k][e];
+        }
         const Bf8 ob = bf8_pack(o);
         if constexpr (STMC) {
           multimem_st_bf8(static_cast<__nv_bfloat16*>(a.xn.p[0]) + off, ob);
@@ -319,6 +346,28 @@ using namespace e2h;
 
 extern "C" {
 
+static int tp_rows_launch(TpReduceArgs& a, bool ldmc, bool stmc, void* stream) {
+  const int threads = a.dim >= 4096 ? 512 : (a.dim >= 1024 ? 128 : 64);
+  const int nv = (a.dim / 8 + threads - 1) / threads;
+  if (nv > 4) return -3;
+  const dim3 grid(a.rows > 0 ? a.rows : 1), block(threads);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define E2H_GO(NV)                                                                          \
+  return (int)(ldmc ? (stmc ? launch(tp_reduce_norm_kernel<NV, true, true>, grid, block, 0, st, a)    \
+                            : launch(tp_reduce_norm_kernel<NV, true, false>, grid, block, 0, st, a))  \
+                    : (stmc ? launch(tp_reduce_norm_kernel<NV, false, true>, grid, block, 0, st, a)   \
+                            : launch(tp_reduce_norm_kernel<NV, false, false>, grid, block, 0, st, a)))
+  if (nv <= 1) E2H_GO(1);
+  if (nv == 2) E2H_GO(2);
+  E2H_GO(4);
+#undef E2H_GO
+}
+
+static void tp_fill_ptrs(TpPtrs& dst, const void* const* src, int n) {
+  for (int i = 0; i < 8; ++i)
+    dst.p[i] = (i < n && src != nullptr) ? const_cast<void*>(src[i]) : nullptr;
+}
+
 // Two-phase form (oneshot = 0):
 //   h_out[rows of this rank] = h_in + sum_r parts[r];  xn[every rank][those rows] = rmsnorm * w.
 //   part_ptrs / xn_ptrs / flag_b_remote: n device addresses (index = rank). `multicast` bit 0:
@@ -335,19 +384,15 @@ int e2h_tp_reduce_norm(const void* h_in, void* h_out, const void* weight,
                        int* status, void* stream) {
   if (n < 1 || n > 8 || rank < 0 || rank >= n || T < 1 || dim % 8) return -1;
   if (h_out == nullptr || weight == nullptr || count == nullptr || ticket == nullptr) return -2;
-  const int threads = dim >= 4096 ? 512 : (dim >= 1024 ? 128 : 64);
-  const int nv = (dim / 8 + threads - 1) / threads;
-  if (nv > 4) return -3;
+  if (!oneshot && flag_b_remote == nullptr) return -2;
   TpReduceArgs a;
   a.h_in = static_cast<const __nv_bfloat16*>(h_in);
   a.h_out = static_cast<__nv_bfloat16*>(h_out);
   a.weight = static_cast<const __nv_bfloat16*>(weight);
-  for (int i = 0; i < 8; ++i) {
-    a.parts.p[i] = i < n ? const_cast<void*>(part_ptrs[i]) : nullptr;
-    a.xn.p[i] = i < n ? const_cast<void*>(xn_ptrs[i]) : nullptr;
-    a.flag_b_remote.p[i] =
-        (i < n && flag_b_remote != nullptr) ? const_cast<void*>(flag_b_remote[i]) : nullptr;
-  }
+  tp_fill_ptrs(a.parts, part_ptrs, n);
+  tp_fill_ptrs(a.xn, xn_ptrs, n);
+  tp_fill_ptrs(a.flag_b_remote, flag_b_remote, n);
+  tp_fill_ptrs(a.flag_a_remote, nullptr, 0);
   a.flag_a = flag_a;
   a.flag_b = flag_b;
   a.count = count;
@@ -362,20 +407,70 @@ int e2h_tp_reduce_norm(const void* h_in, void* h_out, const void* weight,
   a.wait_b = oneshot ? 0 : wait_b;
   a.signal_b = oneshot ? 0 : 1;
   a.n_xn = oneshot ? 1 : n;
+  a.do_reduce = 1;
+  a.do_norm = 1;
+  a.self_signal = 0;
+  a.h_compact = 0;
   a.eps = eps;
-  if (!oneshot && flag_b_remote == nullptr) return -2;
-  const bool ldmc = (multicast & 1) != 0, stmc = !oneshot && (multicast & 2) != 0;
-  const dim3 grid(a.rows > 0 ? a.rows : 1), block(threads);
-  cudaStream_t st = static_cast<cudaStream_t>(stream);
-#define E2H_GO(NV)                                                                          \
-  return (int)(ldmc ? (stmc ? launch(tp_reduce_norm_kernel<NV, true, true>, grid, block, 0, st, a)    \
-                            : launch(tp_reduce_norm_kernel<NV, true, false>, grid, block, 0, st, a))  \
-                    : (stmc ? launch(tp_reduce_norm_kernel<NV, false, true>, grid, block, 0, st, a)   \
-                            : launch(tp_reduce_norm_kernel<NV, false, false>, grid, block, 0, st, a)))
-  if (nv <= 1) E2H_GO(1);
-  if (nv == 2) E2H_GO(2);
-  E2H_GO(4);
-#undef E2H_GO
+  return tp_rows_launch(a, (multicast & 1) != 0, !oneshot && (multicast & 2) != 0, stream);
+}
+
+// The sequence-parallel collectives of training over the same kernel and protocol, by token
+// rows (rank r owns rows [r*T/n, (r+1)*T/n)); `ops` picks the stages:
+//   bit 0  reduce   sum of every rank's partial (+ h_in, the residual) for the owned rows, i.e.
+//                   the reduce-scatter after a row-parallel GEMM (models/tp.py:396-405, :774 of
+//                   the reference); without it the rows are h_in as it is
+//   bit 1  norm     the rows that go out are rmsnorm(rows) * weight instead of the rows
+//   bit 2  gather   write the outgoing rows into every rank's activation buffer and hand-shake,
+//                   i.e. the all-gather before a column-parallel GEMM (models/tp.py:375-393, :750)
+//   bit 3  barrier  no producer kernel raises flag A for this use: the kernel raises it itself
+//                   on start and waits for all ranks (needed by a gather that follows no reduce)
+//   bit 4  compact  h_in / h_out hold the owned rows only
+// h_out (owned rows, optional) receives the summed rows before any normalisation.
+int e2h_tp_rows(int ops, const void* h_in, void* h_out, const void* weight,
+                const void* const* part_ptrs, const void* const* xn_ptrs,
+                const void* const* flag_a_remote, const void* const* flag_b_remote,
+                const int* flag_a, const int* flag_b, int* count, unsigned int* ticket, int n,
+                int rank, int T, int dim, float eps, int multicast, int wait_b, int wait_ms,
+                int* status, void* stream) {
+  const bool reduce = ops & 1, norm = ops & 2, gather = ops & 4, barrier = ops & 8;
+  if (n < 1 || n > 8 || rank < 0 || rank >= n || T < 1 || dim % 8) return -1;
+  if (count == nullptr || ticket == nullptr || flag_a == nullptr) return -2;
+  if (reduce && part_ptrs == nullptr) return -2;
+  if (norm && weight == nullptr) return -2;
+  if (gather && (xn_ptrs == nullptr || flag_b_remote == nullptr || flag_b == nullptr)) return -2;
+  if (barrier && flag_a_remote == nullptr) return -2;
+  if (!reduce && h_in == nullptr) return -2;
+  if (!gather && h_out == nullptr) return -2;
+  TpReduceArgs a;
+  a.h_in = static_cast<const __nv_bfloat16*>(h_in);
+  a.h_out = static_cast<__nv_bfloat16*>(h_out);
+  a.weight = static_cast<const __nv_bfloat16*>(weight);
+  tp_fill_ptrs(a.parts, part_ptrs, n);
+  tp_fill_ptrs(a.xn, xn_ptrs, n);
+  tp_fill_ptrs(a.flag_b_remote, flag_b_remote, n);
+  tp_fill_ptrs(a.flag_a_remote, flag_a_remote, n);
+  a.flag_a = flag_a;
+  a.flag_b = flag_b;
+  a.count = count;
+  a.ticket = ticket;
+  a.status = status;
+  a.wait_cycles = (long long)(wait_ms < 1 ? 1 : wait_ms) * 2000000LL;
+  a.n = n;
+  a.rank = rank;
+  a.dim = dim;
+  a.row0 = (int)((long long)rank * T / n);
+  a.rows = (int)((long long)(rank + 1) * T / n) - a.row0;
+  a.wait_b = gather ? wait_b : 0;
+  a.signal_b = gather ? 1 : 0;
+  a.n_xn = gather ? n : 0;
+  a.do_reduce = reduce ? 1 : 0;
+  a.do_norm = norm ? 1 : 0;
+  a.self_signal = barrier ? 1 : 0;
+  a.h_compact = (ops & 16) ? 1 : 0;
+  a.eps = eps;
+  return tp_rows_launch(a, reduce && (multicast & 1) != 0, gather && (multicast & 2) != 0,
+                        stream);
 }
 
 int e2h_tp_embed_partial(const int* tokens, const void* table, int v0, int rows_local, void* part,

@@ -150,17 +150,19 @@ class ShardUnit:
         else:
             self.shard.grad.add_(out)
 
-    def reduce_grads_p2p(self, rs, slot: int) -> None:
+    def reduce_grads_p2p(self, rs, slot: int, fresh: Optional[bool] = None) -> None:
         """Same result as ``reduce_grads`` through the fused kernel of ``ops/csrc/comm.cu``: the
         flat bf16 gradient already sits in slot ``slot`` of the symmetric buffers ``rs``; raise
         the flags, then pull this rank's slice from every rank, average in fp32 and write (or
-        add to) ``shard.grad`` in one pass."""
+        add to) ``shard.grad`` in one pass. ``fresh`` says that ``shard.grad`` was just created
+        by the caller (on its own stream) and is to be written, not added to."""
         if self.padded > self.total:
             rs.grad_buffer(slot)[self.total:self.padded].zero_()
         rs.signal(slot)
-        fresh = self.shard.grad is None
-        if fresh:
-            self.shard.grad = torch.empty_like(self.shard.data)
+        if fresh is None:
+            fresh = self.shard.grad is None
+            if fresh:
+                self.shard.grad = torch.empty_like(self.shard.data)
         rs.reduce(slot, self.rank * self.shard_size, self.shard_size, self.shard.grad,
                   1.0 / self.world, accumulate=not fresh)
 
@@ -303,6 +305,12 @@ class ShardedDataParallel(nn.Module):
         self._root_buf = (torch.empty(self.root.padded, dtype=self.compute_dtype, device=dev)
                           if self.root else None)
         self._comm_stream = torch.cuda.Stream() if dev.type == "cuda" else None
+        # the gradient reduce-scatter of block i runs on its own stream, under the backward
+        # GEMMs of block i-1 (E2H_RS_OVERLAP=0 keeps it on the compute stream)
+        import os
+        self._rs_stream = (torch.cuda.Stream() if (dev.type == "cuda" and self._rs is not None
+                           and os.environ.get("E2H_RS_OVERLAP", "1") != "0") else None)
+        self._rs_events: Dict[int, "torch.cuda.Event"] = {}
         self._pending: Dict[int, "torch.cuda.Event"] = {}
         self._keep_budget = 0          # bytes of block intermediates kept per forward (0: recompute)
         self._keep_left = 0
@@ -409,6 +417,9 @@ class ShardedDataParallel(nn.Module):
         if self.fused:
             from ..models import fused_block as fb
             slot = self._rs.slot() if self._rs is not None else -1
+            ev = self._rs_events.pop(slot, None)
+            if ev is not None:      # the slot's previous reduce must have read it out
+                torch.cuda.current_stream().wait_event(ev)
             gradbuf = self._rs.grad_buffer(slot) if self._rs is not None else self._grad_buf
             views = unit.grad_views(gradbuf)
             grads = {n.split(".")[-2]: v for n, v in views.items()}
@@ -436,7 +447,18 @@ class ShardedDataParallel(nn.Module):
         if not self.keep_params:
             unit.release()
         if self.fused and self._rs is not None:
-            unit.reduce_grads_p2p(self._rs, slot)
+            if self._rs_stream is None:
+                unit.reduce_grads_p2p(self._rs, slot)
+            else:
+                fresh = unit.shard.grad is None
+                if fresh:           # created on the compute stream, which uses it later
+                    unit.shard.grad = torch.empty_like(unit.shard.data)
+                self._rs_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self._rs_stream):
+                    unit.reduce_grads_p2p(self._rs, slot, fresh=fresh)
+                    done = torch.cuda.Event()
+                    done.record(self._rs_stream)
+                self._rs_events[slot] = done
         else:
             unit.reduce_grads(self._grad_buf)
         return dx
@@ -515,6 +537,9 @@ class ShardedDataParallel(nn.Module):
         """Reduce the root unit's gradients (tensors outside the block stack). With parameter
         shards in peer-readable memory this is also the point where every rank has finished
         reading them for this step: a barrier before the optimizer may overwrite them."""
+        for ev in self._rs_events.values():     # gradient reduces still running on their stream
+            torch.cuda.current_stream().wait_event(ev)
+        self._rs_events.clear()
         if self._lp_bar is not None:
             self._lp_bar.barrier()
         if self.root is None:

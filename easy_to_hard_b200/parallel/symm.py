@@ -521,3 +521,141 @@ class TPReduceSync:
             self.ticket[point:point + 1].data_ptr(), int(self.wait_ms),
             _lib.status_word(out.device).data_ptr(), _lib.stream())
         _lib.check(rc, "tp_gather_logits")
+
+
+class SequenceParallelSync:
+    """The sequence-parallel collectives of training as peer-memory kernels (``e2h_tp_rows`` in
+    ``ops/csrc/tp_reduce.cu``) for activations of ``[T, dim]`` token rows, rank r owning rows
+    ``[r*T/n, (r+1)*T/n)`` (the reference's ``_gather_along_first_dim`` /
+    ``_reduce_scatter_along_first_dim``, models/tp.py:713-777, on its batch-major layout).
+
+    One symmetric allocation holds two partial slots (the row-parallel GEMMs write them in turn
+    and raise flag A of the call site on every rank), one gathered-activation buffer ``xn`` and
+    the flag words of ``n_points`` call sites. A call site must always be used the same way
+    (its flags count its uses); all ranks issue the same sequence of calls.
+
+    * ``reduce(point, slot, residual)``: this rank's rows of the sum of all ranks' partials
+      (+ residual): the reduce-scatter after a row-parallel GEMM.
+    * ``reduce_norm_gather(point, slot, residual, weight)``: the same rows, plus their RMSNorm
+      written into every rank's ``xn``: reduce-scatter, norm and the next all-gather in one pass.
+    * ``gather(point, rows, weight=None)``: all-gather of this rank's rows (optionally of their
+      RMSNorm) into every rank's ``xn``. Nothing before it on the peers orders them against this
+      rank's earlier readers of ``xn``, so the kernel opens with a flag barrier.
+
+    ``xn`` is overwritten by the next gathering call: copy what must live longer. With an
+    NVSwitch multicast mapping the sum is ``multimem.ld_reduce`` and the write-out
+    ``multimem.st``. ``emulated`` builds the ranks of one group inside a process (tests)."""
+
+    def __init__(self, max_tokens: int, dim: int, n_points: int = 8, group=None,
+                 multicast: bool = True, wait_ms: Optional[int] = None,
+                 buf: Optional[SymmetricBuffer] = None):
+        self.T, self.dim, self.n_points = max_tokens, dim, n_points
+        self.part_bytes = (max_tokens * dim * 2 + 255) // 256 * 256
+        self.xn_off = 2 * self.part_bytes
+        self.flag_a_off = 3 * self.part_bytes
+        self.flag_b_off = self.flag_a_off + n_points * 32
+        total = self.flag_b_off + n_points * 32
+        if buf is None:
+            buf = SymmetricBuffer(total, group)
+        self.buf = buf
+        self.world, self.rank = buf.world, buf.rank
+        dev = buf.local.device
+        self.count = torch.zeros(n_points, dtype=torch.int32, device=dev)
+        self.ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
+        self.gemm_ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
+        self.multicast = bool(multicast and buf.multicast_ptr)
+        self.wait_ms = peer_wait_ms() if wait_ms is None else wait_ms
+        self.xn = buf.view(self.xn_off, (max_tokens, dim), torch.bfloat16)
+        self._slots = [buf.view(i * self.part_bytes, (max_tokens, dim), torch.bfloat16)
+                       for i in range(2)]
+        self._next_slot = 0
+
+    @staticmethod
+    def total_bytes(max_tokens: int, dim: int, n_points: int = 8) -> int:
+        return 3 * ((max_tokens * dim * 2 + 255) // 256 * 256) + 2 * n_points * 32
+
+    @classmethod
+    def emulated(cls, max_tokens: int, dim: int, world: int, n_points: int = 8,
+                 wait_ms: int = 50, device="cuda") -> List["SequenceParallelSync"]:
+        bufs = SymmetricBuffer.emulated(cls.total_bytes(max_tokens, dim, n_points), world, device)
+        return [cls(max_tokens, dim, n_points, multicast=False, wait_ms=wait_ms, buf=b)
+                for b in bufs]
+
+    def rows(self, T: int):
+        """(first row, number of rows) this rank owns of a [T, dim] tensor."""
+        r0 = self.rank * T // self.world
+        return r0, (self.rank + 1) * T // self.world - r0
+
+    def _ptrs(self, offset: int):
+        import ctypes as C
+        arr = (C.c_void_p * 8)()
+        for r in range(self.world):
+            arr[r] = self.buf.peer_ptr(r, offset)
+        return arr
+
+    def next_partial(self, T: int):
+        """(slot index, [T, dim] view) of the partial buffer the next row-parallel GEMM writes."""
+        s = self._next_slot
+        self._next_slot ^= 1
+        return s, self._slots[s][:T]
+
+    def signal_ptrs(self, point: int) -> List[int]:
+        off = self.flag_a_off + point * 32 + 4 * self.rank
+        return [self.buf.peer_ptr(r, off) for r in range(self.world)]
+
+    def _run(self, ops: int, point: int, slot: int, h_in, h_out, weight, eps: float, T: int,
+             wait_b: bool = True) -> None:
+        from ..ops import _lib
+        assert T <= self.T and 0 <= point < self.n_points
+        parts = self._ptrs(slot * self.part_bytes)
+        xn = self._ptrs(self.xn_off)
+        mc = 0
+        if self.multicast:
+            mc = 3
+            parts[0] = self.buf.multicast_ptr + slot * self.part_bytes
+            xn[0] = self.buf.multicast_ptr + self.xn_off
+        fa = self._ptrs(self.flag_a_off + point * 32 + 4 * self.rank)
+        fb = self._ptrs(self.flag_b_off + point * 32 + 4 * self.rank)
+        dev = self.buf.local.device
+        rc = _lib.lib().e2h_tp_rows(
+            ops | 16, _lib.ptr(h_in), _lib.ptr(h_out), _lib.ptr(weight), parts, xn, fa, fb,
+            self.buf.view(self.flag_a_off + point * 32, (8,), torch.int32).data_ptr(),
+            self.buf.view(self.flag_b_off + point * 32, (8,), torch.int32).data_ptr(),
+            self.count[point:point + 1].data_ptr(), self.ticket[point:point + 1].data_ptr(),
+            self.world, self.rank, T, self.dim, float(eps), mc, int(wait_b), int(self.wait_ms),
+            _lib.status_word(dev).data_ptr(), _lib.stream())
+        _lib.check(rc, "tp_rows")
+
+    def _own(self, t: Optional[torch.Tensor], T: int):
+        if t is not None:
+            want = (self.rows(T)[1], self.dim)
+            assert t.dtype == torch.bfloat16 and t.is_contiguous() and tuple(t.shape) == want, \
+                (tuple(t.shape), want)
+        return t
+
+    def reduce(self, point: int, slot: int, residual: Optional[torch.Tensor], T: int,
+               out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """[T/n, dim]: this rank's rows of (sum of the partials in ``slot``) + residual."""
+        if out is None:
+            out = torch.empty(self.rows(T)[1], self.dim, dtype=torch.bfloat16,
+                              device=self.buf.local.device)
+        self._run(1, point, slot, self._own(residual, T), self._own(out, T), None, 0.0, T)
+        return out
+
+    def reduce_norm_gather(self, point: int, slot: int, residual: Optional[torch.Tensor],
+                           weight: torch.Tensor, eps: float, T: int, wait_b: bool = True):
+        """(h [T/n, dim] = reduce(...), xn [T, dim] view = every rank's rmsnorm(h) * weight)."""
+        h = torch.empty(self.rows(T)[1], self.dim, dtype=torch.bfloat16,
+                        device=self.buf.local.device)
+        self._run(1 | 2 | 4, point, slot, self._own(residual, T), h, weight, eps, T, wait_b)
+        return h, self.xn[:T]
+
+    def gather(self, point: int, rows: torch.Tensor, T: int,
+               weight: Optional[torch.Tensor] = None, eps: float = 0.0,
+               wait_b: bool = True, barrier: bool = True) -> torch.Tensor:
+        """[T, dim] view of ``xn``: every rank's ``rows`` (their RMSNorm when ``weight`` is
+        given). ``barrier=False`` leaves raising flag A of ``point`` to the caller (the
+        single-process emulation raises all ranks' flags before the first kernel runs)."""
+        ops = 4 | (8 if barrier else 0) | (2 if weight is not None else 0)
+        self._run(ops, point, 0, self._own(rows, T), None, weight, eps, T, wait_b)
+        return self.xn[:T]

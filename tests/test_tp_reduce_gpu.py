@@ -164,3 +164,86 @@ def test_out_of_range_token_id_is_reported_not_dereferenced():
     assert _lib.read_status() == 106
     assert torch.equal(h[:2], table[[3, 31]]) and float(h[2:].abs().max()) == 0.0
     assert float((torch.ones(4, device=dev) * 2).sum()) == 8.0
+
+
+def _signal_ptrs(ptrs, world):
+    from easy_to_hard_b200.ops import _lib
+    arr = (C.c_void_p * 8)()
+    for r, p in enumerate(ptrs):
+        arr[r] = p
+    _lib.check(_lib.lib().e2h_signal_peers(arr, world, _lib.stream()), "signal")
+
+
+@pytest.mark.parametrize("world,T,dim", [(2, 512, 4096), (4, 96, 512), (8, 40, 1024), (2, 7, 256)])
+def test_sequence_parallel_collectives_match_reference(world, T, dim):
+    """Reduce-scatter, reduce-scatter + norm + all-gather, and (norm +) all-gather by token rows,
+    each twice (the flags count uses), emulated ranks on one GPU."""
+    from easy_to_hard_b200.ops import _lib
+    from easy_to_hard_b200.parallel.symm import SequenceParallelSync
+    torch.manual_seed(world + T)
+    dev = "cuda"
+    syncs = SequenceParallelSync.emulated(T, dim, world)
+    w = (torch.randn(dim, device=dev) * 0.5 + 1).bfloat16()
+    _lib.read_status()
+
+    def own(t, r):
+        r0, n = syncs[r].rows(T)
+        return t[r0:r0 + n].contiguous()
+
+    def rms(x):
+        x = x.float()
+        return ((x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + 1e-5)).bfloat16().float()
+                * w.float()).bfloat16()
+
+    for rep in range(2):
+        parts = [(torch.randn(T, dim, device=dev) * 0.3).bfloat16() for _ in range(world)]
+        res = torch.randn(T, dim, device=dev).bfloat16()
+        total = torch.stack([p.float() for p in parts]).sum(0).bfloat16().float()
+        # --- reduce-scatter (+ residual)
+        slots = []
+        for r, s in enumerate(syncs):
+            slot, part = s.next_partial(T)
+            part.copy_(parts[r])
+            slots.append(slot)
+            _signal_ptrs(s.signal_ptrs(2), world)
+        outs = [s.reduce(2, slots[r], own(res, r), T) for r, s in enumerate(syncs)]
+        none = [None] * world
+        torch.cuda.synchronize()
+        want = (res.float() + total).bfloat16()
+        for r in range(world):
+            assert torch.equal(outs[r], own(want, r)), ("reduce", rep, r)
+        # --- reduce-scatter + norm + all-gather
+        for r, s in enumerate(syncs):
+            slot, part = s.next_partial(T)
+            part.copy_(parts[r])
+            slots[r] = slot
+            s.xn.zero_()
+            _signal_ptrs(s.signal_ptrs(1), world)
+        hs = []
+        for r, s in enumerate(syncs):
+            h, _ = s.reduce_norm_gather(1, slots[r], own(res, r), w, 1e-5, T, wait_b=False)
+            hs.append(h)
+        torch.cuda.synchronize()
+        for r, s in enumerate(syncs):
+            assert torch.equal(hs[r], own(want, r))
+            torch.testing.assert_close(s.xn[:T].float(), rms(want).float(), atol=2e-2, rtol=2e-2)
+            assert torch.equal(s.xn[:T], syncs[0].xn[:T])
+        # --- all-gather of rows, plain and normalised
+        for weight in (None, w):
+            pt = 3 if weight is None else 0
+            for s in syncs:
+                s.xn.zero_()
+                _signal_ptrs(s.signal_ptrs(pt), world)
+            for r, s in enumerate(syncs):
+                s.gather(pt, own(res, r), T, weight, 1e-5, wait_b=False, barrier=False)
+            torch.cuda.synchronize()
+            for s in syncs:
+                if weight is None:
+                    assert torch.equal(s.xn[:T], res)
+                else:
+                    torch.testing.assert_close(s.xn[:T].float(), rms(res).float(),
+                                               atol=2e-2, rtol=2e-2)
+        assert _lib.read_status() == 0
+        for s in syncs:
+            assert s.buf.check_canary()
+            assert s.count[:4].tolist() == [rep + 1] * 4
