@@ -37,6 +37,7 @@ class GemmParams(C.Structure):
         ("kcache", C.c_void_p), ("vcache", C.c_void_p),
         ("status", C.c_void_p),
         ("tf", C.c_int),
+        ("th", C.c_int),
         ("kps", C.c_int),
         ("debug_mode", C.c_int),
         ("n_signal", C.c_int),

@@ -8,6 +8,12 @@
 //   * four epilogue warps read the accumulator with tcgen05.ld (warp w owns TMEM lanes
 //     32*(w%4)..+31, i.e. one output feature per thread) and apply the fused epilogue
 //     (plain store, SwiGLU on a dual accumulator, RoPE + KV-cache scatter, residual add, ...);
+//   * the feature tile may be lower than the 128 rows of the instruction (p.th rows, a multiple
+//     of 8): the TMA box then brings only th weight rows per k-block, the MMA still spans 128
+//     lanes (the lanes past th multiply whatever follows in shared memory and are never read
+//     back), and the grid has ceil(F / th) feature tiles. A skinny GEMM is a weight stream, so
+//     what counts is that (nearly) every SM streams an equal share: th is chosen on the host
+//     to make the tile count fit the 148 SMs instead of leaving a third of them idle;
 //   * split-K runs as a thread-block cluster along z: every CTA accumulates its K slice in its
 //     own TMEM, then the cluster does a reduce-scatter over token columns through distributed
 //     shared memory, so each CTA finishes (and runs the epilogue for) its own column slice.
@@ -81,13 +87,20 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   Ctrl* ctrl = reinterpret_cast<Ctrl*>(smem);
   uint8_t* tiles = smem + kCtrlBytes;
   const int stages = p.stages;
-  float* xchg = reinterpret_cast<float*>(tiles + (size_t)stages * p.kps * Plan::stage_bytes);
+  // the stage size follows the tile height (p.th >= 64: the 128-lane MMA then reads at most
+  // 8 KiB past a weight tile, which stays inside the same stage's token tiles)
+  float* xchg = reinterpret_cast<float*>(
+      tiles + (size_t)stages * p.kps *
+                  (((TF == 128) ? p.th : TF) * kTileK * 2 * (DUAL ? 2 : 1) + Plan::b_bytes));
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
   const int S = p.splitk;
   const int rank = (S > 1) ? (int)cluster_ctarank() : 0;
-  const int f0 = blockIdx.x * TF;
+  const int TH = (TF == 128) ? p.th : TF;        // weight rows this CTA streams per k-block
+  const int a_bytes = TH * kTileK * 2;
+  const int stage_bytes = a_bytes * (DUAL ? 2 : 1) + Plan::b_bytes;
+  const int f0 = blockIdx.x * TH;
   const int t0 = blockIdx.y * BN;
 
   const int kb_total = (p.K + kTileK - 1) / kTileK;
@@ -139,7 +152,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     uint32_t ph = 0;
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     const uint32_t tiles0 = smem_u32(tiles);
-    const uint32_t stage_sz = kps * Plan::stage_bytes;
+    const uint32_t stage_sz = kps * stage_bytes;
     int it0 = 0;
     if (early_weights) {
       // the ring is empty: fill every stage's weight part before waiting for the predecessor,
@@ -149,13 +162,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         const uint32_t bar = full0 + 8 * it;
         const uint32_t a_dst = tiles0 + it * stage_sz;
         const int kb = kb_begin + it * kps;
-        mbar_expect_tx(bar, kps * Plan::stage_bytes);
+        mbar_expect_tx(bar, kps * stage_bytes);
         tma_load_3d_hint(a_dst, &tmA, 0, f0, kb, bar, pol_a);
-        if (DUAL) tma_load_3d_hint(a_dst + kps * Plan::a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
+        if (DUAL) tma_load_3d_hint(a_dst + kps * a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
       }
       pdl_wait_prior();
       for (int it = 0; it < n_pre; ++it)
-        tma_load_3d(tiles0 + it * stage_sz + kps * Plan::a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0,
+        tma_load_3d(tiles0 + it * stage_sz + kps * a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0,
                     kb_begin + it * kps, full0 + 8 * it);
       armed = n_pre;
       it0 = n_pre;
@@ -182,31 +195,31 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         // zero filled), k-blocks past this CTA's range are loaded but never multiplied.
         const int kb = kb_begin + it * kps;
         const uint32_t a_dst = st0;
-        mbar_expect_tx(bar, kps * Plan::stage_bytes);
+        mbar_expect_tx(bar, kps * stage_bytes);
         tma_load_3d_hint(a_dst, &tmA, 0, f0, kb, bar, pol_a);
-        if (DUAL) tma_load_3d_hint(a_dst + kps * Plan::a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
-        tma_load_3d(a_dst + kps * Plan::a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0, kb, bar);
+        if (DUAL) tma_load_3d_hint(a_dst + kps * a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
+        tma_load_3d(a_dst + kps * a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0, kb, bar);
         armed = it + 1;
         continue;
       }
-      mbar_expect_tx(bar, kcount * Plan::stage_bytes);
+      mbar_expect_tx(bar, kcount * stage_bytes);
       for (int kk = 0; kk < kcount; ++kk) {
         const int kb = kb_begin + it * kps + kk;
         const int k0 = kb * kTileK;
-        const uint32_t a_dst = st0 + kk * Plan::stage_bytes;
+        const uint32_t a_dst = st0 + kk * stage_bytes;
         if (p.a_tiled) {
           // tile-major weight: tile (feature tile, k block) is one contiguous TF x 64 block
           const int row = (blockIdx.x * kb_total + kb) * TF;
           tma_load_2d_hint(a_dst, &tmA, 0, row, bar, pol_a);
-          if (DUAL) tma_load_2d_hint(a_dst + Plan::a_bytes, &tmA2, 0, row, bar, pol_a);
+          if (DUAL) tma_load_2d_hint(a_dst + a_bytes, &tmA2, 0, row, bar, pol_a);
         } else if (!p.a_mn_major) {
           tma_load_2d_hint(a_dst, &tmA, k0, f0, bar, pol_a);
-          if (DUAL) tma_load_2d_hint(a_dst + Plan::a_bytes, &tmA2, k0, f0, bar, pol_a);
+          if (DUAL) tma_load_2d_hint(a_dst + a_bytes, &tmA2, k0, f0, bar, pol_a);
         } else {
           tma_load_2d(a_dst, &tmA, f0, k0, bar);
           if (TF == 128) tma_load_2d(a_dst + 8192, &tmA, f0 + 64, k0, bar);
         }
-        const uint32_t b_dst = a_dst + Plan::a_bytes * (DUAL ? 2 : 1);
+        const uint32_t b_dst = a_dst + a_bytes * (DUAL ? 2 : 1);
         if (!p.b_mn_major) {
           tma_load_2d(b_dst, &tmB, k0, t0, bar);
         } else {
@@ -240,9 +253,9 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     const uint32_t a_lo0 = sw128_desc_lo(smem_u32(tiles), a_lbo);
     const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles), b_lbo);
     const uint32_t a_ks = a_kstep >> 4, b_ks = b_kstep >> 4;
-    const uint32_t a2_off = (kps * Plan::a_bytes) >> 4;
-    const uint32_t b_off = (kps * Plan::a_bytes * (DUAL ? 2 : 1)) >> 4;
-    const uint32_t stage_step = (kps * Plan::stage_bytes) >> 4;
+    const uint32_t a2_off = (kps * a_bytes) >> 4;
+    const uint32_t b_off = (kps * a_bytes * (DUAL ? 2 : 1)) >> 4;
+    const uint32_t stage_step = (kps * stage_bytes) >> 4;
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     bool ok = true;
     int s = 0;
@@ -276,7 +289,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
                           idesc, accf);
           accf = 1;
         }
-        a_lo += Plan::a_bytes >> 4;
+        a_lo += a_bytes >> 4;
         b_lo += Plan::b_bytes >> 4;
       }
       umma_commit(e_bar);  // stage reusable once these UMMAs have read it
@@ -290,7 +303,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // M = 128: accumulator row r sits on TMEM lane r. M = 64: row r sits on lane
   // (r / 16) * 32 + r % 16, i.e. only the lower 16 lanes of each warp's quarter hold rows.
   const int lane_row = (TF == 128) ? q * 32 + lane : q * 16 + (lane & 15);
-  const bool lane_valid = (TF == 128) || lane < 16;
+  const bool lane_valid = (TF == 128) ? lane_row < TH : lane < 16;
   const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   const int slice = BN / S;               // token columns this CTA finishes
   // issue the TMEM load of 8 token columns of accumulator `a` (0, or 1 = second operand of a
@@ -460,8 +473,9 @@ template <int BN, bool DUAL, int TF>
 static int launch(const E2hGemmParams& p, const CUtensorMap& ta, const CUtensorMap& ta2,
                   const CUtensorMap& tb, cudaStream_t stream) {
   using Plan = SmemPlan<BN, DUAL, TF>;
+  const int th = (TF == 128) ? p.th : TF;
   const size_t smem = 1024 /*alignment slack*/ + kCtrlBytes +
-                      (size_t)p.stages * p.kps * Plan::stage_bytes +
+                      (size_t)p.stages * p.kps * (th * 128 * (DUAL ? 2 : 1) + Plan::b_bytes) +
                       xchg_bytes(BN, p.splitk, DUAL, TF);
   if (smem > 227 * 1024) return -12;
   auto kern = umma_gemm_kernel<BN, DUAL, TF>;
@@ -474,7 +488,7 @@ static int launch(const E2hGemmParams& p, const CUtensorMap& ta, const CUtensorM
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((p.F + TF - 1) / TF, (p.T + BN - 1) / BN, p.splitk);
+  cfg.gridDim = dim3((p.F + th - 1) / th, (p.T + BN - 1) / BN, p.splitk);
   cfg.blockDim = dim3(kThreads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;
@@ -514,11 +528,14 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
   if (((uintptr_t)p.a & 15) || ((uintptr_t)p.b & 15)) return -7;
   if (p.tf != 64 && p.tf != 128) p.tf = 128;
   if (p.tf == 64 && p.bn == 256) return -9;
+  // feature-tile height below the 128 rows of the instruction: K-major weights only
+  if (p.tf != 128 || p.a_mn_major || p.a_tiled || p.th <= 0 || p.th > 128) p.th = p.tf;
+  if (p.th < 64 || (p.th % 8) != 0) return -9;
   if (p.kps < 1) p.kps = 1;
   if (p.kps > 8) p.kps = 8;
   // several k-blocks per stage ride on 3-D boxes: K-major operands with K % 64 == 0 only
   if (p.a_mn_major || p.b_mn_major || p.a_tiled || (p.K % 64) != 0) p.kps = 1;
-  const int stage_bytes = p.kps * (p.tf * 128 * (p.dual ? 2 : 1) + p.bn * 128);
+  const int stage_bytes = p.kps * (p.th * 128 * (p.dual ? 2 : 1) + p.bn * 128);
   const int budget = 227 * 1024 - 2048 - xchg_bytes(p.bn, p.splitk, p.dual, p.tf);
   int max_stages = budget / stage_bytes;
   if (max_stages > kMaxStages) max_stages = kMaxStages;
@@ -533,10 +550,10 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
   int r;
   const long long tiled_rows = (long long)((p.F + p.tf - 1) / p.tf) * kb_total * p.tf;
   if (p.kps > 1) {
-    r = make_map3d(&ta, p.a, p.K, p.F, p.lda, p.tf, p.kps);
+    r = make_map3d(&ta, p.a, p.K, p.F, p.lda, p.th, p.kps);
     if (r) return r;
     if (p.dual) {
-      r = make_map3d(&ta2, p.a2, p.K, p.F, p.lda2, p.tf, p.kps);
+      r = make_map3d(&ta2, p.a2, p.K, p.F, p.lda2, p.th, p.kps);
       if (r) return r;
     } else {
       ta2 = ta;
@@ -547,13 +564,13 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
   if (p.a_tiled)
     r = make_map(&ta, p.a, 64, tiled_rows, 64, p.tf);
   else if (!p.a_mn_major)
-    r = make_map(&ta, p.a, p.K, p.F, p.lda, p.tf);
+    r = make_map(&ta, p.a, p.K, p.F, p.lda, p.th);
   else
     r = make_map(&ta, p.a, p.F, p.K, p.lda, 64);
   if (r) return r;
   if (p.dual) {
     r = p.a_tiled ? make_map(&ta2, p.a2, 64, tiled_rows, 64, p.tf)
-                  : make_map(&ta2, p.a2, p.K, p.F, p.lda2, p.tf);
+                  : make_map(&ta2, p.a2, p.K, p.F, p.lda2, p.th);
     if (r) return r;
   } else {
     ta2 = ta;

@@ -49,6 +49,9 @@ struct E2hGemmParams {
   void* vcache;
   int* status;           // int32 status word (0 = ok)
   int tf;                // features per tile: 128 (default) or 64 (more CTAs for skinny GEMMs)
+  int th;                // e2h_gemm_umma, tf = 128, K-major A: weight rows a CTA streams per
+                         // k-block (64..128, multiple of 8; 0 = tf). The grid has ceil(F / th)
+                         // feature tiles; the MMA still spans 128 lanes
   int kps;               // 64-wide k blocks per pipeline stage (1..8): amortises the barrier
                          // hand-shake when the per-block tensor work is tiny (decode)
   int debug_mode;        // 0; timing experiments only: 1 = skip the MMAs, 2 = skip the loads

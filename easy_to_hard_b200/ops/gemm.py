@@ -73,6 +73,24 @@ def pick_tiles(F: int, T: int, K: int, dual: bool, splitk: Optional[int], bn: Op
     return bn, splitk, stages, tf, kps
 
 
+def pick_stream_tiles(F: int, K: int, bn: int, dual: bool):
+    """Feature-tile height of a skinny K-major GEMM that runs without split-K, or None to keep
+    128-row tiles. The kernel is a weight stream: with 128-row tiles a wide layer leaves SMs
+    idle (11008 features = 86 tiles on 148 SMs), with lower tiles one wave covers nearly all of
+    them (138 tiles of 80 rows). Measured on B200 at 64 tokens (cold L2): the dual w1/w3 GEMM
+    74 -> 54 us; single-accumulator GEMMs, whose tiles already cover 96+ SMs, and anything that
+    needs a split-K cluster (cluster placement, not the SM count, bounds its wave) do not gain,
+    so they keep their tiles."""
+    tiles128 = -(-F // 128)
+    if tiles128 * 2 <= N_SM or tiles128 > N_SM or not dual:
+        return None
+    th = -(-F // N_SM)
+    th = max(64, min(128, -(-th // 8) * 8))
+    if -(-F // th) > N_SM:
+        return None
+    return th
+
+
 def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tensor] = None,
          a2: Optional[torch.Tensor] = None, out2: Optional[torch.Tensor] = None,
          aux: Optional[torch.Tensor] = None, scale: Optional[torch.Tensor] = None,
@@ -82,7 +100,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
          signal=None, ticket: Optional[torch.Tensor] = None,
          persistent: Optional[bool] = None, streamk: Optional[bool] = None, sk_ctas: int = 0,
-         sk_smem_kb: int = 0, pair: Optional[bool] = None) -> None:
+         sk_smem_kb: int = 0, pair: Optional[bool] = None, th: Optional[int] = None) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T]).
     An int8 ``a`` (weight-only quantisation; ``scale`` holds the per-feature scales) streams as
     int8 through the converting kernel for up to 128 tokens and is expanded to a scratch bf16
@@ -131,13 +149,22 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     if use_sk:
         sk_bn = bn if bn in (32, 64, 128) and bn >= T else (32 if T <= 32 else 64 if T <= 64 else 128)
         sk_kps, sk_stages = kps, stages
+    auto_tiles = (splitk is None and tf is None and kps <= 0 and th is None and not w8 and not w4
+                  and not a_mn_major and not b_mn_major and tiled_shape is None and not use_sk
+                  and K % 64 == 0 and STREAM_TILES)
     bn, splitk, stages, tf, kps = pick_tiles(F, T, K, dual, splitk, bn, stages, tf, kps)
+    th = th or 0
+    if auto_tiles and not th and bn <= 128 and T <= bn and splitk == 1:
+        choice = pick_stream_tiles(F, K, bn, dual)
+        if choice is not None:
+            th, kps = choice, 4
     p = GemmParams()
     p.F, p.T, p.K = F, T, K
     p.splitk, p.epi, p.stages = splitk, epi, stages
     p.a_mn_major, p.b_mn_major = int(a_mn_major), int(b_mn_major)
     p.bn, p.dual, p.accumulate, p.pdl = bn, int(dual), int(accumulate), int(pdl)
     p.tf = tf
+    p.th = th
     p.debug_mode = debug_mode
     if signal:
         assert ticket is not None and len(signal) <= 8
@@ -254,6 +281,9 @@ STREAMK_DEFAULT = os.environ.get("E2H_STREAMK", "0") == "1"
 # large GEMMs on CTA pairs (cta_group::2, 256 x 256 tiles): E2H_GEMM_PAIR=0 keeps single-CTA tiles
 PAIR_DEFAULT = os.environ.get("E2H_GEMM_PAIR", "1") != "0"
 STREAMK_SMEM_KB = int(os.environ.get("E2H_STREAMK_SMEM_KB", "0"))   # 0: half an SM per CTA
+# skinny GEMMs: feature-tile height and split-K chosen so that the tiles fill one wave of the SMs
+# (E2H_STREAM_TILES=0 keeps 128-row tiles)
+STREAM_TILES = os.environ.get("E2H_STREAM_TILES", "1") != "0"
 
 
 def _sk_workspace(device):

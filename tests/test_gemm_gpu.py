@@ -166,3 +166,37 @@ def test_cta_pair_tiles_match_fp32(T, F, K):
     assert rel(gemm.linear(x, w, pair=True), gemm.linear(x, w, pair=False).float()) < 1e-2
     torch.cuda.synchronize()
     assert _lib.read_status() == 0
+
+
+@pytest.mark.parametrize("T,F,K", [(64, 12288, 4096), (64, 1536, 4096), (64, 4096, 11008),
+                                   (8, 6144, 2048), (1, 4002, 4096), (33, 1000, 512),
+                                   (64, 4096, 512)])
+def test_stream_tiles_of_lower_height_match_fp32(T, F, K):
+    """Skinny GEMMs pick a feature-tile height between 64 and 128 rows (and a split-K factor)
+    that fills one wave of the SMs; the result is the same product."""
+    from easy_to_hard_b200.ops import gemm
+    th = {12288: 88, 1536: 96, 4096: 112, 6144: 64, 4002: 72, 1000: 80}[F]
+    x, w = _mk(T, K, seed=41), _mk(F, K, scale=0.05, seed=42)
+    y = gemm.linear(x, w, th=th)
+    _check_status()
+    _close(y, x.float() @ w.float().t())
+    res = _mk(T, F, seed=43)
+    y2 = gemm.linear_residual(x, w, res, th=th, splitk=2 if K >= 2048 else 1)
+    _check_status()
+    _close(y2, (x.float() @ w.float().t()).bfloat16().float() + res.float())
+    y32 = gemm.linear(x, w, out_dtype=torch.float32, th=th, kps=2)
+    _check_status()
+    _close(y32, x.float() @ w.float().t())
+
+
+@pytest.mark.parametrize("T,F,K", [(64, 11008, 4096), (64, 1376, 4096), (5, 688, 256)])
+def test_stream_tiles_dual_swiglu(T, F, K):
+    from easy_to_hard_b200.ops import gemm
+    assert gemm.pick_stream_tiles(11008, 4096, 64, True) == 80
+    x = _mk(T, K, seed=44)
+    w1, w3 = _mk(F, K, scale=0.05, seed=45), _mk(F, K, scale=0.05, seed=46)
+    y = gemm.linear_swiglu(x, w1, w3, **({} if F == 11008 else dict(th=72)))
+    _check_status()
+    g = (x.float() @ w1.float().t()).bfloat16().float()
+    u = (x.float() @ w3.float().t()).bfloat16().float()
+    _close(y, torch.nn.functional.silu(g).bfloat16().float() * u)
