@@ -37,6 +37,25 @@ def run(a, wl, ClockSampler):
                               "2 ranks (train_sft.py dereferences the data-parallel group)"}),
                   flush=True)
         return
+    # The reference targets PyTorch 2.2 and imports a private FSDP helper whose signature has
+    # since grown two arguments (models/tp.py:22, :847 there call _get_grad_norm(params,
+    # norm_type)). The helper is wrapped on the PyTorch side so that the old call still works;
+    # the reference's files are untouched.
+    import torch.distributed.fsdp.fully_sharded_data_parallel as _fsdp_mod
+    import inspect
+    if len(inspect.signature(_fsdp_mod._get_grad_norm).parameters) == 4:
+        _orig_norm = _fsdp_mod._get_grad_norm
+
+        def _get_grad_norm_compat(params, norm_type, zero=None, device=None):
+            params = list(params)
+            if device is None:
+                device = (params[0].device if params
+                          else torch.device("cuda", torch.cuda.current_device()))
+            if zero is None:
+                zero = torch.tensor(0.0, device=device)
+            return _orig_norm(params, norm_type, zero, device)
+
+        _fsdp_mod._get_grad_norm = _get_grad_norm_compat
     from models.model import ModelArgs, Transformer
     from models.tp import (apply_tp, clip_grad_norm_, get_data_parallel_world_size,
                            get_model_parallel_group, initialize_model_parallel, maybe_init_dist)
@@ -140,6 +159,8 @@ def run(a, wl, ClockSampler):
             "impl_notes": {"micro_batch": micro, "fsdp": "PyTorch FSDP1 FULL_SHARD" if use_fsdp
                            else "none (data-parallel size 1)",
                            "activation_checkpointing": "every block (the reference's forward)",
+                           "pytorch_compat": "private FSDP helper _get_grad_norm wrapped for the "
+                                             "reference's PyTorch 2.2 call signature",
                            "peak_memory_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
