@@ -72,14 +72,19 @@ class DecodeEngine:
         self.vocab_parallel = bool(getattr(model, "vocab_parallel", False)) and self.tp > 1
         self.vocab_local = model.output.weight.shape[0]
         self.vocab = self.vocab_local * (self.tp if self.vocab_parallel else 1)
-        self.tp_rank = groups.get_model_parallel_rank() if self.tp > 1 else 0
+        # a model sharded over another group than the job's tensor-parallel one names it
+        self.group = getattr(model, "tp_group", None)
+        if self.group is None and self.tp > 1:
+            self.group = groups.get_model_parallel_group()
+        self.tp_rank = getattr(model, "tp_rank", None)
+        if self.tp_rank is None:
+            self.tp_rank = groups.get_model_parallel_rank() if self.tp > 1 else 0
         self.eps = cfg.norm_eps
         if reduce in ("auto", "p2p"):
             reduce = "local"
             if self.tp > 1:     # peer memory reaches every rank of a one-host group only
                 from ..parallel.symm import peer_memory_usable
-                reduce = ("fused" if peer_memory_usable(groups.get_model_parallel_group())
-                          else "nccl")
+                reduce = "fused" if peer_memory_usable(self.group) else "nccl"
         if self.tp == 1:
             reduce = "local"
         # "fused_oneshot" / "fused_twophase" pin the form of the fused reduce (measurements);
@@ -112,7 +117,7 @@ class DecodeEngine:
         if self.reduce == "fused":
             from ..parallel.symm import TPReduceSync
             self.sync = TPReduceSync(
-                B, self.dim, self.n_points, groups.get_model_parallel_group(),
+                B, self.dim, self.n_points, self.group,
                 extra_bytes=B * self.vocab_local * 4 if self.vocab_parallel else 0,
                 oneshot=self.reduce_form)
         if self.sync is not None and not self.sync.oneshot:
@@ -192,7 +197,7 @@ class DecodeEngine:
             part = self.partial[:, :T] if T <= self.B else \
                 torch.empty(1, T, self.dim, dtype=torch.float32, device=self.dev)
             gemm.linear(x, w, out=part[0], scale=sc)
-            dist.all_reduce(part, group=groups.get_model_parallel_group())
+            dist.all_reduce(part, group=self.group)
             Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                       x_out=x_out)
         else:
@@ -348,7 +353,7 @@ class DecodeEngine:
             self.sync_prefill = sp = None
             torch.cuda.empty_cache()
             cap = 1 << max(10, (n_tokens - 1).bit_length())
-            sp = TPReduceSync(cap, self.dim, self.n_points, groups.get_model_parallel_group())
+            sp = TPReduceSync(cap, self.dim, self.n_points, self.group)
             self.sync_prefill = sp
         return sp
 

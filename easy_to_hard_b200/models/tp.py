@@ -119,12 +119,19 @@ def pad_int4_ffn_for_tp(ffn: nn.Module, world: int) -> bool:
     return True
 
 
-def apply_tp(model, requires_grad: bool = False, sequence_parallel: bool = False) -> None:
-    """Shard ``model`` over the tensor-parallel group in place."""
-    world = groups.get_model_parallel_world_size()
+def apply_tp(model, requires_grad: bool = False, sequence_parallel: bool = False,
+             world: Optional[int] = None, rank: Optional[int] = None, group=None) -> None:
+    """Shard ``model`` over the tensor-parallel group in place. ``world`` / ``rank`` / ``group``
+    name another group than the job's tensor-parallel one (the rollout copy of a PPO policy that
+    generates at a wider tensor-parallel degree than it trains at); the model then carries
+    ``tp_group`` / ``tp_rank`` for the decode engine."""
+    explicit = world is not None
+    world = groups.get_model_parallel_world_size() if world is None else world
     if world <= 1:
         return
-    rank = groups.get_model_parallel_rank()
+    rank = groups.get_model_parallel_rank() if rank is None else rank
+    if explicit:
+        model.tp_group, model.tp_rank = group, rank
     cfg = model.config
     assert cfg.n_head % world == 0 and cfg.n_local_heads % world == 0
     model.tp_size = world
@@ -132,14 +139,15 @@ def apply_tp(model, requires_grad: bool = False, sequence_parallel: bool = False
     for blk in model.layers:
         att, ffn = blk.attention, blk.feed_forward
         kv = att.n_local_heads * att.head_dim
-        shard_linear(att.wqkv, "colwise", [att.n_head * att.head_dim, kv, kv], requires_grad)
-        shard_linear(att.wo, "rowwise", None, requires_grad)
+        shard_linear(att.wqkv, "colwise", [att.n_head * att.head_dim, kv, kv], requires_grad,
+                     world, rank)
+        shard_linear(att.wo, "rowwise", None, requires_grad, world, rank)
         att.n_head //= world
         att.n_local_heads //= world
         att.dim //= world
         pad_int4_ffn_for_tp(ffn, world)
         for name, style in (("w1", "colwise"), ("w3", "colwise"), ("w2", "rowwise")):
-            shard_linear(getattr(ffn, name), style, None, requires_grad)
+            shard_linear(getattr(ffn, name), style, None, requires_grad, world, rank)
         for m in (att, ffn):
             m.tp_size, m.sequence_parallel = world, bool(sequence_parallel)
     if model.vocab_parallel:
@@ -150,7 +158,7 @@ def apply_tp(model, requires_grad: bool = False, sequence_parallel: bool = False
         if hasattr(emb, "vocab_start_index"):
             emb.vocab_start_index, emb.vocab_end_index = None, None  # handled by model.embed
         emb.num_embeddings = per
-        shard_linear(model.output, "colwise", None, requires_grad)
+        shard_linear(model.output, "colwise", None, requires_grad, world, rank)
     # the KV cache and attention shapes follow the per-rank head count
     cfg.n_head //= world
     cfg.n_local_heads //= world

@@ -101,6 +101,8 @@ _SIGNATURES = {
     "e2h_tp_embed_partial": [_vp, _vp, _i, _i, _vp, _i, _i, C.POINTER(C.c_void_p), _i, _vp, _vp],
     "e2h_tp_gather_logits": [C.POINTER(C.c_void_p), _i, _i, _i, _vp, _ll, _vp, _vp, _vp, _i, _vp,
                              _vp],
+    "e2h_relayout_pull": [C.POINTER(C.c_void_p), _i, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _ll, _vp,
+                          _vp],
     "e2h_set_pdl": [_i],
     "e2h_set_flag_wait_ms": [_i],
     "e2h_flash_bwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _ll,

@@ -82,9 +82,13 @@ class ShardUnit:
             p.data = torch.empty(0, dtype=compute_dtype, device=dev)
         self.gathered_in: Optional[torch.Tensor] = None
         self.lp_symm = None        # (SymmetricBuffer, byte offset) once shard_lp lives in one
+        self.lp_peers = None       # index of each rank of this group inside that buffer's group
 
-    def move_lp_to(self, sbuf, offset: int) -> None:
-        """Re-home the low-precision shard into symmetric memory (peers read it directly)."""
+    def move_lp_to(self, sbuf, offset: int, peers=None) -> None:
+        """Re-home the low-precision shard into symmetric memory (peers read it directly).
+        ``peers``: for a buffer shared by a larger group than this unit's, the position of each
+        rank of the unit's group inside that larger group."""
+        self.lp_peers = list(peers) if peers is not None else None
         view = sbuf.view(offset, (self.shard_size,), self.compute_dtype)
         view.copy_(self.shard_lp)
         self.shard_lp = view
@@ -105,7 +109,7 @@ class ShardUnit:
             sbuf, off = self.lp_symm
             arr = (C.c_void_p * 8)()
             for r in range(self.world):
-                arr[r] = sbuf.peer_ptr(r, off)
+                arr[r] = sbuf.peer_ptr(self.lp_peers[r] if self.lp_peers else r, off)
             rc = _lib.lib().e2h_p2p_all_gather(arr, self.world, full.data_ptr(),
                                                self.shard_size * 2, None, None, None, 0,
                                                _lib.status_word(full.device).data_ptr(),
@@ -320,6 +324,36 @@ class ShardedDataParallel(nn.Module):
             self.root.gather_into(self._root_buf)   # small: stays gathered
 
     # ------------------------------------------------------------------ plumbing
+    def expose_shards(self, group=None) -> bool:
+        """Make every unit's bf16 shard readable by all ranks of ``group`` (default: the world),
+        not only by this wrapper's data-parallel group: the shards move into one symmetric
+        allocation over ``group``. Needed by ``parallel.relayout.RolloutRelayout``, whose
+        destination ranks pull from shards of other tensor-parallel columns. Collective over
+        ``group``; returns False (nothing changed) where peer memory cannot reach all of it."""
+        from .symm import SymmetricBuffer, peer_memory_usable
+        dev = self.backbone.output.weight.device
+        if dev.type != "cuda" or not dist.is_initialized() or not peer_memory_usable(group):
+            return False
+        if self.compute_dtype != torch.bfloat16:
+            return False
+        sizes = [(u.shard_size * 2 + 255) // 256 * 256 for u in self._all_units()]
+        buf = SymmetricBuffer(sum(sizes), group)
+        big = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+        mine = (dist.get_process_group_ranks(self.group) if self.group is not None
+                else [dist.get_rank()])
+        peers = [big.index(r) for r in mine]
+        off = 0
+        for u, nb in zip(self._all_units(), sizes):
+            u.move_lp_to(buf, off, peers)
+            off += nb
+        self._lp_buf = buf
+        if self._lp_bar is None and self.world > 1:
+            from .symm import P2PChannel
+            self._lp_bar = P2PChannel(256, self.group)
+        torch.cuda.synchronize()
+        dist.barrier(group)
+        return True
+
     def _all_units(self) -> List[ShardUnit]:
         return self.units + ([self.root] if self.root is not None else [])
 

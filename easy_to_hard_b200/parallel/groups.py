@@ -87,8 +87,62 @@ def initialize_model_parallel(model_parallel_size: int, *,
 
 
 def destroy_model_parallel() -> None:
-    global _MESH
+    global _MESH, _ROLLOUT
     _MESH = _Mesh()
+    _ROLLOUT = None
+
+
+_ROLLOUT = None     # (group, ranks, size, rank in group) of the rollout tensor-parallel group
+
+
+def initialize_rollout_parallel(rollout_tp: int) -> None:
+    """Tensor-parallel groups of the PPO rollout engine when generation runs at a wider degree
+    than training (``--rollout_tensor_parallel_size``): runs of ``rollout_tp`` contiguous ranks,
+    each the union of ``rollout_tp / tp`` neighbouring training tensor-parallel groups.
+    Collective over the world (every rank creates every group, in the same order)."""
+    global _ROLLOUT
+    if not dist.is_initialized() or rollout_tp <= 1:
+        _ROLLOUT = None
+        return
+    world, rank = dist.get_world_size(), dist.get_rank()
+    assert world % rollout_tp == 0 and rollout_tp % _MESH.tp_size == 0, \
+        f"rollout TP {rollout_tp} must divide the world ({world}) and be a multiple of the " \
+        f"training TP ({_MESH.tp_size})"
+    if rollout_tp == _MESH.tp_size:
+        _ROLLOUT = (_MESH.tp_group, _MESH.tp_ranks, _MESH.tp_size, _MESH.tp_rank)
+        return
+    for first in range(0, world, rollout_tp):
+        ranks = tuple(range(first, first + rollout_tp))
+        g = dist.new_group(list(ranks))
+        if first <= rank < first + rollout_tp:
+            _ROLLOUT = (g, ranks, rollout_tp, rank - first)
+
+
+def get_rollout_parallel():
+    """(group, ranks, size, rank) of this rank's rollout tensor-parallel group; the training
+    tensor-parallel group when no separate rollout degree was set up."""
+    if _ROLLOUT is not None:
+        return _ROLLOUT
+    return (_MESH.tp_group, _MESH.tp_ranks, _MESH.tp_size, _MESH.tp_rank)
+
+
+class model_parallel_as:
+    """Context in which the tensor-parallel accessors name another group (the rollout group),
+    for code that runs a model sharded over that group through the module path."""
+
+    def __init__(self, group, ranks, size, rank):
+        self.new = (group, tuple(ranks), size, rank)
+
+    def __enter__(self):
+        m = _MESH
+        self.old = (m.tp_group, m.tp_ranks, m.tp_size, m.tp_rank)
+        m.tp_group, m.tp_ranks, m.tp_size, m.tp_rank = self.new
+        return self
+
+    def __exit__(self, *exc):
+        m = _MESH
+        m.tp_group, m.tp_ranks, m.tp_size, m.tp_rank = self.old
+        return False
 
 
 def model_parallel_is_initialized() -> bool:

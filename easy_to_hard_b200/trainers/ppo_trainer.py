@@ -231,6 +231,18 @@ class PPOTrainer(RLTrainer):
             return
         src = self.policy.base_model
         dst = self.unwrapped_policy.base_model
+        if getattr(dst, "tp_group", None) is not None or getattr(self, "_relayout", None):
+            # rollout layout differs from the training layout: every rollout rank pulls the rows
+            # and columns it owns from the training shards over peer memory
+            if getattr(self, "_relayout", None) is None:
+                from ..parallel.relayout import RolloutRelayout
+                assert isinstance(src, ShardedDataParallel), \
+                    "a separate rollout TP degree needs the sharded training wrapper"
+                src.expose_shards(None)
+                self._relayout = RolloutRelayout(src, dst, groups.get_model_parallel_world_size(),
+                                                 groups.get_rollout_parallel()[2])
+            self._relayout.run()
+            return
         if not isinstance(src, ShardedDataParallel):
             sd = {k: v for k, v in src.state_dict().items() if "kv_cache" not in k}
             dst.load_state_dict(sd, strict=False)
@@ -248,6 +260,30 @@ class PPOTrainer(RLTrainer):
                 dst_params[name].data.copy_(full[o:o + n].view(shp))
         # the decode engine reads the rollout model's own tensors (updated in place above), so
         # its captured graphs see the new weights without any refresh
+
+    def _rollout_is_wider(self) -> bool:
+        actor = self.unwrapped_policy
+        return actor is not None and getattr(actor.base_model, "tp_group", None) is not None
+
+    def _respond(self, actor, queries, masks, temperature):
+        """Responses to ``queries`` (identical on the ranks of a training tensor-parallel group).
+        With a wider rollout group the neighbouring training groups pool their queries, the
+        rollout engine generates for all of them at once, and every training group takes its
+        rows back."""
+        if not self._rollout_is_wider():
+            return actor.respond(queries, masks, temperature=temperature)["responses"]
+        group, ranks, size, rank = groups.get_rollout_parallel()
+        tp = groups.get_model_parallel_world_size()
+        n = queries.shape[0]
+
+        def pool(t):
+            every = torch.empty((size * n, *t.shape[1:]), dtype=t.dtype, device=t.device)
+            dist.all_gather_into_tensor(every, t.contiguous(), group=group)
+            return every.view(size // tp, tp, n, *t.shape[1:])[:, 0].reshape(-1, *t.shape[1:])
+        with groups.model_parallel_as(group, ranks, size, rank):
+            out = actor.respond(pool(queries), pool(masks), temperature=temperature)["responses"]
+        mine = rank // tp
+        return out[mine * n:(mine + 1) * n].contiguous()
 
     @staticmethod
     def sub_batched_outputs(model, rollouts_batch: Dict[str, torch.Tensor],
@@ -284,7 +320,7 @@ class PPOTrainer(RLTrainer):
             queries = self.prepare_tp_batch(queries)
             masks = self.prepare_tp_batch(masks)
             answers = self.prepare_tp_batch(answers)
-            responses = actor.respond(queries, masks, temperature=a.temperature)["responses"]
+            responses = self._respond(actor, queries, masks, a.temperature)
             rb = {"queries": queries, "query_attn_masks": masks}
             text_queries = tok.batch_decode(queries, skip_special_tokens=True)
             text_responses = [truncate_after_stop_token(t, tok.eos_token)
@@ -303,7 +339,8 @@ class PPOTrainer(RLTrainer):
         for rb in rollouts:
             seqs = {k: rb[k] for k in ("queries", "query_attn_masks", "responses")}
             n = rb["responses"].shape[0]
-            pol = self.sub_batched_outputs(actor, seqs, n, sub, temperature=a.temperature)
+            scorer = self.policy if self._rollout_is_wider() else actor
+            pol = self.sub_batched_outputs(scorer, seqs, n, sub, temperature=a.temperature)
             rb["logprobs"] = pol["logprobs"].float()
             rb["entropies"] = pol["entropies"].float()
             reg, regw = pol["reg_entropies"].float(), pol["reg_entropies_weight"].float()
@@ -531,7 +568,7 @@ class PPOTrainer(RLTrainer):
         for s in range(0, query_data.size(0), bs):
             queries, masks, answers = common_utils.prepare_inputs(
                 (query_data[s:s + bs], mask_data[s:s + bs], answer_data[s:s + bs]), device=dev)
-            responses = actor.respond(queries, masks, temperature=temperature)["responses"]
+            responses = self._respond(actor, queries, masks, temperature)
             text_queries = tok.batch_decode(queries, skip_special_tokens=True)
             text_responses = [truncate_after_stop_token(t, tok.eos_token)
                               for t in tok.batch_decode(responses, skip_special_tokens=False)]
@@ -613,12 +650,12 @@ def make_models(tokenizer, args, use_tp: bool = True,
             model.train()
         return model
 
-    def generative(trainable, base_path, resume_path=None, bits=16):
+    def generative(trainable, base_path, resume_path=None, bits=16, tp_override=None):
         m = load_model_from_from_ckpt(
             checkpoint_path=base_path, sft_checkpoint_path=resume_path, device=device,
             precision=args.param_dtype if trainable else frozen_dtype, use_tp=use_tp,
             requires_grad=trainable, skip_init=False, vocab_parallel=args.vocab_parallel,
-            sequence_parallel=args.sequence_parallel and trainable)
+            sequence_parallel=args.sequence_parallel and trainable, tp_override=tp_override)
         return finish(m, trainable, bits)
 
     def reward(trainable, base_path, resume_path=None, backbone_only=False, bits=16):
@@ -641,8 +678,13 @@ def make_models(tokenizer, args, use_tp: bool = True,
         args, generative(True, args.base_checkpoint_path,
                          args.policy_checkpoint_path if fresh else None), tokenizer)
     rank0_print("### Creating the rollout copy of the policy ...")
+    # generation may run at a wider tensor-parallel degree than training
+    # (--rollout_tensor_parallel_size): the copy is then sharded over the rollout group
+    rollout = groups.get_rollout_parallel()
+    override = rollout if (use_tp and rollout[2] != groups.get_model_parallel_world_size()) \
+        else None
     unwrapped_policy = rl_model.make_policy_with_base_model(
-        args, generative(False, args.base_checkpoint_path, None), tokenizer)
+        args, generative(False, args.base_checkpoint_path, None, tp_override=override), tokenizer)
     rank0_print("### Creating the value model ...")
     if args.init_value_with_reward:
         base = (args.value_base_checkpoint_path or args.reward_base_checkpoint_path

@@ -165,7 +165,7 @@ class RLTrainer:
         eval_stats = None
         if self.args.eval_steps is not None and step_idx % self.args.eval_steps == 0:
             eval_stats = self.evaluate(step_idx)
-        if step_idx % self.args.save_steps == 0:
+        if self.args.save_steps and step_idx % self.args.save_steps == 0:
             if self.args.save_strategy == "steps":
                 self.save_model(step_idx=step_idx)
             elif self.args.save_strategy != "no":

@@ -349,9 +349,11 @@ def _load_base(model: torch.nn.Module, checkpoint_path: Path) -> None:
 def load_model_from_from_ckpt(checkpoint_path: Path, sft_checkpoint_path: Optional[Path],
                               device, precision: torch.dtype, use_tp: bool, requires_grad: bool,
                               skip_init: bool = False, sequence_parallel: bool = False,
-                              vocab_parallel: bool = False):
+                              vocab_parallel: bool = False, tp_override=None):
     """Policy / SFT model: meta build from the directory name, mmap load, TP sharding, optional
-    warm start from the latest fine-tuned checkpoint (with TP resharding)."""
+    warm start from the latest fine-tuned checkpoint (with TP resharding). ``tp_override``
+    = (group, ranks, size, rank) shards over that group instead of the job's tensor-parallel
+    one (the rollout copy of a PPO policy, ``parallel.groups.get_rollout_parallel``)."""
     checkpoint_path = Path(checkpoint_path)
     _refuse_quantised(checkpoint_path)
     with torch.device("meta"):
@@ -359,7 +361,13 @@ def load_model_from_from_ckpt(checkpoint_path: Path, sft_checkpoint_path: Option
                                       freeze_output=True, freeze_norm=True,
                                       vocab_parallel=vocab_parallel)
     _load_base(model, checkpoint_path)
-    if use_tp:
+    if use_tp and tp_override is not None:
+        g, _, size, rank = tp_override
+        rank0_print(f"Applying tensor parallel ({size} ranks, rollout group) to model ...")
+        apply_tp(model, requires_grad=requires_grad, sequence_parallel=False, world=size,
+                 rank=rank, group=g)
+        skip_init = True      # fine-tuned shards follow the training layout; weights are synced
+    elif use_tp:
         rank0_print("Applying tensor parallel to model ...")
         apply_tp(model, requires_grad=requires_grad, sequence_parallel=sequence_parallel)
     if not skip_init:

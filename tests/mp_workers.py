@@ -330,3 +330,87 @@ def generate_main(rank, world, checkpoint=None, prompt_file=None, output_file=No
                             temperature=0.8, checkpoint_path=Path(checkpoint), compile=False,
                             resume_generation=resume, tensor_parallel_size=tp)
     return {"rank": rank}
+
+
+def rollout_relayout(rank, world, tp=1, rollout_tp=2, device="cpu", generate=True):
+    """Training layout TP=tp x DP=world/tp -> rollout layout TP=rollout_tp: after one SFT step
+    the rollout copy is refreshed from the training shards; returns the largest deviation from
+    the directly re-sharded full weights, and greedy tokens generated at the rollout degree."""
+    from easy_to_hard_b200.models import tp as tpm
+    from easy_to_hard_b200.models.rl_model import generate_tokens
+    from easy_to_hard_b200.parallel import groups
+    from easy_to_hard_b200.parallel.fsdp import ShardedDataParallel
+    from easy_to_hard_b200.parallel.relayout import RolloutRelayout
+    from easy_to_hard_b200.training import SFTStepper
+    from easy_to_hard_b200.utils.checkpoint_utils import merge_tp_checkpoint
+    from easy_to_hard_b200.utils.memory_efficient_adam import MemoryEfficientAdamW
+
+    tpm.initialize_model_parallel(tp)
+    groups.initialize_rollout_parallel(rollout_tp)
+    dev = torch.device(device if device == "cpu" else f"cuda:{rank}")
+    cuda = dev.type == "cuda"
+    dt = torch.bfloat16 if cuda else torch.float32
+    model = tiny_model(dtype=dt).to(dev)
+    heads = (model.config.n_head, model.config.n_local_heads)
+    if tp > 1:
+        tpm.apply_tp(model, requires_grad=True)
+    model.requires_grad_(True)
+    if cuda:
+        for p in model.parameters():
+            p.data = p.data.float()
+    sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group())
+    sdp.train()
+    opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=1e-2, weight_decay=0.0,
+                               optim_dtype=torch.float32, optim_device=dev)
+    ids, labels = (t.to(dev) for t in sft_batch())
+    SFTStepper(sdp, opt).step(ids[:2], labels[:2])
+    # the rollout copy starts from the initial weights and must pick up the trained ones
+    g, ranks, size, rrank = groups.get_rollout_parallel()
+    copy_ = tiny_model(dtype=dt).to(dev)
+    tpm.apply_tp(copy_, world=size, rank=rrank, group=g)
+    copy_ = copy_.to(torch.bfloat16 if cuda else torch.float32).eval()
+    exposed = sdp.expose_shards(None) if cuda else False
+    rl = RolloutRelayout(sdp, copy_, tp, rollout_tp)
+    rl.run()
+    # expectation: the full (TP- and DP-unsharded) trained weights, re-sharded at the rollout degree
+    state = {k: v.cpu() for k, v in sdp.full_state_dict(rank0_only=False).items()
+             if "layers" in k and k.endswith("weight") and "norm" not in k}
+    if tp > 1:
+        shards = [None] * tp
+        dist.all_gather_object(shards, state, group=groups.get_model_parallel_group())
+        state = merge_tp_checkpoint(shards, heads=heads)
+    ref = tiny_model(dtype=torch.float32)
+    ref.load_state_dict({k: v.float() for k, v in state.items()}, strict=False)
+    tpm.apply_tp(ref, world=size, rank=rrank, group=g)
+    got = dict(copy_.named_parameters())
+    got.update(dict(copy_.named_buffers()))
+    worst = 0.0
+    for k, v in ref.state_dict().items():
+        if "layers" in k and k.endswith("weight") and "norm" not in k:
+            worst = max(worst, float((got[k].detach().float().cpu() - v.float()).abs().max()))
+    out = {"max_diff": worst, "pulled": bool(exposed), "bytes": rl.bytes_per_sync}
+    if generate:
+        gq = torch.Generator().manual_seed(31)
+        prompts = torch.randint(0, 1024, (4, 16), generator=gq).to(dev)
+        with groups.model_parallel_as(g, ranks, size, rrank), torch.no_grad():
+            seq = generate_tokens(copy_, prompts, None, 8, temperature=0.0, top_k=None,
+                                  eos_id=None)
+        out["tokens"] = seq.cpu()
+        if cuda:
+            from easy_to_hard_b200.ops import _lib
+            torch.cuda.synchronize()
+            out["status"] = _lib.read_status()
+    return out
+
+
+def ppo_main(rank, world, argv=None):
+    """``train_rl_ppo.main`` as one rank of a gloo job; returns the per-step statistics."""
+    import train_rl_ppo
+    from easy_to_hard_b200.utils.arguments import Arguments
+    from easy_to_hard_b200.utils.hf_argparser import HfArgumentParser
+    args = HfArgumentParser((Arguments,)).parse_args_into_dataclasses(list(argv))[0]
+    history = train_rl_ppo.main(args)
+    return {"steps": len(history),
+            "keys": sorted(history[0].keys()) if history else [],
+            "policy_loss": [float(h["ppo/loss/policy"]) for h in history],
+            "grad_norm": [float(h["ppo/loss/grad_norm_policy"]) for h in history]}

@@ -73,3 +73,16 @@ def test_two_gpu_decode_engine_matches_single_gpu(single_decode, tmp_path, kw):
     # a random tiny bf16 model: a near-tie can flip a greedy token and the rest of that row
     agree = (res[0]["greedy"] == single_decode["greedy"]).float().mean()
     assert float(agree) > 0.8, float(agree)
+
+
+def test_two_gpu_rollout_relayout_pulls_over_peer_memory(tmp_path):
+    """Training layout DP 2 -> rollout layout TP 2 on two GPUs: the rollout copy is refreshed by
+    the pull kernel from the peers' bf16 shards and generates on the decode engine with the
+    rollout group (fused reduce)."""
+    _need_two()
+    res = W.run(W.rollout_relayout, 2, str(tmp_path), tp=1, rollout_tp=2, device="cuda",
+                backend="nccl")
+    for r in res:
+        assert r["pulled"] and r["status"] == 0
+        assert r["max_diff"] < 4e-3, r["max_diff"]        # bf16 copy of the fp32 master weights
+    assert torch.equal(res[0]["tokens"], res[1]["tokens"])

@@ -81,3 +81,40 @@ def test_barrier_and_a_wait_that_runs_out():
     assert _lib.read_status() != 0
     x = torch.ones(8, device="cuda")
     assert float((x + 1).sum()) == 16.0                    # the context still works
+
+
+@pytest.mark.parametrize("dp,rows_src,pitch,row0,col0,rows,cols", [
+    (1, 64, 256, 0, 0, 64, 256), (2, 96, 512, 32, 0, 32, 512), (4, 128, 1024, 0, 256, 128, 256),
+    (8, 344, 256, 86, 0, 86, 256), (4, 256, 688 * 2, 0, 344, 256, 344 - 344 % 8)])
+def test_relayout_pull_kernel_matches_slicing(dp, rows_src, pitch, row0, col0, rows, cols):
+    """The weight re-layout kernel (training shards -> rollout shard) with the data-parallel
+    shards of one flat parameter buffer as separate allocations of one GPU: the pulled block
+    equals the slice of the unsharded matrix."""
+    import ctypes as C
+    from easy_to_hard_b200.ops import _lib
+    torch.manual_seed(dp + rows)
+    flat0 = 1024                                  # the tensor starts inside the flat buffer
+    total = flat0 + rows_src * pitch + 512
+    shard = -(-total // dp // 8) * 8
+    flat = torch.randn(shard * dp, device="cuda").bfloat16()
+    unit_off = 256                                # byte offset of the unit inside each buffer
+    bufs = [torch.zeros(unit_off // 2 + shard, dtype=torch.bfloat16, device="cuda")
+            for _ in range(dp)]
+    for d in range(dp):
+        bufs[d][unit_off // 2:] = flat[d * shard:(d + 1) * shard]
+    arr = (C.c_void_p * 8)()
+    for d in range(dp):
+        arr[d] = bufs[d].data_ptr()
+    dst = torch.zeros(rows, cols, dtype=torch.bfloat16, device="cuda")
+    rc = _lib.lib().e2h_relayout_pull(arr, dp, unit_off, shard, flat0, pitch, row0, col0, rows,
+                                      cols, dst.data_ptr(), _lib.stream())
+    assert rc == 0
+    torch.cuda.synchronize()
+    want = flat[flat0:flat0 + rows_src * pitch].view(rows_src, pitch)[row0:row0 + rows,
+                                                                     col0:col0 + cols]
+    assert torch.equal(dst, want)
+    # a block that leaves the source, or sizes that are not multiples of 8, are refused
+    assert _lib.lib().e2h_relayout_pull(arr, dp, unit_off, shard, flat0, pitch, row0, col0,
+                                        rows, pitch + 8, dst.data_ptr(), _lib.stream()) == -1
+    assert _lib.lib().e2h_relayout_pull(arr, dp, unit_off, shard, flat0 + 4, pitch, row0, col0,
+                                        rows, cols, dst.data_ptr(), _lib.stream()) == -1

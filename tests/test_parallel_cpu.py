@@ -95,3 +95,23 @@ def test_missing_rank_ends_collective_with_error(tmp_path):
     res = W.run(W.rank_never_joins, 2, str(tmp_path), pg_timeout=3)
     assert res[1] == "left"
     assert res[0].startswith("error")
+
+
+def test_rollout_relayout_tp2_dp2_to_tp4(tmp_path):
+    """PPO rollout at a wider tensor-parallel degree than training: four gloo ranks train at
+    TP 2 x DP 2, the rollout copy is sharded TP 4 and refreshed from the training shards; it
+    must equal the trained full weights re-sharded four ways, and all four ranks generate the
+    same tokens with it."""
+    res = W.run(W.rollout_relayout, 4, str(tmp_path), tp=2, rollout_tp=4)
+    for r in res:
+        assert r["max_diff"] < 1e-6, r["max_diff"]
+        assert r["bytes"] > 0
+    for r in res[1:]:
+        assert torch.equal(r["tokens"], res[0]["tokens"])
+
+
+def test_rollout_relayout_dp2_to_tp2(tmp_path):
+    res = W.run(W.rollout_relayout, 2, str(tmp_path), tp=1, rollout_tp=2)
+    for r in res:
+        assert r["max_diff"] < 1e-6
+    assert torch.equal(res[0]["tokens"], res[1]["tokens"])

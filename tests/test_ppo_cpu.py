@@ -126,3 +126,38 @@ def test_train_rl_ppo_end_to_end(workspace, tmp_path):  # noqa: F811
     files = sorted(p.name for p in save.iterdir())
     assert "policy_step_2_rank_0.pt" in files and "value_step_2_rank_0.pt" in files
     assert (save / "rollouts" / "step_1.json").exists()
+
+
+@pytest.mark.parametrize("extra", [
+    ["--tensor_parallel_size", "2", "--vocab_parallel", "True"],
+    ["--tensor_parallel_size", "1", "--rollout_tensor_parallel_size", "2"],
+], ids=["tp2_vocab_parallel", "dp2_rollout_tp2"])
+def test_train_rl_ppo_two_ranks(workspace, tmp_path, extra):  # noqa: F811
+    """One PPO step on two gloo ranks: with the reference recipe's flags (tensor parallel 2,
+    --vocab_parallel True), and with generation at a wider tensor-parallel degree than training
+    (two data-parallel ranks that generate as one TP 2 group; the rollout copy is refreshed from
+    the training shards by the re-layout)."""
+    import mp_workers as W
+    g = torch.Generator().manual_seed(3)
+    data = [{"input": "# Question\n\n" + _sentence(g, 5) + "\n\n# Solution\n\n",
+             "answer": str(i % 7), "gt_answer": str(i % 7), "level": 1 + i % 3}
+            for i in range(16)]
+    (tmp_path / "ppo.json").write_text(json.dumps(data))
+    save = tmp_path / "ppo"
+    ckpt = str(workspace / "tiny-llama" / "model.pth")
+    argv = ["--do_train", "--base_checkpoint_path", ckpt, "--dataset", str(tmp_path / "ppo.json"),
+            "--source_max_len", "24", "--target_max_len", "8", "--total_max_len", "32",
+            "--rollout_batch_size", "8", "--rollout_per_device_batch_size", "4",
+            "--step_batch_size", "8", "--step_per_device_batch_size", "4",
+            "--reward_model_per_device_batch_size", "4", "--per_device_eval_batch_size", "4",
+            "--noptepochs", "1", "--num_train_epochs", "1", "--learning_rate", "1e-4",
+            "--save_strategy", "no", "--save_dir", str(save),
+            "--param_dtype", "fp32", "--optim_dtype", "fp32", "--compute_dtype", "fp32",
+            "--report_to", "none", "--seed", "1", "--kl_coef", "0.01", "--gamma", "1.0",
+            "--lam", "0.95", "--whitening_async_stats", "per_gpu", "--temperature", "1.0",
+            "--max_grad_norm", "1.0", "--stop_token", r"\n\n# Answer\n\n"] + extra
+    res = W.run(W.ppo_main, 2, str(tmp_path / "out"), argv=argv, pg_timeout=300)
+    for r in res:
+        assert r["steps"] >= 1 and "ppo/loss/policy" in r["keys"]
+        assert all(x == x for x in r["policy_loss"])          # no NaN
+    assert res[0]["steps"] == res[1]["steps"]

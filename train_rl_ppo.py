@@ -50,6 +50,8 @@ def main(args: TrainingArguments):
     use_tp = device_id is not None
     if use_tp:
         groups.initialize_model_parallel(args.tensor_parallel_size or dist.get_world_size())
+        if args.rollout_tensor_parallel_size:
+            groups.initialize_rollout_parallel(args.rollout_tensor_parallel_size)
         dist.barrier()
     elif not groups.model_parallel_is_initialized():
         groups.initialize_model_parallel(1)
