@@ -38,15 +38,12 @@ class GemmParams(C.Structure):
         ("status", C.c_void_p),
         ("tf", C.c_int),
         ("th", C.c_int),
+        ("stage_epi", C.c_int),
         ("kps", C.c_int),
-        ("debug_mode", C.c_int),
         ("n_signal", C.c_int),
         ("signal", C.c_void_p * 8),
         ("ticket", C.c_void_p),
         ("a_tiled", C.c_int),
-        ("sk_ctas", C.c_int), ("sk_smem_kb", C.c_int),
-        ("sk_ws", C.c_void_p), ("sk_ws_bytes", C.c_longlong),
-        ("sk_count", C.c_void_p), ("sk_count_len", C.c_int), ("sk_slots", C.c_int),
         ("groupsize", C.c_int), ("qsz", C.c_void_p), ("qsz2", C.c_void_p),
     ]
 
@@ -66,7 +63,6 @@ _SIGNATURES = {
     "e2h_gemm_umma": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_persistent": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_w8": [C.POINTER(GemmParams), _vp],
-    "e2h_gemm_streamk": [C.POINTER(GemmParams), _vp],
     "e2h_gemm_w4": [C.POINTER(GemmParams), _vp],
     "e2h_rmsnorm_fwd": [_vp, _vp, _vp, _i, C.POINTER(C.c_void_p), _i, _vp, _vp, _vp, _vp, _i, _i, _f,
                         _vp, _vp, _vp, _vp, _vp],

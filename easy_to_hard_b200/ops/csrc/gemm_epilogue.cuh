@@ -193,4 +193,132 @@ __device__ __forceinline__ void epilogue8(const E2hGemmParams& p, int f, int t0,
   }
 }
 
+// ---------------------------------------------------------------------------------------------
+// Staged form of the token-major bf16 epilogues (plain store, residual, SwiGLU, RoPE + KV cache)
+// for the one-tile-per-CTA kernel. One thread owns one output feature, so writing its values
+// straight to global memory is 2-byte stores one token row apart: measured on B200, 64 such
+// stores per thread cost 4-9 us per CTA, a quarter of a decode GEMM. Instead every thread puts
+// its values into a [tokens][features] tile in shared memory (stage8) and the four epilogue
+// warps then move the tile with 16-byte accesses, 8 consecutive features of one token per
+// thread (flush_tile): full 32-byte sectors, and the residual is read the same way.
+
+// True when this launch can take the staged path: bf16 token-major output whose rows and tile
+// origins are 16-byte aligned.
+__host__ __device__ inline bool epi_can_stage(const E2hGemmParams& p, int tile_rows) {
+  if (p.epi != E2H_EPI_STORE_BF16 && p.epi != E2H_EPI_RESIDUAL && p.epi != E2H_EPI_SWIGLU &&
+      p.epi != E2H_EPI_ROPE_KV)
+    return false;
+  if ((p.F & 7) || (p.ldo & 7) || (tile_rows & 7)) return false;
+  if (reinterpret_cast<uintptr_t>(p.out) & 15) return false;
+  if (p.epi == E2H_EPI_RESIDUAL && (reinterpret_cast<uintptr_t>(p.aux) & 15)) return false;
+  if (p.epi == E2H_EPI_ROPE_KV &&
+      ((p.head_dim & 7) || (reinterpret_cast<uintptr_t>(p.kcache) & 15) ||
+       (reinterpret_cast<uintptr_t>(p.vcache) & 15)))
+    return false;
+  return true;
+}
+
+// Final bf16 value of 8 consecutive tokens of one feature into the shared tile:
+// tile[(tl + j) * pitch + row] for j < 8 (row < 0: a lane without a feature, nothing is
+// written). The residual of E2H_EPI_RESIDUAL is added by flush_tile. All 32 lanes must call
+// (the RoPE partner value comes from the neighbouring lane).
+template <bool DUAL>
+__device__ __forceinline__ void stage8(const E2hGemmParams& p, int f, int t0, float* v, float* v2,
+                                       __nv_bfloat16* tile, int tl, int pitch, int row) {
+  const bool f_ok = f < p.F;
+  if (p.scale != nullptr) {
+    const float s = f_ok ? p.scale[f] : 0.f;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] *= s;
+    if constexpr (DUAL) {
+      const float s2 = f_ok ? p.scale[p.F + f] : 0.f;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) v2[j] *= s2;
+    }
+  }
+  float y[8];
+  if (p.epi == E2H_EPI_SWIGLU) {
+    if constexpr (DUAL) {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = bf16_round(silu(bf16_round(v[j]))) * bf16_round(v2[j]);
+    }
+  } else if (p.epi == E2H_EPI_ROPE_KV) {
+    const int D = p.head_dim;
+    const int head = f / D;
+    const int d = f - head * D;
+    const bool is_v = head >= p.n_head + p.n_kv;
+    const __nv_bfloat162* freqs2 = static_cast<const __nv_bfloat162*>(p.freqs);
+    const int pos0 = *p.pos_base;
+    int b = t0 / p.sq;
+    int s = t0 - b * p.sq;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int pos = pos0 + s;
+      if (++s == p.sq) s = 0;
+      float cj = 1.f, sj = 0.f;
+      if (!is_v && f_ok && t0 + j < p.T && pos < p.smax) {
+        const __nv_bfloat162 cs = freqs2[(long long)pos * (D / 2) + (d >> 1)];
+        cj = __bfloat162float(cs.x);
+        sj = __bfloat162float(cs.y);
+      }
+      const float x = bf16_round(v[j]);
+      const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
+      y[j] = is_v ? x : ((d & 1) ? (x * cj + partner * sj) : (x * cj - partner * sj));
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) y[j] = v[j];
+  }
+  if (row < 0) return;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) tile[(tl + j) * pitch + row] = __float2bfloat16_rn(y[j]);
+}
+
+// Moves the staged tile (rows = tokens t_first .. t_first + n_tok, columns = features f_first ..
+// f_first + pitch) to its destination, 16 bytes per access. `tid` / `nthreads`: the calling
+// thread's index among the epilogue threads, which have synchronised after stage8.
+__device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bfloat16* tile,
+                                           int pitch, int f_first, int t_first, int n_tok,
+                                           int tid, int nthreads) {
+  const int vpr = pitch >> 3;
+  const int total = n_tok * vpr;
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+  const int pos0 = (p.epi == E2H_EPI_ROPE_KV) ? *p.pos_base : 0;
+  for (int i = tid; i < total; i += nthreads) {
+    const int r = i / vpr;
+    const int fv = (i - r * vpr) << 3;
+    const int t = t_first + r, f = f_first + fv;
+    if (t >= p.T || f >= p.F) continue;
+    uint4 val = *reinterpret_cast<const uint4*>(tile + r * pitch + fv);
+    __nv_bfloat16* dst = out + (long long)t * p.ldo + f;
+    if (p.epi == E2H_EPI_RESIDUAL) {
+      const uint4 res = *reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(p.aux) + (long long)t * p.ldo + f);
+      const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&val);
+      const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&res);
+      uint4 sum;
+      __nv_bfloat162* o = reinterpret_cast<__nv_bfloat162*>(&sum);
+#pragma unroll
+      for (int k = 0; k < 4; ++k)
+        o[k] = __floats2bfloat162_rn(__bfloat162float(a[k].x) + __bfloat162float(b[k].x),
+                                     __bfloat162float(a[k].y) + __bfloat162float(b[k].y));
+      val = sum;
+    } else if (p.epi == E2H_EPI_ROPE_KV) {
+      const int D = p.head_dim;
+      const int head = f / D;
+      const int d = f - head * D;
+      if (head >= p.n_head) {
+        const bool is_k = head < p.n_head + p.n_kv;
+        const int hk = is_k ? head - p.n_head : head - p.n_head - p.n_kv;
+        const int b = t / p.sq;
+        const int pos = pos0 + (t - b * p.sq);
+        if (pos >= p.smax) continue;
+        __nv_bfloat16* cache = static_cast<__nv_bfloat16*>(is_k ? p.kcache : p.vcache);
+        dst = cache + (((long long)b * p.n_kv + hk) * p.smax + pos) * D + d;
+      }
+    }
+    *reinterpret_cast<uint4*>(dst) = val;
+  }
+}
+
 }  // namespace e2h

@@ -139,7 +139,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // weight tiles (weights are never written by a preceding kernel of a PDL chain), the epilogue
   // warps wait before they touch the outputs, the MMA thread touches no global memory.
   pdl_launch_dependents();
-  const bool early_weights = kps > 1 && !p.debug_mode;
+  const bool early_weights = kps > 1;
   if (!(warp == 0 && lane == 0 && early_weights) && !(warp == 1 && lane == 0)) pdl_wait_prior();
 
   if (warp == 0 && lane == 0) {
@@ -182,11 +182,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       if (++s == stages) {
         s = 0;
         ph ^= 1;
-      }
-      if (p.debug_mode == 2 || p.debug_mode == 4) {  // timing experiment: no loads
-        mbar_arrive(bar);
-        armed = it + 1;
-        continue;
       }
       const int kcount = min(kps, n_kb - it * kps);
       if (kps > 1) {
@@ -273,10 +268,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       } else {
         st_lo += stage_step;
       }
-      if (p.debug_mode == 1 || p.debug_mode == 4) {  // timing experiment: no tensor-core work
-        mbar_arrive(e_bar);
-        continue;
-      }
       const int kcount = min(kps, n_kb - it * kps);
       // kps == 1: stage = [A][A2][B]; kps > 1: stage = [A x kps][A2 x kps][B x kps]
       uint32_t a_lo = a_lo0 + cur_lo, b_lo = b_lo0 + cur_lo + b_off;
@@ -355,7 +346,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (S > 1) cluster_sync_all();
 
 
-  if (is_epi && acc_ok && p.debug_mode != 3) {
+  // Staged epilogue: the finished values go through a [tokens][TH] bf16 tile in the (now idle)
+  // pipeline buffers and leave with 16-byte accesses; see gemm_epilogue.cuh.
+  const bool staged = p.stage_epi != 0;
+  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(tiles);
+  if (is_epi && acc_ok) {
     const int c_begin = rank * slice;
     const int f = lane_valid ? f0 + lane_row : p.F;  // rows past F are masked in the epilogue
     for (int c = 0; c < slice; c += 32) {
@@ -393,9 +388,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
             }
           }
         }
-        epilogue8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2);
+        if (staged) {
+          stage8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2, stile,
+                       c + 8 * b, TH, lane_valid ? lane_row : -1);
+        } else {
+          epilogue8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2);
+        }
       }
     }
+  }
+  if (staged && is_epi) {
+    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+    if (acc_ok)
+      flush_tile(p, stile, TH, f0, t0 + rank * slice, slice, threadIdx.x - 64, 128);
   }
 
   if (p.n_signal > 0) __threadfence();  // this thread's output is visible GPU-wide (in L2)
@@ -545,6 +550,12 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
     const int n_it = (kb_total / p.splitk + p.kps - 1) / p.kps;
     if (p.stages > n_it) p.stages = n_it < 1 ? 1 : n_it;
   }
+
+  // staged (shared-memory) epilogue when the output layout allows 16-byte accesses and the
+  // finished tile fits the pipeline buffers it reuses
+  p.stage_epi = (epi_can_stage(p, p.th) &&
+                 (long long)(p.bn / p.splitk) * p.th * 2 <= (long long)p.stages * stage_bytes)
+                    ? 1 : 0;
 
   CUtensorMap ta, ta2, tb;
   int r;

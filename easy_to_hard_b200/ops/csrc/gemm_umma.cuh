@@ -52,21 +52,14 @@ struct E2hGemmParams {
   int th;                // e2h_gemm_umma, tf = 128, K-major A: weight rows a CTA streams per
                          // k-block (64..128, multiple of 8; 0 = tf). The grid has ceil(F / th)
                          // feature tiles; the MMA still spans 128 lanes
+  int stage_epi;         // set by e2h_gemm_umma: the epilogue goes through shared memory and
+                         // leaves with 16-byte accesses (gemm_epilogue.cuh)
   int kps;               // 64-wide k blocks per pipeline stage (1..8): amortises the barrier
                          // hand-shake when the per-block tensor work is tiny (decode)
-  int debug_mode;        // 0; timing experiments only: 1 = skip the MMAs, 2 = skip the loads
   int n_signal;          // > 0: bump signal[0..n_signal) by one when the whole grid is done
   int* signal[8];        // flag words (local or peer-GPU memory), one per tensor-parallel rank
   unsigned int* ticket;  // grid completion counter (local, zero between launches)
   int a_tiled;           // A (and A2) stored tile-major: [F/tf][ceil(K/64)][tf][64], zero padded
-  // work-split ("stream-K") skinny GEMM only
-  int sk_ctas;           // CTAs the (feature tile x k-group) units are divided over (0: one per SM)
-  int sk_smem_kb;        // shared-memory budget per CTA in KiB (0: half an SM, two CTAs resident)
-  float* sk_ws;          // fp32 partial-tile workspace
-  long long sk_ws_bytes; // its capacity
-  unsigned int* sk_count;  // one arrival counter per feature tile, zero between launches
-  int sk_count_len;
-  int sk_slots;          // partial-tile slots reserved per feature tile (set by the entry point)
   // weight-only int4 (e2h_gemm_w4) only
   int groupsize;         // k per (scale, zero) pair
   const void* qsz;       // bf16 [K / groupsize][F][2] (scale, zero) of A
@@ -78,7 +71,6 @@ extern "C" {
 #endif
 // Returns 0 on success, a cudaError_t / negative code otherwise. Launches on `stream`.
 int e2h_gemm_umma(const E2hGemmParams* p, void* stream);
-int e2h_gemm_streamk(const E2hGemmParams* p, void* stream);
 int e2h_gemm_w8(const E2hGemmParams* p, void* stream);
 int e2h_gemm_w4(const E2hGemmParams* p, void* stream);
 #ifdef __cplusplus

@@ -158,7 +158,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   // streams the opening weight tiles (never written by a preceding kernel of the chain) before
   // it waits for the predecessor, every other thread that touches global memory waits first
   pdl_launch_dependents();
-  const bool early_weights = !p.debug_mode;
+  const bool early_weights = true;
   if (!(warp == 0 && lane == 0 && early_weights) && !(warp == 1 && lane == 0)) pdl_wait_prior();
 
   if (warp == 0 && lane == 0) {
@@ -197,11 +197,6 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         ph ^= 1;
       }
       const int kb = kb_begin + it * kW8Kps;
-      if (p.debug_mode & 2) {          // timing experiment without the loads
-        mbar_arrive(bar);
-        armed = it + 1;
-        continue;
-      }
       // boxes are always full size: k-blocks past the matrix are zero filled, k-blocks past this
       // CTA's range are loaded but never multiplied
       mbar_expect_tx(bar, STAGE);
@@ -237,7 +232,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                      kStatusTimeoutFull);
       if (!ok) break;
       tc_fence_after();
-      const int kcount = (p.debug_mode & 4) ? 0 : min(kW8Kps, n_kb - it * kW8Kps);
+      const int kcount = min(kW8Kps, n_kb - it * kW8Kps);
       uint32_t a_lo = a_lo0 + c * (CONV >> 4), b_lo = b_lo0 + st_lo;
       for (int kk = 0; kk < kcount; ++kk) {
 #pragma unroll
@@ -293,7 +288,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                        kStatusTimeoutFull) &&
              mbar_wait(smem_u32(&ctrl->conv_empty[c]), ((it / kW8Conv) & 1) ^ 1, abort_flag,
                        p.status, kStatusTimeoutEmpty);
-      if (ok && !(p.debug_mode & 1)) {   // debug_mode 1: timing experiment without the conversion
+      if (ok) {
         const uint8_t* st = tiles + (size_t)s_cur * STAGE;
         uint8_t* cv = conv + (size_t)c * CONV;
 #pragma unroll
@@ -345,7 +340,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           }
         }
       }
-      if (!(p.debug_mode & 8)) fence_proxy_async_smem();   // generic writes -> tcgen05.mma
+      fence_proxy_async_smem();   // generic writes -> tcgen05.mma
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->conv_full[c]));
     }

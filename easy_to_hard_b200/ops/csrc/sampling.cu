@@ -74,7 +74,13 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
       __syncthreads();
       for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
         const uint32_t key = float_key(row[i]);
-        if ((key & mask) == prefix) atomicAdd(&hist[(key >> shift) & 255u], 1u);
+        if ((key & mask) == prefix) {
+          // logits crowd into a few exponent bins: lanes that hit the same bin elect one of
+          // them to add their count, instead of 32 serialised shared-memory atomics
+          const uint32_t bin = (key >> shift) & 255u;
+          const unsigned peers = __match_any_sync(__activemask(), bin);
+          if ((threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[bin], __popc(peers));
+        }
       }
       __syncthreads();
       if (threadIdx.x == 0) {

@@ -97,10 +97,10 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
          a_mn_major: bool = False, b_mn_major: bool = False, accumulate: bool = False,
          splitk: Optional[int] = None, bn: Optional[int] = None, stages: int = 0,
          rope: Optional[dict] = None, pdl: bool = False, tf: Optional[int] = None,
-         tiled_shape: Optional[tuple] = None, debug_mode: int = 0, kps: int = 0,
+         tiled_shape: Optional[tuple] = None, kps: int = 0,
          signal=None, ticket: Optional[torch.Tensor] = None,
-         persistent: Optional[bool] = None, streamk: Optional[bool] = None, sk_ctas: int = 0,
-         sk_smem_kb: int = 0, pair: Optional[bool] = None, th: Optional[int] = None) -> None:
+         persistent: Optional[bool] = None, pair: Optional[bool] = None,
+         th: Optional[int] = None) -> None:
     """Raw launch. Shapes: a is [F, K] (or [K, F] when a_mn_major), b is [T, K] (or [K, T]).
     An int8 ``a`` (weight-only quantisation; ``scale`` holds the per-feature scales) streams as
     int8 through the converting kernel for up to 128 tokens and is expanded to a scratch bf16
@@ -143,14 +143,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     dual = a2 is not None
     if (w8 or w4) and bn is None:
         bn = 64 if (T <= 64 or dual) else 128
-    sk_ok = (not w8 and not w4 and not a_mn_major and not b_mn_major and tiled_shape is None and T <= 128
-             and K % 64 == 0 and splitk is None and tf is None)
-    use_sk = sk_ok and (streamk if streamk is not None else STREAMK_DEFAULT)
-    if use_sk:
-        sk_bn = bn if bn in (32, 64, 128) and bn >= T else (32 if T <= 32 else 64 if T <= 64 else 128)
-        sk_kps, sk_stages = kps, stages
     auto_tiles = (splitk is None and tf is None and kps <= 0 and th is None and not w8 and not w4
-                  and not a_mn_major and not b_mn_major and tiled_shape is None and not use_sk
+                  and not a_mn_major and not b_mn_major and tiled_shape is None
                   and K % 64 == 0 and STREAM_TILES)
     bn, splitk, stages, tf, kps = pick_tiles(F, T, K, dual, splitk, bn, stages, tf, kps)
     th = th or 0
@@ -165,7 +159,6 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     p.bn, p.dual, p.accumulate, p.pdl = bn, int(dual), int(accumulate), int(pdl)
     p.tf = tf
     p.th = th
-    p.debug_mode = debug_mode
     if signal:
         assert ticket is not None and len(signal) <= 8
         p.n_signal = len(signal)
@@ -212,16 +205,8 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     if w4:
         _lib.check(_lib.lib().e2h_gemm_w4(C.byref(p), _lib.stream()), "e2h_gemm_w4")
         return
-    if use_sk:
-        ws, count = _sk_workspace(a.device)
-        p.bn, p.kps, p.stages, p.splitk, p.tf = sk_bn, sk_kps, sk_stages, 1, 128
-        p.sk_ctas, p.sk_smem_kb = sk_ctas, sk_smem_kb or STREAMK_SMEM_KB
-        p.sk_ws, p.sk_ws_bytes = ws.data_ptr(), ws.numel() * 4
-        p.sk_count, p.sk_count_len = count.data_ptr(), count.numel()
-        _lib.check(_lib.lib().e2h_gemm_streamk(C.byref(p), _lib.stream()), "e2h_gemm_streamk")
-        return
     big = (persistent if persistent is not None else
-           (T > bn and splitk == 1 and tf == 128 and tiled_shape is None and debug_mode == 0
+           (T > bn and splitk == 1 and tf == 128 and tiled_shape is None
             and bn >= 128))
     if big:
         if (pair if pair is not None else PAIR_DEFAULT) and not dual and bn == 256:
@@ -274,30 +259,11 @@ class Int4Weight:
 
 
 _INT8_SCRATCH: dict = {}
-_SK_WS: dict = {}
-# skinny GEMMs (one token tile of at most 128 tokens, K-major operands) may take the work-split
-# kernel (``streamk=True`` per call, or E2H_STREAMK=1 for every eligible call)
-STREAMK_DEFAULT = os.environ.get("E2H_STREAMK", "0") == "1"
 # large GEMMs on CTA pairs (cta_group::2, 256 x 256 tiles): E2H_GEMM_PAIR=0 keeps single-CTA tiles
 PAIR_DEFAULT = os.environ.get("E2H_GEMM_PAIR", "1") != "0"
-STREAMK_SMEM_KB = int(os.environ.get("E2H_STREAMK_SMEM_KB", "0"))   # 0: half an SM per CTA
 # skinny GEMMs: feature-tile height and split-K chosen so that the tiles fill one wave of the SMs
 # (E2H_STREAM_TILES=0 keeps 128-row tiles)
 STREAM_TILES = os.environ.get("E2H_STREAM_TILES", "1") != "0"
-
-
-def _sk_workspace(device):
-    """Per-device partial-tile workspace (fp32, stays in L2) and per-tile arrival counters of the
-    work-split GEMM. One launch at a time may use them: all launches of a device go to one
-    stream (the decode engine's), which orders them."""
-    key = device.index if device.index is not None else torch.cuda.current_device()
-    v = _SK_WS.get(key)
-    if v is None:
-        v = (torch.empty(16 << 20, dtype=torch.float32, device=device),
-             torch.zeros(4096, dtype=torch.int32, device=device))
-        _SK_WS[key] = v
-    return v
-
 
 
 def _expand_int8(w: torch.Tensor, which: int) -> torch.Tensor:
