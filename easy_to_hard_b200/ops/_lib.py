@@ -45,6 +45,7 @@ class GemmParams(C.Structure):
         ("ticket", C.c_void_p),
         ("a_tiled", C.c_int),
         ("groupsize", C.c_int), ("qsz", C.c_void_p), ("qsz2", C.c_void_p),
+        ("phase_clock", C.c_void_p),
     ]
 
 

@@ -61,6 +61,20 @@ def needs_build() -> bool:
     return stamp.read_text().strip() != _digest(list(CSRC.glob("*.cu")) + list(CSRC.glob("*.cuh")))
 
 
+def build_phase_clock() -> Path:
+    """A second library, ``libe2h_b200_phase.so``, with the kernels' phase stamps compiled in
+    (``-DE2H_PHASE_CLOCK``, see ``ptx.cuh``); only the GEMM sources that carry stamps are
+    built. Used by ``bench/gemm_phase_bench.py``; the regular library is not touched."""
+    OUT_DIR.mkdir(parents=True, exist_ok=True)
+    out = OUT_DIR / "libe2h_b200_phase.so"
+    cmd = [_nvcc(), *NVCC_FLAGS, "-DE2H_PHASE_CLOCK", "-shared", "-I", str(CSRC),
+           str(CSRC / "gemm_umma.cu"), "-o", str(out)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"nvcc failed:\n{r.stdout}{r.stderr}")
+    return out
+
+
 def build(force: bool = False, verbose: bool = False) -> Path:
     """Compile and link; returns the path of the shared library. Processes that start together
     (one per GPU under torchrun) take a file lock, so one of them builds and the others find the
@@ -112,5 +126,9 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--phase-clock", action="store_true",
+                    help="also build the library with the kernels' phase stamps compiled in")
     a = ap.parse_args()
     print(build(force=a.force, verbose=a.verbose))
+    if a.phase_clock:
+        print(build_phase_clock())

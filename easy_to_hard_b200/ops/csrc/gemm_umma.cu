@@ -5,9 +5,11 @@
 //   * one thread issues tcgen05.mma (cta_group::1, kind::f16, M = 128, N = 64/128/256) with the
 //     fp32 accumulator in tensor memory; tcgen05.commit releases the stage and, at the end,
 //     signals the epilogue;
-//   * four epilogue warps read the accumulator with tcgen05.ld (warp w owns TMEM lanes
-//     32*(w%4)..+31, i.e. one output feature per thread) and apply the fused epilogue
-//     (plain store, SwiGLU on a dual accumulator, RoPE + KV-cache scatter, residual add, ...);
+//   * eight epilogue warps read the accumulator with tcgen05.ld (warp w owns TMEM lanes
+//     32*(w%4)..+31, i.e. one output feature per thread; the two warps of a lane quarter split
+//     the token columns: the epilogue is bound by instruction issue, one warp per scheduler
+//     leaves it half idle) and apply the fused epilogue (plain store, SwiGLU on a dual
+//     accumulator, RoPE + KV-cache scatter, residual add, ...);
 //   * the feature tile may be lower than the 128 rows of the instruction (p.th rows, a multiple
 //     of 8): the TMA box then brings only th weight rows per k-block, the MMA still spans 128
 //     lanes (the lanes past th multiply whatever follows in shared memory and are never read
@@ -38,7 +40,7 @@ namespace e2h {
 constexpr int kTileF = 128;       // default features per tile = TMEM lanes = UMMA M (64 also supported)
 constexpr int kTileK = 64;        // 64 bf16 = one 128-byte swizzle row
 constexpr int kUmmaK = 16;
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;        // producer warp, MMA warp, eight epilogue warps
 constexpr int kMaxStages = 12;
 constexpr int kCtrlBytes = 1024;  // barriers + tmem holder + abort flag live in the first KiB
 
@@ -111,6 +113,10 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   const int n_it = (n_kb + kps - 1) / kps;
 
   volatile int* abort_flag = &ctrl->abort_flag;
+  // phase stamps (E2H_PHASE_CLOCK builds): 0 entry, 1 set-up done, 2 producer past its wait for
+  // the predecessor, 3 all loads issued, 4 first stage landed, 5 all MMAs issued, 6 accumulator
+  // ready, 7 split-K exchange done, 8 values staged, 9 tile written, 10 tensor memory freed
+  if (threadIdx.x == 0) E2H_PHASE(p.phase_clock, 0);
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
@@ -133,6 +139,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = ctrl->tmem_base;
   if (S > 1) cluster_sync_all();  // every CTA of the cluster is resident before DSMEM traffic
+  if (threadIdx.x == 0) E2H_PHASE(p.phase_clock, 1);
 
   // Programmatic dependent launch: the next kernel may begin its prologue now. This kernel's
   // own wait for its predecessor is taken per role: the producer first streams the opening
@@ -167,6 +174,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
         if (DUAL) tma_load_3d_hint(a_dst + kps * a_bytes, &tmA2, 0, f0, kb, bar, pol_a);
       }
       pdl_wait_prior();
+      E2H_PHASE(p.phase_clock, 2);
       for (int it = 0; it < n_pre; ++it)
         tma_load_3d(tiles0 + it * stage_sz + kps * a_bytes * (DUAL ? 2 : 1), &tmB, 0, t0,
                     kb_begin + it * kps, full0 + 8 * it);
@@ -225,6 +233,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
       armed = it + 1;
     }
+    E2H_PHASE(p.phase_clock, 3);
     // On an abort, wait (bounded) for the copies already in flight into this CTA's smem.
     if (*abort_flag) {
       for (int it = (armed > stages ? armed - stages : 0); it < armed; ++it) {
@@ -258,6 +267,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     for (int it = 0; it < n_it && ok; ++it) {
       ok = mbar_wait(full0 + 8 * s, ph, abort_flag, p.status, kStatusTimeoutFull);
       if (!ok) break;
+      if (it == 0) E2H_PHASE(p.phase_clock, 4);
       tc_fence_after();
       const uint32_t e_bar = empty0 + 8 * s;
       const uint32_t cur_lo = st_lo;
@@ -286,11 +296,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       umma_commit(e_bar);  // stage reusable once these UMMAs have read it
     }
     umma_commit(smem_u32(&ctrl->tmem_full));
+    E2H_PHASE(p.phase_clock, 5);
   }
 
   // ---------------- epilogue warps: accumulator -> registers ----------------
   const bool is_epi = warp >= 2;
   const int q = warp & 3;                 // TMEM lane quarter this warp may touch
+  const int half = (warp - 2) >> 2;       // which of the two warps of that quarter (epilogue)
   // M = 128: accumulator row r sits on TMEM lane r. M = 64: row r sits on lane
   // (r / 16) * 32 + r % 16, i.e. only the lower 16 lanes of each warp's quarter hold rows.
   const int lane_row = (TF == 128) ? q * 32 + lane : q * 16 + (lane & 15);
@@ -313,12 +325,13 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     ok_i = __shfl_sync(0xffffffffu, ok_i, 0);
     acc_ok = ok_i != 0;
     tc_fence_after();
+    if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 6);
     if (S > 1 && acc_ok && n_kb > 0) {
       // reduce-scatter: send the columns owned by each peer into that peer's exchange buffer
       for (int peer = 0; peer < S; ++peer) {
         if (peer == rank) continue;
         const int slot = rank < peer ? rank : rank - 1;
-        for (int c = 0; c < slice; c += 8) {
+        for (int c = 8 * half; c < slice; c += 16) {   // the quarter's two warps alternate
           float v[8];
           issue_acc(0, peer * slice + c, v);
           tmem_ld_wait();
@@ -344,6 +357,7 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
   __syncwarp();
   if (S > 1) cluster_sync_all();
+  if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 7);
 
 
   // Staged epilogue: the finished values go through a [tokens][TH] bf16 tile in the (now idle)
@@ -353,9 +367,23 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   if (is_epi && acc_ok) {
     const int c_begin = rank * slice;
     const int f = lane_valid ? f0 + lane_row : p.F;  // rows past F are masked in the epilogue
-    for (int c = 0; c < slice; c += 32) {
+    // columns of this warp: with 64 or more, alternate groups of 32; with fewer, the first /
+    // second half of the 8-column units
+    const int units = slice >> 3;
+    int c_first, c_last, c_step;
+    if (units >= 8) {
+      c_first = 32 * half;
+      c_last = slice;
+      c_step = 64;
+    } else {
+      const int lo = units == 1 ? 1 : units >> 1;   // units of warp 0 (warp 1 takes the rest)
+      c_first = half ? 8 * lo : 0;
+      c_last = half ? slice : 8 * lo;
+      c_step = 64;
+    }
+    for (int c = c_first; c < c_last; c += c_step) {
       // up to 32 columns per round trip to tensor memory
-      const int nb = (slice - c) >= 32 ? 4 : (slice - c) / 8;
+      const int nb = (c_last - c) >= 32 ? 4 : (c_last - c) / 8;
       float v[32], v2[DUAL ? 32 : 1];
       if (n_kb > 0) {
 #pragma unroll
@@ -397,16 +425,19 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
       }
     }
   }
+  if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 8);
   if (staged && is_epi) {
-    asm volatile("bar.sync 1, 128;" ::: "memory");   // the four epilogue warps
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
     if (acc_ok)
-      flush_tile(p, stile, TH, f0, t0 + rank * slice, slice, threadIdx.x - 64, 128);
+      flush_tile(p, stile, TH, f0, t0 + rank * slice, slice, threadIdx.x - 64, 256);
   }
 
+  if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 9);
   if (p.n_signal > 0) __threadfence();  // this thread's output is visible GPU-wide (in L2)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, Plan::tmem_cols);
+  if (threadIdx.x == 32) E2H_PHASE(p.phase_clock, 10);
   if (p.n_signal > 0 && threadIdx.x == 0) {
     // the last CTA of the grid tells every tensor-parallel peer that this rank's partial
     // output is complete: one release-add on the flag word it owns in each peer's memory

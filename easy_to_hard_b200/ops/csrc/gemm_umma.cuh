@@ -64,6 +64,7 @@ struct E2hGemmParams {
   int groupsize;         // k per (scale, zero) pair
   const void* qsz;       // bf16 [K / groupsize][F][2] (scale, zero) of A
   const void* qsz2;      // same for A2 of a dual GEMM
+  unsigned long long* phase_clock;  // builds with E2H_PHASE_CLOCK only: 16 time stamps per CTA
 };
 
 #ifdef __cplusplus

@@ -420,6 +420,26 @@ __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status
   return true;
 }
 
+// ---- phase clock (kernel development) -------------------------------------------------------------
+// With -DE2H_PHASE_CLOCK (python -m easy_to_hard_b200.ops.build --phase-clock builds a second
+// library with it) a kernel stamps the nanosecond global timer at the phases of its pipeline
+// into a caller-given buffer, 16 slots per CTA; without the flag the macro is empty.
+#ifdef E2H_PHASE_CLOCK
+__device__ __forceinline__ unsigned long long e2h_globaltimer() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define E2H_PHASE(buf, k)                                                                   \
+  do {                                                                                      \
+    if ((buf) != nullptr)                                                                   \
+      (buf)[(size_t)(blockIdx.x + gridDim.x * (blockIdx.y + gridDim.y * blockIdx.z)) * 16 + \
+            (k)] = e2h_globaltimer();                                                       \
+  } while (0)
+#else
+#define E2H_PHASE(buf, k) do { } while (0)
+#endif
+
 // ---- small numeric helpers ------------------------------------------------------------------------
 __device__ __forceinline__ float bf16_round(float x) {
   return __bfloat162float(__float2bfloat16_rn(x));
