@@ -176,34 +176,102 @@ def run_ours(a):
 
     tp.initialize_model_parallel(world)
     cfg = ModelArgs.from_name(MODEL)
-    torch.manual_seed(0)
+
+    def build(reduce, vocab_parallel):
+        """Model (random init, sharded over the N ranks) and its decode engine."""
+        c = ModelArgs.from_name(MODEL)
+        torch.manual_seed(0)
+        with torch.device("cuda"):
+            model = Transformer(c, freeze_tok_embeddings=True, freeze_output=True,
+                                freeze_norm=True,
+                                vocab_parallel=vocab_parallel).to(torch.bfloat16)
+        g = torch.Generator(device="cuda").manual_seed(1234)
+        for name, t in list(model.named_parameters()) + list(model.named_buffers()):
+            if t.dim() == 2:
+                t.data.normal_(0.0, 0.02, generator=g)
+        if world > 1:
+            tp.apply_tp(model)
+            torch.cuda.empty_cache()
+        if a.quant == "int8":
+            from easy_to_hard_b200.models.quantize import WeightOnlyInt8QuantHandler
+            model = WeightOnlyInt8QuantHandler(model).convert_for_runtime_on_the_fly()
+        elif a.quant == "int4":
+            from easy_to_hard_b200.models.quantize import WeightOnlyInt4QuantHandler
+            h = WeightOnlyInt4QuantHandler(model, groupsize=128, inner_k_tiles=8)
+            sd = h.create_quantized_state_dict()
+            model = h.convert_for_runtime()
+            model.load_state_dict(sd, strict=False)
+            del sd
+        if a.quant != "none":
+            model = model.cuda()
+            torch.cuda.empty_cache()
+        model.eval()
+        return model, get_engine(model, BATCH, PROMPT + NEW, reduce=reduce, use_pdl=bool(a.pdl))
+
+    def all_ok(flag: bool) -> bool:
+        if world == 1:
+            return flag
+        import torch.distributed as dist
+        t = torch.tensor([int(flag)], device="cuda")
+        dist.all_reduce(t, op=dist.ReduceOp.MIN)
+        return bool(t.item())
+
+    def ranks_agree(model, probe):
+        """Every rank must produce the same tokens (same seed, bit-identical activations) and
+        no device-side wait may have run out. Every rank reaches every collective here whatever
+        happened on it, so a failure on one rank is seen by all."""
+        digest, err = -1, None
+        try:
+            seq, _ = api.generate(model, probe, None, 24, temperature=TEMPERATURE, top_k=TOP_K,
+                                  seed=123)
+            torch.cuda.synchronize()
+            if _lib.read_status() == 0:
+                digest = int((seq.long() * torch.arange(1, seq.shape[1] + 1,
+                                                        device="cuda")).sum())
+        except Exception as e:  # noqa: BLE001
+            err = e
+        ok = digest >= 0
+        if world > 1:
+            import torch.distributed as dist
+            mine = torch.tensor([digest], dtype=torch.int64, device="cuda")
+            every = [torch.zeros_like(mine) for _ in range(world)]
+            dist.all_gather(every, mine)
+            ok = ok and all(int(e) == int(every[0]) for e in every)
+        return all_ok(ok), err
+
+    def bring_up(reduce, vocab_parallel):
+        """(model, engine, None) when the strategy works on every rank, else (None, None, why)."""
+        model = eng = err = None
+        try:
+            model, eng = build(reduce, vocab_parallel)
+        except Exception as e:  # noqa: BLE001
+            err = e
+        if not all_ok(err is None):
+            return None, None, f"build: {type(err).__name__}: {str(err)[:160]}" if err \
+                else "build failed on a peer"
+        ok, err = ranks_agree(model, probe)
+        if not ok:
+            return None, None, (f"{type(err).__name__}: {str(err)[:160]}" if err else
+                                "ranks disagree or a device-side wait timed out")
+        return model, eng, None
+
     vocab_parallel = bool(a.vocab_parallel) and world > 1 and a.reduce != "nccl" \
         and cfg.vocab_size % world == 0
-    with torch.device("cuda"):
-        model = Transformer(cfg, freeze_tok_embeddings=True, freeze_output=True,
-                            freeze_norm=True, vocab_parallel=vocab_parallel).to(torch.bfloat16)
-    g = torch.Generator(device="cuda").manual_seed(1234)
-    for name, t in list(model.named_parameters()) + list(model.named_buffers()):
-        if t.dim() == 2:
-            t.data.normal_(0.0, 0.02, generator=g)
-    if world > 1:
-        tp.apply_tp(model)
+    probe = torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), dtype=torch.int32,
+                          generator=torch.Generator().manual_seed(99)).cuda()
+    fallback = None
+    model, eng, why = bring_up(a.reduce, vocab_parallel)
+    if model is None:
+        if world == 1 or a.reduce == "nccl":
+            raise RuntimeError(why)
+        # a peer-memory path that does not come up on this box: the library baseline between
+        # our kernels instead, and the bench line says so
+        fallback = why
         torch.cuda.empty_cache()
-    if a.quant == "int8":
-        from easy_to_hard_b200.models.quantize import WeightOnlyInt8QuantHandler
-        model = WeightOnlyInt8QuantHandler(model).convert_for_runtime_on_the_fly()
-    elif a.quant == "int4":
-        from easy_to_hard_b200.models.quantize import WeightOnlyInt4QuantHandler
-        h = WeightOnlyInt4QuantHandler(model, groupsize=128, inner_k_tiles=8)
-        sd = h.create_quantized_state_dict()
-        model = h.convert_for_runtime()
-        model.load_state_dict(sd, strict=False)
-        del sd
-    if a.quant != "none":
-        model = model.cuda()
-        torch.cuda.empty_cache()
-    model.eval()
-    eng = get_engine(model, BATCH, PROMPT + NEW, reduce=a.reduce, use_pdl=bool(a.pdl))
+        _lib.read_status()
+        model, eng, why = bring_up("nccl", False)
+        if model is None:
+            raise RuntimeError(f"the NCCL strategy failed as well: {why}")
 
     gen = torch.Generator().manual_seed(7)
     host_prompts = [torch.randint(0, cfg.vocab_size, (BATCH, PROMPT), generator=gen,
@@ -231,16 +299,7 @@ def run_ours(a):
     clocks = sampler.stop() if rank == 0 else None
     ms_e2e = timed(lambda i: step_e2e(a.warmup + i), a.steps)
     status = _lib.read_status()
-    # every rank must have produced the same tokens (same seed, bit-identical activations)
-    agree = True
-    if world > 1:
-        import torch.distributed as dist
-        seq, _ = api.generate(model, dev_prompts[0], None, 32, temperature=TEMPERATURE,
-                              top_k=TOP_K, seed=123)
-        digest = (seq.long() * torch.arange(1, seq.shape[1] + 1, device="cuda")).sum().reshape(1)
-        every = [torch.zeros_like(digest) for _ in range(world)]
-        dist.all_gather(every, digest)
-        agree = all(int(e) == int(every[0]) for e in every)
+    agree = ranks_agree(model, probe)[0] if world > 1 else True
     toks = BATCH * NEW * a.steps
     key = next(iter(eng._graphs)) if eng._graphs else None
     launches = (eng.prefill_launches + (NEW - 1) * eng.decode_launches(key)) * a.steps
@@ -256,10 +315,13 @@ def run_ours(a):
             "config": decode_config(world, a.quant),
             "impl_notes": {"tp_reduce": eng.reduce,
                            "tp_reduce_form": (None if eng.sync is None else
-                                              "one-shot pull" if eng.sync.oneshot else
+                                              "one-shot pull" + (" (multimem.ld_reduce)"
+                                                                 if eng.sync.multicast else "")
+                                              if eng.sync.oneshot else
                                               "two-phase" + (" (multimem)" if eng.sync.multicast
                                                              else "")),
                            "vocab_parallel": eng.vocab_parallel, "ranks_agree": agree,
+                           "fell_back_to_nccl_because": fallback,
                            "kv_cache": "sized to prompt + new tokens, only the live range is read"},
             "clocks": clocks,
             "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",

@@ -15,6 +15,7 @@ per iteration, max over ranks. Strategies:
     local          no cross-rank traffic at all (GEMM + residual + norm): the floor
     nccl           fp32 partial, dist.all_reduce, norm kernel (the baseline)
     oneshot        tp_reduce.cu, every rank pulls all partials (plain peer loads)
+    oneshot_mc     the same with one multimem.ld_reduce per 16 bytes (the switch adds)
     twophase       tp_reduce.cu, reduce-scatter + all-gather by rows (plain peer loads/stores)
     twophase_mc    the same through the NVSwitch (multimem.ld_reduce / multimem.st), if mapped
 
@@ -69,10 +70,16 @@ def main():
 
     def make(strategy):
         sync = None
-        if strategy in ("oneshot", "twophase", "twophase_mc"):
-            sync = TPReduceSync(B, dim, n_points, tp_group, oneshot=strategy == "oneshot",
-                                multicast=strategy == "twophase_mc")
-            if strategy == "twophase_mc" and not sync.multicast:
+        if strategy in ("oneshot", "oneshot_mc", "twophase", "twophase_mc"):
+            sync = TPReduceSync(B, dim, n_points + 1, tp_group,
+                                oneshot=strategy.startswith("oneshot"),
+                                multicast=strategy.endswith("_mc"))
+            if strategy.endswith("_mc") and not sync.multicast:
+                return None, None
+            if strategy == "oneshot_mc" and not sync.check_multimem_consistency(tp_group, 64):
+                if rank == 0:
+                    print(json.dumps({"strategy": strategy, "ranks_got_different_bits": True}),
+                          flush=True)
                 return None, None
         xn = sync.xn[:B] if (sync is not None and not sync.oneshot) else xn_local
 
@@ -100,7 +107,7 @@ def main():
         torch.cuda.synchronize()
 
     results = {}
-    for strategy in ("local", "nccl", "oneshot", "twophase", "twophase_mc"):
+    for strategy in ("local", "nccl", "oneshot", "oneshot_mc", "twophase", "twophase_mc"):
         if world == 1 and strategy != "local":
             continue
         body, sync = make(strategy)
@@ -139,7 +146,7 @@ def main():
         status = _lib.read_status()
         results[strategy] = us
         part = B * dim * 2
-        nvlink = {"local": 0, "nccl": None, "oneshot": (world - 1) * part,
+        nvlink = {"local": 0, "nccl": None, "oneshot": (world - 1) * part, "oneshot_mc": part,
                   "twophase": 2 * (world - 1) * part // world,
                   "twophase_mc": 2 * part // world}[strategy]
         if rank == 0:

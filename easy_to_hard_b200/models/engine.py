@@ -120,6 +120,9 @@ class DecodeEngine:
                 B, self.dim, self.n_points, self.group,
                 extra_bytes=B * self.vocab_local * 4 if self.vocab_parallel else 0,
                 oneshot=self.reduce_form)
+            # the switch-side sum must give every rank the same bits, or their samplers drift
+            # apart: checked once, plain peer loads otherwise
+            self.sync.check_multimem_consistency(self.group)
         if self.sync is not None and not self.sync.oneshot:
             self.xn = self.sync.xn
         else:

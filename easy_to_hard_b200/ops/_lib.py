@@ -78,8 +78,8 @@ _SIGNATURES = {
     "e2h_adamw": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _vp],
     "e2h_sqnorm": [_vp, _ll, _i, _vp, _vp],
     "e2h_clip_coef": [_vp, _f, _vp, _vp, _vp],
-    "e2h_reward_head": [_vp, _ll, _vp, _vp, _ll, _i, _i, _i, _f, _vp, _i, _vp, _vp, _i, _vp, _vp, _vp,
-                        _vp],
+    "e2h_reward_head": [_vp, _ll, _vp, _vp, _ll, _i, _i, _i, _f, _vp, _i, _ll, _vp, _vp, _i, _vp, _vp,
+                        _vp, _vp],
     "e2h_gae": [_vp, _vp, _vp, _vp, _i, _i, _f, _f, _vp],
     "e2h_flash_fwd": [_vp, _ll, _ll, _ll, _vp, _vp, _ll, _ll, _ll, _vp, _ll, _ll, _ll, _vp, _vp,
                       _i, _i, _i, _i, _i, _i, _f, _vp, _vp],

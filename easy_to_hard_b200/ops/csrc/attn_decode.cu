@@ -57,9 +57,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 
   pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
   pdl_wait_prior();
-  const int pos = *pos_ptr;              // index of the newest token (already in the cache)
+  int pos = *pos_ptr;                    // index of the newest token (already in the cache)
+  // positions come from device memory: keep every cache row that is read inside the allocation
+  if (pos >= smax) pos = smax - 1;
+  if (pos < 0) pos = 0;
   int start = left_pad ? left_pad[b] : 0;
   if (start > pos) start = pos;
+  if (start < 0) start = 0;
   // keys of this split
   const int total = pos - start + 1;
   const int per = (total + n_split - 1) / n_split;

@@ -25,7 +25,8 @@ __global__ void __launch_bounds__(256)
 reward_head_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
                    const __nv_bfloat16* __restrict__ w_norm, const __nv_bfloat16* __restrict__ head,
                    long long ldh, int dim, int k0, int klen, float eps,
-                   const int* __restrict__ index, int n_rows, float* __restrict__ dots,
+                   const int* __restrict__ index, int n_rows, long long x_rows,
+                   float* __restrict__ dots,
                    float* __restrict__ reward, int finalize, const float* __restrict__ labels,
                    const float* __restrict__ weights, float* __restrict__ loss_acc) {
   pdl_wait_prior();
@@ -33,7 +34,9 @@ reward_head_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
   const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (warp >= n_rows) return;
-  const long long src_row = index ? (long long)index[warp] : (long long)warp;
+  long long src_row = index ? (long long)index[warp] : (long long)warp;
+  // gathered rows come from device memory: a row outside x reads row 0 instead of faulting
+  if (src_row < 0 || src_row >= x_rows) src_row = 0;
   const __nv_bfloat16* xr = x + src_row * ldx;
   const int nvec = dim >> 3;                       // 16-byte vectors in the row
   uint4 v[NV];
@@ -107,11 +110,12 @@ reward_head_kernel(const __nv_bfloat16* __restrict__ x, long long ldx,
 // loss_acc: fp32 [2] (+= weighted BCE sum, += weight sum). Returns 0 or a cudaError_t / negative.
 extern "C" int e2h_reward_head(const void* x, long long ldx, const void* w_norm, const void* head,
                                long long ldh, int dim, int k0, int klen, float eps,
-                               const void* index, int n_rows, void* dots, void* reward,
-                               int finalize, const void* labels, const void* weights,
-                               void* loss_acc, void* stream_v) {
+                               const void* index, int n_rows, long long x_rows, void* dots,
+                               void* reward, int finalize, const void* labels,
+                               const void* weights, void* loss_acc, void* stream_v) {
   using namespace e2h;
   if (n_rows <= 0) return 0;
+  if (x_rows < 1 || (index == nullptr && n_rows > x_rows)) return -1;
   if (dim <= 0 || (dim % 8) || (k0 % 8) || (klen % 8) || k0 < 0 || k0 + klen > dim) return -1;
   if ((ldx % 8) || (ldh % 8) || ((uintptr_t)x & 15) || ((uintptr_t)head & 15) ||
       ((uintptr_t)w_norm & 15))
@@ -123,7 +127,7 @@ extern "C" int e2h_reward_head(const void* x, long long ldx, const void* w_norm,
                      static_cast<const __nv_bfloat16*>(x), ldx,                                  \
                      static_cast<const __nv_bfloat16*>(w_norm),                                  \
                      static_cast<const __nv_bfloat16*>(head), ldh, dim, k0, klen, eps,           \
-                     static_cast<const int*>(index), n_rows, static_cast<float*>(dots),          \
+                     static_cast<const int*>(index), n_rows, x_rows, static_cast<float*>(dots),  \
                      static_cast<float*>(reward), finalize, static_cast<const float*>(labels),   \
                      static_cast<const float*>(weights), static_cast<float*>(loss_acc))
   if (dim <= 2 * 256) E2H_RH(2);

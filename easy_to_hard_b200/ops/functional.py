@@ -245,7 +245,7 @@ def reward_head(x: torch.Tensor, norm_weight: torch.Tensor, head_weight: torch.T
     nw = norm_weight.to(torch.bfloat16).contiguous()
     rc = _lib.lib().e2h_reward_head(
         x.data_ptr(), x.stride(0), nw.data_ptr(), head_weight.data_ptr(), head_weight.stride(0),
-        dim, k0, klen, eps, _lib.ptr(index), n, dots.data_ptr(), reward.data_ptr(),
+        dim, k0, klen, eps, _lib.ptr(index), n, x.shape[0], dots.data_ptr(), reward.data_ptr(),
         int(finalize), _lib.ptr(labels), _lib.ptr(weights), _lib.ptr(acc), _s())
     _lib.check(rc, "reward_head")
     return reward, dots, acc

@@ -411,7 +411,7 @@ class TPReduceSync:
         self.count = torch.zeros(n_points, dtype=torch.int32, device=dev)
         self.ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
         self.gemm_ticket = torch.zeros(n_points, dtype=torch.int32, device=dev)
-        self.multicast = bool(multicast and buf.multicast_ptr and not self.oneshot)
+        self.multicast = bool(multicast and buf.multicast_ptr)
         self.wait_ms = wait_ms
         self._regions = [buf.view(0, (max_tokens, dim), torch.bfloat16),
                          buf.view(self.part_bytes, (max_tokens, dim), torch.bfloat16)]
@@ -480,6 +480,9 @@ class TPReduceSync:
             assert xn_out is not None and xn_out.stride(0) == self.dim
             xn = (C.c_void_p * 8)()
             xn[0] = xn_out.data_ptr()
+            if self.multicast:      # one multimem.ld_reduce per 16 bytes instead of n peer loads
+                mc = 1
+                parts[0] = self.buf.multicast_ptr + self._region(point) * self.part_bytes
         else:
             xn = self._ptrs(self.part_bytes)
             fb = self._ptrs(self.flag_b_off + point * 32 + 4 * self.rank)
@@ -494,6 +497,45 @@ class TPReduceSync:
             self.world, self.rank, T, self.dim, float(eps), mc, int(wait_b), int(self.oneshot),
             int(self.wait_ms), _lib.status_word(h_out.device).data_ptr(), _lib.stream())
         _lib.check(rc, "tp_reduce_norm")
+
+    def check_multimem_consistency(self, group=None, trials: int = 16) -> bool:
+        """One-shot form with ``multimem.ld_reduce``: every rank asks the switch for the sum of
+        the same addresses on its own, and the ranks only stay in lock step if they all get the
+        same bits. This runs the reduce on random partials and compares the results of all ranks
+        bit for bit; on any difference the multicast form is switched off for this object (the
+        plain loads sum in rank order and are identical by construction). Collective; uses the
+        last call site, whose counters advance by ``trials`` on every rank."""
+        if not (self.oneshot and self.multicast and self.world > 1):
+            return True
+        dev = self.buf.local.device
+        point = self.n_points - 1
+        T = min(self.T, 64)
+        g = torch.Generator(device=dev).manual_seed(1000 + self.rank)
+        w = torch.ones(self.dim, dtype=torch.bfloat16, device=dev)
+        h = torch.zeros(T, self.dim, dtype=torch.bfloat16, device=dev)
+        xn = torch.empty(T, self.dim, dtype=torch.bfloat16, device=dev)
+        same = True
+        import ctypes as C
+        from ..ops import _lib
+        for _ in range(trials):
+            part = self.partial_out(point, T)
+            part.copy_((torch.randn(T, self.dim, device=dev, generator=g) * 3).to(torch.bfloat16))
+            arr = (C.c_void_p * 8)()
+            for r, p in enumerate(self.flag_a_remote(point)):
+                arr[r] = p
+            _lib.check(_lib.lib().e2h_signal_peers(arr, self.world, _lib.stream()), "signal")
+            out = torch.empty(T, self.dim, dtype=torch.bfloat16, device=dev)
+            self.reduce_norm(point, h, out, w, 1e-5, T, xn_out=xn)
+            every = [torch.empty_like(out) for _ in range(self.world)]
+            dist.all_gather(every, out, group=group)
+            same = same and all(torch.equal(e, every[0]) for e in every)
+            dist.barrier(group)      # nobody overwrites its partial while a peer still reads it
+        flag = torch.tensor([int(same)], device=dev)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN, group=group)
+        same = bool(flag.item())
+        if not same:
+            self.multicast = False
+        return same
 
     def embed_partial(self, point: int, tokens: torch.Tensor, table: torch.Tensor, v0: int) -> None:
         """partial[t] = table[tokens[t] - v0] for ids this rank's vocabulary shard holds, zeros
