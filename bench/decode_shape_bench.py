@@ -34,6 +34,14 @@ def main():
     ap.add_argument("--layers", type=int, default=32)
     ap.add_argument("--pdl", type=int, default=1)
     ap.add_argument("--hbm_gbs", type=float, default=6453.1)
+    ap.add_argument("--gemm_phases", default="", help="run the GEMMs of the step through the "
+                    "phase-stamp build (python -m easy_to_hard_b200.ops.build --phase-clock) and "
+                    "write, per GEMM launch of one replayed step, the phase times (median over "
+                    "its CTAs) on one clock; diagnosis only, the printed step time is then that "
+                    "of the stamping build")
+    ap.add_argument("--timeline", default="", help="write the kernels of one replayed step "
+                    "(name, start, duration from the profiler's activity records) to this file; "
+                    "for reading the gaps between kernels, never for a reported time")
     a = ap.parse_args()
     from easy_to_hard_b200.models.model import ModelArgs, Transformer
     from easy_to_hard_b200.models import tp as tpm
@@ -41,6 +49,7 @@ def main():
     from easy_to_hard_b200.ops import _lib
 
     torch.cuda.set_device(0)
+    stamp_log = use_phase_build() if a.gemm_phases else None
     cfg = ModelArgs.from_name("llemma-7b-32016")
     cfg.n_layer = a.layers
     with torch.device("cuda"):
@@ -70,7 +79,11 @@ def main():
     prompt = torch.randint(0, cfg.vocab_size, (B, a.ctx), device="cuda", dtype=torch.int32)
     eng.prefill(prompt, None, 0.7, 50, 0, -1)
     key = (B, 0.7, 50, -1)
+    if stamp_log is not None:
+        stamp_log["on"] = True
     graph, launches = eng._graph_for(key)
+    if stamp_log is not None:
+        stamp_log["on"] = False
     for _ in range(a.steps):          # warm-up, also moves the context forward
         graph.replay()
     torch.cuda.synchronize()
@@ -93,7 +106,119 @@ def main():
         "kv_mb": round(kv_bytes / 1e6, 1), "hbm_floor_us": round(floor_us, 1),
         "fraction_of_measured_copy_bw": round(floor_us / us, 3),
         "status": _lib.read_status()}), flush=True)
+    if a.timeline:
+        write_timeline(graph, a.timeline)
+    if stamp_log is not None:
+        write_gemm_phases(graph, stamp_log, a.gemm_phases)
     eng._graphs.clear()
+
+
+PHASES = ["entry", "set-up done", "producer past wait", "loads issued", "first stage landed",
+          "MMAs issued", "accumulator ready", "exchange done", "values staged", "tile written",
+          "tmem freed"]
+STAMP_SLOTS = 256 * 16          # int64 words per launch: 16 per CTA
+
+
+def use_phase_build():
+    """Route e2h_gemm_umma through the stamping build; while ``log["on"]`` every launch gets its
+    own region of the stamp buffer (the launches recorded into the decode graph)."""
+    import ctypes as C
+    from easy_to_hard_b200.ops import _lib, build
+    from easy_to_hard_b200.ops._lib import GemmParams
+    path = build.OUT_DIR / "libe2h_b200_phase.so"
+    if not path.exists():
+        path = build.build_phase_clock()
+    phase = C.CDLL(str(path))
+    phase.e2h_gemm_umma.argtypes = [C.POINTER(GemmParams), C.c_void_p]
+    phase.e2h_gemm_umma.restype = C.c_int
+    log = {"on": False, "launches": [],
+           "stamps": torch.zeros(512 * STAMP_SLOTS, dtype=torch.int64, device="cuda")}
+    real = _lib.lib()
+
+    class WithStamps:
+        def __getattr__(self, name):
+            return getattr(real, name)
+
+        def e2h_gemm_umma(self, pref, stream):
+            p = pref._obj
+            if log["on"] and len(log["launches"]) < 512:
+                p.phase_clock = log["stamps"].data_ptr() + len(log["launches"]) * STAMP_SLOTS * 8
+                log["launches"].append((p.F, p.K, p.splitk, p.dual))
+            return phase.e2h_gemm_umma(C.byref(p), stream)
+
+    shim = WithStamps()
+    _lib.lib = lambda: shim
+    return log
+
+
+def write_gemm_phases(graph, log, path):
+    log["stamps"].zero_()
+    torch.cuda.synchronize()
+    graph.replay()
+    torch.cuda.synchronize()
+    t = log["stamps"].view(-1, STAMP_SLOTS // 16, 16).cpu()
+    base = None
+    with open(path, "w") as f:
+        f.write("# us since the first GEMM CTA of the step started; median over the CTAs of the "
+                "launch (entry: min / median / max)\n")
+        f.write("# F K splitk dual CTAs | " + " | ".join(PHASES) + "\n")
+        for i, (F, K, sk, dual) in enumerate(log["launches"]):
+            rows = t[i]
+            rows = rows[rows[:, 0] > 0]
+            if not len(rows):
+                continue
+            if base is None:
+                base = int(rows[:, 0].min())
+            cells = []
+            for k in range(len(PHASES)):
+                col = rows[:, k]
+                col = (col[col > 0] - base).float() / 1e3
+                if not len(col):
+                    cells.append("-")
+                elif k == 0:
+                    cells.append(f"{float(col.min()):.1f}/{float(col.median()):.1f}/"
+                                 f"{float(col.max()):.1f}")
+                else:
+                    cells.append(f"{float(col.median()):.1f}")
+            last = (rows[:, 1:].max() - base).item() / 1e3
+            f.write(f"{F} {K} {sk} {dual} {len(rows)} | " + " | ".join(cells)
+                    + f" | end {last:.1f}\n")
+
+
+def write_timeline(graph, path):
+    """Kernel start / duration records of the second of two replays, and their summary: time
+    covered by at least one kernel, idle time between kernels, overlap."""
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA, ProfilerActivity.CPU]) as prof:
+        graph.replay()
+        torch.cuda.synchronize()
+        graph.replay()
+        torch.cuda.synchronize()
+    ev = sorted(((e.time_range.start, e.time_range.end, e.name) for e in prof.events()
+                 if e.device_type == torch.autograd.DeviceType.CUDA and "memcpy" not in e.name.lower()
+                 and "memset" not in e.name.lower()), key=lambda x: x[0])
+    ev = ev[len(ev) // 2:]
+    t0 = ev[0][0]
+    covered, idle, end = 0.0, 0.0, ev[0][0]
+    per = {}
+    for s_, e_, name in ev:
+        if s_ > end:
+            idle += s_ - end
+            covered += e_ - s_
+        else:
+            covered += max(0.0, e_ - end)
+        end = max(end, e_)
+        short = name.split("(")[0].split("<")[0].split("::")[-1]
+        d = per.setdefault(short, [0, 0.0])
+        d[0] += 1
+        d[1] += e_ - s_
+    with open(path, "w") as f:
+        f.write(json.dumps({"kernels": len(ev), "span_us": round(end - t0, 1),
+                            "covered_us": round(covered, 1), "idle_us": round(idle, 1),
+                            "by_kernel": {k: [v[0], round(v[1], 1)] for k, v in per.items()}})
+                + "\n")
+        for s_, e_, name in ev:
+            f.write(f"{s_ - t0:10.2f} {e_ - s_:8.2f} {name[:90]}\n")
 
 
 if __name__ == "__main__":

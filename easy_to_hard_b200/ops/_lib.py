@@ -74,7 +74,8 @@ _SIGNATURES = {
     "e2h_swiglu_fwd": [_vp, _vp, _vp, _ll, _vp],
     "e2h_swiglu_bwd": [_vp, _vp, _vp, _vp, _vp, _ll, _vp],
     "e2h_rope": [_vp, _vp, _vp, _vp, _i, _i, _i, _ll, _i, _vp],
-    "e2h_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp],
+    "e2h_attn_decode": [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _f, _i, _vp, _vp,
+                        _vp],
     "e2h_adamw": [_vp, _vp, _vp, _vp, _ll, _i, _i, _i, _f, _f, _f, _f, _f, _f, _f, _vp, _vp, _vp],
     "e2h_sqnorm": [_vp, _ll, _i, _vp, _vp],
     "e2h_clip_coef": [_vp, _f, _vp, _vp, _vp],

@@ -4,27 +4,62 @@
 // (models/model.py:121-129, 343-344); this kernel reads only the live range
 // [left_pad[b], pos] of each row, which is what makes batched decode HBM-bound on the
 // useful bytes only. It is a pure streaming kernel (every K/V byte is used once per q head),
-// so it runs on the CUDA cores with 16-byte loads; grouped-query attention reuses each K/V
-// row for the G query heads that share it.
+// so the arithmetic runs on the CUDA cores; grouped-query attention reuses each K/V row for the
+// G query heads that share it.
 //
 // Layouts: q [B, n_head*D] bf16, caches [max_batch, n_kv, smax, D] bf16, out [B, n_head*D] bf16.
-// Grid: (n_kv * B, n_split). Each CTA has 4 warps; a half-warp (16 lanes x 8 elements) owns
-// one key row at a time. With n_split > 1 the CTA writes (m, l, acc) partials; they are merged
-// either by the last CTA of each (sequence, kv head) to arrive (a ticket counter per pair, no
-// extra launch) or, when no ticket array is given, by a second kernel.
+//
+// Work split (with more pairs than resident CTAs; with fewer, every pair is simply cut into
+// equal parts, one per CTA): the live keys of every (sequence, kv head) are cut into chunks of
+// 32 keys, all chunks are numbered (sequence, head, chunk) and every CTA takes one contiguous run of that
+// numbering, the same number of chunks for all: the CTAs finish together whatever the batch,
+// the head count and the context lengths are, and a CTA pays the latency of its first loads
+// once, not once per (sequence, head). A producer thread streams the K and V rows of the run
+// with bulk copies (cp.async.bulk: the rows of one head are contiguous in the cache) through a
+// ring of shared-memory stages and runs ahead across (sequence, head) boundaries; four
+// consumer warps follow, a half-warp (16 lanes x 8 elements) owning one key row at a time.
+// A (sequence, head) that lies inside one run is written straight to `out`; one that is cut by
+// run boundaries leaves (m, l, acc) partials, and the last of its CTAs to arrive (a ticket
+// counter per pair) merges them in CTA order, so the result does not depend on timing.
+//
+// All mbarrier waits are bounded; a time-out sets the status word (codes 101 / 102), the CTA stops
+// issuing copies, waits (bounded) for the ones in flight, still reaches its barriers and returns.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <float.h>
 #include <stdint.h>
+#include <stdlib.h>
+#include <mutex>
 
 #include "launch.cuh"
 #include "ptx.cuh"
 
 namespace e2h {
 
-constexpr int kWarps = 4;
+constexpr int kWarps = 4;           // consumer warps; warp kWarps is the producer
 constexpr int kSlots = kWarps * 2;  // half-warps per CTA
-constexpr int kKeysPerIter = 4;     // independent 16-byte loads in flight per lane
+constexpr int kKeysPerIter = 4;     // key rows per half-warp and stage
+constexpr int kChunk = kSlots * kKeysPerIter;   // key rows per pipeline stage
+constexpr int kAttnMaxStages = 8;
+constexpr int kAttnThreads = (kWarps + 1) * 32;
+constexpr int kAttnMaxParts = 8;    // CTAs that may share one (sequence, kv head)
+constexpr int kAttnMaxB = 512;      // sequences per launch (longer batches go in slices)
+
+__host__ __device__ constexpr int attn_smem_bytes(int D, int stages) {
+  return stages * 2 * kChunk * D * 2;
+}
+
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void* src, uint32_t bytes,
+                                             uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+      ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void consumers_sync() {
+  asm volatile("bar.sync 1, %0;" ::"n"(kWarps * 32) : "memory");
+}
 
 __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
   const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
@@ -35,25 +70,46 @@ __device__ __forceinline__ void unpack8(const uint4& r, float* f) {
   }
 }
 
+// Position in the numbering of all chunks: sequence b, kv head hk, chunk ch of nc, first live key.
+struct AttnWalk {
+  int b, hk, ch, nc, start;
+};
+
 // D = 16 * 8 * R : each lane of the half-warp holds R groups of 8 consecutive elements.
 template <int D, int G>
-__global__ void __launch_bounds__(kWarps * 32)
+__global__ void __launch_bounds__(kAttnThreads)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
                    const __nv_bfloat16* __restrict__ vcache, __nv_bfloat16* __restrict__ out,
                    float* __restrict__ partial, const int* __restrict__ pos_ptr,
-                   const int* __restrict__ left_pad, int n_head, int n_kv, int smax, float scale,
-                   int n_split, unsigned int* __restrict__ tickets) {
+                   const int* __restrict__ left_pad, int B, int n_head, int n_kv, int smax,
+                   float scale, int max_parts, int fixed_parts,
+                   unsigned int* __restrict__ tickets, int* __restrict__ status, int stages) {
   constexpr int R = D / 128 > 0 ? D / 128 : 1;       // 8-element groups per lane (D=128 -> 1)
   constexpr int LPK = D >= 128 ? 16 : D / 8;          // lanes per key row
+  constexpr int kTileBytes = kChunk * D * 2;          // K (or V) rows of one stage
   static_assert(D == 64 || D == 128 || D == 256, "head_dim must be 64, 128 or 256");
-  const int b = blockIdx.x / n_kv;
-  const int hk = blockIdx.x - b * n_kv;
-  const int split = blockIdx.y;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int half = lane / 16;            // which key of the pair this half-warp handles
   const int hl = lane & 15;
   const bool lane_active = hl < LPK;
   const int slot = warp * 2 + half;
+
+  extern __shared__ __align__(128) uint8_t attn_smem[];
+  __shared__ uint64_t bar_full[kAttnMaxStages], bar_empty[kAttnMaxStages];
+  __shared__ int abort_word, nc_max_s, is_last_s;
+  __shared__ int pre[kAttnMaxB + 1];     // chunks of the sequences before b (per kv head)
+  __shared__ int first_key[kAttnMaxB];
+  __shared__ float sm_m[kSlots][G], sm_l[kSlots][G];
+  __shared__ float sm_acc[kSlots][G][D];
+  volatile int* abort_flag = &abort_word;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < stages; ++s) {
+      mbar_init(smem_u32(&bar_full[s]), 1);
+      mbar_init(smem_u32(&bar_empty[s]), kWarps);
+    }
+    abort_word = 0;
+    fence_mbar_init();
+  }
 
   pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
   pdl_wait_prior();
@@ -61,223 +117,400 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   // positions come from device memory: keep every cache row that is read inside the allocation
   if (pos >= smax) pos = smax - 1;
   if (pos < 0) pos = 0;
-  int start = left_pad ? left_pad[b] : 0;
-  if (start > pos) start = pos;
-  if (start < 0) start = 0;
-  // keys of this split
-  const int total = pos - start + 1;
-  const int per = (total + n_split - 1) / n_split;
-  const int k_begin = start + split * per;
-  const int k_end = min(pos + 1, k_begin + per);
-
-  float qv[G][R][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const int h = hk * G + g;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (lane_active) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(
-            q + ((long long)b * n_head + h) * D + (r * LPK + hl) * 8);
-        unpack8(raw, qv[g][r]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qv[g][r][i] *= scale;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qv[g][r][i] = 0.f;
+  if (warp == 0) {
+    int run = 0, ncm = 0;
+    for (int b0 = 0; b0 < B; b0 += 32) {
+      const int b = b0 + lane;
+      int nc = 0, start = 0;
+      if (b < B) {
+        start = left_pad ? left_pad[b] : 0;
+        if (start > pos) start = pos;
+        if (start < 0) start = 0;
+        nc = (pos - start + kChunk) / kChunk;       // ceil((pos - start + 1) / kChunk) >= 1
+        first_key[b] = start;
       }
+      int x = nc;
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int y = __shfl_up_sync(0xffffffffu, x, o);
+        if (lane >= o) x += y;
+      }
+      if (b < B) pre[b + 1] = run + x;
+      run += __shfl_sync(0xffffffffu, x, 31);
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) nc = max(nc, __shfl_xor_sync(0xffffffffu, nc, o));
+      ncm = max(ncm, nc);
+    }
+    if (lane == 0) {
+      pre[0] = 0;
+      nc_max_s = ncm;
     }
   }
-  float m[G], l[G], acc[G][R][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -FLT_MAX;
-    l[g] = 0.f;
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[g][r][i] = 0.f;
+  __syncthreads();
+
+  // this CTA's run [lo, hi) of the chunk numbering
+  const int total = pre[B] * n_kv;
+  int per, lo, hi;
+  if (fixed_parts > 0) {
+    // fewer pairs than resident CTAs: every pair is cut into fixed_parts equal parts, one per
+    // CTA (fixed_parts == 1: one CTA per pair, nothing to merge)
+    const int item = blockIdx.x / fixed_parts, part = blockIdx.x - item * fixed_parts;
+    const int b = item / n_kv, hk = item - b * n_kv;
+    const int nc = pre[b + 1] - pre[b];
+    per = (nc + fixed_parts - 1) / fixed_parts;
+    lo = pre[b] * n_kv + hk * nc + part * per;
+    hi = min(pre[b] * n_kv + (hk + 1) * nc, lo + per);
+  } else {
+    per = (total + (int)gridDim.x - 1) / (int)gridDim.x;
+    per = max(per, (nc_max_s + max_parts - 2) / (max_parts - 1));   // at most max_parts CTAs per pair
+    lo = min(total, (int)blockIdx.x * per);
+    hi = min(total, lo + per);
+  }
+  if (lo >= hi) return;
+
+  AttnWalk w;
+  {
+    int l = 0, r = B - 1;                 // largest b with pre[b] * n_kv <= lo
+    while (l < r) {
+      const int mid = (l + r + 1) >> 1;
+      if (pre[mid] * n_kv <= lo) l = mid; else r = mid - 1;
+    }
+    w.b = l;
+    w.nc = pre[l + 1] - pre[l];
+    const int rem = lo - pre[l] * n_kv;
+    w.hk = rem / w.nc;
+    w.ch = rem - w.hk * w.nc;
+    w.start = first_key[l];
   }
 
-  const __nv_bfloat16* kbase = kcache + ((long long)b * n_kv + hk) * smax * D;
-  const __nv_bfloat16* vbase = vcache + ((long long)b * n_kv + hk) * smax * D;
-
-  for (int j0 = k_begin; j0 < k_end; j0 += kSlots * kKeysPerIter) {
-    uint4 kr[kKeysPerIter][R], vr[kKeysPerIter][R];
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int j = j0 + u * kSlots + slot;
-      const bool ok = j < k_end && lane_active;
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const long long o = (long long)j * D + (r * LPK + hl) * 8;
-        kr[u][r] = ok ? __ldg(reinterpret_cast<const uint4*>(kbase + o)) : make_uint4(0, 0, 0, 0);
-        vr[u][r] = ok ? __ldg(reinterpret_cast<const uint4*>(vbase + o)) : make_uint4(0, 0, 0, 0);
+  if (warp == kWarps) {
+    // ---- producer: one thread streams the K and V rows of every chunk of the run
+    if (lane == 0) {
+      int issued = 0, s = 0, ph = 1;   // ph: the parity that "stage s is free again" completes with
+      bool dead = false;
+      for (int P = lo; P < hi && !dead;) {
+        const int n_here = min(w.nc - w.ch, hi - P);
+        const __nv_bfloat16* kb = kcache + ((long long)w.b * n_kv + w.hk) * smax * D;
+        const __nv_bfloat16* vb = vcache + ((long long)w.b * n_kv + w.hk) * smax * D;
+        for (int i = 0; i < n_here; ++i) {
+          if (issued >= stages &&
+              !mbar_wait(smem_u32(&bar_empty[s]), ph, abort_flag, status, kStatusTimeoutEmpty)) {
+            dead = true;
+            break;
+          }
+          const int j0 = w.start + (w.ch + i) * kChunk;
+          const uint32_t bytes = (uint32_t)min(kChunk, pos + 1 - j0) * D * 2;
+          const uint32_t full = smem_u32(&bar_full[s]);
+          const uint32_t dst = smem_u32(attn_smem) + s * 2 * kTileBytes;
+          mbar_expect_tx(full, 2 * bytes);
+          bulk_load_1d(dst, kb + (long long)j0 * D, bytes, full);
+          bulk_load_1d(dst + kTileBytes, vb + (long long)j0 * D, bytes, full);
+          ++issued;
+          if (++s == stages) {
+            s = 0;
+            ph ^= 1;
+          }
+        }
+        P += n_here;
+        w.ch = 0;
+        if (++w.hk == n_kv && P < hi) {
+          w.hk = 0;
+          ++w.b;
+          w.nc = pre[w.b + 1] - pre[w.b];
+          w.start = first_key[w.b];
+        }
       }
-    }
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int j = j0 + u * kSlots + slot;
-      const bool ok = j < k_end;
-      float kf[R][8], vf[R][8];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        unpack8(kr[u][r], kf[r]);
-        unpack8(vr[u][r], vf[r]);
-      }
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float s = 0.f;
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) s += qv[g][r][i] * kf[r][i];
-        // reduce over the 16 lanes of the half-warp
-        s += __shfl_xor_sync(0xffffffffu, s, 8);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        if (ok) {
-          const float mn = fmaxf(m[g], s);
-          const float corr = __expf(m[g] - mn);
-          const float pj = __expf(s - mn);
-          l[g] = l[g] * corr + pj;
-#pragma unroll
-          for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][r][i] = acc[g][r][i] * corr + pj * vf[r][i];
-          m[g] = mn;
+      if (*abort_flag) {
+        // gave up: no more copies are issued; let those on their way land (bounded) before the
+        // CTA's shared memory goes back to the SM
+        for (int c = max(0, issued - stages); c < issued; ++c) {
+          const long long t0 = clock64();
+          while (!mbar_try_wait(smem_u32(&bar_full[c % stages]), (c / stages) & 1) &&
+                 clock64() - t0 < kWaitLimitCycles) {
+          }
         }
       }
     }
+    return;
   }
 
-  // merge the 8 half-warp partials of the CTA through shared memory
-  __shared__ float sm_m[kSlots][G], sm_l[kSlots][G];
-  __shared__ float sm_acc[kSlots][G][D];
+  // ---- consumers
+  int s = 0, ph = 0;
+  bool dead = false;     // a wait ran out: skip the data, keep walking so that every barrier is met
+  for (int P = lo; P < hi;) {
+    const int n_here = min(w.nc - w.ch, hi - P);
+    const bool whole = w.ch == 0 && n_here == w.nc;
+    float qv[G][R][8];
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (hl == 0) {
-      sm_m[slot][g] = m[g];
-      sm_l[slot][g] = l[g];
+    for (int g = 0; g < G; ++g) {
+      const int h = w.hk * G + g;
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        if (lane_active) {
+          const uint4 raw = *reinterpret_cast<const uint4*>(
+              q + ((long long)w.b * n_head + h) * D + (r * LPK + hl) * 8);
+          unpack8(raw, qv[g][r]);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) qv[g][r][i] *= scale;
+        } else {
+#pragma unroll
+          for (int i = 0; i < 8; ++i) qv[g][r][i] = 0.f;
+        }
+      }
     }
-    if (lane_active) {
+    float m[G], l[G], acc[G][R][8];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      m[g] = -FLT_MAX;
+      l[g] = 0.f;
 #pragma unroll
       for (int r = 0; r < R; ++r)
 #pragma unroll
-        for (int i = 0; i < 8; ++i) sm_acc[slot][g][(r * LPK + hl) * 8 + i] = acc[g][r][i];
+        for (int i = 0; i < 8; ++i) acc[g][r][i] = 0.f;
     }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx - g * D;
-    float mm = -FLT_MAX;
+
+    for (int c = 0; c < n_here; ++c) {
+      if (!dead && !mbar_wait(smem_u32(&bar_full[s]), ph, abort_flag, status, kStatusTimeoutFull))
+        dead = true;
+      if (!dead) {
+        const int j0 = w.start + (w.ch + c) * kChunk;
+        const uint8_t* ks = attn_smem + s * 2 * kTileBytes;
+        const uint8_t* vs = ks + kTileBytes;
+        uint4 kr[kKeysPerIter][R], vr[kKeysPerIter][R];
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) mm = fmaxf(mm, sm_m[s][g]);
-    float ll = 0.f, a = 0.f;
+        for (int u = 0; u < kKeysPerIter; ++u) {
+          const int row = u * kSlots + slot;
+          const bool ok = j0 + row <= pos && lane_active;
 #pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      const float w = (sm_m[s][g] == -FLT_MAX) ? 0.f : __expf(sm_m[s][g] - mm);
-      ll += sm_l[s][g] * w;
-      a += sm_acc[s][g][d] * w;
-    }
-    const int h = hk * G + g;
-    if (n_split == 1) {
-      out[((long long)b * n_head + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
-    } else {
-      float* pp = partial + (((long long)b * n_head + h) * n_split + split) * (D + 2);
-      pp[d] = a;
-      if (d == 0) {
-        pp[D] = mm;
-        pp[D + 1] = ll;
+          for (int r = 0; r < R; ++r) {
+            const int o = (row * D + (r * LPK + hl) * 8) * 2;
+            kr[u][r] = ok ? *reinterpret_cast<const uint4*>(ks + o) : make_uint4(0, 0, 0, 0);
+            vr[u][r] = ok ? *reinterpret_cast<const uint4*>(vs + o) : make_uint4(0, 0, 0, 0);
+          }
+        }
+        // the values are in registers: the stage can be refilled while they are used
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+#pragma unroll
+        for (int u = 0; u < kKeysPerIter; ++u) {
+          const bool ok = j0 + u * kSlots + slot <= pos;
+          float kf[R][8], vf[R][8];
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            unpack8(kr[u][r], kf[r]);
+            unpack8(vr[u][r], vf[r]);
+          }
+#pragma unroll
+          for (int g = 0; g < G; ++g) {
+            float sc = 0.f;
+#pragma unroll
+            for (int r = 0; r < R; ++r)
+#pragma unroll
+              for (int i = 0; i < 8; ++i) sc += qv[g][r][i] * kf[r][i];
+            // reduce over the 16 lanes of the half-warp
+            sc += __shfl_xor_sync(0xffffffffu, sc, 8);
+            sc += __shfl_xor_sync(0xffffffffu, sc, 4);
+            sc += __shfl_xor_sync(0xffffffffu, sc, 2);
+            sc += __shfl_xor_sync(0xffffffffu, sc, 1);
+            if (ok) {
+              const float mn = fmaxf(m[g], sc);
+              const float corr = __expf(m[g] - mn);
+              const float pj = __expf(sc - mn);
+              l[g] = l[g] * corr + pj;
+#pragma unroll
+              for (int r = 0; r < R; ++r)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[g][r][i] = acc[g][r][i] * corr + pj * vf[r][i];
+              m[g] = mn;
+            }
+          }
+        }
+      }
+      if (++s == stages) {
+        s = 0;
+        ph ^= 1;
       }
     }
-  }
-  if (n_split == 1 || tickets == nullptr) return;
-  // merge in place of a second launch: the last split of this (sequence, kv head) to finish
-  // combines all of them (the ticket word returns to zero for the next launch)
-  __shared__ int is_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int t = atomicAdd(&tickets[blockIdx.x], 1u);
-    is_last = (t == (unsigned int)n_split - 1) ? 1 : 0;
-    if (is_last) tickets[blockIdx.x] = 0;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx - g * D;
-    const int h = hk * G + g;
-    const float* pp = partial + ((long long)b * n_head + h) * n_split * (D + 2);
-    float mm = -FLT_MAX;
-    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(pp + s * (D + 2) + D));
-    float ll = 0.f, a = 0.f;
-    for (int s = 0; s < n_split; ++s) {
-      const float ms = __ldcg(pp + s * (D + 2) + D);
-      const float w = (ms == -FLT_MAX) ? 0.f : __expf(ms - mm);
-      ll += __ldcg(pp + s * (D + 2) + D + 1) * w;
-      a += __ldcg(pp + s * (D + 2) + d) * w;
+
+    // ---- this (sequence, head) is done as far as this CTA goes: merge the 8 half-warp partials
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (hl == 0) {
+        sm_m[slot][g] = m[g];
+        sm_l[slot][g] = l[g];
+      }
+      if (lane_active) {
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) sm_acc[slot][g][(r * LPK + hl) * 8 + i] = acc[g][r][i];
+      }
     }
-    out[((long long)b * n_head + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+    consumers_sync();
+    // which of the pair's CTAs this one is, and how many there are
+    int part, parts;
+    if (fixed_parts > 0) {
+      part = (int)blockIdx.x % fixed_parts;
+      parts = (w.nc + per - 1) / per;
+    } else {
+      const int item_lo = pre[w.b] * n_kv + w.hk * w.nc;
+      const int cta_first = item_lo / per, cta_last = (item_lo + w.nc - 1) / per;
+      part = (int)blockIdx.x - cta_first;
+      parts = cta_last - cta_first + 1;
+    }
+    for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+      const int g = idx / D, d = idx - g * D;
+      float mm = -FLT_MAX;
+#pragma unroll
+      for (int t = 0; t < kSlots; ++t) mm = fmaxf(mm, sm_m[t][g]);
+      float ll = 0.f, a = 0.f;
+#pragma unroll
+      for (int t = 0; t < kSlots; ++t) {
+        const float wt = (sm_m[t][g] == -FLT_MAX) ? 0.f : __expf(sm_m[t][g] - mm);
+        ll += sm_l[t][g] * wt;
+        a += sm_acc[t][g][d] * wt;
+      }
+      const int h = w.hk * G + g;
+      if (whole) {
+        out[((long long)w.b * n_head + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+      } else {
+        float* pp = partial + (((long long)w.b * n_head + h) * max_parts + part) * (D + 2);
+        pp[d] = a;
+        if (d == 0) {
+          pp[D] = mm;
+          pp[D + 1] = ll;
+        }
+      }
+    }
+    if (!whole) {
+      // the last of the pair's CTAs to get here combines all parts, in CTA order (the ticket
+      // word returns to zero for the next launch)
+      __threadfence();
+      consumers_sync();
+      if (threadIdx.x == 0) {
+        const unsigned int t = atomicAdd(&tickets[w.b * n_kv + w.hk], 1u);
+        is_last_s = (t == (unsigned int)parts - 1) ? 1 : 0;
+        if (is_last_s) tickets[w.b * n_kv + w.hk] = 0;
+      }
+      consumers_sync();
+      if (is_last_s) {
+        __threadfence();
+        for (int idx = threadIdx.x; idx < G * D; idx += kWarps * 32) {
+          const int g = idx / D, d = idx - g * D;
+          const int h = w.hk * G + g;
+          const float* pp = partial + ((long long)w.b * n_head + h) * max_parts * (D + 2);
+          float mm = -FLT_MAX;
+          for (int t = 0; t < parts; ++t) mm = fmaxf(mm, __ldcg(pp + t * (D + 2) + D));
+          float ll = 0.f, a = 0.f;
+          for (int t = 0; t < parts; ++t) {
+            const float ms = __ldcg(pp + t * (D + 2) + D);
+            const float wt = (ms == -FLT_MAX) ? 0.f : __expf(ms - mm);
+            ll += __ldcg(pp + t * (D + 2) + D + 1) * wt;
+            a += __ldcg(pp + t * (D + 2) + d) * wt;
+          }
+          out[((long long)w.b * n_head + h) * D + d] =
+              __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
+        }
+      }
+    }
+    consumers_sync();      // the merge buffers are free for the next pair
+
+    P += n_here;
+    w.ch = 0;
+    if (++w.hk == n_kv && P < hi) {
+      w.hk = 0;
+      ++w.b;
+      w.nc = pre[w.b + 1] - pre[w.b];
+      w.start = first_key[w.b];
+    }
   }
 }
 
-template <int D>
-__global__ void attn_decode_merge_kernel(const float* __restrict__ partial,
-                                         __nv_bfloat16* __restrict__ out, int n_split) {
-  const long long bh = blockIdx.x;
-  pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
-  pdl_wait_prior();
-  const float* pp = partial + bh * n_split * (D + 2);
-  float mm = -FLT_MAX;
-  for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, pp[s * (D + 2) + D]);
-  for (int d = threadIdx.x; d < D; d += blockDim.x) {
-    float ll = 0.f, a = 0.f;
-    for (int s = 0; s < n_split; ++s) {
-      const float ms = pp[s * (D + 2) + D];
-      const float w = (ms == -FLT_MAX) ? 0.f : __expf(ms - mm);
-      ll += pp[s * (D + 2) + D + 1] * w;
-      a += pp[s * (D + 2) + d] * w;
-    }
-    out[bh * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
-  }
+// Resident CTAs per SM at this pipeline depth (shared memory is what limits them), at most 4.
+static int attn_ctas_per_sm(int D, int G, int stages) {
+  // static shared memory of the kernel, plus the 1 KB that the system keeps per resident CTA
+  const int fixed = (2 * kAttnMaxB + 1) * 4 + kSlots * G * (D + 2) * 4 + 256 + 1024;
+  const int n = (227 * 1024) / (attn_smem_bytes(D, stages) + fixed);
+  return n < 1 ? 1 : n > 4 ? 4 : n;
 }
 
 template <int D, int G>
 static int launch_decode(const void* q, const void* k, const void* v, void* out, float* partial,
                          const int* pos, const int* left_pad, int B, int n_head, int n_kv, int smax,
-                         float scale, int n_split, cudaStream_t stream,
-                         unsigned int* tickets = nullptr) {
-  dim3 grid(n_kv * B, n_split);
-  cudaError_t e = launch(attn_decode_kernel<D, G>, grid, dim3(kWarps * 32), 0, stream,
-                         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k,
-                         (const __nv_bfloat16*)v, (__nv_bfloat16*)out, partial, pos, left_pad,
-                         n_head, n_kv, smax, scale, n_split, tickets);
-  if (e == cudaSuccess && n_split > 1 && tickets == nullptr)
-    e = launch(attn_decode_merge_kernel<D>, dim3(B * n_head), dim3(128), 0, stream,
-               (const float*)partial, (__nv_bfloat16*)out, n_split);
-  return (int)e;
+                         float scale, int max_parts, cudaStream_t stream, unsigned int* tickets,
+                         int* status) {
+  // E2H_ATTN_STAGES: pipeline depth (16 KB of K and V each at head_dim 128), default 3
+  static const int stages = [] {
+    const char* e = getenv("E2H_ATTN_STAGES");
+    const int v_ = e ? atoi(e) : 3;
+    return v_ < 2 ? 2 : v_ > kAttnMaxStages ? kAttnMaxStages : v_;
+  }();
+  // more than 48 KB of dynamic shared memory has to be asked for once per device
+  static std::mutex mu;
+  static bool asked[64];
+  static int n_sm[64];
+  int dev = 0;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return (int)e;
+  if (dev < 0 || dev >= 64) return -5;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (!asked[dev]) {
+      e = cudaFuncSetAttribute(attn_decode_kernel<D, G>,
+                               cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               attn_smem_bytes(D, kAttnMaxStages));
+      if (e != cudaSuccess) return (int)e;
+      e = cudaDeviceGetAttribute(&n_sm[dev], cudaDevAttrMultiProcessorCount, dev);
+      if (e != cudaSuccess) return (int)e;
+      asked[dev] = true;
+    }
+  }
+  if (max_parts > kAttnMaxParts) max_parts = kAttnMaxParts;
+  const long long q_stride = (long long)n_head * D;
+  for (int b0 = 0; b0 < B; b0 += kAttnMaxB) {     // batches beyond kAttnMaxB go in slices
+    const int nb = B - b0 < kAttnMaxB ? B - b0 : kAttnMaxB;
+    const int resident = n_sm[dev] * attn_ctas_per_sm(D, G, stages);
+    int fixed_parts = 0;
+    if (max_parts <= 1) {
+      fixed_parts = 1;
+    } else if (nb * n_kv <= resident) {
+      fixed_parts = resident / (nb * n_kv);      // all CTAs resident at once
+      if (fixed_parts > max_parts) fixed_parts = max_parts;
+    }
+    const int grid = fixed_parts > 0 ? nb * n_kv * fixed_parts : resident;
+    e = launch(attn_decode_kernel<D, G>, dim3(grid), dim3(kAttnThreads),
+               attn_smem_bytes(D, stages), stream,
+               (const __nv_bfloat16*)q + b0 * q_stride,
+               (const __nv_bfloat16*)k + (long long)b0 * n_kv * smax * D,
+               (const __nv_bfloat16*)v + (long long)b0 * n_kv * smax * D,
+               (__nv_bfloat16*)out + b0 * q_stride,
+               partial ? partial + (long long)b0 * n_head * max_parts * (D + 2) : nullptr, pos,
+               left_pad ? left_pad + b0 : nullptr, nb, n_head, n_kv, smax, scale, max_parts,
+               fixed_parts, tickets ? tickets + (long long)b0 * n_kv : nullptr, status, stages);
+    if (e != cudaSuccess) return (int)e;
+  }
+  return 0;
 }
 
 }  // namespace e2h
 
-// partial: fp32 scratch of B*n_head*n_split*(D+2) floats, needed only when n_split > 1.
-// tickets: optional uint32 [B*n_kv], zero before the first launch (every launch leaves it zero):
-// with it the splits are merged inside the kernel, without it by a second launch.
+// max_parts: how many CTAs may share one (sequence, kv head), 1..8. With 1 every pair gets a CTA
+// of its own and neither `partial` nor `tickets` is touched; otherwise
+//   partial: fp32 scratch of B*n_head*max_parts*(D+2) floats (need not be initialised),
+//   tickets: uint32 [B*n_kv], zero before the first launch (every launch leaves it zero).
 extern "C" int e2h_attn_decode(const void* q, const void* kcache, const void* vcache, void* out,
                                float* partial, const int* pos, const int* left_pad, int B,
                                int n_head, int n_kv, int head_dim, int smax, float scale,
-                               int n_split, unsigned int* tickets, void* stream_v) {
+                               int max_parts, unsigned int* tickets, int* status,
+                               void* stream_v) {
   using namespace e2h;
   cudaStream_t stream = (cudaStream_t)stream_v;
-  if (n_head % n_kv) return -1;
-  if (n_split > 1 && partial == nullptr) return -2;
+  if (B < 1 || n_kv < 1 || n_head % n_kv) return -1;
+  if (max_parts > 1 && (partial == nullptr || tickets == nullptr)) return -2;
   const int G = n_head / n_kv;
 #define E2H_GO(D_, G_)                                                                          \
   return launch_decode<D_, G_>(q, kcache, vcache, out, partial, pos, left_pad, B, n_head, n_kv, \
-                               smax, scale, n_split, stream, tickets)
+                               smax, scale, max_parts, stream, tickets, status)
   if (head_dim == 128) {
     if (G == 1) E2H_GO(128, 1);
     if (G == 4) E2H_GO(128, 4);
@@ -305,10 +538,16 @@ constexpr long long kStaticPartialFloats = 64LL * 32 * 8 * (128 + 2);
 static __device__ __align__(256) float g_static_partial[kStaticPartialFloats];
 
 constexpr int kMaxDevices = 64;
+// one ticket word per (sequence, kv head); zero in the library image, and every launch leaves
+// them zero
+constexpr int kStaticTickets = 16384;
+static __device__ unsigned int g_static_tickets[kStaticTickets];
+
 static float* g_static_partial_ptr[kMaxDevices];   // per device, filled on that device's first call
+static unsigned int* g_static_tickets_ptr[kMaxDevices];
 static std::mutex g_static_partial_mu;
 
-static int static_partial_for_current_device(float** ptr) {
+static int static_partial_for_current_device(float** ptr, unsigned int** tickets) {
   int dev = -1;
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return (int)e;
@@ -322,9 +561,18 @@ static int static_partial_for_current_device(float** ptr) {
               cudaGetErrorString(e));
       return (int)e;
     }
+    unsigned int* t = nullptr;
+    e = cudaGetSymbolAddress((void**)&t, g_static_tickets);
+    if (e != cudaSuccess) {
+      fprintf(stderr, "e2h_attn_decode_static: cudaGetSymbolAddress failed: %s\n",
+              cudaGetErrorString(e));
+      return (int)e;
+    }
     g_static_partial_ptr[dev] = p;
+    g_static_tickets_ptr[dev] = t;
   }
   *ptr = g_static_partial_ptr[dev];
+  *tickets = g_static_tickets_ptr[dev];
   return 0;
 }
 }  // namespace e2h
@@ -336,24 +584,25 @@ extern "C" int e2h_attn_decode_static(const void* q, const void* kcache, const v
   using namespace e2h;
   if (B < 1 || n_head < 1 || n_kv < 1 || n_split < 1 || n_head % n_kv) return -1;
   const long long need = (long long)B * n_head * n_split * (head_dim + 2);
-  if (n_split > 1 && need > kStaticPartialFloats) {
+  if (n_split > 1 && (need > kStaticPartialFloats || (long long)B * n_kv > kStaticTickets)) {
     fprintf(stderr,
             "e2h_attn_decode_static: B*n_head*n_split*(head_dim+2) = %lld floats exceeds the "
-            "fixed scratch of %lld floats (64 x 32 heads x 8 splits x head_dim 128); use fewer "
-            "splits or e2h_attn_decode with a caller-provided buffer\n",
-            need, kStaticPartialFloats);
+            "fixed scratch of %lld floats (64 x 32 heads x 8 parts x head_dim 128), or B*n_kv "
+            "exceeds %d; use fewer parts or e2h_attn_decode with a caller-provided buffer\n",
+            need, kStaticPartialFloats, kStaticTickets);
     return -4;
   }
   float* partial = nullptr;
+  unsigned int* tickets = nullptr;
   if (n_split > 1) {
-    const int rc = static_partial_for_current_device(&partial);
+    const int rc = static_partial_for_current_device(&partial, &tickets);
     if (rc != 0) return rc;
   }
   cudaStream_t stream = (cudaStream_t)stream_v;
   const int G = n_head / n_kv;
 #define E2H_GO(D_, G_)                                                                          \
   return launch_decode<D_, G_>(q, kcache, vcache, out, partial, pos, left_pad, B, n_head, n_kv, \
-                               smax, scale, n_split, stream)
+                               smax, scale, n_split, stream, tickets, nullptr)
   if (head_dim == 128) {
     if (G == 1) E2H_GO(128, 1);
     if (G == 4) E2H_GO(128, 4);

@@ -218,13 +218,43 @@ __host__ __device__ inline bool epi_can_stage(const E2hGemmParams& p, int tile_r
   return true;
 }
 
+// What the RoPE + KV-cache epilogue needs per thread (one feature), fetched once per tile
+// instead of once per 8 token columns: the cache position and, when every sequence
+// contributes one token (decode), the one (cos, sin) pair that rotates all of them.
+struct RopePre {
+  int pos0;       // cache position of the first token of every sequence
+  int d;          // index of the feature inside its head
+  int is_v;       // value head: stored as it is
+  float cj, sj;   // decode (p.sq == 1): rotation factors of position pos0
+};
+
+// live == 0 (rehearsal before the predecessor kernel has finished): no global memory is read.
+__device__ __forceinline__ RopePre rope_prepare(const E2hGemmParams& p, int f, int live) {
+  RopePre r;
+  const int D = p.head_dim;
+  const int head = f / D;
+  r.d = f - head * D;
+  r.is_v = head >= p.n_head + p.n_kv ? 1 : 0;
+  r.pos0 = live ? *p.pos_base : 0;
+  r.cj = 1.f;
+  r.sj = 0.f;
+  if (live && p.sq == 1 && !r.is_v && f < p.F && r.pos0 < p.smax && r.pos0 >= 0) {
+    const __nv_bfloat162 cs =
+        static_cast<const __nv_bfloat162*>(p.freqs)[(long long)r.pos0 * (D / 2) + (r.d >> 1)];
+    r.cj = __bfloat162float(cs.x);
+    r.sj = __bfloat162float(cs.y);
+  }
+  return r;
+}
+
 // Final bf16 value of 8 consecutive tokens of one feature into the shared tile:
 // tile[(tl + j) * pitch + row] for j < 8 (row < 0: a lane without a feature, nothing is
 // written). The residual of E2H_EPI_RESIDUAL is added by flush_tile. All 32 lanes must call
 // (the RoPE partner value comes from the neighbouring lane).
 template <bool DUAL>
 __device__ __forceinline__ void stage8(const E2hGemmParams& p, int f, int t0, float* v, float* v2,
-                                       __nv_bfloat16* tile, int tl, int pitch, int row) {
+                                       __nv_bfloat16* tile, int tl, int pitch, int row,
+                                       const RopePre* rope = nullptr) {
   const bool f_ok = f < p.F;
   if (p.scale != nullptr) {
     const float s = f_ok ? p.scale[f] : 0.f;
@@ -243,47 +273,56 @@ __device__ __forceinline__ void stage8(const E2hGemmParams& p, int f, int t0, fl
       for (int j = 0; j < 8; ++j) y[j] = bf16_round(silu(bf16_round(v[j]))) * bf16_round(v2[j]);
     }
   } else if (p.epi == E2H_EPI_ROPE_KV) {
+    const RopePre rp = rope ? *rope : rope_prepare(p, f, 1);
     const int D = p.head_dim;
-    const int head = f / D;
-    const int d = f - head * D;
-    const bool is_v = head >= p.n_head + p.n_kv;
-    const __nv_bfloat162* freqs2 = static_cast<const __nv_bfloat162*>(p.freqs);
-    const int pos0 = *p.pos_base;
-    int b = t0 / p.sq;
-    int s = t0 - b * p.sq;
+    if (p.sq == 1) {
+      // decode: every token sits at cache position pos0
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int pos = pos0 + s;
-      if (++s == p.sq) s = 0;
-      float cj = 1.f, sj = 0.f;
-      if (!is_v && f_ok && t0 + j < p.T && pos < p.smax) {
-        const __nv_bfloat162 cs = freqs2[(long long)pos * (D / 2) + (d >> 1)];
-        cj = __bfloat162float(cs.x);
-        sj = __bfloat162float(cs.y);
+      for (int j = 0; j < 8; ++j) {
+        const float x = bf16_round(v[j]);
+        const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
+        y[j] = rp.is_v ? x
+                       : ((rp.d & 1) ? (x * rp.cj + partner * rp.sj) : (x * rp.cj - partner * rp.sj));
       }
-      const float x = bf16_round(v[j]);
-      const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
-      y[j] = is_v ? x : ((d & 1) ? (x * cj + partner * sj) : (x * cj - partner * sj));
+    } else {
+      int b = t0 / p.sq;
+      int s_ = t0 - b * p.sq;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int pos = rp.pos0 + s_;
+        if (++s_ == p.sq) s_ = 0;
+        float cj = 1.f, sj = 0.f;
+        if (row >= 0 && !rp.is_v && f_ok && t0 + j < p.T && pos < p.smax) {
+          const __nv_bfloat162 cs =
+              static_cast<const __nv_bfloat162*>(p.freqs)[(long long)pos * (D / 2) + (rp.d >> 1)];
+          cj = __bfloat162float(cs.x);
+          sj = __bfloat162float(cs.y);
+        }
+        const float x = bf16_round(v[j]);
+        const float partner = __shfl_xor_sync(0xffffffffu, x, 1);
+        y[j] = rp.is_v ? x : ((rp.d & 1) ? (x * cj + partner * sj) : (x * cj - partner * sj));
+      }
     }
   } else {
 #pragma unroll
     for (int j = 0; j < 8; ++j) y[j] = v[j];
   }
-  if (row < 0) return;
 #pragma unroll
-  for (int j = 0; j < 8; ++j) tile[(tl + j) * pitch + row] = __float2bfloat16_rn(y[j]);
+  for (int j = 0; j < 8; ++j)
+    if (row >= 0) tile[(tl + j) * pitch + row] = __float2bfloat16_rn(y[j]);
 }
 
 // Moves the staged tile (rows = tokens t_first .. t_first + n_tok, columns = features f_first ..
 // f_first + pitch) to its destination, 16 bytes per access. `tid` / `nthreads`: the calling
-// thread's index among the epilogue threads, which have synchronised after stage8.
+// thread's index among the epilogue threads, which have synchronised after stage8. With
+// live == 0 (the rehearsal of epilogue_tile_staged) no global memory is touched.
 __device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bfloat16* tile,
                                            int pitch, int f_first, int t_first, int n_tok,
-                                           int tid, int nthreads) {
+                                           int tid, int nthreads, int live = 1) {
   const int vpr = pitch >> 3;
   const int total = n_tok * vpr;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-  const int pos0 = (p.epi == E2H_EPI_ROPE_KV) ? *p.pos_base : 0;
+  const int pos0 = (p.epi == E2H_EPI_ROPE_KV && live) ? *p.pos_base : 0;
   for (int i = tid; i < total; i += nthreads) {
     const int r = i / vpr;
     const int fv = (i - r * vpr) << 3;
@@ -292,8 +331,10 @@ __device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bf
     uint4 val = *reinterpret_cast<const uint4*>(tile + r * pitch + fv);
     __nv_bfloat16* dst = out + (long long)t * p.ldo + f;
     if (p.epi == E2H_EPI_RESIDUAL) {
-      const uint4 res = *reinterpret_cast<const uint4*>(
-          static_cast<const __nv_bfloat16*>(p.aux) + (long long)t * p.ldo + f);
+      uint4 res = make_uint4(0u, 0u, 0u, 0u);
+      if (live)
+        res = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.aux) +
+                                              (long long)t * p.ldo + f);
       const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&val);
       const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&res);
       uint4 sum;
@@ -317,7 +358,7 @@ __device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bf
         dst = cache + (((long long)b * p.n_kv + hk) * p.smax + pos) * D + d;
       }
     }
-    *reinterpret_cast<uint4*>(dst) = val;
+    if (live) *reinterpret_cast<uint4*>(dst) = val;
   }
 }
 

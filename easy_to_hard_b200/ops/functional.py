@@ -146,50 +146,50 @@ def rope(x: torch.Tensor, freqs: torch.Tensor, pos: torch.Tensor, n_heads: int, 
 _ATTN_SCRATCH: dict = {}
 
 
-def attn_decode_splits(B: int, n_kv: int) -> int:
-    """KV splits per (sequence, kv head): the kernel is a pure stream, so it wants about eight
-    resident CTAs on each of the 148 SMs to keep enough loads in flight."""
-    n_split = 1
-    while B * n_kv * n_split < 1024 and n_split < 16:
-        n_split *= 2
-    return n_split
+def attn_decode_splits(B: int, n_kv: int, smax: Optional[int] = None) -> int:
+    """How many CTAs may share one (sequence, kv head) in ``attn_decode``: the kernel deals the
+    32-key chunks of all pairs out evenly, so a pair may be cut by run boundaries; 8 lets the
+    runs be as short as an eighth of the longest context. ``E2H_ATTN_SPLITS=1`` gives every
+    pair a CTA of its own (no scratch, no merge)."""
+    import os
+    forced = os.environ.get("E2H_ATTN_SPLITS")
+    return max(1, min(8, int(forced))) if forced else 8
 
 
 def attn_decode(q: torch.Tensor, kcache: torch.Tensor, vcache: torch.Tensor, pos: torch.Tensor,
                 left_pad: Optional[torch.Tensor], n_head: int, out: Optional[torch.Tensor] = None,
-                n_split: int = 0, scratch: Optional[torch.Tensor] = None,
-                fused_merge: bool = True) -> torch.Tensor:
+                n_split: int = 0, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One query token per sequence against the static cache, live range [left_pad[b], pos].
 
-    q [B, n_head*D] bf16; caches [max_batch, n_kv, smax, D]; pos int32 device scalar. With
-    several KV splits the partial results go to ``scratch`` (a per-device buffer by default, so
-    calls on one device must be ordered on one stream) and are merged by the last split to
-    finish, or by a second launch with ``fused_merge=False``."""
+    q [B, n_head*D] bf16; caches [max_batch, n_kv, smax, D]; pos int32 device scalar.
+    ``n_split`` (1..8, 0 = default) is the number of CTAs that may share one (sequence, kv head);
+    their partial results go to ``scratch`` (a per-device buffer by default, so calls on one
+    device must be ordered on one stream) and are merged by the last of them to finish."""
     B = q.shape[0]
     n_kv, smax, D = kcache.shape[1], kcache.shape[2], kcache.shape[3]
     if out is None:
         out = torch.empty_like(q)
     if n_split <= 0:
-        n_split = attn_decode_splits(B, n_kv)
+        n_split = attn_decode_splits(B, n_kv, smax)
+    n_split = min(n_split, 8)
     tickets = None
     if n_split > 1:
         need = B * n_head * n_split * (D + 2)
+        key = q.device.index
+        buf = _ATTN_SCRATCH.get(key)
+        if buf is None or buf[0].numel() < need or buf[1].numel() < B * n_kv:
+            buf = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device),
+                   torch.zeros(max(B * n_kv, 4096), dtype=torch.int32, device=q.device))
+            _ATTN_SCRATCH[key] = buf
+        tickets = buf[1]
         if scratch is None:
-            key = q.device.index
-            buf = _ATTN_SCRATCH.get(key)
-            if buf is None or buf[0].numel() < need or buf[1].numel() < B * n_kv:
-                buf = (torch.empty(max(need, 1 << 20), dtype=torch.float32, device=q.device),
-                       torch.zeros(max(B * n_kv, 4096), dtype=torch.int32, device=q.device))
-                _ATTN_SCRATCH[key] = buf
-            scratch, tickets = buf
-        elif fused_merge:
-            tickets = torch.zeros(B * n_kv, dtype=torch.int32, device=q.device)
-        if not fused_merge:
-            tickets = None
+            scratch = buf[0]
+        assert scratch.numel() >= need and scratch.dtype == torch.float32
     rc = _lib.lib().e2h_attn_decode(q.data_ptr(), kcache.data_ptr(), vcache.data_ptr(),
                                     out.data_ptr(), _lib.ptr(scratch), pos.data_ptr(),
                                     _lib.ptr(left_pad), B, n_head, n_kv, D, smax,
-                                    1.0 / math.sqrt(D), n_split, _lib.ptr(tickets), _s())
+                                    1.0 / math.sqrt(D), n_split, _lib.ptr(tickets),
+                                    _lib.status_word(q.device).data_ptr(), _s())
     _lib.check(rc, "attn_decode")
     return out
 

@@ -87,21 +87,27 @@ def test_attn_decode(B, n_head, n_kv, D, pos, n_split):
     assert torch.allclose(o.view(B, n_head, 1, D).float(), want.float(), rtol=2e-2, atol=2e-2)
 
 
-def test_attn_decode_in_kernel_merge_matches_the_two_launch_form_and_replays():
-    """Split-KV partials merged by the last CTA of each (sequence, kv head) to finish: same
-    result as the separate merge launch, and the ticket words return to zero, so a second call
-    (and a graph replay) works without any reset."""
+def test_attn_decode_shared_pairs_merge_in_kernel_and_replay():
+    """(sequence, kv head) pairs cut by the CTAs' run boundaries are merged by the last of their
+    CTAs to finish: close to the one-CTA-per-pair form, bit-identical from call to call
+    (the parts are combined in CTA order), and the ticket words return to zero, so later calls
+    (and graph replays) need no reset. Long contexts with few pairs force up to 8 parts."""
     from easy_to_hard_b200.ops import functional as Fn
-    B, n_head, n_kv, D, smax, pos = 6, 8, 2, 128, 512, 411
-    q = _mk(B, n_head * D, seed=31)
-    kc, vc = _mk(B, n_kv, smax, D, seed=32), _mk(B, n_kv, smax, D, seed=33)
-    p = torch.tensor([pos], dtype=torch.int32, device="cuda")
-    two = Fn.attn_decode(q, kc, vc, p, None, n_head, n_split=8, fused_merge=False)
-    for _ in range(3):
-        one = Fn.attn_decode(q, kc, vc, p, None, n_head, n_split=8)
-        assert torch.equal(one, two)
-    auto = Fn.attn_decode(q, kc, vc, p, None, n_head)           # split count picked by size
-    assert torch.allclose(auto.float(), two.float(), rtol=2e-2, atol=2e-2)
+    for B, n_head, n_kv, D, smax, pos in [(6, 8, 2, 128, 512, 411), (2, 32, 32, 128, 4096, 4001),
+                                          (64, 32, 32, 128, 640, 607), (9, 32, 8, 128, 300, 290)]:
+        q = _mk(B, n_head * D, seed=31)
+        kc, vc = _mk(B, n_kv, smax, D, seed=32), _mk(B, n_kv, smax, D, seed=33)
+        left = torch.randint(0, pos // 3, (B,), device="cuda", dtype=torch.int32)
+        p = torch.tensor([pos], dtype=torch.int32, device="cuda")
+        whole = Fn.attn_decode(q, kc, vc, p, left, n_head, n_split=1)
+        first = Fn.attn_decode(q, kc, vc, p, left, n_head, n_split=8)
+        assert torch.allclose(first.float(), whole.float(), rtol=2e-2, atol=2e-2)
+        for n_split in (8, 2, 0):
+            again = Fn.attn_decode(q, kc, vc, p, left, n_head, n_split=n_split)
+            if n_split in (8, 0):
+                assert torch.equal(again, first)
+            else:
+                assert torch.allclose(again.float(), whole.float(), rtol=2e-2, atol=2e-2)
     _status_ok()
 
 
