@@ -125,9 +125,12 @@ def use_phase_build():
     import ctypes as C
     from easy_to_hard_b200.ops import _lib, build
     from easy_to_hard_b200.ops._lib import GemmParams
-    path = build.OUT_DIR / "libe2h_b200_phase.so"
-    if not path.exists():
-        path = build.build_phase_clock()
+    import os
+    path = os.environ.get("E2H_PHASE_LIB")      # another stamping build, for A/B comparisons
+    if not path:
+        path = build.OUT_DIR / "libe2h_b200_phase.so"
+        if not path.exists():
+            path = build.build_phase_clock()
     phase = C.CDLL(str(path))
     phase.e2h_gemm_umma.argtypes = [C.POINTER(GemmParams), C.c_void_p]
     phase.e2h_gemm_umma.restype = C.c_int

@@ -228,17 +228,16 @@ struct RopePre {
   float cj, sj;   // decode (p.sq == 1): rotation factors of position pos0
 };
 
-// live == 0 (rehearsal before the predecessor kernel has finished): no global memory is read.
-__device__ __forceinline__ RopePre rope_prepare(const E2hGemmParams& p, int f, int live) {
+__device__ __forceinline__ RopePre rope_prepare(const E2hGemmParams& p, int f) {
   RopePre r;
   const int D = p.head_dim;
   const int head = f / D;
   r.d = f - head * D;
   r.is_v = head >= p.n_head + p.n_kv ? 1 : 0;
-  r.pos0 = live ? *p.pos_base : 0;
+  r.pos0 = *p.pos_base;
   r.cj = 1.f;
   r.sj = 0.f;
-  if (live && p.sq == 1 && !r.is_v && f < p.F && r.pos0 < p.smax && r.pos0 >= 0) {
+  if (p.sq == 1 && !r.is_v && f < p.F && r.pos0 < p.smax && r.pos0 >= 0) {
     const __nv_bfloat162 cs =
         static_cast<const __nv_bfloat162*>(p.freqs)[(long long)r.pos0 * (D / 2) + (r.d >> 1)];
     r.cj = __bfloat162float(cs.x);
@@ -273,7 +272,7 @@ __device__ __forceinline__ void stage8(const E2hGemmParams& p, int f, int t0, fl
       for (int j = 0; j < 8; ++j) y[j] = bf16_round(silu(bf16_round(v[j]))) * bf16_round(v2[j]);
     }
   } else if (p.epi == E2H_EPI_ROPE_KV) {
-    const RopePre rp = rope ? *rope : rope_prepare(p, f, 1);
+    const RopePre rp = rope ? *rope : rope_prepare(p, f);
     const int D = p.head_dim;
     if (p.sq == 1) {
       // decode: every token sits at cache position pos0
@@ -292,7 +291,7 @@ __device__ __forceinline__ void stage8(const E2hGemmParams& p, int f, int t0, fl
         const int pos = rp.pos0 + s_;
         if (++s_ == p.sq) s_ = 0;
         float cj = 1.f, sj = 0.f;
-        if (row >= 0 && !rp.is_v && f_ok && t0 + j < p.T && pos < p.smax) {
+        if (!rp.is_v && f_ok && t0 + j < p.T && pos < p.smax) {
           const __nv_bfloat162 cs =
               static_cast<const __nv_bfloat162*>(p.freqs)[(long long)pos * (D / 2) + (rp.d >> 1)];
           cj = __bfloat162float(cs.x);
@@ -307,22 +306,21 @@ __device__ __forceinline__ void stage8(const E2hGemmParams& p, int f, int t0, fl
 #pragma unroll
     for (int j = 0; j < 8; ++j) y[j] = v[j];
   }
+  if (row < 0) return;
 #pragma unroll
-  for (int j = 0; j < 8; ++j)
-    if (row >= 0) tile[(tl + j) * pitch + row] = __float2bfloat16_rn(y[j]);
+  for (int j = 0; j < 8; ++j) tile[(tl + j) * pitch + row] = __float2bfloat16_rn(y[j]);
 }
 
 // Moves the staged tile (rows = tokens t_first .. t_first + n_tok, columns = features f_first ..
 // f_first + pitch) to its destination, 16 bytes per access. `tid` / `nthreads`: the calling
-// thread's index among the epilogue threads, which have synchronised after stage8. With
-// live == 0 (the rehearsal of epilogue_tile_staged) no global memory is touched.
+// thread's index among the epilogue threads, which have synchronised after stage8.
 __device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bfloat16* tile,
                                            int pitch, int f_first, int t_first, int n_tok,
-                                           int tid, int nthreads, int live = 1) {
+                                           int tid, int nthreads) {
   const int vpr = pitch >> 3;
   const int total = n_tok * vpr;
   __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
-  const int pos0 = (p.epi == E2H_EPI_ROPE_KV && live) ? *p.pos_base : 0;
+  const int pos0 = (p.epi == E2H_EPI_ROPE_KV) ? *p.pos_base : 0;
   for (int i = tid; i < total; i += nthreads) {
     const int r = i / vpr;
     const int fv = (i - r * vpr) << 3;
@@ -331,10 +329,8 @@ __device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bf
     uint4 val = *reinterpret_cast<const uint4*>(tile + r * pitch + fv);
     __nv_bfloat16* dst = out + (long long)t * p.ldo + f;
     if (p.epi == E2H_EPI_RESIDUAL) {
-      uint4 res = make_uint4(0u, 0u, 0u, 0u);
-      if (live)
-        res = *reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.aux) +
-                                              (long long)t * p.ldo + f);
+      const uint4 res = *reinterpret_cast<const uint4*>(
+          static_cast<const __nv_bfloat16*>(p.aux) + (long long)t * p.ldo + f);
       const __nv_bfloat162* a = reinterpret_cast<const __nv_bfloat162*>(&val);
       const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&res);
       uint4 sum;
@@ -358,7 +354,7 @@ __device__ __forceinline__ void flush_tile(const E2hGemmParams& p, const __nv_bf
         dst = cache + (((long long)b * p.n_kv + hk) * p.smax + pos) * D + d;
       }
     }
-    if (live) *reinterpret_cast<uint4*>(dst) = val;
+    *reinterpret_cast<uint4*>(dst) = val;
   }
 }
 

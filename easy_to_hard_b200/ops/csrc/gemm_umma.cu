@@ -27,7 +27,6 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdio.h>
-#include <stdlib.h>
 #include <string.h>
 #include <mutex>
 
@@ -76,108 +75,6 @@ struct SmemPlan {
 __host__ __device__ inline int xchg_bytes(int bn, int splitk, int dual, int tf) {
   if (splitk <= 1) return 0;
   return (splitk - 1) * (bn / splitk) * tf * 4 * (dual ? 2 : 1);
-}
-
-// What an epilogue thread needs to finish its part of the CTA's tile.
-struct EpiTile {
-  uint32_t taddr;       // tensor-memory address of this warp's lane quarter
-  int lane_row;         // accumulator row (feature within the tile) of this thread
-  int lane_valid;       // the row exists (tile height, 64-row layout)
-  int half;             // which of the two warps of the lane quarter
-  int rank, S, slice;   // split-K: this CTA's rank, cluster size, token columns it finishes
-  int n_kb;             // k blocks accumulated (0: the accumulator was never written)
-  int f0, t0, TH;
-  const float* xchg;    // partial sums received from the other CTAs of the cluster
-  __nv_bfloat16* stile; // staging tile (the pipeline buffers, idle by then)
-  int tid;              // index among the 256 epilogue threads
-};
-
-// 8 accumulator columns into v, only if `on` (the registers keep their values otherwise).
-__device__ __forceinline__ void tmem_ld_x8_if(uint32_t taddr, float* v, int on) {
-  uint32_t* r = reinterpret_cast<uint32_t*>(v);
-  asm volatile(
-      "{\n"
-      ".reg .pred P;\n"
-      "setp.ne.s32 P, %9, 0;\n"
-      "@P tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];\n"
-      "}\n"
-      : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]),
-        "+r"(r[7])
-      : "r"(taddr), "r"(on)
-      : "memory");
-}
-
-// The staged epilogue of one CTA tile: accumulator -> registers -> fused epilogue -> shared
-// staging tile -> 16-byte stores. It is one function, not inlined, because it is called twice:
-// a decode step runs a few hundred different kernel launches between two uses of this code, so
-// its first execution in a launch finds none of it in the SM's instruction cache and stalls on
-// one fetch after another (measured inside the decode graph: 8-9.5 us from "accumulator ready"
-// to "values staged", against 2.3-4.1 us for the same launch repeated in isolation). The
-// epilogue warps are idle while the weights stream, so they first walk through the function
-// with live == 0 -- the same instructions, with the tensor-memory loads, all stores and all
-// global loads predicated off (the walk happens before the predecessor kernel has finished, and
-// a line read then could be served stale from L1 later) -- and the second, real call runs from
-// the instruction cache.
-template <int BN, bool DUAL, int TF>
-__device__ __noinline__ void epilogue_tile_staged(const E2hGemmParams& p, const EpiTile e,
-                                                  const int live) {
-  const int c_begin = e.rank * e.slice;
-  const int f = e.lane_valid ? e.f0 + e.lane_row : p.F;  // rows past F are masked in the epilogue
-  const int row = (live && e.lane_valid) ? e.lane_row : -1;
-  // columns of this warp: with 64 or more, alternate groups of 32; with fewer, the first /
-  // second half of the 8-column units
-  const int units = e.slice >> 3;
-  int c_first, c_last;
-  if (units >= 8) {
-    c_first = 32 * e.half;
-    c_last = e.slice;
-  } else {
-    const int lo = units == 1 ? 1 : units >> 1;   // units of warp 0 (warp 1 takes the rest)
-    c_first = e.half ? 8 * lo : 0;
-    c_last = e.half ? e.slice : 8 * lo;
-  }
-  const int ld_on = (live && e.n_kb > 0) ? 1 : 0;
-  RopePre rope;
-  if (p.epi == E2H_EPI_ROPE_KV) rope = rope_prepare(p, f, live);
-  for (int c = c_first; c < c_last; c += 64) {
-    // up to 32 columns per round trip to tensor memory
-    const int nb = (c_last - c) >= 32 ? 4 : (c_last - c) / 8;
-    float v[32], v2[DUAL ? 32 : 1];
-#pragma unroll
-    for (int j = 0; j < 32; ++j) {
-      v[j] = 0.f;
-      if constexpr (DUAL) v2[j] = 0.f;
-    }
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      if (b < nb) {
-        tmem_ld_x8_if(e.taddr + c_begin + c + 8 * b, v + 8 * b, ld_on);
-        if constexpr (DUAL) tmem_ld_x8_if(e.taddr + BN + c_begin + c + 8 * b, v2 + 8 * b, ld_on);
-      }
-    }
-    tmem_ld_wait();
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      if (b >= nb) continue;
-      if (e.S > 1) {
-        for (int slot = 0; slot < e.S - 1; ++slot) {
-          const float* src = e.xchg + (size_t)(slot * e.slice + c + 8 * b) * TF + e.lane_row;
-#pragma unroll
-          for (int j = 0; j < 8; ++j) v[8 * b + j] += src[j * TF];
-          if constexpr (DUAL) {
-            const float* src2 = src + (size_t)(e.S - 1) * e.slice * TF;
-#pragma unroll
-            for (int j = 0; j < 8; ++j) v2[8 * b + j] += src2[j * TF];
-          }
-        }
-      }
-      stage8<DUAL>(p, f, e.t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2, e.stile,
-                   c + 8 * b, e.TH, row, &rope);
-    }
-  }
-  if (live && e.tid == 0) E2H_PHASE(p.phase_clock, 8);
-  asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
-  flush_tile(p, e.stile, e.TH, e.f0, e.t0 + c_begin, e.slice, e.tid, 256, live);
 }
 
 template <int BN, bool DUAL, int TF>
@@ -250,33 +147,6 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // warps wait before they touch the outputs, the MMA thread touches no global memory.
   pdl_launch_dependents();
   const bool early_weights = kps > 1;
-  // epilogue threads: their part of the tile, and (p.stage_epi == 2) the walk through the
-  // epilogue code that brings it into the instruction cache while the predecessor drains and
-  // the first weight tiles are on their way (nothing is written, see epilogue_tile_staged)
-  EpiTile epi_tile;
-  {
-    const int q_ = warp & 3;
-    const int lane_row_ = (TF == 128) ? q_ * 32 + lane : q_ * 16 + (lane & 15);
-    epi_tile.taddr = tmem_base + (static_cast<uint32_t>(q_ * 32) << 16);
-    epi_tile.lane_row = lane_row_;
-    epi_tile.lane_valid = ((TF == 128) ? lane_row_ < TH : lane < 16) ? 1 : 0;
-    epi_tile.half = (warp - 2) >> 2;
-    epi_tile.rank = rank;
-    epi_tile.S = S;
-    epi_tile.slice = BN / S;
-    epi_tile.n_kb = n_kb;
-    epi_tile.f0 = f0;
-    epi_tile.t0 = t0;
-    epi_tile.TH = TH;
-    epi_tile.xchg = xchg;
-    epi_tile.stile = reinterpret_cast<__nv_bfloat16*>(tiles);
-    epi_tile.tid = (int)threadIdx.x - 64;
-  }
-  // the flag goes through an asm statement so that the compiler cannot tell the two calls apart
-  // and build a copy of the function for each (which would defeat the purpose)
-  int live_no, live_yes;
-  asm volatile("mov.u32 %0, 0;\n\tmov.u32 %1, 1;" : "=r"(live_no), "=r"(live_yes));
-  if (warp >= 2 && p.stage_epi == 2) epilogue_tile_staged<BN, DUAL, TF>(p, epi_tile, live_no);
   if (!(warp == 0 && lane == 0 && early_weights) && !(warp == 1 && lane == 0)) pdl_wait_prior();
 
   if (warp == 0 && lane == 0) {
@@ -493,63 +363,75 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   // Staged epilogue: the finished values go through a [tokens][TH] bf16 tile in the (now idle)
   // pipeline buffers and leave with 16-byte accesses; see gemm_epilogue.cuh.
   const bool staged = p.stage_epi != 0;
+  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(tiles);
   if (is_epi && acc_ok) {
-    if (staged) {
-      epilogue_tile_staged<BN, DUAL, TF>(p, epi_tile, live_yes);
+    const int c_begin = rank * slice;
+    const int f = lane_valid ? f0 + lane_row : p.F;  // rows past F are masked in the epilogue
+    // columns of this warp: with 64 or more, alternate groups of 32; with fewer, the first /
+    // second half of the 8-column units
+    const int units = slice >> 3;
+    int c_first, c_last, c_step;
+    if (units >= 8) {
+      c_first = 32 * half;
+      c_last = slice;
+      c_step = 64;
     } else {
-      const int c_begin = rank * slice;
-      const int f = lane_valid ? f0 + lane_row : p.F;  // rows past F are masked in the epilogue
-      const int units = slice >> 3;
-      int c_first, c_last;
-      if (units >= 8) {
-        c_first = 32 * half;
-        c_last = slice;
-      } else {
-        const int lo = units == 1 ? 1 : units >> 1;
-        c_first = half ? 8 * lo : 0;
-        c_last = half ? slice : 8 * lo;
-      }
-      for (int c = c_first; c < c_last; c += 64) {
-        const int nb = (c_last - c) >= 32 ? 4 : (c_last - c) / 8;
-        float v[32], v2[DUAL ? 32 : 1];
-        if (n_kb > 0) {
-#pragma unroll
-          for (int b = 0; b < 4; ++b) {
-            if (b < nb) {
-              issue_acc(0, c_begin + c + 8 * b, v + 8 * b);
-              if constexpr (DUAL) issue_acc(1, c_begin + c + 8 * b, v2 + 8 * b);
-            }
-          }
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            v[j] = 0.f;
-            if constexpr (DUAL) v2[j] = 0.f;
-          }
-        }
+      const int lo = units == 1 ? 1 : units >> 1;   // units of warp 0 (warp 1 takes the rest)
+      c_first = half ? 8 * lo : 0;
+      c_last = half ? slice : 8 * lo;
+      c_step = 64;
+    }
+    RopePre rope;
+    if (staged && p.epi == E2H_EPI_ROPE_KV) rope = rope_prepare(p, f);
+    for (int c = c_first; c < c_last; c += c_step) {
+      // up to 32 columns per round trip to tensor memory
+      const int nb = (c_last - c) >= 32 ? 4 : (c_last - c) / 8;
+      float v[32], v2[DUAL ? 32 : 1];
+      if (n_kb > 0) {
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          if (b >= nb) continue;
-          if (S > 1) {
-            for (int slot = 0; slot < S - 1; ++slot) {
-              const float* src = xchg + (size_t)(slot * slice + c + 8 * b) * TF + lane_row;
+          if (b < nb) {
+            issue_acc(0, c_begin + c + 8 * b, v + 8 * b);
+            if constexpr (DUAL) issue_acc(1, c_begin + c + 8 * b, v2 + 8 * b);
+          }
+        }
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) v[8 * b + j] += src[j * TF];
-              if constexpr (DUAL) {
-                const float* src2 = src + (size_t)(S - 1) * slice * TF;
+        for (int j = 0; j < 32; ++j) {
+          v[j] = 0.f;
+          if constexpr (DUAL) v2[j] = 0.f;
+        }
+      }
 #pragma unroll
-                for (int j = 0; j < 8; ++j) v2[8 * b + j] += src2[j * TF];
-              }
+      for (int b = 0; b < 4; ++b) {
+        if (b >= nb) continue;
+        if (S > 1) {
+          for (int slot = 0; slot < S - 1; ++slot) {
+            const float* src = xchg + (size_t)(slot * slice + c + 8 * b) * TF + lane_row;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v[8 * b + j] += src[j * TF];
+            if constexpr (DUAL) {
+              const float* src2 = src + (size_t)(S - 1) * slice * TF;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v2[8 * b + j] += src2[j * TF];
             }
           }
+        }
+        if (staged) {
+          stage8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2, stile,
+                       c + 8 * b, TH, lane_valid ? lane_row : -1, &rope);
+        } else {
           epilogue8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2);
         }
       }
-      if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 8);
     }
-  } else if (is_epi && staged) {
-    asm volatile("bar.sync 1, 256;" ::: "memory");   // keep the barrier of the staged path whole
+  }
+  if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 8);
+  if (staged && is_epi) {
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+    if (acc_ok)
+      flush_tile(p, stile, TH, f0, t0 + rank * slice, slice, threadIdx.x - 64, 256);
   }
 
   if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 9);
@@ -707,13 +589,6 @@ extern "C" int e2h_gemm_umma(const E2hGemmParams* pp, void* stream_v) {
   p.stage_epi = (epi_can_stage(p, p.th) &&
                  (long long)(p.bn / p.splitk) * p.th * 2 <= (long long)p.stages * stage_bytes)
                     ? 1 : 0;
-  // skinny (decode) launches: the epilogue warps first walk through the epilogue code, see
-  // epilogue_tile_staged; E2H_EPI_DRY=0 turns it off
-  static const bool dry = [] {
-    const char* e = getenv("E2H_EPI_DRY");
-    return !(e && e[0] == '0');
-  }();
-  if (p.stage_epi && p.kps > 1 && dry) p.stage_epi = 2;
 
   CUtensorMap ta, ta2, tb;
   int r;

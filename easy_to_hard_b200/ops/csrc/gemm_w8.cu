@@ -9,11 +9,14 @@
 //   warps 2-9   converters during the main loop (two threads per feature row, 64 k each):
 //               int8 -> bf16 two values per instruction -- a byte permute drops each byte into the
 //               mantissa of bf16(128) (0x4300 | low 7 bits), and one packed bf16 subtraction of
-//               128 or 256 (chosen by the sign bit) yields the exact integer -- written as the
-//               128-byte-swizzled K-major A tile that tcgen05.mma reads, two alternating buffers;
-//               afterwards warps 2-5 run the epilogue;
-//   warp 1      one thread issues tcgen05.mma (M = 128, N = BN, K = 16) from the converted tile
-//               and the activation tile into the fp32 accumulator in tensor memory.
+//               128 or 256 (chosen by the sign bit) yields the exact integer. The converted row
+//               goes straight from registers into TENSOR memory (tcgen05.st, the thread's own
+//               lane, 32 columns = 64 k), where tcgen05.mma reads it as its A operand: the
+//               expanded tile never touches shared memory, whose bandwidth (16 KB read + 32 KB
+//               written + 32 KB read back per 128 k) held the earlier form at the bf16 rate.
+//               Several buffers alternate; afterwards the eight warps run the epilogue;
+//   warp 1      one thread issues tcgen05.mma (M = 128, N = BN, K = 16; A from tensor memory,
+//               the activation tile from shared memory) into the fp32 accumulator.
 //
 // The integers -128..127 are exact in bf16, so the product equals the reference's
 // F.linear(x, w_int8.to(bf16)) * scales (models/quantize.py:397-398) up to accumulation order;
@@ -41,7 +44,9 @@ constexpr int kW8MaxStages = 8;
 constexpr int kW8Ctrl = 1024;
 constexpr int kW8Kps = 2;          // 64-wide k-blocks per pipeline stage
 constexpr int kW8ConvMax = 4;      // converted-tile buffers: 4 (2 for a dual GEMM, whose tiles are twice as large)
-constexpr int kA16Bytes = 128 * 128;
+constexpr int kW8ACol0 = 128;      // tensor-memory column of the first converted-tile buffer
+constexpr int kW8ACols = 64;       // columns of one converted [128 x 128 k] bf16 tile
+constexpr int kW8TmemCols = 512;
 
 struct CtrlW8 {
   uint64_t full[kW8MaxStages];
@@ -99,14 +104,20 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                     const __grid_constant__ CUtensorMap tmB, const E2hGemmParams p) {
   constexpr int NMAT = DUAL ? 2 : 1;
   // the conversion -> MMA -> commit round trip of one buffer takes about 2 us; several buffers
-  // in flight hide it
+  // in flight hide it. Tensor memory: accumulators in columns [0, 128), converted tiles in
+  // [128, 384): 4 buffers of 64 columns (2 of 128 for a dual GEMM).
   constexpr int kW8Conv = DUAL ? 2 : 4;
   constexpr int B_BYTES = BN * 128;
-  constexpr int AQ_BYTES = 128 * 16 * QB;   // quantised weight tile of one stage: 128 rows x 128 k
-  constexpr int STAGE = AQ_BYTES * NMAT + kW8Kps * B_BYTES;
-  constexpr int CONV = kW8Kps * kA16Bytes * NMAT;
+  // quantised weight tile of one stage: TH rows x 128 k. TH = p.th (64..128): with lower tiles
+  // a wide layer covers (nearly) all SMs in one wave instead of leaving a third of them idle;
+  // the MMA still spans 128 lanes, the lanes past TH hold zeros and are never read back
+  const int TH = p.th;
+  const int AQ_BYTES = TH * 16 * QB;
+  const int STAGE = AQ_BYTES * NMAT + kW8Kps * B_BYTES;
+  constexpr int CONV_COLS = kW8ACols * NMAT;
   constexpr int ACC_COLS = BN * NMAT;
-  constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : 256;
+  static_assert(ACC_COLS <= kW8ACol0 && kW8ACol0 + kW8Conv * CONV_COLS <= kW8TmemCols, "tmem");
+  constexpr int TMEM_COLS = kW8TmemCols;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) &
                                              ~uintptr_t(1023));
@@ -114,12 +125,11 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   uint8_t* tiles = smem + kW8Ctrl;
   const int stages = p.stages;
   float* xchg = reinterpret_cast<float*>(tiles + (size_t)stages * STAGE);
-  uint8_t* conv = reinterpret_cast<uint8_t*>(xchg) + w8_xchg_bytes(BN, p.splitk, DUAL);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int S = p.splitk;
   const int rank = (S > 1) ? (int)cluster_ctarank() : 0;
-  const int f0 = blockIdx.x * 128;
+  const int f0 = blockIdx.x * TH;
   const int t0 = blockIdx.y * BN;
   // the K range is split in units of one int8 tile (128 k = two bf16 k-blocks)
   const int kb2_total = p.K / 128;
@@ -219,7 +229,6 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     // descriptors: constant high word, base low words once, one add per instruction; stage and
     // phase are running counters (no division in this dependent scalar chain)
     const uint32_t d_hi = sw128_desc_hi(1024);
-    const uint32_t a_lo0 = sw128_desc_lo(smem_u32(conv), 16);
     const uint32_t b_lo0 = sw128_desc_lo(smem_u32(tiles) + AQ_BYTES * NMAT, 16);
     const uint32_t full0 = smem_u32(&ctrl->full[0]), empty0 = smem_u32(&ctrl->empty[0]);
     bool ok = true;
@@ -233,17 +242,17 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       if (!ok) break;
       tc_fence_after();
       const int kcount = min(kW8Kps, n_kb - it * kW8Kps);
-      uint32_t a_lo = a_lo0 + c * (CONV >> 4), b_lo = b_lo0 + st_lo;
+      // A: 8 columns (16 k) per instruction, 32 columns per 64-wide k block
+      uint32_t a_col = tmem_base + kW8ACol0 + c * CONV_COLS, b_lo = b_lo0 + st_lo;
       for (int kk = 0; kk < kcount; ++kk) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
-          umma_f16_lohi(tmem_base, a_lo + 2 * k, d_hi, b_lo + 2 * k, d_hi, idesc, accf);
+          umma_f16_ts(tmem_base, a_col + 8 * k, b_lo + 2 * k, d_hi, idesc, accf);
           if (DUAL)
-            umma_f16_lohi(tmem_base + BN, a_lo + ((kW8Kps * kA16Bytes) >> 4) + 2 * k, d_hi,
-                          b_lo + 2 * k, d_hi, idesc, accf);
+            umma_f16_ts(tmem_base + BN, a_col + kW8ACols + 8 * k, b_lo + 2 * k, d_hi, idesc, accf);
           accf = 1;
         }
-        a_lo += kA16Bytes >> 4;
+        a_col += 32;
         b_lo += B_BYTES >> 4;
       }
       umma_commit(empty0 + 8 * s);                   // activation tile (and int8 tile) reusable
@@ -260,14 +269,15 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   }
 
   const bool is_conv = warp >= 2;
-  const bool is_epi = warp >= 2 && warp < 6;
-  const int q = warp & 3;
-  const int lane_row = q * 32 + lane;                 // feature row = TMEM lane (epilogue warps)
+  const bool is_epi = warp >= 2;
+  const int q = warp & 3;                             // tensor-memory lane quarter of this warp
+  const int half = (warp - 2) >> 2;                   // which of the quarter's two warps
+  const int lane_row = q * 32 + lane;                 // feature row = tensor-memory lane
+  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   if (is_conv) {
-    // ---------------- converters: int8 tile -> swizzled bf16 A tiles ----------------
-    // thread (row, half): the 64 int8 of `row` that make up bf16 k-block `half` of the stage
-    const int ct = threadIdx.x - 64;                  // 0 .. 255
-    const int row = ct & 127, half = ct >> 7;
+    // ---------------- converters: quantised tile -> bf16 rows in tensor memory ----------------
+    // thread (row, half): the 64 k of `row` that make up bf16 k-block `half` of the stage
+    const int row = lane_row;
     const int sw = row & 7;                           // 128B-swizzle term of this row
     bool ok = true;
     int s = 0;
@@ -288,25 +298,25 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
                        kStatusTimeoutFull) &&
              mbar_wait(smem_u32(&ctrl->conv_empty[c]), ((it / kW8Conv) & 1) ^ 1, abort_flag,
                        p.status, kStatusTimeoutEmpty);
+      tc_fence_after();
       if (ok) {
         const uint8_t* st = tiles + (size_t)s_cur * STAGE;
-        uint8_t* cv = conv + (size_t)c * CONV;
 #pragma unroll
         for (int m = 0; m < NMAT; ++m) {
-          uint8_t* dst = cv + (m * kW8Kps + half) * kA16Bytes + row * 128;
-          if constexpr (QB == 8) {
+          uint32_t o[32];                             // 64 k of this row, two per word
+          if (row >= TH) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) o[j] = 0u;
+          } else if constexpr (QB == 8) {
             const uint8_t* src = st + m * AQ_BYTES + row * 128;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {             // 16 int8 -> two 16-byte bf16 chunks
+            for (int j = 0; j < 4; ++j) {             // 16 int8 -> eight words
               const uint4 raw =
                   *reinterpret_cast<const uint4*>(src + (((4 * half + j) ^ sw) << 4));
-              uint4 o0, o1;
-              cvt4_s8_bf16(raw.x, o0.x, o0.y);
-              cvt4_s8_bf16(raw.y, o0.z, o0.w);
-              cvt4_s8_bf16(raw.z, o1.x, o1.y);
-              cvt4_s8_bf16(raw.w, o1.z, o1.w);
-              *reinterpret_cast<uint4*>(dst + (((2 * j) ^ sw) << 4)) = o0;
-              *reinterpret_cast<uint4*>(dst + (((2 * j + 1) ^ sw) << 4)) = o1;
+              cvt4_s8_bf16(raw.x, o[8 * j + 0], o[8 * j + 1]);
+              cvt4_s8_bf16(raw.y, o[8 * j + 2], o[8 * j + 3]);
+              cvt4_s8_bf16(raw.z, o[8 * j + 4], o[8 * j + 5]);
+              cvt4_s8_bf16(raw.w, o[8 * j + 6], o[8 * j + 7]);
             }
           } else {
             // int4 tile: 128 rows x 64 bytes, 64-byte swizzle (16-byte chunk c of a row sits at
@@ -323,31 +333,29 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             const __nv_bfloat162 zr2 = __bfloat162bfloat162(pair.y);
             const int sw4 = (row >> 1) & 3;
 #pragma unroll
-            for (int cc = 0; cc < 2; ++cc) {          // 16 bytes = 32 nibbles -> four bf16 chunks
+            for (int cc = 0; cc < 2; ++cc) {          // 16 bytes = 32 nibbles -> sixteen words
               const uint4 raw =
                   *reinterpret_cast<const uint4*>(src + (((2 * half + cc) ^ sw4) << 4));
               const uint32_t wds[4] = {raw.x, raw.y, raw.z, raw.w};
 #pragma unroll
               for (int wi = 0; wi < 4; ++wi) {
-                uint4 o;
-                o.x = cvt2_u4_bf16(wds[wi], 0, sc2, zr2);
-                o.y = cvt2_u4_bf16(wds[wi], 1, sc2, zr2);
-                o.z = cvt2_u4_bf16(wds[wi], 2, sc2, zr2);
-                o.w = cvt2_u4_bf16(wds[wi], 3, sc2, zr2);
-                *reinterpret_cast<uint4*>(dst + (((4 * cc + wi) ^ sw) << 4)) = o;
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                  o[16 * cc + 4 * wi + j] = cvt2_u4_bf16(wds[wi], j, sc2, zr2);
               }
             }
           }
+          tmem_st_x32(taddr + kW8ACol0 + c * CONV_COLS + m * kW8ACols + 32 * half, o);
         }
       }
-      fence_proxy_async_smem();   // generic writes -> tcgen05.mma
+      tmem_st_wait();
+      tc_fence_before();          // the stores are ordered before the arrival below
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&ctrl->conv_full[c]));
     }
   }
 
   // ---------------- epilogue: accumulator -> registers -> fused epilogue ----------------
-  const uint32_t taddr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
   const int slice = BN / S;
   bool acc_ok = true;
   if (is_epi) {
@@ -359,11 +367,12 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     acc_ok = ok_i != 0;
     tc_fence_after();
     if (S > 1 && acc_ok && n_kb > 0) {
-      // reduce-scatter over token columns through distributed shared memory
+      // reduce-scatter over token columns through distributed shared memory; the quarter's two
+      // warps alternate over the 8-column groups
       for (int peer = 0; peer < S; ++peer) {
         if (peer == rank) continue;
         const int slot = rank < peer ? rank : rank - 1;
-        for (int c = 0; c < slice; c += 8) {
+        for (int c = 8 * half; c < slice; c += 16) {
 #pragma unroll
           for (int m = 0; m < NMAT; ++m) {
             float v[8];
@@ -381,36 +390,74 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
   __syncwarp();
   if (S > 1) cluster_sync_all();
 
+  // Staged epilogue (gemm_epilogue.cuh): the finished values go through a [tokens][128] bf16
+  // tile in the (now idle) pipeline buffers and leave with 16-byte accesses.
+  const bool staged = p.stage_epi != 0;
+  __nv_bfloat16* stile = reinterpret_cast<__nv_bfloat16*>(tiles);
   if (is_epi && acc_ok) {
     const int c_begin = rank * slice;
-    const int f = f0 + lane_row;
-    for (int c = 0; c < slice; c += 8) {
-      float v[8], v2[DUAL ? 8 : 1];
+    const bool lane_valid = lane_row < TH;
+    const int f = lane_valid ? f0 + lane_row : p.F;   // rows past the tile are masked
+    // columns of this warp: with 64 or more, alternate groups of 32; with fewer, the first /
+    // second half of the 8-column units
+    const int units = slice >> 3;
+    int c_first, c_last;
+    if (units >= 8) {
+      c_first = 32 * half;
+      c_last = slice;
+    } else {
+      const int lo = units == 1 ? 1 : units >> 1;
+      c_first = half ? 8 * lo : 0;
+      c_last = half ? slice : 8 * lo;
+    }
+    RopePre rope;
+    if (staged && p.epi == E2H_EPI_ROPE_KV) rope = rope_prepare(p, f);
+    for (int c = c_first; c < c_last; c += 64) {
+      const int nb = (c_last - c) >= 32 ? 4 : (c_last - c) / 8;
+      float v[32], v2[DUAL ? 32 : 1];
       if (n_kb > 0) {
-        tmem_ld_x8(taddr + c_begin + c, v);
-        if constexpr (DUAL) tmem_ld_x8(taddr + BN + c_begin + c, v2);
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          if (b < nb) {
+            tmem_ld_x8(taddr + c_begin + c + 8 * b, v + 8 * b);
+            if constexpr (DUAL) tmem_ld_x8(taddr + BN + c_begin + c + 8 * b, v2 + 8 * b);
+          }
+        }
         tmem_ld_wait();
       } else {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
+        for (int j = 0; j < 32; ++j) {
           v[j] = 0.f;
           if constexpr (DUAL) v2[j] = 0.f;
         }
       }
-      if (S > 1) {
-        for (int slot = 0; slot < S - 1; ++slot) {
-          const float* src = xchg + (size_t)(slot * slice + c) * 128 + lane_row;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) v[j] += src[j * 128];
-          if constexpr (DUAL) {
-            const float* src2 = src + (size_t)(S - 1) * slice * 128;
+      for (int b = 0; b < 4; ++b) {
+        if (b >= nb) continue;
+        if (S > 1) {
+          for (int slot = 0; slot < S - 1; ++slot) {
+            const float* src = xchg + (size_t)(slot * slice + c + 8 * b) * 128 + lane_row;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) v2[j] += src2[j * 128];
+            for (int j = 0; j < 8; ++j) v[8 * b + j] += src[j * 128];
+            if constexpr (DUAL) {
+              const float* src2 = src + (size_t)(S - 1) * slice * 128;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) v2[8 * b + j] += src2[j * 128];
+            }
           }
         }
+        if (staged) {
+          stage8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2, stile,
+                       c + 8 * b, TH, lane_valid ? lane_row : -1, &rope);
+        } else {
+          epilogue8<DUAL>(p, f, t0 + c_begin + c + 8 * b, v + 8 * b, DUAL ? v2 + 8 * b : v2);
+        }
       }
-      epilogue8<DUAL>(p, f, t0 + c_begin + c, v, v2);
     }
+  }
+  if (staged && is_epi) {
+    asm volatile("bar.sync 1, 256;" ::: "memory");   // the eight epilogue warps
+    if (acc_ok) flush_tile(p, stile, TH, f0, t0 + rank * slice, slice, threadIdx.x - 64, 256);
   }
 
   if (p.n_signal > 0) __threadfence();
@@ -469,12 +516,12 @@ static int w8_map3d(CUtensorMap* m, const void* base, long long K, long long row
 // Packed int4 operand [rows, K / 2 bytes] seen as {64 bytes, rows, K / 128}: one box
 // {64, 128, 1} is the [128 rows x 128 k] tile of a stage, 64-byte swizzle.
 static int w4_map3d(CUtensorMap* m, const void* base, long long K, long long rows,
-                    long long ld_bytes) {
+                    long long ld_bytes, int box_rows) {
   W8EncodeFn fn = w8_encode_fn();
   if (!fn) return -10;
   cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(K / 128)};
   cuuint64_t strides[2] = {(cuuint64_t)ld_bytes, 64u};
-  cuuint32_t box[3] = {64u, 128u, 1u};
+  cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, 1u};
   cuuint32_t estr[3] = {1u, 1u, 1u};
   CUresult r = fn(m, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(base), dims, strides, box,
                   estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
@@ -485,10 +532,12 @@ static int w4_map3d(CUtensorMap* m, const void* base, long long K, long long row
 template <int BN, bool DUAL, int QB>
 static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
   constexpr int NMAT = DUAL ? 2 : 1;
-  constexpr int kW8Conv = DUAL ? 2 : 4;
-  constexpr int STAGE = 128 * 16 * QB * NMAT + kW8Kps * BN * 128;
-  constexpr int CONV = kW8Kps * kA16Bytes * NMAT;
-  const int fixed = 1024 + kW8Ctrl + w8_xchg_bytes(BN, p.splitk, DUAL) + kW8Conv * CONV;
+  // tile height: 128, or p.th (64..128; a multiple of 8 rows for int8, of 16 for int4, so that
+  // every part of a stage starts on a swizzle-atom boundary)
+  if (p.th <= 0) p.th = 128;
+  if (p.th < 64 || p.th > 128 || (p.th % (QB == 8 ? 8 : 16))) return -12;
+  const int STAGE = p.th * 16 * QB * NMAT + kW8Kps * BN * 128;
+  const int fixed = 1024 + kW8Ctrl + w8_xchg_bytes(BN, p.splitk, DUAL);
   int stages = (227 * 1024 - fixed) / STAGE;
   if (stages > kW8MaxStages) stages = kW8MaxStages;
   if (p.stages > 0 && p.stages < stages) stages = p.stages;
@@ -496,20 +545,30 @@ static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
   if (stages > n_it) stages = n_it < 1 ? 1 : n_it;
   if (stages < 1) return -8;
   p.stages = stages;
+  // staged (shared-memory) epilogue when the output layout allows 16-byte accesses and the
+  // finished tile fits the pipeline buffers it reuses
+  p.stage_epi = (epi_can_stage(p, p.th) &&
+                 (long long)(BN / p.splitk) * p.th * 2 <= (long long)stages * STAGE)
+                    ? 1 : 0;
   CUtensorMap ta, ta2, tb;
-  int r = QB == 8 ? w8_map3d(&ta, p.a, p.K, p.F, p.lda, 128, 1, true)
-                  : w4_map3d(&ta, p.a, p.K, p.F, p.lda);
+  int r = QB == 8 ? w8_map3d(&ta, p.a, p.K, p.F, p.lda, p.th, 1, true)
+                  : w4_map3d(&ta, p.a, p.K, p.F, p.lda, p.th);
   if (r) return r;
   if (DUAL) {
-    r = QB == 8 ? w8_map3d(&ta2, p.a2, p.K, p.F, p.lda2, 128, 1, true)
-                : w4_map3d(&ta2, p.a2, p.K, p.F, p.lda2);
+    r = QB == 8 ? w8_map3d(&ta2, p.a2, p.K, p.F, p.lda2, p.th, 1, true)
+                : w4_map3d(&ta2, p.a2, p.K, p.F, p.lda2, p.th);
     if (r) return r;
   } else {
     ta2 = ta;
   }
   r = w8_map3d(&tb, p.b, p.K, p.T, p.ldb, BN, kW8Kps, false);
   if (r) return r;
-  const size_t smem = (size_t)fixed + (size_t)stages * STAGE;
+  // The kernel takes all 512 tensor-memory columns of its SM, and tensor memory is claimed by the
+  // running CTA, not by the launch: a second CTA of the same cluster on the same SM would wait
+  // for columns that its partner only frees after the cluster barrier. Asking for more than
+  // half of the SM's shared memory keeps every SM at one CTA of this kernel.
+  size_t smem = (size_t)fixed + (size_t)stages * STAGE;
+  if (smem < 120 * 1024) smem = 120 * 1024;
   auto kern = umma_gemm_w8_kernel<BN, DUAL, QB>;
   static size_t configured = 0;
   if (smem > configured) {
@@ -520,7 +579,7 @@ static int w8_launch(E2hGemmParams& p, cudaStream_t stream) {
   }
   cudaLaunchConfig_t cfg;
   memset(&cfg, 0, sizeof(cfg));
-  cfg.gridDim = dim3((p.F + 127) / 128, (p.T + BN - 1) / BN, p.splitk);
+  cfg.gridDim = dim3((p.F + p.th - 1) / p.th, (p.T + BN - 1) / BN, p.splitk);
   cfg.blockDim = dim3(kW8Threads, 1, 1);
   cfg.dynamicSmemBytes = smem;
   cfg.stream = stream;

@@ -10,10 +10,14 @@
 // argmax with ties going to the lowest index.
 //
 // The k-th largest value is found exactly with a 4-pass, 8-bit radix select over the
-// order-preserving integer image of the fp32 logits; the logits row (<= 128 KiB) stays in L2.
+// order-preserving integer image of the fp32 logits. The row (128 KB at a 32k vocabulary) is
+// copied into shared memory once with 16-byte loads and all five passes read it from there: the
+// passes are chains of dependent loads (a warp-wide match between them), which from L2 cost
+// ~13 us per pass and ~100 us per step; rows that do not fit stay in global memory.
 #include <cuda_runtime.h>
 #include <float.h>
 #include <stdint.h>
+#include <mutex>
 
 #include "launch.cuh"
 #include "ptx.cuh"
@@ -38,7 +42,8 @@ __device__ __forceinline__ uint4 philox(uint4 ctr, uint2 key) {
   return ctr;
 }
 
-constexpr int kSampThreads = 512;
+constexpr int kSampThreads = 1024;
+constexpr int kSampMaxSmemRow = 188 * 1024;     // bytes of one logits row kept in shared memory
 
 // logits   : fp32 [B, ld]
 // pos_ptr  : device scalar, position of the token that produced these logits; the sampled
@@ -50,8 +55,14 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
               int top_k, unsigned long long seed, int* pos_ptr, int advance_pos,
               int* __restrict__ next_tok, int* __restrict__ seq, long long seq_ld, int seq_len,
               int eos_id, int* __restrict__ eos_flag, int* __restrict__ n_unfinished,
-              unsigned int* ticket, const unsigned long long* __restrict__ seed_ptr) {
+              unsigned int* ticket, const unsigned long long* __restrict__ seed_ptr,
+              int row_in_smem) {
+  extern __shared__ __align__(16) float srow[];
   __shared__ unsigned int hist[256];
+  // one histogram per warp: the logits crowd into two or three exponent bins, and a thousand
+  // atomics on one shared-memory word from 32 warps serialise (20 us of the 37 us this kernel
+  // took with a single histogram)
+  __shared__ unsigned int whist[kSampThreads / 32][256];
   __shared__ uint32_t sh_prefix, sh_remaining;
   __shared__ float red_v[kSampThreads / 32];
   __shared__ int red_i[kSampThreads / 32];
@@ -59,6 +70,18 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
   const float* row = logits + (long long)b * ld;
   pdl_wait_prior();
   pdl_launch_dependents();
+  if (row_in_smem) {
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+      const float4* src4 = reinterpret_cast<const float4*>(row);
+      float4* dst4 = reinterpret_cast<float4*>(srow);
+      for (int i = threadIdx.x; i < vocab / 4; i += blockDim.x) dst4[i] = src4[i];
+      for (int i = (vocab & ~3) + threadIdx.x; i < vocab; i += blockDim.x) srow[i] = row[i];
+    } else {
+      for (int i = threadIdx.x; i < vocab; i += blockDim.x) srow[i] = row[i];
+    }
+    __syncthreads();
+    row = srow;
+  }
   const int pos = *pos_ptr;
   // a seed kept in device memory lets one captured graph serve every generation call
   if (seed_ptr != nullptr) seed = *seed_ptr;
@@ -70,28 +93,56 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
     uint32_t prefix = 0, mask = 0;
     uint32_t remaining = top_k;
     for (int shift = 24; shift >= 0; shift -= 8) {
-      for (int i = threadIdx.x; i < 256; i += blockDim.x) hist[i] = 0;
-      __syncthreads();
+      unsigned int* mine = whist[threadIdx.x >> 5];
+      for (int i = threadIdx.x & 31; i < 256; i += 32) mine[i] = 0;
+      __syncwarp();
       for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
         const uint32_t key = float_key(row[i]);
         if ((key & mask) == prefix) {
-          // logits crowd into a few exponent bins: lanes that hit the same bin elect one of
-          // them to add their count, instead of 32 serialised shared-memory atomics
+          // lanes that hit the same bin elect one of them to add their count
           const uint32_t bin = (key >> shift) & 255u;
           const unsigned peers = __match_any_sync(__activemask(), bin);
-          if ((threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&hist[bin], __popc(peers));
+          if ((threadIdx.x & 31) == (unsigned)(__ffs(peers) - 1)) atomicAdd(&mine[bin], __popc(peers));
         }
       }
       __syncthreads();
-      if (threadIdx.x == 0) {
-        uint32_t rem = remaining;
-        int bin = 255;
-        for (; bin > 0; --bin) {
-          if (hist[bin] >= rem) break;
-          rem -= hist[bin];
+      if (threadIdx.x < 256) {
+        unsigned int sum = 0;
+#pragma unroll 8
+        for (int w = 0; w < kSampThreads / 32; ++w) sum += whist[w][threadIdx.x];
+        hist[threadIdx.x] = sum;
+      }
+      __syncthreads();
+      if (threadIdx.x < 32) {
+        // the bin that holds the `remaining`-th largest key: lane l owns bins 8l..8l+7, a
+        // suffix sum over the lanes finds the lane, a short scan the bin
+        const int l = threadIdx.x;
+        uint32_t mine = 0;
+#pragma unroll
+        for (int j = 0; j < 8; ++j) mine += hist[8 * l + j];
+        uint32_t above = mine;                 // keys in bins >= 8l (suffix sum, inclusive)
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+          const uint32_t y = __shfl_down_sync(0xffffffffu, above, o);
+          if (l + o < 32) above += y;
         }
-        sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
-        sh_remaining = rem;
+        const bool has = above >= remaining;   // true for lanes 0..L, L = the lane we want
+        const unsigned m = __ballot_sync(0xffffffffu, has);
+        const int L = m ? 31 - __clz(m) : 0;
+        if (l == L) {
+          uint32_t rem = remaining - (above - mine);   // rank inside this lane's bins
+          int bin = 8 * l + 7;
+          for (; bin > 8 * l; --bin) {
+            if (hist[bin] >= rem) break;
+            rem -= hist[bin];
+          }
+          if (!m) {          // fewer keys than asked for (cannot happen with top_k < vocab)
+            bin = 0;
+            rem = 1;
+          }
+          sh_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
+          sh_remaining = rem;
+        }
       }
       __syncthreads();
       prefix = sh_prefix;
@@ -169,7 +220,24 @@ extern "C" int e2h_sample(const float* logits, long long ld, int B, int vocab, f
                           const unsigned long long* seed_ptr, void* stream) {
   using namespace e2h;
   if (advance_pos && ticket == nullptr) return -1;
-  return (int)launch(sample_kernel, dim3(B), dim3(kSampThreads), 0, (cudaStream_t)stream, logits,
-                     ld, vocab, temperature, top_k, seed, pos_ptr, advance_pos, next_tok, seq,
-                     seq_ld, seq_len, eos_id, eos_flag, n_unfinished, ticket, seed_ptr);
+  const size_t row_bytes = ((size_t)vocab * 4 + 15) / 16 * 16;
+  const int in_smem = row_bytes <= (size_t)kSampMaxSmemRow ? 1 : 0;
+  if (in_smem) {
+    static std::mutex mu;
+    static bool asked[64];
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    std::lock_guard<std::mutex> lock(mu);
+    if (dev >= 0 && dev < 64 && !asked[dev]) {
+      e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               kSampMaxSmemRow);
+      if (e != cudaSuccess) return (int)e;
+      asked[dev] = true;
+    }
+  }
+  return (int)launch(sample_kernel, dim3(B), dim3(kSampThreads), in_smem ? row_bytes : 0,
+                     (cudaStream_t)stream, logits, ld, vocab, temperature, top_k, seed, pos_ptr,
+                     advance_pos, next_tok, seq, seq_ld, seq_len, eos_id, eos_flag, n_unfinished,
+                     ticket, seed_ptr, in_smem);
 }

@@ -152,6 +152,15 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
         choice = pick_stream_tiles(F, K, bn, dual)
         if choice is not None:
             th, kps = choice, 4
+    if (w8 or w4) and not th and splitk == 1 and STREAM_TILES:
+        # the converting kernel is bound by bytes in flight per SM: a tile height that puts a
+        # CTA on (nearly) every SM; rows per tile a multiple of 8 (int8) or 16 (int4)
+        q = 16 if w4 else 8
+        tiles128 = -(-F // 128)
+        if tiles128 * 2 > N_SM and tiles128 <= N_SM:
+            cand = max(64, min(128, -(-(-(-F // N_SM)) // q) * q))
+            if -(-F // cand) <= N_SM:
+                th = cand
     p = GemmParams()
     p.F, p.T, p.K = F, T, K
     p.splitk, p.epi, p.stages = splitk, epi, stages

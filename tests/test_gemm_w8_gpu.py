@@ -36,6 +36,28 @@ def test_w8_linear(T, F, K, splitk):
     assert float(err) < 2e-5, float(err)        # exact integers, fp32 accumulation
 
 
+@pytest.mark.parametrize("F,th,dual", [(1100, 80, False), (1408, 88, False), (1100, 80, True),
+                                       (11008, None, True)])
+def test_w8_lower_tiles(F, th, dual):
+    """Tile heights below 128 rows (what the host picks so that a wide layer covers all SMs):
+    same result as the fp32 reference, rows past the tile and past F never leak."""
+    from easy_to_hard_b200.ops import _lib, gemm
+    T, K = 64, 1024
+    x, w1, s1 = _case(T, F, K, 5)
+    if dual:
+        _, w3, s3 = _case(T, F, K, 6)
+        act = gemm.linear_swiglu(x, w1, w3, scale=torch.cat([s1, s3]), th=th)
+        g, u = _ref(x, w1, s1).bfloat16().float(), _ref(x, w3, s3).bfloat16().float()
+        want = torch.nn.functional.silu(g).bfloat16().float() * u
+        assert float((act.float() - want).abs().max()) < 0.03 * float(want.abs().max()) + 1e-3
+    else:
+        out32 = gemm.linear(x, w1, scale=s1, out_dtype=torch.float32, th=th)
+        want = _ref(x, w1, s1)
+        assert float((out32 - want).abs().max() / want.abs().max()) < 2e-5
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+
+
 def test_w8_residual_and_swiglu():
     from easy_to_hard_b200.ops import _lib, gemm
     T, F, K = 64, 640, 1024
