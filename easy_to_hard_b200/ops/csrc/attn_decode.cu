@@ -438,198 +438,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
   }
 }
 
-// Few (sequence, kv head) pairs (fewer than the streaming kernel's resident CTAs): what counts is
-// the fixed latency per CTA, not the bytes in flight. One CTA per (pair, split) with plain
-// 16-byte loads, no shared-memory ring and no prologue beyond reading the positions; grid
-// (n_kv * B, n_split), the last split of a pair to finish merges the partials (ticket word).
-template <int D, int G>
-__global__ void __launch_bounds__(kWarps * 32)
-attn_decode_direct_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
-                   const __nv_bfloat16* __restrict__ vcache, __nv_bfloat16* __restrict__ out,
-                   float* __restrict__ partial, const int* __restrict__ pos_ptr,
-                   const int* __restrict__ left_pad, int n_head, int n_kv, int smax, float scale,
-                   int n_split, unsigned int* __restrict__ tickets) {
-  constexpr int R = D / 128 > 0 ? D / 128 : 1;       // 8-element groups per lane (D=128 -> 1)
-  constexpr int LPK = D >= 128 ? 16 : D / 8;          // lanes per key row
-  static_assert(D == 64 || D == 128 || D == 256, "head_dim must be 64, 128 or 256");
-  const int b = blockIdx.x / n_kv;
-  const int hk = blockIdx.x - b * n_kv;
-  const int split = blockIdx.y;
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int half = lane / 16;            // which key of the pair this half-warp handles
-  const int hl = lane & 15;
-  const bool lane_active = hl < LPK;
-  const int slot = warp * 2 + half;
-
-  pdl_launch_dependents();   // the successor may start its prologue / weight prefetch already
-  pdl_wait_prior();
-  int pos = *pos_ptr;                    // index of the newest token (already in the cache)
-  // positions come from device memory: keep every cache row that is read inside the allocation
-  if (pos >= smax) pos = smax - 1;
-  if (pos < 0) pos = 0;
-  int start = left_pad ? left_pad[b] : 0;
-  if (start > pos) start = pos;
-  if (start < 0) start = 0;
-  // keys of this split
-  const int total = pos - start + 1;
-  const int per = (total + n_split - 1) / n_split;
-  const int k_begin = start + split * per;
-  const int k_end = min(pos + 1, k_begin + per);
-
-  float qv[G][R][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const int h = hk * G + g;
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      if (lane_active) {
-        const uint4 raw = *reinterpret_cast<const uint4*>(
-            q + ((long long)b * n_head + h) * D + (r * LPK + hl) * 8);
-        unpack8(raw, qv[g][r]);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qv[g][r][i] *= scale;
-      } else {
-#pragma unroll
-        for (int i = 0; i < 8; ++i) qv[g][r][i] = 0.f;
-      }
-    }
-  }
-  float m[G], l[G], acc[G][R][8];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = -FLT_MAX;
-    l[g] = 0.f;
-#pragma unroll
-    for (int r = 0; r < R; ++r)
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[g][r][i] = 0.f;
-  }
-
-  const __nv_bfloat16* kbase = kcache + ((long long)b * n_kv + hk) * smax * D;
-  const __nv_bfloat16* vbase = vcache + ((long long)b * n_kv + hk) * smax * D;
-
-  for (int j0 = k_begin; j0 < k_end; j0 += kSlots * kKeysPerIter) {
-    uint4 kr[kKeysPerIter][R], vr[kKeysPerIter][R];
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int j = j0 + u * kSlots + slot;
-      const bool ok = j < k_end && lane_active;
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        const long long o = (long long)j * D + (r * LPK + hl) * 8;
-        kr[u][r] = ok ? __ldg(reinterpret_cast<const uint4*>(kbase + o)) : make_uint4(0, 0, 0, 0);
-        vr[u][r] = ok ? __ldg(reinterpret_cast<const uint4*>(vbase + o)) : make_uint4(0, 0, 0, 0);
-      }
-    }
-#pragma unroll
-    for (int u = 0; u < kKeysPerIter; ++u) {
-      const int j = j0 + u * kSlots + slot;
-      const bool ok = j < k_end;
-      float kf[R][8], vf[R][8];
-#pragma unroll
-      for (int r = 0; r < R; ++r) {
-        unpack8(kr[u][r], kf[r]);
-        unpack8(vr[u][r], vf[r]);
-      }
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float s = 0.f;
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-#pragma unroll
-          for (int i = 0; i < 8; ++i) s += qv[g][r][i] * kf[r][i];
-        // reduce over the 16 lanes of the half-warp
-        s += __shfl_xor_sync(0xffffffffu, s, 8);
-        s += __shfl_xor_sync(0xffffffffu, s, 4);
-        s += __shfl_xor_sync(0xffffffffu, s, 2);
-        s += __shfl_xor_sync(0xffffffffu, s, 1);
-        if (ok) {
-          const float mn = fmaxf(m[g], s);
-          const float corr = __expf(m[g] - mn);
-          const float pj = __expf(s - mn);
-          l[g] = l[g] * corr + pj;
-#pragma unroll
-          for (int r = 0; r < R; ++r)
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[g][r][i] = acc[g][r][i] * corr + pj * vf[r][i];
-          m[g] = mn;
-        }
-      }
-    }
-  }
-
-  // merge the 8 half-warp partials of the CTA through shared memory
-  __shared__ float sm_m[kSlots][G], sm_l[kSlots][G];
-  __shared__ float sm_acc[kSlots][G][D];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (hl == 0) {
-      sm_m[slot][g] = m[g];
-      sm_l[slot][g] = l[g];
-    }
-    if (lane_active) {
-#pragma unroll
-      for (int r = 0; r < R; ++r)
-#pragma unroll
-        for (int i = 0; i < 8; ++i) sm_acc[slot][g][(r * LPK + hl) * 8 + i] = acc[g][r][i];
-    }
-  }
-  __syncthreads();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx - g * D;
-    float mm = -FLT_MAX;
-#pragma unroll
-    for (int s = 0; s < kSlots; ++s) mm = fmaxf(mm, sm_m[s][g]);
-    float ll = 0.f, a = 0.f;
-#pragma unroll
-    for (int s = 0; s < kSlots; ++s) {
-      const float w = (sm_m[s][g] == -FLT_MAX) ? 0.f : __expf(sm_m[s][g] - mm);
-      ll += sm_l[s][g] * w;
-      a += sm_acc[s][g][d] * w;
-    }
-    const int h = hk * G + g;
-    if (n_split == 1) {
-      out[((long long)b * n_head + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
-    } else {
-      float* pp = partial + (((long long)b * n_head + h) * n_split + split) * (D + 2);
-      pp[d] = a;
-      if (d == 0) {
-        pp[D] = mm;
-        pp[D + 1] = ll;
-      }
-    }
-  }
-  if (n_split == 1 || tickets == nullptr) return;
-  // merge in place of a second launch: the last split of this (sequence, kv head) to finish
-  // combines all of them (the ticket word returns to zero for the next launch)
-  __shared__ int is_last;
-  __threadfence();
-  __syncthreads();
-  if (threadIdx.x == 0) {
-    const unsigned int t = atomicAdd(&tickets[blockIdx.x], 1u);
-    is_last = (t == (unsigned int)n_split - 1) ? 1 : 0;
-    if (is_last) tickets[blockIdx.x] = 0;
-  }
-  __syncthreads();
-  if (!is_last) return;
-  __threadfence();
-  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
-    const int g = idx / D, d = idx - g * D;
-    const int h = hk * G + g;
-    const float* pp = partial + ((long long)b * n_head + h) * n_split * (D + 2);
-    float mm = -FLT_MAX;
-    for (int s = 0; s < n_split; ++s) mm = fmaxf(mm, __ldcg(pp + s * (D + 2) + D));
-    float ll = 0.f, a = 0.f;
-    for (int s = 0; s < n_split; ++s) {
-      const float ms = __ldcg(pp + s * (D + 2) + D);
-      const float w = (ms == -FLT_MAX) ? 0.f : __expf(ms - mm);
-      ll += __ldcg(pp + s * (D + 2) + D + 1) * w;
-      a += __ldcg(pp + s * (D + 2) + d) * w;
-    }
-    out[((long long)b * n_head + h) * D + d] = __float2bfloat16_rn(ll > 0.f ? a / ll : 0.f);
-  }
-}
-
 // Resident CTAs per SM at this pipeline depth (shared memory is what limits them), at most 4.
 static int attn_ctas_per_sm(int D, int G, int stages) {
   // static shared memory of the kernel, plus the 1 KB that the system keeps per resident CTA
@@ -648,11 +456,6 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
     const char* e = getenv("E2H_ATTN_STAGES");
     const int v_ = e ? atoi(e) : 3;
     return v_ < 2 ? 2 : v_ > kAttnMaxStages ? kAttnMaxStages : v_;
-  }();
-  // E2H_ATTN_KERNEL=stream / direct forces one of the two kernels (measurement switch)
-  static const int which = [] {
-    const char* e = getenv("E2H_ATTN_KERNEL");
-    return !e ? 0 : e[0] == 's' ? 1 : e[0] == 'd' ? 2 : 0;
   }();
   static const bool plain_l2 = [] {
     const char* e = getenv("E2H_ATTN_L2HINT");
@@ -683,21 +486,6 @@ static int launch_decode(const void* q, const void* k, const void* v, void* out,
   for (int b0 = 0; b0 < B; b0 += kAttnMaxB) {     // batches beyond kAttnMaxB go in slices
     const int nb = B - b0 < kAttnMaxB ? B - b0 : kAttnMaxB;
     const int resident = n_sm[dev] * attn_ctas_per_sm(D, G, stages);
-    if (max_parts > 1 && which != 1 && (which == 2 || nb * n_kv < resident)) {
-      // few pairs: the direct kernel, split until about eight CTAs sit on every SM
-      int n_split = 1;
-      while (nb * n_kv * n_split < 1024 && 2 * n_split <= max_parts) n_split *= 2;
-      e = launch(attn_decode_direct_kernel<D, G>, dim3(nb * n_kv, n_split), dim3(kWarps * 32), 0,
-                 stream, (const __nv_bfloat16*)q + b0 * q_stride,
-                 (const __nv_bfloat16*)k + (long long)b0 * n_kv * smax * D,
-                 (const __nv_bfloat16*)v + (long long)b0 * n_kv * smax * D,
-                 (__nv_bfloat16*)out + b0 * q_stride,
-                 partial + (long long)b0 * n_head * max_parts * (D + 2), pos,
-                 left_pad ? left_pad + b0 : nullptr, n_head, n_kv, smax, scale, n_split,
-                 tickets + (long long)b0 * n_kv);
-      if (e != cudaSuccess) return (int)e;
-      continue;
-    }
     int fixed_parts = 0;
     if (max_parts <= 1) {
       fixed_parts = 1;
