@@ -303,37 +303,55 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         // the values are in registers: the stage can be refilled while they are used
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&bar_empty[s]));
+        // the four keys of this half-warp go through the running softmax together: one
+        // rescale of the accumulator per four keys instead of one per key (the kernel is close
+        // to instruction-issue bound: 63 % issue-active at 0.86 of the copy bandwidth)
+        float kf[kKeysPerIter][R][8];
 #pragma unroll
-        for (int u = 0; u < kKeysPerIter; ++u) {
-          const bool ok = j0 + u * kSlots + slot <= pos;
-          float kf[R][8], vf[R][8];
+        for (int u = 0; u < kKeysPerIter; ++u)
 #pragma unroll
-          for (int r = 0; r < R; ++r) {
-            unpack8(kr[u][r], kf[r]);
-            unpack8(vr[u][r], vf[r]);
-          }
+          for (int r = 0; r < R; ++r) unpack8(kr[u][r], kf[u][r]);
 #pragma unroll
-          for (int g = 0; g < G; ++g) {
-            float sc = 0.f;
+        for (int g = 0; g < G; ++g) {
+          float sc[kKeysPerIter];
+#pragma unroll
+          for (int u = 0; u < kKeysPerIter; ++u) {
+            float d = 0.f;
 #pragma unroll
             for (int r = 0; r < R; ++r)
 #pragma unroll
-              for (int i = 0; i < 8; ++i) sc += qv[g][r][i] * kf[r][i];
-            // reduce over the 16 lanes of the half-warp
-            sc += __shfl_xor_sync(0xffffffffu, sc, 8);
-            sc += __shfl_xor_sync(0xffffffffu, sc, 4);
-            sc += __shfl_xor_sync(0xffffffffu, sc, 2);
-            sc += __shfl_xor_sync(0xffffffffu, sc, 1);
-            if (ok) {
-              const float mn = fmaxf(m[g], sc);
-              const float corr = __expf(m[g] - mn);
-              const float pj = __expf(sc - mn);
-              l[g] = l[g] * corr + pj;
+              for (int i = 0; i < 8; ++i) d += qv[g][r][i] * kf[u][r][i];
+            sc[u] = d;
+          }
+          // reduce over the 16 lanes of the half-warp, the four keys interleaved
 #pragma unroll
-              for (int r = 0; r < R; ++r)
+          for (int o = 8; o > 0; o >>= 1)
 #pragma unroll
-                for (int i = 0; i < 8; ++i) acc[g][r][i] = acc[g][r][i] * corr + pj * vf[r][i];
-              m[g] = mn;
+            for (int u = 0; u < kKeysPerIter; ++u) sc[u] += __shfl_xor_sync(0xffffffffu, sc[u], o);
+          float mn = m[g];
+#pragma unroll
+          for (int u = 0; u < kKeysPerIter; ++u)
+            if (j0 + u * kSlots + slot <= pos) mn = fmaxf(mn, sc[u]);
+          const float corr = __expf(m[g] - mn);
+          float pj[kKeysPerIter], psum = 0.f;
+#pragma unroll
+          for (int u = 0; u < kKeysPerIter; ++u) {
+            pj[u] = (j0 + u * kSlots + slot <= pos) ? __expf(sc[u] - mn) : 0.f;
+            psum += pj[u];
+          }
+          l[g] = l[g] * corr + psum;
+          m[g] = mn;
+#pragma unroll
+          for (int r = 0; r < R; ++r) {
+            float vf[kKeysPerIter][8];
+#pragma unroll
+            for (int u = 0; u < kKeysPerIter; ++u) unpack8(vr[u][r], vf[u]);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              float a = acc[g][r][i] * corr;
+#pragma unroll
+              for (int u = 0; u < kKeysPerIter; ++u) a += pj[u] * vf[u][i];
+              acc[g][r][i] = a;
             }
           }
         }

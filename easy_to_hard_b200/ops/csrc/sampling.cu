@@ -9,8 +9,12 @@
 // and never materialises probabilities. Greedy decoding (temperature == 0) is the plain
 // argmax with ties going to the lowest index.
 //
-// The k-th largest value is found exactly with a 4-pass, 8-bit radix select over the
-// order-preserving integer image of the fp32 logits. The row (128 KB at a 32k vocabulary) is
+// The k-th largest value is found exactly. Fast path (row in shared memory, top_k <= 256): the
+// k-th largest of 256 group maxima is a lower bound of the pivot (at least k entries reach it),
+// so only the handful of entries at or above it are collected (typically 50-70 of 32016) and
+// the pivot is picked among them by rank counting; the sampling pass then also runs over those
+// candidates only. Otherwise, or if more than 2048 entries reach the bound (many equal logits):
+// a 4-pass, 8-bit radix select over the order-preserving integer image of the fp32 logits. The row (128 KB at a 32k vocabulary) is
 // copied into shared memory once with 16-byte loads and all five passes read it from there: the
 // passes are chains of dependent loads (a warp-wide match between them), which from L2 cost
 // ~13 us per pass and ~100 us per step; rows that do not fit stay in global memory.
@@ -44,6 +48,8 @@ __device__ __forceinline__ uint4 philox(uint4 ctr, uint2 key) {
 
 constexpr int kSampThreads = 1024;
 constexpr int kSampMaxSmemRow = 188 * 1024;     // bytes of one logits row kept in shared memory
+constexpr int kSampGroups = 256;                // group maxima of the fast path
+constexpr int kSampCandMax = 2048;              // candidates the fast path can hold
 
 // logits   : fp32 [B, ld]
 // pos_ptr  : device scalar, position of the token that produced these logits; the sampled
@@ -64,6 +70,13 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
   // took with a single histogram)
   __shared__ unsigned int whist[kSampThreads / 32][256];
   __shared__ uint32_t sh_prefix, sh_remaining;
+  // the fast path's arrays live in the radix histograms' storage (the two never overlap in time)
+  static_assert(kSampThreads + 2 * kSampCandMax <= (kSampThreads / 32) * 256, "fast-path arrays");
+  uint32_t* gmax = &whist[0][0];                 // per-thread, then per-group maximum keys
+  uint32_t* cand_key = gmax + kSampThreads;
+  int* cand_idx = reinterpret_cast<int*>(cand_key + kSampCandMax);
+  __shared__ uint32_t sh_bound, sh_pivot;
+  __shared__ int n_cand;
   __shared__ float red_v[kSampThreads / 32];
   __shared__ int red_i[kSampThreads / 32];
   const int b = blockIdx.x;
@@ -88,7 +101,65 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
   const bool greedy = temperature <= 0.f;
 
   uint32_t pivot_key = 0;  // keep everything
-  if (!greedy && top_k > 0 && top_k < vocab) {
+  bool have_cands = false; // the entries >= pivot_key are (among) the first n_cand candidates
+  if (!greedy && top_k > 0 && top_k < vocab && row_in_smem && top_k <= kSampGroups) {
+    // ---- fast path
+    uint32_t lm = 0;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) lm = max(lm, float_key(row[i]));
+    gmax[threadIdx.x] = lm;
+    if (threadIdx.x == 0) n_cand = 0;
+    __syncthreads();
+    if (threadIdx.x < kSampGroups) {
+      uint32_t g = lm;
+      for (int t = threadIdx.x + kSampGroups; t < kSampThreads; t += kSampGroups) g = max(g, gmax[t]);
+      lm = g;
+    }
+    __syncthreads();
+    if (threadIdx.x < kSampGroups) gmax[threadIdx.x] = lm;
+    __syncthreads();
+    if (threadIdx.x < kSampGroups) {
+      // rank of this group's maximum among the 256 (ties broken by group index): the one of
+      // rank top_k - 1 is the bound
+      int gt = 0;
+      for (int j = 0; j < kSampGroups; ++j) {
+        const uint32_t o = gmax[j];
+        gt += (o > lm || (o == lm && j < (int)threadIdx.x)) ? 1 : 0;
+      }
+      if (gt == top_k - 1) sh_bound = lm;
+    }
+    __syncthreads();
+    const uint32_t bound = sh_bound;
+    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+      const uint32_t key = float_key(row[i]);
+      if (key >= bound) {
+        const int slot = atomicAdd(&n_cand, 1);
+        if (slot < kSampCandMax) {
+          cand_key[slot] = key;
+          cand_idx[slot] = i;
+        }
+      }
+    }
+    __syncthreads();
+    const int n = n_cand;
+    if (n <= kSampCandMax) {
+      // the k-th largest key: the candidate with fewer than k keys above it and at least k at
+      // or above it (all such candidates carry the same key)
+      for (int c = threadIdx.x; c < n; c += blockDim.x) {
+        const uint32_t v = cand_key[c];
+        int above = 0, at_or_above = 0;
+        for (int j = 0; j < n; ++j) {
+          const uint32_t o = cand_key[j];
+          above += o > v ? 1 : 0;
+          at_or_above += o >= v ? 1 : 0;
+        }
+        if (above < top_k && top_k <= at_or_above) sh_pivot = v;
+      }
+      __syncthreads();
+      pivot_key = sh_pivot;
+      have_cands = true;
+    }
+  }
+  if (!greedy && top_k > 0 && top_k < vocab && !have_cands) {
     // radix select of the k-th largest key, most significant byte first
     uint32_t prefix = 0, mask = 0;
     uint32_t remaining = top_k;
@@ -155,7 +226,9 @@ sample_kernel(const float* __restrict__ logits, long long ld, int vocab, float t
   const float inv_t = greedy ? 1.f : 1.f / fmaxf(temperature, 1e-5f);
   float best = -FLT_MAX;
   int best_i = 0x7fffffff;
-  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+  const int n_scan = have_cands ? n_cand : vocab;
+  for (int c = threadIdx.x; c < n_scan; c += blockDim.x) {
+    const int i = have_cands ? cand_idx[c] : c;
     const float x = row[i];
     if (float_key(x) < pivot_key) continue;
     float score = x * inv_t;
