@@ -55,7 +55,7 @@ def parse():
     ap.add_argument("--steps", type=int, default=3)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode", choices=["decode", "sft"],
+    ap.add_argument("--workload", default="decode", choices=["decode", "sft", "prm"],
                     help="decode: batched generation (headline); sft: full-parameter SFT step")
     ap.add_argument("--quant", default="none", choices=["none", "int8", "int4"],
                     help="decode: weight-only quantisation of the linears (int4: groups of 128)")
@@ -494,6 +494,109 @@ def run_ours_sft(a):
         print(json.dumps(out), flush=True)
 
 
+PRM_SEQ, PRM_PER_DEVICE = 1024, 16
+
+
+def run_ours_prm(a):
+    """Process-reward-model training step of the 7B architecture (the reference's recipe,
+    examples/README.md:59-79 of the reference: TP 1, sharded data parallel over all ranks, 16
+    sequences of 1024 tokens per device): backbone + two-row reward head, weighted per-token
+    binary cross-entropy, fp32 master weights and moments, bf16 compute. value = trained
+    tokens/s of the whole job (weak scaling: the global batch grows with N)."""
+    import torch
+    rank, local, world = dist_setup(a.gpus)
+    from easy_to_hard_b200.models.model import ModelArgs
+    from easy_to_hard_b200.models import tp
+    from easy_to_hard_b200.models.reward_model import (RewardArgs, RewardModel,
+                                                      apply_reward_modeling_head)
+    from easy_to_hard_b200.parallel import groups
+    from easy_to_hard_b200.parallel.fsdp import ShardedDataParallel
+    from easy_to_hard_b200.training import TrainStepper, pointwise_reward_loss
+    from easy_to_hard_b200.utils.memory_efficient_adam import MemoryEfficientAdamW
+    from easy_to_hard_b200.ops import _lib
+
+    tp.initialize_model_parallel(1)
+    cfg = ModelArgs.from_name(MODEL)
+    torch.manual_seed(0)
+    with torch.device("cuda"):
+        model = RewardModel(RewardArgs(backbone_args=cfg), freeze_tok_embeddings=True,
+                            freeze_output=True, freeze_norm=True).to(torch.bfloat16)
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    for name, t in list(model.named_parameters()) + list(model.named_buffers()):
+        if t.dim() == 2:
+            t.data.normal_(0.0, 0.02, generator=g)
+    apply_reward_modeling_head(model.backbone_model, requires_grad=True, init_sceheme="random")
+    model.requires_grad_(True)
+    sdp = ShardedDataParallel(model, process_group=groups.get_data_parallel_group(),
+                              param_dtype=torch.float32, compute_dtype=torch.bfloat16,
+                              reduce_dtype=torch.bfloat16)
+    sdp.train()
+    torch.cuda.empty_cache()
+    opt = MemoryEfficientAdamW(list(sdp.optimizer_parameters()), lr=2e-5, betas=(0.9, 0.95),
+                               weight_decay=0.0, optim_dtype=torch.float32,
+                               optim_device=torch.device("cuda"))
+    stepper = TrainStepper(sdp, opt, None, pointwise_reward_loss, 1.0)
+    gen = torch.Generator().manual_seed(200 + rank)
+    host = []
+    for _ in range(a.steps + a.warmup):
+        ids = torch.randint(0, cfg.vocab_size, (PRM_PER_DEVICE, PRM_SEQ), generator=gen)
+        labels = torch.randint(0, 2, (PRM_PER_DEVICE, PRM_SEQ), generator=gen).float()
+        # step boundaries (one position in ~24) carry the weight, as the step-level labels do
+        weights = (torch.rand(PRM_PER_DEVICE, PRM_SEQ, generator=gen) < 1 / 24).float()
+        host.append(tuple(t.pin_memory() for t in (ids, labels, weights)))
+    dev = [tuple(t.cuda() for t in b) for b in host]
+    host_loss = torch.zeros(1, dtype=torch.float32).pin_memory()
+    micro = max(1, min(a.micro, PRM_PER_DEVICE))
+
+    def step_device(i):
+        stepper.step(*dev[i % len(dev)], micro_batch_size=micro)
+
+    def step_e2e(i):
+        batch = tuple(t.to("cuda", non_blocking=True) for t in host[i % len(host)])
+        loss, _ = stepper.step(*batch, micro_batch_size=micro)
+        host_loss.copy_(loss.float().reshape(1), non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+
+    for i in range(a.warmup):
+        step_device(i)
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    ms = timed(lambda i: step_device(a.warmup + i), a.steps)
+    clocks = sampler.stop() if rank == 0 else None
+    ms_e2e = timed(lambda i: step_e2e(a.warmup + i), a.steps)
+    status = _lib.read_status()
+    toks = PRM_PER_DEVICE * world * PRM_SEQ * a.steps
+    n_micro = -(-PRM_PER_DEVICE // micro)
+    kept = int(getattr(sdp, "_keep_budget", 0) > 0)
+    launches = (cfg.n_layer * (9 + 17 + (0 if kept else 9)) * n_micro + cfg.n_layer * 2 + 40) \
+        * a.steps
+    if rank == 0:
+        flops = 6 * 6.6e9 * PRM_PER_DEVICE * world * PRM_SEQ
+        out = {
+            "metric": "prm_train_tokens_per_s", "value": toks / (ms / 1e3), "unit": "tokens/s",
+            "n_gpus": world, "steps": a.steps, "warmup": a.warmup, "ms_per_step": ms / a.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic (random token ids, labels and step weights, random-init weights)",
+            "impl": "ours",
+            "config": {"model": "Llemma-7B architecture + 2-row reward head",
+                       "global_batch": PRM_PER_DEVICE * world, "seq_len": PRM_SEQ,
+                       "parallelism": f"tp1xfsdp{world}",
+                       "optimizer": "AdamW lr 2e-5 betas 0.9/0.95, fp32 master weights, fp32 "
+                                    "moments, bf16 compute, gradient clipping at 1.0",
+                       "loss": "weighted per-token binary cross-entropy",
+                       "l2": "inputs larger than L2 (13 GB of bf16 weights per pass)"},
+            "impl_notes": {"micro_batch": micro,
+                           "model_tflops_per_gpu": flops / (ms / a.steps / 1e3) / 1e12 / world,
+                           "peak_memory_gib": round(torch.cuda.max_memory_allocated() / 2 ** 30, 1)},
+            "clocks": clocks,
+            "e2e": {"value": toks / (ms_e2e / 1e3), "unit": "tokens/s",
+                    "h2d_bytes_per_step": PRM_PER_DEVICE * PRM_SEQ * 16, "d2h_bytes_per_step": 4},
+            "gpu_launches": launches, "kernel_status": status,
+        }
+        print(json.dumps(out), flush=True)
+
+
 def run_reference(a):
     """The unmodified reference on the same workload: its own generate() for decode, its own
     training step (FSDP1, its AdamW, its tensor-parallel hooks) for SFT."""
@@ -511,6 +614,8 @@ def run_reference(a):
         from baseline import reference_runner, reference_sft_runner
     except Exception as e:  # noqa: BLE001
         return unavailable(f"reference runner import failed: {type(e).__name__}: {e}")
+    if a.workload == "prm":
+        return unavailable("no reference arm is wired for the reward-model training workload")
     try:
         if a.workload == "sft":
             reference_sft_runner.run(a, dict(seq=SFT_SEQ, global_batch=SFT_GLOBAL_BATCH,
@@ -530,6 +635,8 @@ if __name__ == "__main__":
         run_reference(args)
     elif args.workload == "sft":
         run_ours_sft(args)
+    elif args.workload == "prm":
+        run_ours_prm(args)
     else:
         run_ours(args)
     finish()

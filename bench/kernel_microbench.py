@@ -77,6 +77,22 @@ def cases(T: int, B: int, S: int, ctx: int):
     att = 4.0 * B * HEADS * S * S * HEAD_DIM / 2          # causal: half of the score matrix
     out["flash_fwd"] = (lambda: flash.flash_fwd(q, k, v, None, return_lse=True), att, 0)
     out["flash_bwd"] = (lambda: flash.flash_bwd(q, k, v, o, do, lse), 2.5 * att, 0)
+    # the bar on the same box: PyTorch's scaled_dot_product_attention with the flash backend,
+    # which is what the reference model calls (models/model.py:338-342 of the reference)
+    from torch.nn.attention import SDPBackend, sdpa_kernel
+    qs, ks, vs = (t.transpose(1, 2).detach().clone().requires_grad_(True) for t in (q, k, v))
+    dos = do.transpose(1, 2).contiguous()
+
+    def sdpa_fwd():
+        with sdpa_kernel(SDPBackend.FLASH_ATTENTION):
+            return torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True)
+
+    def sdpa_fwd_bwd():
+        sdpa_fwd().backward(dos)
+        qs.grad = ks.grad = vs.grad = None
+
+    out["sdpa_flash_fwd"] = (lambda: sdpa_fwd(), att, 0)
+    out["sdpa_flash_fwd_bwd"] = (sdpa_fwd_bwd, 3.5 * att, 0)
     # decode: 64 rows
     xd = _bf(64, DIM)
     hd = _bf(64, DIM)

@@ -283,8 +283,30 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     int s = 0;
     uint32_t ph = 0;
     const int gshift = QB == 4 ? __ffs(p.groupsize) - 1 : 0;   // group size is a power of two
+    // int4: the (scale, zero) pair of this row's group is a global load; the pair of the next
+    // stage is fetched one iteration ahead so that its latency hides behind the barrier waits
+    // and the conversion of the current stage
+    __nv_bfloat162 sz_next[NMAT];
+    auto load_sz = [&](int it_) {
+      if constexpr (QB == 4) {
+        const int f = f0 + row;
+        const int kglob = (kb_begin + it_ * kW8Kps + half) * 64;
+#pragma unroll
+        for (int m = 0; m < NMAT; ++m) {
+          const __nv_bfloat162* szp = static_cast<const __nv_bfloat162*>(m == 0 ? p.qsz : p.qsz2);
+          sz_next[m] = (f < p.F && row < TH && it_ < n_it)
+                           ? szp[(long long)(kglob >> gshift) * p.F + f]
+                           : __floats2bfloat162_rn(0.f, 0.f);
+        }
+      }
+    };
+    load_sz(0);
     for (int it = 0; it < n_it; ++it) {
       const int c = it % kW8Conv;
+      __nv_bfloat162 sz_cur[NMAT];
+#pragma unroll
+      for (int m = 0; m < NMAT; ++m) sz_cur[m] = sz_next[m];
+      load_sz(it + 1);
       const int s_cur = s;
       const uint32_t ph_cur = ph;
       if (++s == stages) {
@@ -323,12 +345,7 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             // c ^ ((row >> 1) & 3)); this thread's 64 k are chunks 2*half and 2*half + 1.
             // One (scale, zero) pair per feature and group: [K / g][F][2] bf16.
             const uint8_t* src = st + m * AQ_BYTES + row * 64;
-            const int f = f0 + row;
-            const int kglob = (kb_begin + it * kW8Kps + half) * 64;
-            const __nv_bfloat162* szp =
-                static_cast<const __nv_bfloat162*>(m == 0 ? p.qsz : p.qsz2);
-            __nv_bfloat162 pair = __floats2bfloat162_rn(0.f, 0.f);
-            if (f < p.F) pair = szp[(long long)(kglob >> gshift) * p.F + f];
+            const __nv_bfloat162 pair = sz_cur[m];
             const __nv_bfloat162 sc2 = __bfloat162bfloat162(pair.x);
             const __nv_bfloat162 zr2 = __bfloat162bfloat162(pair.y);
             const int sw4 = (row >> 1) & 3;
