@@ -95,7 +95,7 @@ def main():
                     Fn.fused_residual_rmsnorm(h, nw, 1e-5, partials=part32, h_out=h, x_out=xn)
                 else:
                     gemm.linear(act, w2[k], out=sync.partial_out(i, B),
-                                signal=sync.flag_a_remote(i),
+                                signal=sync.flag_a_signal(i),
                                 ticket=sync.gemm_ticket[i:i + 1])
                     sync.reduce_norm(i, h, h, nw, 1e-5, B, xn_out=xn)
                 gemm.linear(xn, w1[k], out=act)

@@ -204,7 +204,7 @@ class DecodeEngine:
             Fn.fused_residual_rmsnorm(h, next_norm_w, self.eps, partials=part, h_out=h_out,
                                       x_out=x_out)
         else:
-            gemm.linear(x, w, out=sync.partial_out(point, T), signal=sync.flag_a_remote(point),
+            gemm.linear(x, w, out=sync.partial_out(point, T), signal=sync.flag_a_signal(point),
                         ticket=sync.gemm_ticket[point:point + 1], scale=sc)
             sync.reduce_norm(point, h, h_out, next_norm_w, self.eps, T, xn_out=x_out)
         self._count(2)
@@ -229,7 +229,7 @@ class DecodeEngine:
         if self.vocab_parallel:
             pt = self.n_points - 1
             gemm.linear(x, m.output.weight, out=self.logits_shard[:B],
-                        signal=self.sync.flag_a_remote(pt),
+                        signal=self.sync.flag_a_signal(pt),
                         ticket=self.sync.gemm_ticket[pt:pt + 1])
             self.sync.gather_logits(pt, B, self.vocab_local, logits)
             self._count(1)

@@ -431,7 +431,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       }
     }
     if (staged && et == 0) {
-      if (p.n_signal > 0) {
+      if (p.n_signal != 0) {
         // a completion signal follows: the TMA stores must have been written to global memory,
         // not merely have read their shared-memory source, before peers are told to read
         asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
@@ -442,7 +442,7 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   }
 
-  if (p.n_signal > 0) __threadfence();
+  if (p.n_signal != 0) __threadfence();
   tc_fence_before();
   __syncthreads();
   if constexpr (PAIR) {
@@ -453,12 +453,16 @@ umma_gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   } else {
     if (warp == 1) tmem_dealloc(tmem_base, 512);
   }
-  if (p.n_signal > 0 && threadIdx.x == 0) {
+  if (p.n_signal != 0 && threadIdx.x == 0) {
     __threadfence();
     if (atomicAdd(p.ticket, 1u) == gridDim.x - 1) {
       *p.ticket = 0;
       __threadfence_system();
-      for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+      if (p.n_signal < 0) {   // signal[0] is the word's multicast address: one add reaches all
+        multimem_red_release_sys_add(p.signal[0], 1);
+      } else {
+        for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+      }
     }
   }
 }

@@ -435,12 +435,12 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
   }
 
   if (warp == 2 && lane == 0) E2H_PHASE(p.phase_clock, 9);
-  if (p.n_signal > 0) __threadfence();  // this thread's output is visible GPU-wide (in L2)
+  if (p.n_signal != 0) __threadfence();  // this thread's output is visible GPU-wide (in L2)
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, Plan::tmem_cols);
   if (threadIdx.x == 32) E2H_PHASE(p.phase_clock, 10);
-  if (p.n_signal > 0 && threadIdx.x == 0) {
+  if (p.n_signal != 0 && threadIdx.x == 0) {
     // the last CTA of the grid tells every tensor-parallel peer that this rank's partial
     // output is complete: one release-add on the flag word it owns in each peer's memory
     __threadfence();
@@ -448,7 +448,11 @@ umma_gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant_
     if (atomicAdd(p.ticket, 1u) == total - 1) {
       *p.ticket = 0;
       __threadfence_system();
-      for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+      if (p.n_signal < 0) {   // signal[0] is the word's multicast address: one add reaches all
+        multimem_red_release_sys_add(p.signal[0], 1);
+      } else {
+        for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+      }
     }
   }
 }

@@ -56,7 +56,9 @@ struct E2hGemmParams {
                          // leaves with 16-byte accesses (gemm_epilogue.cuh)
   int kps;               // 64-wide k blocks per pipeline stage (1..8): amortises the barrier
                          // hand-shake when the per-block tensor work is tiny (decode)
-  int n_signal;          // > 0: bump signal[0..n_signal) by one when the whole grid is done
+  int n_signal;          // > 0: bump signal[0..n_signal) by one when the whole grid is done;
+                         // -1: signal[0] is a multicast address, one multimem.red bumps the
+                         // word on every GPU of the mapping
   int* signal[8];        // flag words (local or peer-GPU memory), one per tensor-parallel rank
   unsigned int* ticket;  // grid completion counter (local, zero between launches)
   int a_tiled;           // A (and A2) stored tile-major: [F/tf][ceil(K/64)][tf][64], zero padded

@@ -477,17 +477,21 @@ umma_gemm_w8_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
     if (acc_ok) flush_tile(p, stile, TH, f0, t0 + rank * slice, slice, threadIdx.x - 64, 256);
   }
 
-  if (p.n_signal > 0) __threadfence();
+  if (p.n_signal != 0) __threadfence();
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
-  if (p.n_signal > 0 && threadIdx.x == 0) {
+  if (p.n_signal != 0 && threadIdx.x == 0) {
     __threadfence();
     const unsigned int total = gridDim.x * gridDim.y * gridDim.z;
     if (atomicAdd(p.ticket, 1u) == total - 1) {
       *p.ticket = 0;
       __threadfence_system();
-      for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+      if (p.n_signal < 0) {   // signal[0] is the word's multicast address: one add reaches all
+        multimem_red_release_sys_add(p.signal[0], 1);
+      } else {
+        for (int r = 0; r < p.n_signal; ++r) red_release_sys_add(p.signal[r], 1);
+      }
     }
   }
 }

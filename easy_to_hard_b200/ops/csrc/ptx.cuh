@@ -440,6 +440,11 @@ __device__ __forceinline__ void red_release_sys_add(int* p, int v) {
   asm volatile("red.release.sys.global.add.s32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 // Bounded wait for *p >= want. Returns false (and records kStatusTimeoutFlag) on time-out.
+// The same add on one word of every GPU of a multicast (NVSwitch) mapping at once: `mc` is the
+// word's address in the multicast view of a symmetric allocation.
+__device__ __forceinline__ void multimem_red_release_sys_add(int* mc, int v) {
+  asm volatile("multimem.red.release.sys.global.add.u32 [%0], %1;" ::"l"(mc), "r"(v) : "memory");
+}
 __device__ __forceinline__ bool wait_flag_ge(const int* p, int want, int* status,
                                              long long limit = kWaitLimitCycles) {
   const long long t0 = clock64();

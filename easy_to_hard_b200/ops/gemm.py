@@ -73,6 +73,15 @@ def pick_tiles(F: int, T: int, K: int, dual: bool, splitk: Optional[int], bn: Op
     return bn, splitk, stages, tf, kps
 
 
+class MulticastSignal:
+    """``signal=`` for a GEMM whose completion flag lives in a symmetric allocation with an
+    NVSwitch multicast mapping: the flag word's address in the multicast view. The last CTA
+    bumps the word on every GPU with one ``multimem.red`` instead of one remote add per rank."""
+
+    def __init__(self, address: int):
+        self.address = int(address)
+
+
 def pick_stream_tiles(F: int, K: int, bn: int, dual: bool):
     """Feature-tile height of a skinny K-major GEMM that runs without split-K, or None to keep
     128-row tiles. The kernel is a weight stream: with 128-row tiles a wide layer leaves SMs
@@ -168,7 +177,12 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, epi: int, out: Optional[torch.Tens
     p.bn, p.dual, p.accumulate, p.pdl = bn, int(dual), int(accumulate), int(pdl)
     p.tf = tf
     p.th = th
-    if signal:
+    if isinstance(signal, MulticastSignal):
+        assert ticket is not None
+        p.n_signal = -1
+        p.signal[0] = signal.address
+        p.ticket = ticket.data_ptr()
+    elif signal:
         assert ticket is not None and len(signal) <= 8
         p.n_signal = len(signal)
         for i, f in enumerate(signal):

@@ -449,6 +449,19 @@ class TPReduceSync:
         off = self.flag_a_off + point * 32 + 4 * self.rank
         return [self.buf.peer_ptr(r, off) for r in range(self.world)]
 
+    def flag_a_signal(self, point: int):
+        """What a producer GEMM takes as ``signal=``: with a multicast mapping the one address
+        through which a single ``multimem.red`` raises this rank's flag-A word on every rank
+        (the per-rank adds of ``flag_a_remote`` cost a microsecond each at eight ranks),
+        otherwise the list of per-rank addresses."""
+        import os
+        if self.buf.multicast_ptr and self.world > 1 and \
+                os.environ.get("E2H_MULTIMEM_SIGNAL", "1") != "0":
+            from ..ops.gemm import MulticastSignal
+            return MulticastSignal(self.buf.multicast_ptr + self.flag_a_off + point * 32
+                                   + 4 * self.rank)
+        return self.flag_a_remote(point)
+
     def flag_a(self, point: int) -> torch.Tensor:
         return self.buf.view(self.flag_a_off + point * 32, (8,), torch.int32)
 
