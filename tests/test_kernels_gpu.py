@@ -111,6 +111,36 @@ def test_attn_decode_shared_pairs_merge_in_kernel_and_replay():
     _status_ok()
 
 
+@pytest.mark.parametrize("top_k,ties", [(50, False), (1, False), (256, False), (300, False),
+                                        (50, True), (3, True)])
+def test_sampler_pivot_paths_keep_exactly_the_top_k(top_k, ties):
+    """The top-k pivot comes from the candidate path (row in shared memory, k <= 256), from
+    the radix select (k > 256) or from the radix select as the fall-back (more entries tie at
+    the bound than the candidate list holds): in every case a draw is one of the entries
+    whose value is at least the k-th largest, and over many draws all of them turn up."""
+    from easy_to_hard_b200.ops import functional as Fn
+    B, V = 32, 32016
+    g = torch.Generator(device="cuda").manual_seed(77)
+    row = torch.randn(V, device="cuda", generator=g) * 2
+    if ties:
+        row[torch.randperm(V, device="cuda", generator=g)[:6000]] = 7.5   # 6000 equal maxima
+    logits = row[None].expand(B, V).contiguous()
+    kth = row.topk(top_k).values[-1]
+    allowed = row >= kth                      # ties with the pivot are kept, as the reference does
+    pos = torch.zeros(1, dtype=torch.int32, device="cuda")
+    nxt = torch.zeros(B, dtype=torch.int32, device="cuda")
+    seen = torch.zeros(V, dtype=torch.bool, device="cuda")
+    for it in range(40 if allowed.sum() < 400 else 8):
+        pos.fill_(it)
+        Fn.sample(logits, temperature=1.5, top_k=top_k, seed=99, pos=pos, next_tok=nxt,
+                  advance_pos=False)
+        assert allowed[nxt.long()].all()
+        seen[nxt.long()] = True
+    if int(allowed.sum()) <= 50:
+        assert int(seen.sum()) >= min(int(allowed.sum()), 20)
+    _status_ok()
+
+
 def test_sampler_greedy_topk_and_bookkeeping():
     from easy_to_hard_b200.ops import functional as Fn
     B, V = 16, 32016
