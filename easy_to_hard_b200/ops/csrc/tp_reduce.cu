@@ -292,7 +292,11 @@ __global__ void tp_embed_partial_kernel(const int* __restrict__ tokens,
     if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
       *ticket = 0;
       __threadfence_system();
-      for (int r = 0; r < n; ++r) red_release_sys_add(static_cast<int*>(flag_a_remote.p[r]), 1);
+      if (n < 0) {   // p[0] is the word's multicast address: one add reaches every rank
+        multimem_red_release_sys_add(static_cast<int*>(flag_a_remote.p[0]), 1);
+      } else {
+        for (int r = 0; r < n; ++r) red_release_sys_add(static_cast<int*>(flag_a_remote.p[r]), 1);
+      }
     }
   }
 }
@@ -476,9 +480,11 @@ int e2h_tp_rows(int ops, const void* h_in, void* h_out, const void* weight,
 int e2h_tp_embed_partial(const int* tokens, const void* table, int v0, int rows_local, void* part,
                          int T, int dim, const void* const* flag_a_remote, int n,
                          unsigned int* ticket, void* stream) {
-  if (dim % 8 || n < 1 || n > 8 || T < 1) return -1;
+  // n == -1: flag_a_remote[0] is the multicast address of the flag word
+  if (dim % 8 || n == 0 || n < -1 || n > 8 || T < 1) return -1;
   TpPtrs f;
-  for (int i = 0; i < 8; ++i) f.p[i] = i < n ? const_cast<void*>(flag_a_remote[i]) : nullptr;
+  const int n_ptr = n < 0 ? 1 : n;
+  for (int i = 0; i < 8; ++i) f.p[i] = i < n_ptr ? const_cast<void*>(flag_a_remote[i]) : nullptr;
   return (int)launch(tp_embed_partial_kernel, dim3(T), dim3(128), 0,
                      static_cast<cudaStream_t>(stream), tokens,
                      static_cast<const __nv_bfloat16*>(table), v0, rows_local,

@@ -558,11 +558,17 @@ class TPReduceSync:
         T = tokens.numel()
         assert T <= self.T and tokens.dtype == torch.int32 and table.shape[1] == self.dim
         fa = (C.c_void_p * 8)()
-        for r, p in enumerate(self.flag_a_remote(point)):
-            fa[r] = p
+        sig = self.flag_a_signal(point)
+        if isinstance(sig, list):
+            n_sig = self.world
+            for r, p in enumerate(sig):
+                fa[r] = p
+        else:                       # one multimem.red on the flag's multicast address
+            n_sig = -1
+            fa[0] = sig.address
         rc = _lib.lib().e2h_tp_embed_partial(
             tokens.data_ptr(), table.data_ptr(), int(v0), table.shape[0],
-            self.partial_out(point, T).data_ptr(), T, self.dim, fa, self.world,
+            self.partial_out(point, T).data_ptr(), T, self.dim, fa, n_sig,
             self.gemm_ticket[point:point + 1].data_ptr(), _lib.stream())
         _lib.check(rc, "tp_embed_partial")
 
