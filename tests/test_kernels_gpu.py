@@ -71,7 +71,8 @@ def test_rmsnorm_bwd_and_swiglu_bwd():
 
 @pytest.mark.parametrize("B,n_head,n_kv,D,pos,n_split", [
     (64, 32, 32, 128, 300, 1), (3, 8, 2, 128, 77, 1), (2, 8, 8, 64, 40, 4), (1, 32, 8, 128, 500, 8),
-    (5, 4, 1, 64, 0, 1), (4, 8, 1, 128, 33, 2)])
+    (5, 4, 1, 64, 0, 1), (4, 8, 1, 128, 33, 2),
+    (600, 4, 1, 64, 70, 8)])        # more sequences than one launch takes: goes in slices
 def test_attn_decode(B, n_head, n_kv, D, pos, n_split):
     from easy_to_hard_b200.ops import functional as Fn, reference
     smax = 512
