@@ -5,6 +5,7 @@
 // Numerics follow the reference model (models/model.py:370-377, 400-412): statistics in fp32,
 // the normalised value rounded to bf16 before the multiplication with the bf16 weight.
 #include <cuda_runtime.h>
+#include <stdlib.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
 
@@ -370,6 +371,45 @@ static int launch_parts_rows(const void* h_in, const PartPtrs& parts, int n_part
   return (int)cudaGetLastError();
 }
 
+// Decode-sized RMSNorm (a few dozen rows): what counts is the chain of latencies, not bytes.
+// One CTA per row, one 16-byte vector per thread, so a row is one load, one block sum and one
+// store; the weight vector is fetched before the wait for the predecessor kernel (weights are
+// never written inside a programmatic-dependent-launch chain). Same arithmetic as
+// rmsnorm_fwd_kernel: x = bf16(bf16(h * rstd) * w).
+__global__ void rmsnorm_row_latency_kernel(const __nv_bfloat16* __restrict__ h_in,
+                                           const __nv_bfloat16* __restrict__ weight,
+                                           __nv_bfloat16* __restrict__ h_out,
+                                           __nv_bfloat16* __restrict__ x_out,
+                                           float* __restrict__ rstd_out, int dim, float eps) {
+  __shared__ float red[32];
+  const int i = threadIdx.x * 8;
+  const bool on = i < dim;
+  BF8 wv;
+  if (on) wv = *reinterpret_cast<const BF8*>(weight + i);
+  pdl_launch_dependents();
+  pdl_wait_prior();
+  const long long base = (long long)blockIdx.x * dim;
+  float v[8], w[8];
+  float ss = 0.f;
+  if (on) {
+    const BF8 hv = *reinterpret_cast<const BF8*>(h_in + base + i);
+    unpack8(hv, v);
+    unpack8(wv, w);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss += v[e] * v[e];
+    if (h_out != nullptr) *reinterpret_cast<BF8*>(h_out + base + i) = hv;
+  }
+  ss = block_sum(ss, red);
+  const float rstd = rsqrtf(ss / dim + eps);
+  if (rstd_out != nullptr && threadIdx.x == 0) rstd_out[blockIdx.x] = rstd;
+  if (on) {
+    float o[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) o[e] = bf16_round(v[e] * rstd) * w[e];
+    *reinterpret_cast<BF8*>(x_out + base + i) = pack8(o);
+  }
+}
+
 extern "C" {
 
 int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb, int emb_rows,
@@ -403,6 +443,20 @@ int e2h_rmsnorm_fwd(const void* h_in, const int* tokens, const void* emb, int em
     if (nv <= 1) E2H_GO(1); else if (nv == 2) E2H_GO(2); else if (nv <= 4) E2H_GO(4);
 #undef E2H_GO
     if (nv <= 4) return (int)cudaGetLastError();
+  }
+  // a few rows (decode): the latency-oriented kernel, one 16-byte vector per thread
+  static const bool latency_form = [] {   // E2H_NORM_LATENCY=0: measurement switch
+    const char* e = getenv("E2H_NORM_LATENCY");
+    return !(e && e[0] == '0');
+  }();
+  if (latency_form && T < 256 && h_in != nullptr && tokens == nullptr && n_part == 0 &&
+      x_out != nullptr && flags == nullptr && dim % 8 == 0 && dim / 8 <= 1024 && aligned16(h_in) &&
+      aligned16(x_out) && aligned16(weight) && (h_out == nullptr || aligned16(h_out))) {
+    const int threads_l = (dim / 8 + 31) / 32 * 32;
+    return (int)launch(rmsnorm_row_latency_kernel, dim3(T), dim3(threads_l), 0,
+                       (cudaStream_t)stream, (const __nv_bfloat16*)h_in,
+                       (const __nv_bfloat16*)weight, (__nv_bfloat16*)h_out,
+                       (__nv_bfloat16*)x_out, rstd_out, dim, eps);
   }
   const int threads = dim >= 2048 ? 512 : 128;
   const size_t smem = (dim + 32) * sizeof(float);
