@@ -161,6 +161,17 @@ struct TpReduceArgs {
 template <int NV, bool LDMC, bool STMC>
 __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
   __shared__ float red[32];
+  // the norm weight is a constant of the model: fetched before the waits, so that its latency
+  // hides behind them instead of following the block sum
+  const int nvec0 = a.dim >> 3;
+  Bf8 wv[NV];
+  if (a.do_norm && a.n_xn > 0) {
+#pragma unroll
+    for (int k = 0; k < NV; ++k) {
+      const int i = threadIdx.x + k * blockDim.x;
+      if (i < nvec0) wv[k] = *reinterpret_cast<const Bf8*>(a.weight + 8 * i);
+    }
+  }
   pdl_launch_dependents();
   pdl_wait_prior();
   const int want = *a.count + 1;
@@ -229,7 +240,7 @@ __global__ void tp_reduce_norm_kernel(const TpReduceArgs a) {
         float o[8];
         if (a.do_norm) {
           float w[8];
-          bf8_unpack(*reinterpret_cast<const Bf8*>(a.weight + 8 * i), w);
+          bf8_unpack(wv[k], w);
 #pragma unroll
           for (int e = 0; e < 8; ++e) o[e] = bf16_round(v[k][e] * rstd) * w[e];
         } else {
