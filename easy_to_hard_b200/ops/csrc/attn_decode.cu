@@ -11,8 +11,8 @@
 //
 // Work split (with more pairs than resident CTAs; with fewer, every pair is simply cut into
 // equal parts, one per CTA): the live keys of every (sequence, kv head) are cut into chunks of
-// 32 keys, all chunks are numbered (sequence, head, chunk) and every CTA takes one contiguous run of that
-// numbering, the same number of chunks for all: the CTAs finish together whatever the batch,
+// 32 keys, all chunks are numbered (sequence, head, chunk) and every CTA takes one contiguous
+// run of that numbering, the same number of chunks for all: the CTAs finish together whatever the batch,
 // the head count and the context lengths are, and a CTA pays the latency of its first loads
 // once, not once per (sequence, head). A producer thread streams the K and V rows of the run
 // with bulk copies (cp.async.bulk: the rows of one head are contiguous in the cache) through a
@@ -22,8 +22,9 @@
 // run boundaries leaves (m, l, acc) partials, and the last of its CTAs to arrive (a ticket
 // counter per pair) merges them in CTA order, so the result does not depend on timing.
 //
-// All mbarrier waits are bounded; a time-out sets the status word (codes 101 / 102), the CTA stops
-// issuing copies, waits (bounded) for the ones in flight, still reaches its barriers and returns.
+// All mbarrier waits are bounded; a time-out sets the status word (codes 101 / 102), the CTA
+// stops issuing copies, waits (bounded) for the ones in flight, still reaches its barriers and
+// returns.
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <float.h>
